@@ -1,0 +1,191 @@
+"""The cache manager: paged keys and values per layer group, block tables per request,
+and slots for per-request state of fixed size.
+
+Layer calls with the same needs (number of KV heads, head size, window) form a group;
+a group has a page pool and block tables of its own, and every call in it has its own
+storage indexed by the group's page numbers.  Beside the pages, each call that
+declares fixed-size state gets one slab ``[max_slots, *shape]`` that is zeroed when a
+request is admitted; the reference keeps such state outside its paged pool, indexed
+by sequence slot, in the same way (crates/thuban_architectures/src/qwen35/state.rs:5-55).
+Phi-MoE has one group and no state.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..errors import CacheError
+from .pages import NO_PAGE, GroupPages
+
+
+@dataclass(frozen=True)
+class KVSpec:
+    """What a mixer needs cached per token: keys and values of this shape.  ``window``
+    0 means every key stays reachable; otherwise only the last ``window`` positions."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Fixed-size state a mixer keeps per request (shape without the slot axis)."""
+    shape: tuple
+    dtype: torch.dtype = torch.float32
+
+
+class GroupCache:
+    """Device side of one group: K/V storage for each of its calls and the block table."""
+
+    def __init__(self, spec: KVSpec, calls, pages: GroupPages, dtype, device):
+        self.spec = spec
+        self.calls = list(calls)
+        self.pages = pages
+        P = pages.page_size
+        n = pages.pool.n_pages
+        # [call, k|v, page, kv_head, position in page, head_dim]: one page of one head is a
+        # contiguous P x head_dim tile
+        self.storage = torch.zeros((len(self.calls), 2, n, spec.num_kv_heads, P, spec.head_dim),
+                                   dtype=dtype, device=device)
+        self.block_table = torch.full((len(pages.tables), pages.max_pages_per_request), NO_PAGE,
+                                      dtype=torch.int32, device=device)
+        self._host_table = torch.full((len(pages.tables), pages.max_pages_per_request), NO_PAGE,
+                                      dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            self._host_table = self._host_table.pin_memory()
+
+    def sync_tables(self):
+        """Copy the rows of changed block tables to the device."""
+        dirty = self.pages.dirty_slots
+        if not dirty:
+            return
+        for slot in dirty:
+            row = self.pages.tables[slot].pages
+            self._host_table[slot].fill_(NO_PAGE)
+            if row:
+                self._host_table[slot, :len(row)] = torch.tensor(row, dtype=torch.int32)
+        lo, hi = min(dirty), max(dirty) + 1
+        self.block_table[lo:hi].copy_(self._host_table[lo:hi], non_blocking=True)
+        dirty.clear()
+
+    def view(self, call_index: int):
+        i = self.calls.index(call_index)
+        return CacheView(self.storage[i, 0], self.storage[i, 1], self.block_table, self.pages.page_size,
+                         self.spec)
+
+
+@dataclass
+class CacheView:
+    """What a mixer call sees of the cache: its K and V pages [page, kv_head, P, head_dim]
+    and its group's block table [slot, logical page]."""
+    k: torch.Tensor
+    v: torch.Tensor
+    block_table: torch.Tensor
+    page_size: int
+    spec: KVSpec
+
+
+class CacheManager:
+    """Slots, pages and state for all requests of one model.
+
+    ``kv_calls``: call index -> KVSpec for calls that own a cache.
+    ``state_calls``: call index -> StateSpec for calls with fixed-size state.
+    """
+
+    def __init__(self, kv_calls: dict, state_calls: dict, *, page_size: int, n_pages: int,
+                 max_slots: int, max_context: int, dtype, device):
+        if page_size <= 0 or page_size % 16:
+            raise CacheError(f"page_size must be a positive multiple of 16, got {page_size}")
+        self.page_size = int(page_size)
+        self.max_slots = int(max_slots)
+        self.max_context = int(max_context)
+        self.device = device
+        max_pages_per_request = -(-max_context // page_size)
+        by_spec: dict = {}
+        for call, spec in kv_calls.items():
+            by_spec.setdefault(spec, []).append(call)
+        self.groups: list[GroupCache] = []
+        self._group_of_call = {}
+        for spec, calls in by_spec.items():
+            pages = GroupPages(n_pages, page_size, spec.window, max_slots, max_pages_per_request)
+            g = GroupCache(spec, calls, pages, dtype, device)
+            for c in calls:
+                self._group_of_call[c] = g
+            self.groups.append(g)
+        self.state = {call: torch.zeros((max_slots, *spec.shape), dtype=spec.dtype, device=device)
+                      for call, spec in state_calls.items()}
+        self._free_slots = list(range(max_slots - 1, -1, -1))
+        self._live: set[int] = set()
+
+    # ------------------------------------------------------------------ slots
+    @property
+    def free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def admit(self) -> int:
+        """Take a slot for a new request and zero its state."""
+        if not self._free_slots:
+            raise CacheError("no free request slot")
+        slot = self._free_slots.pop()
+        self._live.add(slot)
+        for s in self.state.values():
+            s[slot].zero_()
+        return slot
+
+    def release(self, slot: int):
+        """Give back the slot and every page it holds."""
+        if slot not in self._live:
+            raise CacheError(f"slot {slot} released twice or never admitted")
+        for g in self.groups:
+            g.pages.release_all(slot)
+        self._live.remove(slot)
+        self._free_slots.append(slot)
+
+    # ------------------------------------------------------------------ pages
+    def pages_needed(self, slot: int, start: int, end: int) -> int:
+        """The largest number of new pages any group needs to run positions [start, end)."""
+        return max((g.pages.pages_needed(slot, start, end) for g in self.groups), default=0)
+
+    def free_pages(self) -> int:
+        return min((g.pages.pool.free_pages for g in self.groups), default=1 << 30)
+
+    def can_run(self, slot: int, start: int, end: int) -> bool:
+        if end > self.max_context:
+            return False
+        return all(g.pages.pages_needed(slot, start, end) <= g.pages.pool.free_pages for g in self.groups)
+
+    def ensure(self, slot: int, start: int, end: int):
+        """Make pages cover what running positions [start, end) reads and writes."""
+        if slot not in self._live:
+            raise CacheError(f"slot {slot} is not admitted")
+        if end > self.max_context:
+            raise CacheError(f"context limit {self.max_context} reached")
+        if not self.can_run(slot, start, end):
+            raise CacheError(f"page pool exhausted: slot {slot} needs {self.pages_needed(slot, start, end)} "
+                             f"pages, {self.free_pages()} free")
+        for g in self.groups:
+            g.pages.ensure(slot, start, end)
+
+    def advance(self, slot: int, next_pos: int):
+        """After a step: positions below the windows of all later queries are given back."""
+        for g in self.groups:
+            g.pages.release_behind(slot, next_pos)
+
+    def sync(self):
+        for g in self.groups:
+            g.sync_tables()
+
+    def view(self, call_index: int) -> CacheView | None:
+        g = self._group_of_call.get(call_index)
+        return g.view(call_index) if g is not None else None
+
+    def state_of(self, call_index: int):
+        return self.state.get(call_index)
+
+    def check(self):
+        for g in self.groups:
+            g.pages.check()
+        assert len(set(self._free_slots)) == len(self._free_slots)
+        assert not (set(self._free_slots) & self._live)
+        assert len(self._free_slots) + len(self._live) == self.max_slots

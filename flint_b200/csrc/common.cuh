@@ -1,0 +1,75 @@
+// Shared helpers of the sm_100a kernels: element types, loads that widen to float,
+// stores that narrow from float, warp reductions and the error convention.
+//
+// Every exported function is extern "C", takes raw device pointers and a stream, does
+// no allocation, and returns 0 or a negative code; the text of the last error is
+// kept per thread and read with <module>_last_error().
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define FLINT_F32 0
+#define FLINT_BF16 1
+
+namespace flint {
+
+static thread_local char g_error[512];
+
+inline int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+inline int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);  // round to nearest even
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+__device__ __forceinline__ float block_sum(float v, float* smem32) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // smem32 may still be read from an earlier call
+  if (lane == 0) smem32[warp] = v;
+  __syncthreads();
+  const int nwarps = (blockDim.x + 31) >> 5;
+  float r = (lane < nwarps) ? smem32[lane] : 0.f;
+  r = warp_sum(r);
+  return r;
+}
+
+}  // namespace flint
+
+// Dispatch on a run-time element type code to a lambda templated on the C++ type.
+#define FLINT_DISPATCH_DTYPE(code, T, ...)                        \
+  do {                                                            \
+    if ((code) == FLINT_F32) { using T = float; __VA_ARGS__; }    \
+    else { using T = __nv_bfloat16; __VA_ARGS__; }                \
+  } while (0)

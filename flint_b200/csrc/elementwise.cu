@@ -1,0 +1,186 @@
+// Row-wise kernels: embedding lookup, LayerNorm / RMSNorm, rotary position encoding
+// fused with the write of keys and values into the paged cache, row gather, and the
+// weighted sum of the two selected experts' outputs into the residual stream.
+//
+// Reference counterparts (WGSL, crates/thuban_kernel/wgsl/): embed.wgsl, norm.wgsl
+// (mode 3 = LayerNorm with bias), rope.wgsl + kv_store.wgsl, add.wgsl.  All arithmetic
+// is float32; only loads widen and stores narrow.
+#include <stdarg.h>
+#include "common.cuh"
+
+using namespace flint;
+
+// --------------------------------------------------------------------------- embed
+template <typename TT>
+__global__ void embed_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
+                             float* __restrict__ out, int T, int H, int V, float scale) {
+  const int r = blockIdx.x;
+  int id = ids[r];
+  id = id < 0 ? 0 : (id >= V ? V - 1 : id);  // ids are validated on the host; never read outside
+  const TT* src = table + (size_t)id * H;
+  float* dst = out + (size_t)r * H;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) dst[d] = to_f32(src[d]) * scale;
+}
+
+extern "C" int flint_embed(const int* ids, const void* table, int table_dtype, float* out,
+                           int T, int H, int V, float scale, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
+  const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
+  FLINT_DISPATCH_DTYPE(table_dtype, TT,
+      embed_kernel<TT><<<T, threads, 0, stream>>>(ids, (const TT*)table, out, T, H, V, scale));
+  return check_launch("embed");
+}
+
+// --------------------------------------------------------------------------- norm
+// mode 0: LayerNorm (x-mean)*rsqrt(var+eps)*gamma (+beta), var = mean((x-mean)^2)
+// mode 1: RMSNorm   x*rsqrt(mean(x^2)+eps)*gamma
+// One block per output row; statistics in float32 with three passes over the row (the
+// row stays in L1 between passes).  row_index, if given, selects the input row.
+__global__ void norm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
+                            const float* __restrict__ gamma, const float* __restrict__ beta,
+                            float eps, int mode, float* __restrict__ out_f32,
+                            __nv_bfloat16* __restrict__ out_bf16, int H) {
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src_row = row_index ? row_index[r] : r;
+  const float* xr = x + (size_t)src_row * H;
+  float mean = 0.f;
+  if (mode == 0) {
+    float s = 0.f;
+    for (int d = threadIdx.x; d < H; d += blockDim.x) s += xr[d];
+    mean = block_sum(s, red) / (float)H;
+  }
+  float ss = 0.f;
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    const float c = xr[d] - mean;
+    ss += c * c;
+  }
+  const float var = block_sum(ss, red) / (float)H;
+  const float inv = 1.0f / sqrtf(var + eps);
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    float y = (xr[d] - mean) * inv * gamma[d];
+    if (beta) y += beta[d];
+    if (out_f32) out_f32[(size_t)r * H + d] = y;
+    if (out_bf16) out_bf16[(size_t)r * H + d] = __float2bfloat16_rn(y);
+  }
+}
+
+extern "C" int flint_norm(const float* x, const int* row_index, const float* gamma,
+                          const float* beta, float eps, int mode, float* out_f32, void* out_bf16,
+                          int rows, int H, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0) return fail("norm: bad width %d", H);
+  if (mode != 0 && mode != 1) return fail("norm: unknown mode %d", mode);
+  if (!out_f32 && !out_bf16) return fail("norm: no output given");
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  norm_kernel<<<rows, threads, 0, stream>>>(x, row_index, gamma, beta, eps, mode, out_f32,
+                                            (__nv_bfloat16*)out_bf16, H);
+  return check_launch("norm");
+}
+
+// --------------------------------------------------------------------------- rope + kv write
+// qkv [T, (nq+2*nkv)*hd] float32: q heads, then k heads, then v heads.
+// q and k are rotated (NeoX half-split over the first `rot` dims of each head) by the row of
+// the cos/sin tables that belongs to the token's position; q goes to q_out, k and v go to
+// the token's place in the paged cache: page = block_table[slot, pos / P], row pos % P.
+template <typename TQ, typename TC>
+__global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
+                               const int* __restrict__ slot, const float* __restrict__ cos_t,
+                               const float* __restrict__ sin_t, int rot, TQ* __restrict__ q_out,
+                               TC* __restrict__ k_cache, TC* __restrict__ v_cache,
+                               const int* __restrict__ block_table, int max_pages, int page_size,
+                               int nq, int nkv, int hd, int write_kv, int* __restrict__ status) {
+  const int t = blockIdx.x;
+  const int head = blockIdx.y;  // 0..nq-1 q, nq..nq+nkv-1 k, then v
+  const int p = pos[t];
+  const int half = rot >> 1;
+  const float* src = qkv + ((size_t)t * (nq + 2 * nkv) + head) * hd;
+  const bool is_q = head < nq;
+  const bool is_v = head >= nq + nkv;
+  if (!is_q && !write_kv) return;
+  size_t cache_row = 0;
+  if (!is_q) {
+    const int page = block_table[(size_t)slot[t] * max_pages + p / page_size];
+    if (page < 0) {  // the host must have allocated the page; record and skip
+      if (threadIdx.x == 0) atomicExch(status, 1);
+      return;
+    }
+    const int kvh = is_v ? head - nq - nkv : head - nq;
+    cache_row = (((size_t)page * nkv + kvh) * page_size + (p % page_size)) * hd;
+  }
+  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    float y;
+    if (is_v || d >= rot) {
+      y = src[d];
+    } else {
+      const int i = d < half ? d : d - half;
+      const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
+      y = d < half ? src[d] * c - src[d + half] * s : src[d] * c + src[d - half] * s;
+    }
+    if (is_q) q_out[((size_t)t * nq + head) * hd + d] = from_f32<TQ>(y);
+    else if (is_v) v_cache[cache_row + d] = from_f32<TC>(y);
+    else k_cache[cache_row + d] = from_f32<TC>(y);
+  }
+}
+
+extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* slot,
+                                   const float* cos_t, const float* sin_t, int rot, void* q_out,
+                                   int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
+                                   const int* block_table, int max_pages, int page_size, int T,
+                                   int nq, int nkv, int hd, int write_kv, int* status,
+                                   cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (rot < 0 || rot > hd || (rot & 1)) return fail("rope: rotary size %d does not fit head size %d", rot, hd);
+  if (page_size <= 0) return fail("rope: bad page size %d", page_size);
+  dim3 grid(T, nq + 2 * nkv);
+  const int threads = hd >= 128 ? 128 : (hd > 32 ? 64 : 32);
+  FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
+      (rope_kv_kernel<TQ, TC><<<grid, threads, 0, stream>>>(
+          qkv, pos, slot, cos_t, sin_t, rot, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,
+          max_pages, page_size, nq, nkv, hd, write_kv, status))));
+  return check_launch("rope_kv_write");
+}
+
+// --------------------------------------------------------------------------- row gather
+// out[r, :] = x[index[r], :] for rows of row_bytes bytes (a multiple of 4); a negative
+// index gives a row of zeros.
+__global__ void gather_rows_kernel(const uint32_t* __restrict__ x, const int* __restrict__ index,
+                                   uint32_t* __restrict__ out, int words) {
+  const int r = blockIdx.x;
+  const int src = index[r];
+  for (int d = threadIdx.x; d < words; d += blockDim.x)
+    out[(size_t)r * words + d] = src < 0 ? 0u : x[(size_t)src * words + d];
+}
+
+extern "C" int flint_gather_rows(const void* x, const int* index, void* out, int rows,
+                                 int row_bytes, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (row_bytes <= 0 || (row_bytes & 3)) return fail("gather_rows: row size %d bytes is not a multiple of 4", row_bytes);
+  gather_rows_kernel<<<rows, 256, 0, stream>>>((const uint32_t*)x, index, (uint32_t*)out, row_bytes / 4);
+  return check_launch("gather_rows");
+}
+
+// --------------------------------------------------------------------------- expert combine
+// h[t,:] += g[t,0]*y[row_of[t,0],:] + g[t,1]*y[row_of[t,1],:]   (always in this order)
+__global__ void moe_combine_kernel(float* __restrict__ h, const float* __restrict__ y,
+                                   const int* __restrict__ row_of, const float* __restrict__ gates,
+                                   int H) {
+  const int t = blockIdx.x;
+  const int r0 = row_of[2 * t], r1 = row_of[2 * t + 1];
+  const float g0 = gates[2 * t], g1 = gates[2 * t + 1];
+  for (int d = threadIdx.x; d < H; d += blockDim.x) {
+    float acc = g0 * y[(size_t)r0 * H + d];
+    acc += g1 * y[(size_t)r1 * H + d];
+    h[(size_t)t * H + d] += acc;
+  }
+}
+
+extern "C" int flint_moe_combine(float* h, const float* y, const int* row_of, const float* gates,
+                                 int T, int H, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  moe_combine_kernel<<<T, 256, 0, stream>>>(h, y, row_of, gates, H);
+  return check_launch("moe_combine");
+}
+
+extern "C" const char* flint_elementwise_last_error() { return g_error; }

@@ -1,0 +1,144 @@
+// Routing for a top-2 mixture of experts: router logits and sparsemixer selection, and
+// the plan that sorts token rows by expert for the grouped products.
+//
+// The reference has no mixture of experts (its feed-forward is dense:
+// crates/thuban_model/src/ops/mlp.rs:24-79); these kernels have no counterpart there.
+// Router logits, the mask threshold and both softmaxes are float32 in every mode.
+#include <math.h>
+#include <stdarg.h>
+#include "common.cuh"
+
+using namespace flint;
+
+namespace {
+constexpr int MAX_E = 256;
+
+// One warp per token.  logits s_e = <x, Wr[e]>, then (all lanes redundantly, on registers
+// read from shared memory):
+//   i1 = argmax s (lowest index on ties), m1 = s[i1]
+//   keep_j = !((m1 - s_j) / max(|s_j|, m1) > 2 eps);  g1 = e^{s_i1 - m1} / sum_{keep} e^{s_j - m1}
+//   the same again over s without i1 for (i2, g2); the gates are not renormalised.
+template <typename TW>
+__global__ void router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr,
+                                          float eps, int* __restrict__ expert_ids,
+                                          float* __restrict__ gates, float* __restrict__ logits_out,
+                                          int T, int H, int E) {
+  extern __shared__ float smem[];   // per warp: E logits
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= T) return;
+  float* s = smem + warp * E;
+  const float* xr = x + (size_t)t * H;
+  for (int e = 0; e < E; ++e) {
+    const TW* w = wr + (size_t)e * H;
+    float a = 0.f;
+    for (int d = lane; d < H; d += 32) a = fmaf(xr[d], to_f32(w[d]), a);
+    a = warp_sum(a);
+    if (lane == 0) {
+      s[e] = a;
+      if (logits_out) logits_out[(size_t)t * E + e] = a;
+    }
+  }
+  __syncwarp();
+  if (lane != 0) return;
+  int sel[2];
+  float gate[2];
+  int excluded = -1;
+  for (int r = 0; r < 2; ++r) {
+    float m = -INFINITY;
+    int im = 0;
+    for (int e = 0; e < E; ++e)
+      if (e != excluded && s[e] > m) { m = s[e]; im = e; }
+    float denom = 0.f;
+    for (int e = 0; e < E; ++e) {
+      if (e == excluded) continue;
+      const float factor = fmaxf(fabsf(s[e]), m);
+      const bool masked = ((m - s[e]) / factor) > 2.0f * eps;
+      if (!masked) denom += expf(s[e] - m);
+    }
+    sel[r] = im;
+    gate[r] = 1.0f / denom;   // e^{m - m} / denom
+    excluded = im;
+  }
+  expert_ids[2 * t] = sel[0];
+  expert_ids[2 * t + 1] = sel[1];
+  gates[2 * t] = gate[0];
+  gates[2 * t + 1] = gate[1];
+}
+
+// One block.  expert_ids [T*2] -> per-expert counts, offsets (exclusive scan), the sorted row
+// of every (token, choice) and the tile map for the grouped products.
+__global__ void moe_plan_kernel(const int* __restrict__ expert_ids, int n_assign, int E,
+                                int tile_rows, int* __restrict__ counts, int* __restrict__ offsets,
+                                int* __restrict__ row_of, int* __restrict__ token_of,
+                                int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                                int* __restrict__ n_tiles, int max_tiles) {
+  __shared__ int cnt[MAX_E];
+  __shared__ int off[MAX_E + 1];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  // rank of each assignment inside its expert (the order inside an expert has no effect on
+  // any result: rows are independent in the products and are added back per token)
+  for (int a = threadIdx.x; a < n_assign; a += blockDim.x) row_of[a] = atomicAdd(&cnt[expert_ids[a]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = run;
+      counts[e] = cnt[e];
+      offsets[e] = run;
+      for (int r = 0; r < cnt[e]; r += tile_rows) {
+        if (tiles < max_tiles) {
+          tile_expert[tiles] = e;
+          tile_row0[tiles] = run + r;
+        }
+        ++tiles;
+      }
+      run += cnt[e];
+    }
+    off[E] = run;
+    offsets[E] = run;
+    *n_tiles = tiles < max_tiles ? tiles : max_tiles;
+  }
+  __syncthreads();
+  for (int a = threadIdx.x; a < n_assign; a += blockDim.x) {
+    const int row = off[expert_ids[a]] + row_of[a];
+    row_of[a] = row;
+    token_of[row] = a >> 1;
+  }
+}
+}  // namespace
+
+extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dtype, float eps,
+                                        int* expert_ids, float* gates, float* logits_out, int T,
+                                        int H, int E, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (E < 2 || E > MAX_E) return fail("router: %d experts (supported: 2..%d)", E, MAX_E);
+  const int warps = 4;
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  const int blocks = (T + warps - 1) / warps;
+  FLINT_DISPATCH_DTYPE(w_dtype, TW,
+      (router_sparsemixer_kernel<TW><<<blocks, warps * 32, smem, stream>>>(
+          x, (const TW*)wr, eps, expert_ids, gates, logits_out, T, H, E)));
+  return check_launch("router_sparsemixer");
+}
+
+// Upper bound of row tiles for n_assign rows over E experts.
+extern "C" int flint_moe_max_tiles(int n_assign, int E, int tile_rows) {
+  return n_assign / tile_rows + (E < n_assign ? E : n_assign);
+}
+
+extern "C" int flint_moe_plan(const int* expert_ids, int n_assign, int E, int tile_rows, int* counts,
+                              int* offsets, int* row_of, int* token_of, int* tile_expert,
+                              int* tile_row0, int* n_tiles, int max_tiles, cudaStream_t stream) {
+  if (n_assign <= 0) return 0;
+  if (E < 1 || E > MAX_E) return fail("moe_plan: %d experts (supported: 1..%d)", E, MAX_E);
+  if (tile_rows <= 0) return fail("moe_plan: bad tile size %d", tile_rows);
+  if (max_tiles < flint_moe_max_tiles(n_assign, E, tile_rows))
+    return fail("moe_plan: tile map of %d entries is too small", max_tiles);
+  moe_plan_kernel<<<1, 1024, 0, stream>>>(expert_ids, n_assign, E, tile_rows, counts, offsets, row_of,
+                                          token_of, tile_expert, tile_row0, n_tiles, max_tiles);
+  return check_launch("moe_plan");
+}
+
+extern "C" const char* flint_moe_last_error() { return g_error; }

@@ -1,0 +1,310 @@
+"""Python face of the CUDA kernels: one method per kernel, taking torch tensors.
+
+``CudaOps`` checks types and shapes, hands raw pointers and the current stream to the
+``extern "C"`` launchers and raises ``KernelError`` with the launcher's message on any
+refusal.  It has no fallback: on a machine without the compiled extension or without
+a CUDA device it raises.  The reference wraps its shaders the same way, one function
+per shader building the scalar and binding lists (crates/thuban_model/src/ops/*.rs).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from dataclasses import dataclass
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+F32, BF16 = 0, 1
+
+
+def _code(dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _check(t, name, dtype=None, dims=None, contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dims is not None and t.dim() != dims:
+        raise KernelError(f"{name} must have {dims} dims, got shape {tuple(t.shape)}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+@dataclass
+class MoePlan:
+    """Rows sorted by expert: where each (token, choice) went and which expert owns each
+    row tile.  All tensors live on the device; nothing is read back."""
+    n_experts: int
+    tile_rows: int
+    max_tiles: int
+    counts: torch.Tensor       # [E]
+    offsets: torch.Tensor      # [E+1]
+    row_of: torch.Tensor       # [T, 2] sorted row of (token, choice)
+    token_of: torch.Tensor     # [2T] token of each sorted row
+    tile_expert: torch.Tensor  # [max_tiles]
+    tile_row0: torch.Tensor    # [max_tiles]
+    n_tiles: torch.Tensor      # [1]
+
+
+class CudaOps:
+    """The kernel set on one CUDA device."""
+
+    name = "cuda"
+
+    def __init__(self, device="cuda:0"):
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: flint_b200 runs on the GPU only and has no CPU fallback")
+        self.device = torch.device(device)
+        self._libs = {}
+        self.launches = 0
+
+    # ------------------------------------------------------------------ plumbing
+    def _fn(self, module, name):
+        lib = self._libs.get(module)
+        if lib is None:
+            lib = build.load_module(module)
+            getattr(lib, f"flint_{module}_last_error").restype = ctypes.c_char_p
+            self._libs[module] = lib
+        return getattr(lib, name)
+
+    def _run(self, module, name, *args):
+        fn = self._fn(module, name)
+        rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self.launches += 1
+        if rc != 0:
+            msg = getattr(self._libs[module], f"flint_{module}_last_error")()
+            raise KernelError((msg or b"unknown kernel error").decode())
+
+    def preload(self, modules=None):
+        """Compile and load modules ahead of their first use."""
+        mods = list(modules or build.available_modules())
+        build.compile_all(mods)
+        for m in mods:
+            self._fn(m, f"flint_{m}_last_error")
+
+    # ------------------------------------------------------------------ row-wise
+    def embed(self, ids, table, out, scale=1.0):
+        _check(ids, "ids", torch.int32, 1)
+        _check(table, "table", dims=2)
+        _check(out, "out", torch.float32, 2)
+        T, (V, H) = ids.numel(), table.shape
+        if tuple(out.shape) != (T, H):
+            raise KernelError(f"embed: out must be [{T}, {H}]")
+        self._run("elementwise", "flint_embed", _ptr(ids), _ptr(table), c_int(_code(table.dtype)), _ptr(out),
+                  c_int(T), c_int(H), c_int(V), c_float(scale))
+
+    def norm(self, x, gamma, beta, eps, mode, out_f32=None, out_bf16=None, row_index=None):
+        """mode 'layer' or 'rms'; writes float32 and/or bfloat16 copies of the result."""
+        _check(x, "x", torch.float32, 2)
+        H = x.shape[1]
+        rows = row_index.numel() if row_index is not None else x.shape[0]
+        _check(gamma, "gamma", torch.float32, 1)
+        if gamma.numel() != H or (beta is not None and (beta.numel() != H or beta.dtype != torch.float32)):
+            raise KernelError("norm: scale and bias must be float32 of the row width")
+        for o, dt in ((out_f32, torch.float32), (out_bf16, torch.bfloat16)):
+            if o is not None:
+                _check(o, "norm output", dt, 2)
+                if tuple(o.shape) != (rows, H):
+                    raise KernelError(f"norm: output must be [{rows}, {H}]")
+        if row_index is not None:
+            _check(row_index, "row_index", torch.int32, 1)
+        self._run("elementwise", "flint_norm", _ptr(x), _ptr(row_index), _ptr(gamma), _ptr(beta), c_float(eps),
+                  c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), c_int(rows), c_int(H))
+
+    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status):
+        _check(qkv, "qkv", torch.float32, 2)
+        T = qkv.shape[0]
+        if qkv.shape[1] != (nq + 2 * nkv) * hd:
+            raise KernelError("rope_kv_write: qkv width does not match the head counts")
+        _check(q_out, "q_out", dims=2)
+        _check(cos, "cos", torch.float32, 2)
+        _check(sin, "sin", torch.float32, 2)
+        if cos.shape[1] * 2 != rot and rot > 0:
+            raise KernelError("rope_kv_write: table width must be rot/2")
+        if cache is not None:
+            k, v, bt, P = cache.k, cache.v, cache.block_table, cache.page_size
+            cdt = _code(k.dtype)
+            if tuple(k.shape[1:]) != (nkv, P, hd):
+                raise KernelError(f"rope_kv_write: cache pages are {tuple(k.shape[1:])}, expected {(nkv, P, hd)}")
+            max_pages = bt.shape[1]
+        else:
+            if write_kv:
+                raise KernelError("rope_kv_write: no cache to write to")
+            k = v = bt = None
+            cdt, P, max_pages = F32, 16, 0
+        self._run("elementwise", "flint_rope_kv_write", _ptr(qkv), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin),
+                  c_int(rot), _ptr(q_out), c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(cdt), _ptr(bt),
+                  c_int(max_pages), c_int(P), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write_kv else 0),
+                  _ptr(status))
+
+    def gather_rows(self, x, index, out):
+        _check(x, "x", dims=2)
+        _check(index, "index", torch.int32, 1)
+        _check(out, "out", x.dtype, 2)
+        if out.shape[0] != index.numel() or out.shape[1] != x.shape[1]:
+            raise KernelError("gather_rows: output shape does not match")
+        self._run("elementwise", "flint_gather_rows", _ptr(x), _ptr(index), _ptr(out), c_int(index.numel()),
+                  c_int(x.shape[1] * x.element_size()))
+
+    def moe_combine(self, h, y, row_of, gates):
+        _check(h, "h", torch.float32, 2)
+        _check(y, "y", torch.float32, 2)
+        T, H = h.shape
+        if y.shape[1] != H or row_of.numel() != 2 * T or gates.numel() != 2 * T:
+            raise KernelError("moe_combine: shapes do not match")
+        self._run("elementwise", "flint_moe_combine", _ptr(h), _ptr(y), _ptr(row_of), _ptr(gates), c_int(T), c_int(H))
+
+    # ------------------------------------------------------------------ matrix products
+    def gemm(self, x, w, out, bias=None, accumulate=False):
+        """out = x @ w.T (+ bias) (+ out).  x [M,K], w [N,K], out [M,N]."""
+        self._gemm(x, w, None, out, bias, accumulate, "silu", None)
+
+    def gated_gemm(self, x, w_gate, w_up, out, act="silu", plan: MoePlan | None = None):
+        """out = act(x @ w_gate.T) * (x @ w_up.T); with a plan, rows are grouped by expert
+        and the weights are [E, N, K]."""
+        self._gemm(x, w_gate, w_up, out, None, False, act, plan)
+
+    def grouped_gemm(self, x, w, out, plan: MoePlan):
+        """out[r] = x[r] @ w[expert of row r].T; w [E, N, K]."""
+        self._gemm(x, w, None, out, None, False, "silu", plan)
+
+    def _gemm(self, x, w, w_up, out, bias, accumulate, act, plan):
+        _check(x, "x", dims=2, contiguous=False)
+        _check(out, "out", dims=2, contiguous=False)
+        if x.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("gemm: rows must be contiguous")
+        _check(w, "w")
+        M, K = x.shape
+        if plan is None:
+            if w.dim() != 2:
+                raise KernelError("gemm: dense weights must be [N, K]")
+            N = w.shape[0]
+        else:
+            if w.dim() != 3 or w.shape[0] != plan.n_experts:
+                raise KernelError("gemm: grouped weights must be [E, N, K]")
+            N = w.shape[1]
+        if w.shape[-1] != K or tuple(out.shape) != (M, N):
+            raise KernelError(f"gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
+        if w_up is not None and (w_up.shape != w.shape or w_up.dtype != w.dtype):
+            raise KernelError("gemm: gate and up weights must match")
+        if bias is not None:
+            _check(bias, "bias", torch.float32, 1)
+            if bias.numel() != N:
+                raise KernelError("gemm: bias length does not match")
+        act_code = {"silu": 0, "gelu_pytorch_tanh": 1}[act]
+        self._gemm_simt(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+
+    def _gemm_simt(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
+        if plan is not None and plan.tile_rows != 64:
+            raise KernelError("gemm_simt: the plan must use 64-row tiles")
+        self._run("gemm_simt", "flint_gemm_simt", _ptr(x), c_int(_code(x.dtype)), c_int(x.stride(0)), _ptr(w),
+                  _ptr(w_up), c_int(_code(w.dtype)), _ptr(bias), _ptr(out), c_int(_code(out.dtype)),
+                  c_int(out.stride(0)), c_int(1 if accumulate else 0), c_int(act_code),
+                  _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
+                  _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
+                  c_int(plan.max_tiles if plan else 0), c_int(M), c_int(N), c_int(K))
+
+    # ------------------------------------------------------------------ attention
+    def attention_splits(self, T, nq, nkv, max_kv_len):
+        """How to split the key range so that the device is filled: (keys per split, splits)."""
+        g_chunks = -(-(nq // nkv) // 4)
+        base = T * nkv * g_chunks
+        if base >= 2048 or max_kv_len <= 64:
+            return max(max_kv_len, 1), 1
+        n = min(-(-max_kv_len // 64), -(-2048 // base))
+        keys = -(-max_kv_len // n)
+        keys = -(-keys // 32) * 32
+        return keys, -(-max_kv_len // keys)
+
+    def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None):
+        _check(q, "q", dims=2)
+        _check(out, "out", q.dtype, 2)
+        T = q.shape[0]
+        if q.shape[1] != nq * hd or tuple(out.shape) != (T, nq * hd):
+            raise KernelError("paged_attention: q/out width does not match the head counts")
+        if tuple(cache.k.shape[1:]) != (nkv, cache.page_size, hd):
+            raise KernelError("paged_attention: cache pages do not match the head counts")
+        span = min(max_kv_len, window) if window else max_kv_len
+        split_keys, n_splits = splits or self.attention_splits(T, nq, nkv, span)
+        scratch = None
+        if n_splits > 1:
+            scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+        self._run("attention", "flint_paged_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
+                  c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
+                  c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(_code(out.dtype)), c_int(T),
+                  c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
+                  _ptr(scratch))
+
+    # ------------------------------------------------------------------ routing
+    def router_sparsemixer(self, x, wr, eps, expert_ids, gates, logits_out=None):
+        _check(x, "x", torch.float32, 2)
+        _check(wr, "router weight", dims=2)
+        T, H = x.shape
+        E = wr.shape[0]
+        if wr.shape[1] != H:
+            raise KernelError("router: weight width does not match")
+        _check(expert_ids, "expert_ids", torch.int32)
+        _check(gates, "gates", torch.float32)
+        self._run("moe", "flint_router_sparsemixer", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_float(eps),
+                  _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
+
+    def moe_plan(self, expert_ids, n_experts, tile_rows) -> MoePlan:
+        _check(expert_ids, "expert_ids", torch.int32)
+        n = expert_ids.numel()
+        dev = expert_ids.device
+        max_tiles = n // tile_rows + min(n_experts, n)
+        ints = torch.empty(n_experts + (n_experts + 1) + n + n + 2 * max_tiles + 1, dtype=torch.int32, device=dev)
+        o = 0
+        parts = []
+        for size in (n_experts, n_experts + 1, n, n, max_tiles, max_tiles, 1):
+            parts.append(ints[o:o + size])
+            o += size
+        counts, offsets, row_of, token_of, tile_expert, tile_row0, n_tiles = parts
+        self._run("moe", "flint_moe_plan", _ptr(expert_ids), c_int(n), c_int(n_experts), c_int(tile_rows),
+                  _ptr(counts), _ptr(offsets), _ptr(row_of), _ptr(token_of), _ptr(tile_expert), _ptr(tile_row0),
+                  _ptr(n_tiles), c_int(max_tiles))
+        return MoePlan(n_experts, tile_rows, max_tiles, counts, offsets, row_of.view(-1, 2), token_of,
+                       tile_expert, tile_row0, n_tiles)
+
+    # ------------------------------------------------------------------ sampling
+    def argmax(self, logits, out):
+        _check(logits, "logits", torch.float32, 2)
+        _check(out, "out", torch.int32, 1)
+        self._run("sampling", "flint_argmax", _ptr(logits), _ptr(out), c_int(logits.shape[0]), c_int(logits.shape[1]))
+
+    def sample(self, logits, params, context, work, out):
+        """params [R, 8] float32: temperature, top_k, top_p, min_p, repeat_penalty, u, n_context, 0;
+        context [R, C] int32 (recent tokens, -1 padded); work [R, V] float32 scratch."""
+        _check(logits, "logits", torch.float32, 2)
+        _check(params, "params", torch.float32, 2)
+        _check(context, "context", torch.int32, 2)
+        _check(work, "work", torch.float32, 2)
+        _check(out, "out", torch.int32, 1)
+        R, V = logits.shape
+        if params.shape != (R, 8) or context.shape[0] != R or work.shape != (R, V) or out.numel() != R:
+            raise KernelError("sample: shapes do not match")
+        self._run("sampling", "flint_sample", _ptr(logits), _ptr(params), _ptr(context), c_int(context.shape[1]),
+                  _ptr(work), _ptr(out), c_int(R), c_int(V))
+
+
+_DEFAULT: dict = {}
+
+
+def get_ops(device="cuda:0") -> CudaOps:
+    key = str(torch.device(device))
+    if key not in _DEFAULT:
+        _DEFAULT[key] = CudaOps(device)
+    return _DEFAULT[key]

@@ -1,0 +1,227 @@
+"""The generic model: parts built from a ``ModelSpec``, tensors loaded by name, and the
+step function.
+
+``Model.step(entries)`` runs exactly the tokens it is given, as one batch, against the
+cache that earlier steps left, and returns float32 logits ``[wanted, vocab]`` for the
+wanted places, in the order of the entries and of each entry's ``want``.  It is the
+counterpart of the reference's ``LanguageModel::forward``
+(crates/thuban_model/src/traits.rs:29-46,
+crates/thuban_architectures/src/transformer/forward.rs:51-508), with two differences:
+positions come with the batch, and the wanted rows are gathered *before* the final
+norm and the output head, so that the head runs on the wanted rows only.
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.spec import ModelSpec
+from ..errors import ConfigError, ModelError
+from ..parts.base import BuildContext, matmul_dtype
+from ..registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from ..weights.loader import load_tensors
+from ..weights.sources import SafetensorsSource, WeightSpec
+from .step import StepEntry, StepStaging
+
+_ROLE_REGISTRY = {"norm1": NORMS, "norm2": NORMS, "mixer": MIXERS, "ffn": FEED_FORWARDS}
+
+
+def registry_for_role(role: str):
+    if role.startswith("norm"):
+        return NORMS
+    if role.startswith("mixer"):
+        return MIXERS
+    if role.startswith("ffn"):
+        return FEED_FORWARDS
+    raise ConfigError(f"no part registry for role {role!r}")
+
+
+class Layer:
+    def __init__(self, spec, ctx):
+        self.spec = spec
+        self.parts = {role: registry_for_role(role).get(ps.kind)(ps.params, ctx) for role, ps in spec.parts.items()}
+        self.block = BLOCKS.get(spec.block)(self.parts)
+        missing = [r for r in self.block.roles if r not in self.parts]
+        if missing:
+            raise ConfigError(f"block {spec.block!r} needs parts {missing}")
+
+    def weights(self):
+        out = {}
+        for role, part in self.parts.items():
+            for name, ws in part.weights().items():
+                out[self.spec.prefix + self.spec.names[role] + name] = ws
+        return out
+
+    def load(self, tensors):
+        for role, part in self.parts.items():
+            pre = self.spec.prefix + self.spec.names[role]
+            part.load({name: tensors[pre + name] for name in part.weights() if pre + name in tensors})
+
+
+def expected_tensors(spec: ModelSpec, layers) -> dict:
+    """Every tensor name the model reads, with its shape and role."""
+    exp = {spec.embed_name + "weight": WeightSpec((spec.vocab_size, spec.hidden_size))}
+    for layer in layers:
+        exp.update(layer.weights())
+    return exp
+
+
+class Model:
+    """Parts + tensors + cache + step function for one model on one device."""
+
+    def __init__(self, spec: ModelSpec, source, *, dtype="bfloat16", device="cuda:0", ops=None,
+                 page_size=64, n_pages=None, max_slots=8, max_context=None, max_step_tokens=8192):
+        if dtype not in ("bfloat16", "float32"):
+            raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
+        self.spec = spec
+        self.compute = dtype
+        self.device = torch.device(device)
+        if ops is None:
+            from ..csrc.ops import get_ops
+            ops = get_ops(self.device)
+        self.ops = ops
+        self.ctx = BuildContext(ops=ops, device=self.device, compute=dtype)
+        self.layers = [Layer(ls, self.ctx) for ls in spec.layers]
+        self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, self.ctx)
+
+        expected = expected_tensors(spec, self.layers)
+        for name, ws in self.final_norm.weights().items():
+            expected[spec.final_norm_name + name] = ws
+        if not spec.tie_word_embeddings:
+            expected[spec.head_name + "weight"] = WeightSpec((spec.vocab_size, spec.hidden_size))
+        if spec.head_bias:
+            expected[spec.head_name + "bias"] = WeightSpec((spec.vocab_size,), role="vector")
+        self.expected = expected
+        tensors = load_tensors(source, expected, dtype, self.device)
+        self.embed_table = tensors[spec.embed_name + "weight"]
+        self.head_weight = self.embed_table if spec.tie_word_embeddings else tensors[spec.head_name + "weight"]
+        self.head_bias = tensors.get(spec.head_name + "bias")
+        self.final_norm.load({n: tensors[spec.final_norm_name + n] for n in self.final_norm.weights()})
+        for layer in self.layers:
+            layer.load(tensors)
+        del tensors
+
+        # ---- the run order and who owns which cache
+        self.order = list(spec.order)
+        kv_calls, state_calls = {}, {}
+        for i, call in enumerate(self.order):
+            if not 0 <= call.layer < len(self.layers):
+                raise ConfigError(f"run order names layer {call.layer}, the model has {len(self.layers)}")
+            mixer = self.layers[call.layer].parts.get("mixer")
+            if call.cache_of is not None:
+                if not 0 <= call.cache_of < i or self.order[call.cache_of].cache_of is not None:
+                    raise ConfigError(f"call {i} must read the cache of an earlier call that owns one")
+                continue
+            if mixer is None:
+                continue
+            ks = mixer.cache_spec()
+            if ks is not None:
+                kv_calls[i] = ks
+            ss = mixer.state_spec()
+            if ss is not None:
+                state_calls[i] = ss
+        self.max_context = int(max_context or spec.max_positions)
+        if self.max_context > spec.max_positions:
+            raise ConfigError(f"max_context {self.max_context} exceeds the model's {spec.max_positions} positions")
+        if n_pages is None:
+            n_pages = max_slots * -(-self.max_context // page_size)
+        cache_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        self.cache = CacheManager(kv_calls, state_calls, page_size=page_size, n_pages=n_pages, max_slots=max_slots,
+                                  max_context=self.max_context, dtype=cache_dtype, device=self.device)
+        self.staging = StepStaging(max_step_tokens, self.device)
+        self.max_step_tokens = max_step_tokens
+
+    # ------------------------------------------------------------------ facts
+    @property
+    def vocab_size(self):
+        return self.spec.vocab_size
+
+    @property
+    def eos_token_ids(self):
+        return tuple(self.spec.eos_token_ids)
+
+    def weight_bytes(self):
+        seen, total = set(), 0
+        def add(t):
+            nonlocal total
+            if t is not None and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+        add(self.embed_table); add(self.head_weight); add(self.head_bias)
+        for layer in self.layers:
+            for part in layer.parts.values():
+                for v in vars(part).values():
+                    if isinstance(v, torch.Tensor):
+                        add(v)
+        return total
+
+    # ------------------------------------------------------------------ the step function
+    def step(self, entries, record=None, attention_splits=None) -> torch.Tensor:
+        """Run one batch.  ``entries``: list of StepEntry.  Pages for every entry must
+        have been made by ``cache.ensure``.  Returns logits [wanted, vocab] float32."""
+        for e in entries:
+            for g in self.cache.groups:
+                t = g.pages.tables[e.slot]
+                if len(t.pages) * g.pages.page_size < e.start_pos + len(e.tokens):
+                    raise ModelError(f"slot {e.slot}: pages do not cover positions up to "
+                                     f"{e.start_pos + len(e.tokens) - 1}")
+        self.cache.sync()
+        step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
+        step.record = record
+        step.attention_splits = attention_splits
+        return self.forward(step)
+
+    def forward(self, step) -> torch.Tensor:
+        ops, spec = self.ops, self.spec
+        T = step.n_tokens
+        h = torch.empty((T, spec.hidden_size), dtype=torch.float32, device=self.device)
+        ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
+        for i, call in enumerate(self.order):
+            layer = self.layers[call.layer]
+            owner = i if call.cache_of is None else call.cache_of
+            layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),
+                                writes_cache=call.cache_of is None)
+        R = step.n_want
+        logits = torch.empty((R, spec.vocab_size), dtype=torch.float32, device=self.device)
+        if R:
+            wdt = self.head_weight.dtype
+            x = self.final_norm.forward(h, (wdt,), row_index=step.want_rows)[wdt]
+            ops.gemm(x, self.head_weight, logits, bias=self.head_bias)
+        return logits
+
+    def check_status(self):
+        """Raise if a kernel met a position without a page (synchronises)."""
+        if int(self.staging.status.item()) != 0:
+            self.staging.status.zero_()
+            raise ModelError("a kernel met a position whose page was not allocated")
+
+
+# ---------------------------------------------------------------------- loading by config.json
+
+def read_config(model_dir) -> dict:
+    path = Path(model_dir) / "config.json"
+    if not path.is_file():
+        raise ConfigError(f"{path} not found")
+    try:
+        return json.loads(path.read_text())
+    except ValueError as e:
+        raise ConfigError(f"{path} is not valid JSON: {e}") from None
+
+
+def architecture_of(config: dict):
+    archs = config.get("architectures")
+    if not archs or not isinstance(archs, list) or not isinstance(archs[0], str):
+        raise ConfigError("config.json has no 'architectures' entry; registered: " + ", ".join(ARCHITECTURES.names()))
+    return ARCHITECTURES.get(archs[0])
+
+
+def load_model(model_dir, **kw) -> Model:
+    """Build the model that config.json names and load its tensors from the folder."""
+    from .. import models  # noqa: F401  (registers the built-in architectures)
+    cfg = read_config(model_dir)
+    arch = architecture_of(cfg)
+    spec = arch.model_spec(arch.parse_config(cfg))
+    return Model(spec, SafetensorsSource(model_dir), **kw)

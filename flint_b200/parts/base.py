@@ -1,0 +1,103 @@
+"""What every part of a layer looks like to the model that holds it.
+
+A part gets its sizes and constants as parameters, names the tensors it expects under
+its own prefix, receives them once, and then runs on whatever rows a step brings.
+No part knows which architecture it is in; the reference's ops take spec structs in
+the same spirit (``NormSpec``, ``AttnSpec``, ``RopeArgs``, ``MlpSpec``:
+crates/thuban_model/src/ops/*.rs).
+
+Interfaces
+----------
+Norm          ``forward(x, want, row_index=None) -> {dtype: tensor}``
+              x is the float32 residual stream [T, H]; ``want`` is the set of element
+              types the next part asked for.
+Mixer         ``input_dtypes()``, ``cache_spec()``, ``state_spec()``,
+              ``forward(x, residual, step, cache, state, writes_cache=True)``:
+              adds its output into ``residual`` (float32 [T, H]) in place.
+FeedForward   ``input_dtypes()``, ``forward(x, residual, step)``: adds into ``residual``.
+PositionEncoding  ``rotary_dim``, ``tables() -> (cos, sin)`` float32 [positions, rotary_dim/2].
+Block         ``forward(residual, step, cache, state, writes_cache)``: the arrangement of
+              the parts of one layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..weights.sources import WeightSpec
+
+
+@dataclass
+class BuildContext:
+    """What parts need to know about where they run."""
+    ops: object                    # the kernel set
+    device: torch.device
+    compute: str                   # "bfloat16" or "float32"
+    shared: dict = field(default_factory=dict)   # things built once per model (position tables)
+
+    @property
+    def act_dtype(self):
+        return torch.bfloat16 if self.compute == "bfloat16" else torch.float32
+
+
+class Part:
+    """Base of all parts: parameters in, tensor specs out, tensors in."""
+
+    def __init__(self, params: dict, ctx: BuildContext):
+        self.params = dict(params)
+        self.ctx = ctx
+        self.ops = ctx.ops
+
+    def weights(self) -> dict:
+        """name (under this part's prefix) -> WeightSpec"""
+        return {}
+
+    def load(self, tensors: dict):
+        """Receives the tensors named by ``weights()`` (already on the device and typed
+        by the loader's policy)."""
+
+    def input_dtypes(self):
+        return (self.ctx.act_dtype,)
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def state_spec(self):
+        return None
+
+    def forward(self, x, residual, step, cache, state, writes_cache=True):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, residual, step):
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, x, want, row_index=None):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    rotary_dim = 0
+
+    def tables(self):
+        raise NotImplementedError
+
+
+def matmul_dtype(*ws):
+    """The element type a product over these stored matrices runs in: bfloat16 only if
+    all of them are bfloat16, else float32."""
+    return torch.bfloat16 if all(w.dtype == torch.bfloat16 for w in ws) else torch.float32
+
+
+def vec(n, init="normal", optional=False):
+    return WeightSpec((n,), role="vector", init=init, optional=optional)
+
+
+def mat(*shape):
+    return WeightSpec(tuple(shape), role="matrix")

@@ -1,0 +1,96 @@
+"""Feed-forward parts: a dense gated MLP and a top-2 sparsemixer mixture of experts.
+
+Dense: h += (act(x Wg^T) * (x Wu^T)) Wd^T, as the reference's feed-forward
+(crates/thuban_model/src/ops/mlp.rs:24-79).  Mixture of experts (no counterpart in
+the reference): float32 router logits, sparsemixer top-2 selection, rows sorted by
+expert, two grouped products, and the gated sum of the two experts' outputs added to
+the residual stream in a fixed order.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..errors import ConfigError
+from ..registry import FEED_FORWARDS
+from .base import FeedForward, mat, matmul_dtype
+
+TILE_ROWS = 64
+
+
+@FEED_FORWARDS.register("gated_mlp")
+class GatedMLP(FeedForward):
+    """params: hidden_size, intermediate_size, act; tensors gate_proj/up_proj [I,H], down_proj [H,I]."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.act = params.get("act", "silu")
+
+    def weights(self):
+        return {"gate_proj.weight": mat(self.inter, self.hidden), "up_proj.weight": mat(self.inter, self.hidden),
+                "down_proj.weight": mat(self.hidden, self.inter)}
+
+    def load(self, t):
+        dt = matmul_dtype(*t.values())
+        self.w_gate, self.w_up, self.w_down = (t[k].to(dt) for k in
+                                               ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+
+    def input_dtypes(self):
+        return (self.w_gate.dtype,)
+
+    def forward(self, x, residual, step):
+        xin = x[self.w_gate.dtype]
+        a = torch.empty((xin.shape[0], self.inter), dtype=self.w_gate.dtype, device=xin.device)
+        self.ops.gated_gemm(xin, self.w_gate, self.w_up, a, self.act)
+        self.ops.gemm(a, self.w_down, residual, accumulate=True)
+
+
+@FEED_FORWARDS.register("sparsemixer_moe")
+class SparseMixerMoE(FeedForward):
+    """params: hidden_size, intermediate_size, num_experts, jitter_eps, act.
+    tensors: gate.weight [E,H]; experts.{e}.w1 / w3 [I,H] (gate / up), w2 [H,I] (down)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        self.E = int(params["num_experts"])
+        if not 2 <= self.E <= 256:
+            raise ConfigError(f"num_experts {self.E} is not supported (2..256)")
+        self.eps = float(params["jitter_eps"])
+        self.act = params.get("act", "silu")
+
+    def weights(self):
+        w = {"gate.weight": mat(self.E, self.hidden)}
+        for e in range(self.E):
+            w[f"experts.{e}.w1.weight"] = mat(self.inter, self.hidden)
+            w[f"experts.{e}.w2.weight"] = mat(self.hidden, self.inter)
+            w[f"experts.{e}.w3.weight"] = mat(self.inter, self.hidden)
+        return w
+
+    def load(self, t):
+        self.w_router = t["gate.weight"]
+        dt = matmul_dtype(*(t[k] for k in t if k.startswith("experts.")))
+        stack = lambda n: torch.stack([t[f"experts.{e}.{n}.weight"].to(dt) for e in range(self.E)], 0).contiguous()
+        self.w1, self.w3, self.w2 = stack("w1"), stack("w3"), stack("w2")
+
+    def input_dtypes(self):
+        return (torch.float32, self.w1.dtype)
+
+    def forward(self, x, residual, step):
+        ops = self.ops
+        x32, xa = x[torch.float32], x[self.w1.dtype]
+        T = x32.shape[0]
+        dev = x32.device
+        ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
+        gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
+        ops.router_sparsemixer(x32, self.w_router, self.eps, ids, gates)
+        plan = ops.moe_plan(ids, self.E, TILE_ROWS)
+        xs = torch.empty((2 * T, self.hidden), dtype=xa.dtype, device=dev)
+        ops.gather_rows(xa, plan.token_of, xs)
+        a = torch.empty((2 * T, self.inter), dtype=self.w1.dtype, device=dev)
+        ops.gated_gemm(xs, self.w1, self.w3, a, self.act, plan)
+        y = torch.empty((2 * T, self.hidden), dtype=torch.float32, device=dev)
+        ops.grouped_gemm(a, self.w2, y, plan)
+        ops.moe_combine(residual, y, plan.row_of, gates)
+        if step.record is not None:
+            step.record.setdefault("experts", []).append(ids)
