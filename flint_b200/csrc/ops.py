@@ -239,6 +239,8 @@ class CudaOps:
             raise KernelError("paged_attention: cache pages do not match the head counts")
         span = min(max_kv_len, window) if window else max_kv_len
         split_keys, n_splits = splits or self.attention_splits(T, nq, nkv, span)
+        if split_keys * n_splits < span:
+            raise KernelError(f"paged_attention: {n_splits} splits of {split_keys} keys do not cover {span} keys")
         scratch = None
         if n_splits > 1:
             scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)

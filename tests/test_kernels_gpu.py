@@ -1,0 +1,281 @@
+"""Each CUDA kernel alone beside its plain reference, at sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+from flint_b200.cache.manager import CacheView, KVSpec
+from kernel_refs import RefOps
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from flint_b200.csrc.ops import get_ops
+    return get_ops(DEV)
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return RefOps(torch.float64)
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(a, b, rtol, atol):
+    a, b = a.double().cpu(), b.double().cpu()
+    err = (a - b).abs()
+    bound = atol + rtol * b.abs()
+    assert (err <= bound).all(), f"max err {err.max().item():.3e}, worst excess {(err - bound).max().item():.3e}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,V", [(1, 40, 17), (37, 1000, 333), (5, 4096, 64)])
+def test_embed(ops, ref, dtype, T, H, V):
+    table = rnd(V, H, dtype=dtype)
+    ids = torch.randint(0, V, (T,), dtype=torch.int32)
+    out = torch.empty(T, H, device=DEV)
+    ops.embed(ids.to(DEV), table.to(DEV), out, 1.0)
+    exp = torch.empty(T, H)
+    ref.embed(ids, table, exp)
+    assert torch.equal(out.cpu(), exp)
+
+
+@pytest.mark.parametrize("mode,bias", [("layer", True), ("layer", False), ("rms", False)])
+@pytest.mark.parametrize("T,H", [(1, 24), (33, 96), (7, 1000), (3, 4096), (2, 5000)])
+def test_norm(ops, ref, mode, bias, T, H):
+    x = rnd(T, H, scale=3.0) + 1.5          # a mean far from zero shows a one-pass variance
+    gamma, beta = 1 + rnd(H, seed=1) * 0.1, (rnd(H, seed=2) * 0.1 if bias else None)
+    o32, o16 = torch.empty(T, H, device=DEV), torch.empty(T, H, device=DEV, dtype=torch.bfloat16)
+    ops.norm(x.to(DEV), gamma.to(DEV), beta.to(DEV) if bias else None, 1e-5, mode, out_f32=o32, out_bf16=o16)
+    e32 = torch.empty(T, H)
+    ref.norm(x, gamma, beta, 1e-5, mode, out_f32=e32)
+    close(o32, e32, 1e-5, 1e-5)
+    close(o16, e32, 1e-2, 1e-2)
+    # gathered rows
+    idx = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    o = torch.empty(3, H, device=DEV)
+    ops.norm(x.to(DEV), gamma.to(DEV), beta.to(DEV) if bias else None, 1e-5, mode, out_f32=o, row_index=idx.to(DEV))
+    close(o, e32[idx.long()], 1e-5, 1e-5)
+
+
+GEMM_SHAPES = [(1, 16, 64), (3, 17, 33), (64, 64, 64), (65, 130, 100), (200, 96, 80), (7, 384, 96), (130, 250, 1000)]
+
+
+@pytest.mark.parametrize("xd,wd,od", [(torch.float32,) * 3, (torch.bfloat16, torch.bfloat16, torch.float32),
+                                      (torch.bfloat16, torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.float32, torch.float32)])
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_dense(ops, ref, xd, wd, od, M, N, K):
+    x, w, b = rnd(M, K, dtype=xd), rnd(N, K, dtype=wd, seed=1), rnd(N, seed=2)
+    out0 = rnd(M, N, dtype=od, seed=3)
+    for bias, acc in ((None, False), (b, False), (b, True)):
+        out = out0.clone().to(DEV)
+        ops.gemm(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV) if bias is not None else None, accumulate=acc)
+        exp = out0.clone().double()
+        ref.gemm(x, w, exp, bias=bias, accumulate=acc)
+        tol = (1e-5, 1e-4) if od == torch.float32 else (1e-2, 1e-2)
+        close(out, exp, *tol)
+
+
+def test_gemm_strided_output(ops, ref):
+    x, w = rnd(9, 40), rnd(24, 40, seed=1)
+    full = torch.zeros(9, 100, device=DEV)
+    ops.gemm(x.to(DEV), w.to(DEV), full[:, :24])
+    exp = torch.zeros(9, 24, dtype=torch.float64)
+    ref.gemm(x, w, exp)
+    close(full[:, :24], exp, 1e-5, 1e-4)
+    assert (full[:, 24:] == 0).all()
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu_pytorch_tanh"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_and_grouped(ops, ref, act, dtype):
+    T, H, I, E = 75, 96, 80, 6
+    ids = torch.randint(0, E, (T, 2), dtype=torch.int32)
+    ids[:, 1] = (ids[:, 0] + 1 + ids[:, 1] % (E - 1)) % E
+    ids[ids == 4] = 0                      # expert 4 gets no rows
+    ids[:, 1] = torch.where(ids[:, 1] == ids[:, 0], (ids[:, 0] + 1) % E, ids[:, 1])
+    plan = ops.moe_plan(ids.to(DEV), E, 64)
+    rplan = ref.moe_plan(ids, E, 64)
+    assert torch.equal(plan.counts.cpu(), rplan.counts) and torch.equal(plan.offsets.cpu(), rplan.offsets)
+    assert int(plan.n_tiles.item()) == int(rplan.n_tiles.item())
+    nt = int(plan.n_tiles)
+    assert torch.equal(plan.tile_expert.cpu()[:nt], rplan.tile_expert[:nt])
+    assert torch.equal(plan.tile_row0.cpu()[:nt], rplan.tile_row0[:nt])
+    # every (token, choice) has a row of its own inside its expert's range, and token_of inverts row_of
+    row_of, token_of = plan.row_of.cpu().long(), plan.token_of.cpu().long()
+    assert sorted(row_of.reshape(-1).tolist()) == list(range(2 * T))
+    off = plan.offsets.cpu().long()
+    e_of = ids.long()
+    assert ((row_of >= off[e_of]) & (row_of < off[e_of + 1])).all()
+    assert torch.equal(token_of[row_of], torch.arange(T)[:, None].expand(T, 2))
+
+    x = rnd(T, H, dtype=dtype)
+    xs = torch.empty(2 * T, H, dtype=dtype, device=DEV)
+    ops.gather_rows(x.to(DEV), plan.token_of, xs)
+    assert torch.equal(xs.cpu(), x[token_of])
+    w1, w3, w2 = (rnd(E, I, H, dtype=dtype, seed=1, scale=0.1), rnd(E, I, H, dtype=dtype, seed=2, scale=0.1),
+                  rnd(E, H, I, dtype=dtype, seed=3, scale=0.1))
+    a = torch.empty(2 * T, I, dtype=dtype, device=DEV)
+    ops.gated_gemm(xs, w1.to(DEV), w3.to(DEV), a, act, plan)
+    # the reference works on the same row order
+    from flint_b200.csrc.ops import MoePlan
+    cplan = MoePlan(E, 64, plan.max_tiles, *(t.cpu() for t in (plan.counts, plan.offsets, plan.row_of, plan.token_of,
+                                                             plan.tile_expert, plan.tile_row0, plan.n_tiles)))
+    ea = torch.zeros(2 * T, I, dtype=torch.float64)
+    ref.gated_gemm(xs.cpu(), w1, w3, ea, act, cplan)
+    tol = (1e-5, 1e-4) if dtype == torch.float32 else (2e-2, 2e-2)
+    close(a, ea, *tol)
+    y = torch.empty(2 * T, H, device=DEV)
+    ops.grouped_gemm(a, w2.to(DEV), y, plan)
+    ey = torch.zeros(2 * T, H, dtype=torch.float64)
+    ref.grouped_gemm(a.cpu(), w2, ey, cplan)
+    close(y, ey, 1e-5, 1e-5)
+    gates = torch.rand(T, 2)
+    h0 = rnd(T, H, seed=9)
+    h = h0.clone().to(DEV)
+    ops.moe_combine(h, y, plan.row_of, gates.to(DEV))
+    eh = h0.clone().double()
+    ref.moe_combine(eh, y.cpu(), cplan.row_of, gates)
+    close(h, eh, 1e-5, 1e-5)
+    # dense gated product (one "expert")
+    d = torch.empty(T, I, dtype=dtype, device=DEV)
+    ops.gated_gemm(x.to(DEV), w1[0].to(DEV), w3[0].to(DEV), d, act)
+    ed = torch.zeros(T, I, dtype=torch.float64)
+    ref.gated_gemm(x, w1[0], w3[0], ed, act)
+    close(d, ed, *tol)
+
+
+@pytest.mark.parametrize("wd", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,E,eps", [(50, 96, 6, 0.05), (9, 1000, 16, 0.01), (33, 64, 4, 0.3), (4, 40, 3, 0.01)])
+def test_router_sparsemixer(ops, ref, wd, T, H, E, eps):
+    x, wr = rnd(T, H), rnd(E, H, dtype=wd, seed=1, scale=0.3)
+    # hand-made rows: a tie for the maximum, a negative maximum, a runner-up inside the mask band
+    tie = torch.zeros(H); x[0] = tie
+    ids, gates = torch.empty(T, 2, dtype=torch.int32, device=DEV), torch.empty(T, 2, device=DEV)
+    lg = torch.empty(T, E, device=DEV)
+    ops.router_sparsemixer(x.to(DEV), wr.to(DEV), eps, ids, gates, lg)
+    eids, egates, elg = torch.empty(T, 2, dtype=torch.int32), torch.empty(T, 2, dtype=torch.float64), torch.empty(T, E, dtype=torch.float64)
+    RefOps(torch.float64).router_sparsemixer(x, wr, eps, eids, egates, elg)
+    close(lg, elg, 1e-5, 1e-5)
+    assert torch.equal(ids.cpu(), eids)
+    close(gates, egates, 1e-4, 1e-5)
+    assert ids.cpu()[0].tolist() == [0, 1]      # ties go to the lowest index
+
+
+def test_sparsemixer_by_hand(ops):
+    """Router logits chosen by an identity-like weight so that the selection can be checked by hand:
+    s = [2, 1.9, -1, 0.5], eps 0.1 -> threshold 0.2.  First pick 0; (2-1.9)/2=0.05 keeps 1, others
+    masked: g1 = 1/(1+e^-0.1).  Second pick 1 (m2=1.9): (1.9-0.5)/1.9 > 0.2 masked, (1.9+1)/1.9 masked:
+    g2 = 1."""
+    H, E = 8, 4
+    wr = torch.zeros(E, H); wr[0, 0] = wr[1, 1] = wr[2, 2] = wr[3, 3] = 1.0
+    x = torch.zeros(2, H); x[0, :4] = torch.tensor([2.0, 1.9, -1.0, 0.5])
+    x[1, :4] = torch.tensor([-3.0, -1.0, -1.05, -2.0])   # negative maximum: factor = |s|
+    ids, gates = torch.empty(2, 2, dtype=torch.int32, device=DEV), torch.empty(2, 2, device=DEV)
+    ops.router_sparsemixer(x.to(DEV), wr.to(DEV), 0.1, ids, gates)
+    assert ids.cpu().tolist() == [[0, 1], [1, 2]]
+    g = gates.cpu()
+    assert abs(g[0, 0].item() - 1 / (1 + math.exp(-0.1))) < 1e-6 and abs(g[0, 1].item() - 1.0) < 1e-6
+    # row 1: m1=-1: (-1+1.05)/1.05=0.0476 keeps 2; (-1+2)/2=.5, (-1+3)/3=.67 masked -> g1=1/(1+e^-0.05)
+    assert abs(g[1, 0].item() - 1 / (1 + math.exp(-0.05))) < 1e-6
+    # second pick 2 (m2=-1.05): (-1.05+2)/2=.475 masked, (-1.05+3)/3=.65 masked -> g2 = 1
+    assert abs(g[1, 1].item() - 1.0) < 1e-6
+
+
+def make_cache(n_pages, nkv, P, hd, dtype, slots, max_pages, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    k = torch.randn(n_pages, nkv, P, hd, generator=g).to(dtype)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(dtype)
+    bt = torch.full((slots, max_pages), -1, dtype=torch.int32)
+    return k, v, bt
+
+
+def views(k, v, bt, P, nkv, hd, window):
+    spec = KVSpec(nkv, hd, window)
+    return (CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec), CacheView(k.clone(), v.clone(), bt.clone(), P, spec))
+
+
+@pytest.mark.parametrize("qd,cd", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("nq,nkv,hd,P,window", [(4, 2, 16, 16, 0), (3, 1, 32, 16, 48), (6, 1, 48, 32, 0),
+                                                 (32, 8, 128, 64, 0), (5, 5, 80, 16, 20), (16, 2, 256, 16, 0)])
+def test_rope_write_and_attention(ops, ref, qd, cd, nq, nkv, hd, P, window):
+    slots, max_pages, n_pages = 3, 12, 30
+    k, v, bt = make_cache(n_pages, nkv, P, hd, cd, slots, max_pages)
+    # scattered pages: slot 0 holds 150 positions, slot 2 holds 37
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+    bt[0, :10] = perm[:10]; bt[2, :3] = perm[10:13]
+    lens = {0: min(150, 10 * P), 2: min(37, 3 * P)}
+    dv, cv = views(k, v, bt, P, nkv, hd, window)
+    # rows: a portion of slot 0 ending at its last position, and one decoded token of slot 2
+    n0 = 23
+    pos = torch.tensor(list(range(lens[0] - n0, lens[0])) + [lens[2] - 1], dtype=torch.int32)
+    slot = torch.tensor([0] * n0 + [2], dtype=torch.int32)
+    T = pos.numel()
+    rot = hd if hd != 80 else 48
+    maxpos = 256
+    ang = torch.arange(maxpos, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(rot // 2, dtype=torch.float64) * 2 / rot))
+    cos, sin = (torch.cos(ang) * 1.2).float(), (torch.sin(ang) * 1.2).float()
+    qkv = rnd(T, (nq + 2 * nkv) * hd)
+    q_d = torch.empty(T, nq * hd, dtype=qd, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(qkv.to(DEV), pos.to(DEV), slot.to(DEV), cos.to(DEV), sin.to(DEV), rot, q_d, dv, nq, nkv, hd, True, status)
+    q_r = torch.empty(T, nq * hd, dtype=torch.float64)
+    ref.rope_kv_write(qkv, pos, slot, cos, sin, rot, q_r, cv, nq, nkv, hd, True, None)
+    assert int(status.item()) == 0
+    tol = (1e-6, 1e-6) if qd == torch.float32 else (1e-2, 1e-2)
+    close(q_d, q_r, *tol)
+    close(dv.k, cv.k, *((1e-6, 1e-6) if cd == torch.float32 else (1e-2, 1e-2)))
+    close(dv.v, cv.v, 0, 0)
+    # make one far key stand out for row 0 of slot 0, so that a kernel that skips it is caught
+    out_d = torch.empty(T, nq * hd, dtype=qd, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    for splits in (None, (32, -(-min(lens[0], window or 10 ** 9) // 32)), (64, -(-min(lens[0], window or 10 ** 9) // 64))):
+        ops.paged_attention(q_d, dv, pos.to(DEV), slot.to(DEV), out_d, nq, nkv, hd, window, scale, max(lens.values()), splits=splits)
+        out_r = torch.empty(T, nq * hd, dtype=torch.float64)
+        # the reference reads the device's cache content (bf16-rounded where it is) and the device's q
+        cv2 = CacheView(dv.k.cpu(), dv.v.cpu(), bt, P, dv.spec)
+        ref.paged_attention(q_d.cpu(), cv2, pos, slot, out_r, nq, nkv, hd, window, scale, max(lens.values()))
+        close(out_d, out_r, *((2e-5, 2e-5) if qd == torch.float32 else (2e-2, 2e-2)))
+
+
+def test_attention_far_key_stands_out(ops, ref):
+    """One key far back among hundreds gets a large score: the output must be (almost) its value."""
+    nq, nkv, hd, P = 2, 1, 32, 16
+    n_pages, L = 40, 600
+    k, v, bt = make_cache(n_pages, nkv, P, hd, torch.float32, 1, 40, seed=3)
+    k *= 0.05
+    bt[0, :38] = torch.arange(38, dtype=torch.int32).flip(0)
+    far = 3
+    q = rnd(1, nq * hd) * 0.05
+    k[bt[0, far // P].long(), 0, far % P] = q[0, :hd] * 4000.0      # head 0's query matches this key
+    dv, cv = views(k, v, bt, P, nkv, hd, 0)
+    pos, slot = torch.tensor([L - 1], dtype=torch.int32), torch.tensor([0], dtype=torch.int32)
+    out = torch.empty(1, nq * hd, device=DEV)
+    for splits in (None, (32, 19), (600, 1)):
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, 0, 1 / math.sqrt(hd), L, splits=splits)
+        exp = torch.empty(1, nq * hd, dtype=torch.float64)
+        ref.paged_attention(q, cv, pos, slot, exp, nq, nkv, hd, 0, 1 / math.sqrt(hd), L)
+        close(out, exp, 1e-4, 1e-5)
+        close(out[0, :hd], v[bt[0, far // P].long(), 0, far % P], 1e-3, 1e-3)
+    # with a window that ends just after the far key it must vanish; one position wider and it is back
+    for window, present in ((L - 1 - far, False), (L - far, True)):
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, 1 / math.sqrt(hd), L)
+        is_far = torch.allclose(out[0, :hd].cpu(), v[bt[0, far // P].long(), 0, far % P], atol=1e-3)
+        assert is_far == present
+
+
+@pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (3, 32064)])
+def test_argmax(ops, R, V):
+    lg = rnd(R, V)
+    lg[0, 3] = lg[0, min(7, V - 1)] = 100.0        # first maximum wins
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    ops.argmax(lg.to(DEV), out)
+    assert out.cpu().tolist() == torch.argmax(lg, -1).tolist()
+    assert out.cpu()[0].item() == 3
