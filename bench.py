@@ -1,0 +1,289 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine at Phi-mini-MoE layer sizes, random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 (a "step" is
+one decode step of the whole batch, timed on the device with CUDA events); ``e2e`` is
+the same through ``Engine.step`` with host tokens in and out; ``prefill`` is one
+2,048-token prompt; ``roofline`` relates the bytes a decode step must read to its time;
+``points`` has decode at batch 1 and 64.  The engine runs on one GPU: for ``--gpus N``
+with N > 1 it says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import random
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+# Phi-mini-MoE layer sizes (the third configuration of BASELINE.json)
+MINI = {
+    "architectures": ["PhimoeForCausalLM"], "model_type": "phimoe",
+    "vocab_size": 32064, "hidden_size": 4096, "intermediate_size": 960, "num_hidden_layers": 32,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
+    "max_position_embeddings": 131072, "original_max_position_embeddings": 4096, "rope_theta": 10000.0,
+    "sliding_window": 131072, "rms_norm_eps": 1e-5, "hidden_act": "silu",
+    "attention_bias": True, "lm_head_bias": True, "tie_word_embeddings": False,
+    "num_local_experts": 16, "num_experts_per_tok": 2, "router_jitter_noise": 0.01,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            d = json.load(open(path))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except (ValueError, KeyError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+def mini_config(layers=None):
+    cfg = dict(MINI)
+    r = random.Random(7)
+    cfg["rope_scaling"] = {"type": "longrope",
+                           "short_factor": [round(r.uniform(1, 4), 4) for _ in range(64)],
+                           "long_factor": [round(r.uniform(1, 4), 4) for _ in range(64)]}
+    if layers:
+        cfg["num_hidden_layers"] = layers
+    return cfg
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v == "Active"})
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def build_model(cfg, max_slots, ctx, device="cuda:0"):
+    import torch
+    from flint_b200.engine.loading import expected_from_config
+    from flint_b200.engine.model import Model
+    from flint_b200.weights.sources import RandomSource
+    spec, expected = expected_from_config(cfg)
+    src = RandomSource(expected, seed=0, dtype=torch.bfloat16, on_device=True)
+    return Model(spec, src, dtype="bfloat16", device=device, page_size=64, n_pages=max_slots * (ctx // 64),
+                 max_slots=max_slots, max_context=ctx, max_step_tokens=max(2048, max_slots))
+
+
+def step_flops(cfg, n_tokens, kv_lens):
+    """Multiply-add flops x2 of one step: projections, attention over the cache, router, two experts."""
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    nq, nkv, hd, E = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_local_experts"]
+    per_tok = 2 * H * (nq + 2 * nkv) * hd + 2 * nq * hd * H + 2 * H * E + 2 * (3 * H * I) * 2
+    attn = sum(4 * nq * hd * k for k in kv_lens)       # QK^T and PV per (token, keys seen)
+    return L * (n_tokens * per_tok + attn)
+
+
+def decode_bytes(cfg, model, batch_kv_lens, distinct_experts):
+    """Bytes a decode step must read: every weight it uses once, and the live requests' cache."""
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    nq, nkv, hd, E, V = (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"],
+                         cfg["num_local_experts"], cfg["vocab_size"])
+    attn_w = ((nq + 2 * nkv) * hd * H + nq * hd * H) * 2
+    router = E * H * 2
+    expert = 3 * H * I * 2
+    weights = L * (attn_w + router) + sum(distinct_experts) * expert + V * H * 2
+    kv = sum(batch_kv_lens) * nkv * hd * 2 * 2 * L
+    return weights + kv
+
+
+def run_decode(model, cfg, batch, prompt_len, steps, warmup, rng, count_experts=True):
+    """Prefill ``batch`` requests of ``prompt_len`` random tokens, then time decode steps."""
+    import torch
+    from flint_b200.engine.step import StepEntry
+    V = cfg["vocab_size"]
+    slots = [model.cache.admit() for _ in range(batch)]
+    for s in slots:
+        toks = [rng.randrange(V) for _ in range(prompt_len)]
+        model.cache.ensure(s, 0, prompt_len)
+        model.step([StepEntry(s, 0, toks, [])])
+    pos = prompt_len
+    distinct = None
+    if count_experts:
+        rec = {}
+        for s in slots:
+            model.cache.ensure(s, pos, pos + 1)
+        model.step([StepEntry(s, pos, [rng.randrange(V)], [0]) for s in slots], record=rec)
+        distinct = [int(torch.unique(ids).numel()) for ids in rec["experts"]]
+        pos += 1
+
+    def one():
+        nonlocal pos
+        for s in slots:
+            model.cache.ensure(s, pos, pos + 1)
+        out = model.step([StepEntry(s, pos, [rng.randrange(V)], [0]) for s in slots])
+        pos += 1
+        return out
+    for _ in range(warmup):
+        one()
+    torch.cuda.synchronize()
+    l0 = model.ops.launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = model.ops.launches - l0
+    kv_lens = [pos] * batch
+    for s in slots:
+        model.cache.release(s)
+    return {"ms": ms, "tok_s": batch * 1000.0 / ms, "launches": launches, "distinct": distinct, "kv_lens": kv_lens}
+
+
+def run_prefill(model, cfg, n_tokens, reps, warmup, rng):
+    import torch
+    from flint_b200.engine.step import StepEntry
+    V = cfg["vocab_size"]
+    times = []
+    for i in range(warmup + reps):
+        s = model.cache.admit()
+        toks = [rng.randrange(V) for _ in range(n_tokens)]
+        model.cache.ensure(s, 0, n_tokens)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        model.step([StepEntry(s, 0, toks, [n_tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+        model.cache.release(s)
+    return statistics.median(times)
+
+
+def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
+    """The same decode through the public entry point: Engine.step, host tokens in and out."""
+    import torch
+    from flint_b200.engine.engine import Engine
+    from flint_b200.sampling.params import SamplingParams
+    eng = Engine(model, SamplingParams.greedy(), seed=1, prefill_chunk=2048, max_step_tokens=2048 + batch)
+    V = cfg["vocab_size"]
+    ids = [eng.create([rng.randrange(V) for _ in range(prompt_len)], steps + warmup + 8) for _ in range(batch)]
+    while any(r.remaining > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_tok = 0
+    for _ in range(steps):
+        n_tok += eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    h2d = model.staging.host.numel() * 4
+    for i in ids:
+        eng.close(i)
+    return {"tok_s": n_tok / dt, "h2d": h2d, "d2h": batch * 4, "ms": dt * 1000 / steps}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-tokens", type=int, default=2048)
+    ap.add_argument("--ctx-size", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are named)")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "formetaohy/Flint is a Rust workspace that reaches the GPU only through wgpu on Vulkan/Metal: "
+                          "no Python package to install offline, no cargo here, no graphics API on this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    pk = peaks()
+    cfg = mini_config(args.layers)
+    rng = random.Random(0)
+    max_batch = max(args.batch, 1 if args.no_points else 64)
+    model = build_model(cfg, max_batch, args.ctx_size)
+
+    clocks = ClockSampler()
+    clocks.start()
+    pre_ms = run_prefill(model, cfg, 2048, reps=3, warmup=3, rng=rng)
+    dec = run_decode(model, cfg, args.batch, args.prompt_tokens, args.steps, warmup, rng)
+    clock = clocks.stop()
+    e2e = run_e2e(model, cfg, args.batch, args.prompt_tokens, args.steps, warmup, rng)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(run_decode(model, cfg, b, args.prompt_tokens, max(8, args.steps // 2), warmup,
+                                                      rng, count_experts=False)["tok_s"], 1)
+
+    pre_flops = step_flops(cfg, 2048, range(1, 2049))
+    bytes_step = decode_bytes(cfg, model, dec["kv_lens"], dec["distinct"])
+    achieved = bytes_step / (dec["ms"] * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s at batch 8 (Phi-mini-MoE layer sizes, 2,048-token prompts, context 4,096)",
+        "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
+        "config": {"model": "Phi-mini-MoE sizes", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
+                   "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "experts": 16, "top_k": 2,
+                   "expert_intermediate": 960, "vocab": 32064, "global_batch": args.batch,
+                   "prompt_tokens": args.prompt_tokens, "seq_len": args.ctx_size, "page_size": 64,
+                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed every step)",
+                   "peaks": pk["source"]},
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
+                "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
+        "gpu_launches": dec["launches"],
+        "prefill": {"value": round(2048 * 1000.0 / pre_ms, 1), "tokens": 2048, "ms": round(pre_ms, 3),
+                    "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": bytes_step,
+                     "distinct_experts_per_layer": round(sum(dec["distinct"]) / len(dec["distinct"]), 2)},
+        "points": points,
+        "clocks": clock,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -73,7 +73,8 @@ class Model:
     """Parts + tensors + cache + step function for one model on one device."""
 
     def __init__(self, spec: ModelSpec, source, *, dtype="bfloat16", device="cuda:0", ops=None,
-                 page_size=64, n_pages=None, max_slots=8, max_context=None, max_step_tokens=8192):
+                 page_size=64, n_pages=None, max_slots=8, max_context=None, max_step_tokens=8192,
+                 use_graphs=True):
         if dtype not in ("bfloat16", "float32"):
             raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}")
         self.spec = spec
@@ -133,6 +134,12 @@ class Model:
                                   max_context=self.max_context, dtype=cache_dtype, device=self.device)
         self.staging = StepStaging(max_step_tokens, self.device)
         self.max_step_tokens = max_step_tokens
+        # decode steps (one token per entry) are captured once per batch size and key-range
+        # split, and replayed: their hundreds of small launches would otherwise be bound by
+        # the host
+        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self._graphs = {}
+        self.graph_max_batch = 256
 
     # ------------------------------------------------------------------ facts
     @property
@@ -172,7 +179,43 @@ class Model:
         step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
         step.record = record
         step.attention_splits = attention_splits
+        if (self.use_graphs and record is None and attention_splits is None
+                and step.n_tokens == len(entries) <= self.graph_max_batch and step.n_want == step.n_tokens):
+            return self._graphed_decode(step)
         return self.forward(step)
+
+    def _decode_splits(self, step):
+        """Key-range split for a decode batch, from a bucketed context length so that
+        few graphs are needed as requests grow."""
+        bucket = 256
+        while bucket < step.max_kv_len:
+            bucket *= 2
+        spans = [bucket]
+        for i, call in enumerate(self.order):
+            mixer = self.layers[call.layer].parts.get("mixer")
+            ks = mixer.cache_spec() if mixer is not None else None
+            if ks is not None and ks.window:
+                spans.append(min(bucket, ks.window))
+        return bucket, spans
+
+    def _graphed_decode(self, step):
+        bucket, _ = self._decode_splits(step)
+        key = (step.n_tokens, bucket)
+        entry = self._graphs.get(key)
+        step.max_kv_len = bucket          # splits are chosen for the bucket, not the exact length
+        if entry is None:
+            self.forward(step)            # loads modules and warms the allocator outside the capture
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = self.ops.launches
+            with torch.cuda.graph(graph):
+                logits = self.forward(step)
+            entry = (graph, logits, self.ops.launches - before)
+            self._graphs[key] = entry
+        graph, logits, n = entry
+        graph.replay()
+        self.ops.launches += n
+        return logits
 
     def forward(self, step) -> torch.Tensor:
         ops, spec = self.ops, self.spec
