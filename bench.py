@@ -98,7 +98,7 @@ def build_model(cfg, max_slots, ctx, device="cuda:0"):
     spec, expected = expected_from_config(cfg)
     src = RandomSource(expected, seed=0, dtype=torch.bfloat16, on_device=True)
     return Model(spec, src, dtype="bfloat16", device=device, page_size=64, n_pages=max_slots * (ctx // 64),
-                 max_slots=max_slots, max_context=ctx, max_step_tokens=max(2048, max_slots))
+                 max_slots=max_slots, max_context=ctx, max_step_tokens=2048 + max_slots)
 
 
 def step_flops(cfg, n_tokens, kv_lens):

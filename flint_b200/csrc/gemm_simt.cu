@@ -29,7 +29,7 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
                  const TW* __restrict__ w_up, const float* __restrict__ bias,
                  TO* __restrict__ out, int ldo, int accumulate, int act,
                  const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
-                 const int* __restrict__ n_tiles, const int* __restrict__ offsets,
+                 const int* __restrict__ n_tiles, const int* __restrict__ offsets, int tile_rows,
                  int M, int N, int K) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
@@ -40,7 +40,7 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
     if ((int)blockIdx.y >= *n_tiles) return;
     expert = tile_expert[blockIdx.y];
     row0 = tile_row0[blockIdx.y];
-    row_end = offsets[expert + 1];
+    row_end = min(offsets[expert + 1], row0 + tile_rows);
   }
   const int col0 = blockIdx.x * BN;
   const TW* we = w + (size_t)expert * N * K;
@@ -103,16 +103,17 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
 
 // x [rows, K] (row stride ldx), w / w_up [E, N, K], out [rows, N] (row stride ldo).
 // Dense: tile_expert == NULL, rows = M, one "expert".  Grouped: rows of expert e are
-// offsets[e] .. offsets[e+1]-1, and tile i covers up to 64 rows from tile_row0[i] of
+// offsets[e] .. offsets[e+1]-1, and tile i covers up to tile_rows (<= 64) rows from tile_row0[i] of
 // expert tile_expert[i]; only the first *n_tiles tiles exist (max_tiles bounds the grid).
 extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* w, const void* w_up,
                                int w_dtype, const float* bias, void* out, int out_dtype, int ldo,
                                int accumulate, int act, const int* tile_expert,
                                const int* tile_row0, const int* n_tiles, const int* offsets,
-                               int max_tiles, int M, int N, int K, cudaStream_t stream) {
+                               int max_tiles, int tile_rows, int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return fail("gemm_simt: K=%d", K);
   if (w_up && accumulate) return fail("gemm_simt: a gated product cannot accumulate");
+  if (tile_expert && (tile_rows < 1 || tile_rows > BM)) return fail("gemm_simt: row tiles of %d rows (1..%d)", tile_rows, BM);
   const int tiles_m = tile_expert ? max_tiles : (M + BM - 1) / BM;
   if (tiles_m <= 0) return 0;
   if (tiles_m > 65535) return fail("gemm_simt: %d row tiles exceed the grid limit", tiles_m);
@@ -122,11 +123,11 @@ extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* 
     if (w_up)                                                                                     \
       gemm_simt_kernel<TX, TW, TO, true><<<grid, THREADS, 0, stream>>>(                           \
           (const TX*)x, ldx, (const TW*)w, (const TW*)w_up, bias, (TO*)out, ldo, accumulate, act, \
-          tile_expert, tile_row0, n_tiles, offsets, M, N, K);                                     \
+          tile_expert, tile_row0, n_tiles, offsets, tile_rows, M, N, K);                                     \
     else                                                                                          \
       gemm_simt_kernel<TX, TW, TO, false><<<grid, THREADS, 0, stream>>>(                          \
           (const TX*)x, ldx, (const TW*)w, nullptr, bias, (TO*)out, ldo, accumulate, act,         \
-          tile_expert, tile_row0, n_tiles, offsets, M, N, K);                                     \
+          tile_expert, tile_row0, n_tiles, offsets, tile_rows, M, N, K);                                     \
   } while (0)
   FLINT_DISPATCH_DTYPE(x_dtype, TX, FLINT_DISPATCH_DTYPE(w_dtype, TW,
       FLINT_DISPATCH_DTYPE(out_dtype, TO, LAUNCH(TX, TW, TO))));

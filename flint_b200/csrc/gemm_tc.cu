@@ -1,0 +1,466 @@
+// bfloat16 matrix products on the 5th-generation tensor cores (tcgen05) of sm_100a:
+//   out[r, n] = sum_k x[r, k] * W[n, k]      x [rows, K] bf16, W [N, K] bf16, fp32 accumulation.
+//
+// Layout of one CTA's tile.  The *weights* sit on the MMA's M side: a tile is 128 output
+// features (rows of W) by BN token rows of x (BN = 16..256).  So the accumulator in tensor
+// memory has one lane per output feature and one column per token, and small batches
+// (decode) need no padding to 128 rows: a batch of 8 runs as a 128 x 16 tile that streams
+// the weights once.  Both operands are K-major in shared memory, 64 bf16 (128 bytes) per
+// row, 128-byte swizzle, loaded by TMA (cp.async.bulk.tensor.2d, no multicast); the
+// K loop is a ring of `stages` buffers with full/empty mbarriers.
+//
+// Roles (192 threads): warp 0 lane 0 issues TMA loads; warp 1 allocates tensor memory and
+// its lane 0 issues tcgen05.mma (4 of K=16 per 64-wide block) and tcgen05.commit; warps
+// 2..5 wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes) and
+// run the epilogue: bias, SiLU/GELU gate times up (two accumulators), add to the output
+// (residual stream), narrowing to bf16, or a float32 partial tile when the K range is
+// split over several CTAs (then a second kernel sums the partials in a fixed order).
+// Grouped products (experts) use the same kernel: rows are sorted by expert and a tile
+// map names the expert and first row of each row tile; the experts' weights are one
+// stacked [E*N, K] tensor, so a tile that hangs over the end of an expert reads rows
+// of the next one and the epilogue masks them.
+//
+// Every wait on an mbarrier is bounded: after about two seconds the kernel sets an error
+// flag, lets its copies land, frees its tensor memory and returns.
+//
+// Reference counterparts: crates/thuban_kernel/wgsl/gemm_coop_m16.wgsl (cooperative-matrix
+// 16x16x16 tiles, f16), gemm.wgsl (ACC=1 residual add), gemv.wgsl (decode), bias.wgsl,
+// swiglu.wgsl.
+#include <cuda.h>
+#include <math.h>
+#include <stdarg.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+using namespace flint;
+
+namespace {
+
+constexpr int BM = 128;          // output features per tile (MMA M)
+constexpr int BK = 64;           // bf16 per K block = one 128-byte swizzle row
+constexpr int THREADS = 192;
+constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+
+struct Params {
+  void* out;
+  const float* bias;
+  float* partial;              // [splits, rows, N] when splits > 1
+  const int* tile_expert;
+  const int* tile_row0;
+  const int* n_tiles;
+  const int* offsets;
+  int* error_flag;
+  int out_dtype, ldo, accumulate, act;
+  int rows, N, K;
+  int kb_per_split, splits, stages;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false (and raises *abort) when the limit passes or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 255) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > WAIT_CYCLES) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float* v) {
+  uint32_t r[8];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
+// start address, leading offset (unused with swizzle, by convention 1), stride between groups of 8
+// rows = 1024 bytes, descriptor version 1 (sm_100), layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = bn.
+__device__ __forceinline__ uint32_t instr_desc(int bn) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ float act_fn(float g, int act) {
+  if (act == 0) return g / (1.0f + __expf(-g));
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+
+template <int BN, bool GATED>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u,
+               const __grid_constant__ CUtensorMap map_x, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * 16 + 1];   // full[stages], empty[stages], accumulator
+  __shared__ uint32_t tmem_holder;
+  __shared__ int abort_flag;
+
+  if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
+  // ---- which tile
+  int expert = 0, row0 = blockIdx.y * BN, row_end = p.rows;
+  if (p.tile_expert) {
+    if ((int)blockIdx.y >= *p.n_tiles) return;
+    expert = p.tile_expert[blockIdx.y];
+    row0 = p.tile_row0[blockIdx.y];
+    row_end = p.offsets[expert + 1];
+  }
+  const int f0 = blockIdx.x * BM;                 // first feature of the tile inside the expert
+  const int w_row = expert * p.N + f0;            // row in the stacked weight tensor
+  const int total_kb = (p.K + BK - 1) / BK;
+  const int kb0 = blockIdx.z * p.kb_per_split;
+  const int nkb = min(total_kb, kb0 + p.kb_per_split) - kb0;
+
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (GATED ? 2 * BN : BN) < 32 ? 32 : (GATED ? 2 * BN : BN);
+  const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int stages = p.stages;
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), accum_bar = smem_u32(&bars[32]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(accum_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = tmem_holder;
+  volatile int* ab = &abort_flag;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    for (int i = 0; i < nkb; ++i) {
+      const int s = i % stages;
+      if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, ab)) break;
+      const uint32_t a = tiles + s * STAGE_BYTES;
+      const uint32_t bar = full0 + 8 * s;
+      mbar_expect_tx(bar, STAGE_BYTES);
+      const int kx = (kb0 + i) * BK;
+      tma_load_2d(a, &map_w, kx, w_row, bar);
+      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w_row, bar);
+      tma_load_2d(a + A_BYTES * (GATED ? 2 : 1), &map_x, kx, row0, bar);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------------------------------------------------------- MMA issuer
+    const uint32_t idesc = instr_desc(BN);
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % stages;
+      ok = mbar_wait(full0 + 8 * s, (i / stages) & 1, ab);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a = tiles + s * STAGE_BYTES;
+      const uint32_t b = a + A_BYTES * (GATED ? 2 : 1);
+#pragma unroll
+      for (int k = 0; k < BK / 16; ++k) {
+        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+        const uint64_t bd = smem_desc(b + k * 32);
+        umma_bf16(tmem, smem_desc(a + k * 32), bd, idesc, acc);
+        if (GATED) umma_bf16(tmem + BN, smem_desc(a + A_BYTES + k * 32), bd, idesc, acc);
+      }
+      umma_commit(empty0 + 8 * s);   // frees the stage when these MMAs have read it
+    }
+    if (ok) umma_commit(accum_bar);
+  } else if (warp >= 2) {
+    // ---------------------------------------------------------------- epilogue
+    if (mbar_wait(accum_bar, 0, ab)) {
+      tc_fence_after();
+      const int q = warp & 3;                       // this warp's quarter of the 128 lanes
+      const int f = f0 + q * 32 + lane;             // output feature of this thread
+      const bool f_ok = f < p.N;
+      const float bias = (p.bias && f_ok && p.splits == 1) ? p.bias[f] : 0.f;
+      const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 8) {
+        if (row0 + c0 >= row_end) break;            // uniform in the warp
+        float v[8], u[8];
+        tmem_ld8(lane_addr + c0, v);
+        if (GATED) tmem_ld8(lane_addr + BN + c0, u);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int r = row0 + c0 + c;
+          if (r >= row_end || !f_ok) continue;
+          float y = v[c];
+          if (GATED) y = act_fn(y, p.act) * u[c];
+          if (p.splits > 1) {
+            p.partial[((size_t)blockIdx.z * p.rows + r) * p.N + f] = y;
+            continue;
+          }
+          y += bias;
+          const size_t o = (size_t)r * p.ldo + f;
+          if (p.out_dtype == FLINT_F32) {
+            float* out = (float*)p.out;
+            out[o] = p.accumulate ? out[o] + y : y;
+          } else {
+            __nv_bfloat16* out = (__nv_bfloat16*)p.out;
+            out[o] = __float2bfloat16_rn(p.accumulate ? __bfloat162float(out[o]) + y : y);
+          }
+        }
+      }
+    }
+  }
+  // ---- teardown: everyone meets, tensor memory is freed by the warp that took it
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    if (threadIdx.x == 0) {
+      atomicExch(p.error_flag, 1);
+      const long long t0 = clock64();     // let copies in flight land before the block ends
+      while (clock64() - t0 < 200000) {}
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// out[r, f] = sum_z partial[z, r, f] (+ bias[f]) (+ out[r, f])
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int rows, int N,
+                                     const float* __restrict__ bias, void* __restrict__ out, int out_dtype,
+                                     int ldo, int accumulate) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)rows * N) return;
+  const int r = (int)(i / N), f = (int)(i % N);
+  float y = 0.f;
+  for (int z = 0; z < splits; ++z) y += partial[(size_t)z * rows * N + i];
+  if (bias) y += bias[f];
+  const size_t o = (size_t)r * ldo + f;
+  if (out_dtype == FLINT_F32) {
+    float* po = (float*)out;
+    po[o] = accumulate ? po[o] + y : y;
+  } else {
+    __nv_bfloat16* po = (__nv_bfloat16*)out;
+    po[o] = __float2bfloat16_rn(accumulate ? __bfloat162float(po[o]) + y : y);
+  }
+}
+
+// ------------------------------------------------------------------ host: tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor [rows, K] with a row stride of ld elements; box = 64 x box_rows, 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* ptr, long long rows, int K, long long ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail("gemm_tc: cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return 0;
+}
+
+struct MapKey {
+  const void* ptr; long long rows; int K; int box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && box == o.box; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (std::hash<long long>()(k.rows) * 31) ^ (size_t)k.K * 131 ^ (size_t)k.box;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;   // weights never move: encode once
+
+int weight_map(CUtensorMap* m, const void* ptr, long long rows, int K) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapKey key{ptr, rows, K, BM};
+  auto it = g_weight_maps.find(key);
+  if (it == g_weight_maps.end()) {
+    CUtensorMap fresh;
+    if (int rc = make_map(&fresh, ptr, rows, K, K, BM)) return rc;
+    if (g_weight_maps.size() > 4096) g_weight_maps.clear();
+    it = g_weight_maps.emplace(key, fresh).first;
+  }
+  *m = it->second;
+  return 0;
+}
+
+template <int BN, bool GATED>
+int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, const Params& p, dim3 grid,
+           cudaStream_t stream) {
+  constexpr int stage_bytes = BM * BK * 2 * (GATED ? 2 : 1) + BN * BK * 2;
+  const size_t smem = (size_t)p.stages * stage_bytes + 1024;
+  static bool configured = false;   // per instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024);
+    if (e != cudaSuccess) return fail("gemm_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  gemm_tc_kernel<BN, GATED><<<grid, THREADS, smem, stream>>>(mw, mu, mx, p);
+  return check_launch("gemm_tc");
+}
+
+}  // namespace
+
+// Stages of the K ring for a token tile of bn rows: as many as fit about 100 KB (two blocks
+// per SM), at least 3, at most 8 (wide tiles take up to 192 KB and run one block per SM).
+extern "C" int flint_gemm_tc_stages(int bn, int gated) {
+  const int stage = BM * BK * 2 * (gated ? 2 : 1) + bn * BK * 2;
+  int s = (bn >= 128 ? 192 * 1024 : 100 * 1024) / stage;
+  if (s < 3) s = 3;
+  while (s * stage > 192 * 1024) --s;
+  return s > 8 ? 8 : s;
+}
+
+// Floats of scratch needed for a K split.
+extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
+  return splits > 1 ? (long long)splits * rows * N : 0;
+}
+
+// x [rows, K] bf16 with row stride ldx; w / w_up [E, N, K] bf16 (E = 1 when dense); out [rows, N].
+// bn: token rows per tile (16, 32, 64, 128 or 256); with a tile map it must equal the plan's tile size.
+// splits > 1 divides the K blocks over several CTAs and needs `partial` (not with a gated product).
+// error_flag: device int, set to 1 if a bounded wait ran out.
+extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* w_up, const float* bias, void* out,
+                             int out_dtype, int ldo, int accumulate, int act, const int* tile_expert,
+                             const int* tile_row0, const int* n_tiles, const int* offsets, int max_tiles,
+                             int n_experts, int rows, int N, int K, int bn, int splits, float* partial,
+                             int* error_flag, cudaStream_t stream) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
+  if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (w_up && ((uintptr_t)w_up & 15)))
+    return fail("gemm_tc: operands must be 16-byte aligned");
+  if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("gemm_tc: bad token tile %d", bn);
+  if (splits < 1) return fail("gemm_tc: bad split %d", splits);
+  if (splits > 1 && (w_up || !partial)) return fail("gemm_tc: a K split needs scratch and cannot be gated");
+  if (!error_flag) return fail("gemm_tc: needs an error flag");
+  const int total_kb = (K + BK - 1) / BK;
+  if (splits > total_kb) splits = total_kb;
+  const int kbps = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kbps - 1) / kbps;            // no empty split
+  const int tiles_n = tile_expert ? max_tiles : (rows + bn - 1) / bn;
+  if (tiles_n <= 0) return 0;
+  if (tiles_n > 65535) return fail("gemm_tc: %d row tiles exceed the grid limit", tiles_n);
+
+  CUtensorMap mw, mu, mx;
+  if (int rc = weight_map(&mw, w, (long long)n_experts * N, K)) return rc;
+  if (w_up) { if (int rc = weight_map(&mu, w_up, (long long)n_experts * N, K)) return rc; }
+  else mu = mw;
+  if (int rc = make_map(&mx, x, rows, K, ldx, bn)) return rc;
+
+  Params p;
+  p.out = out; p.bias = bias; p.partial = partial;
+  p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.n_tiles = n_tiles; p.offsets = offsets;
+  p.error_flag = error_flag;
+  p.out_dtype = out_dtype; p.ldo = ldo; p.accumulate = accumulate; p.act = act;
+  p.rows = rows; p.N = N; p.K = K;
+  p.kb_per_split = kbps; p.splits = splits;
+  p.stages = flint_gemm_tc_stages(bn, w_up != nullptr);
+  if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;
+  dim3 grid((N + BM - 1) / BM, tiles_n, splits);
+  int rc;
+#define CASE(B)                                                                             \
+  case B:                                                                                   \
+    rc = w_up ? launch<B, true>(mw, mu, mx, p, grid, stream) : launch<B, false>(mw, mu, mx, p, grid, stream); \
+    break;
+  switch (bn) {
+    CASE(16) CASE(32) CASE(64) CASE(128)
+    case 256:
+      if (w_up) return fail("gemm_tc: a gated product takes token tiles up to 128");
+      rc = launch<256, false>(mw, mu, mx, p, grid, stream);
+      break;
+    default: rc = fail("gemm_tc: bad token tile %d", bn);
+  }
+#undef CASE
+  if (rc || splits == 1) return rc;
+  const size_t n = (size_t)rows * N;
+  splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(partial, splits, rows, N, bias, out,
+                                                                        out_dtype, ldo, accumulate);
+  return check_launch("gemm_tc split reduce");
+}
+
+extern "C" const char* flint_gemm_tc_last_error() { return g_error; }

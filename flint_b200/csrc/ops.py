@@ -70,6 +70,8 @@ class CudaOps:
         self.device = torch.device(device)
         self._libs = {}
         self.launches = 0
+        self.tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a tensor-core
+        # kernel whose bounded wait ran out
 
     # ------------------------------------------------------------------ plumbing
     def _fn(self, module, name):
@@ -205,17 +207,61 @@ class CudaOps:
             if bias.numel() != N:
                 raise KernelError("gemm: bias length does not match")
         act_code = {"silu": 0, "gelu_pytorch_tanh": 1}[act]
-        self._gemm_simt(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+        if self.tensor_core_ok(x, w, plan):
+            self._gemm_tc(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+        else:
+            self._gemm_simt(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+
+    # bfloat16 x bfloat16 with 16-byte aligned rows goes to the tensor cores; everything else
+    # (float32 operands: the true 32-bit path; odd K) to the float32 pipes
+    def tensor_core_ok(self, x, w, plan=None):
+        return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+                and (plan is None or plan.tile_rows in (16, 32, 64, 128)))
+
+    @staticmethod
+    def token_tile(rows, gated=False):
+        for bn in (16, 32, 64, 128):
+            if rows <= bn:
+                return bn
+        return 128 if gated else 256
+
+    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype):
+        """Row-tile size the plan should use for grouped products over these weights."""
+        if weight_dtype != torch.bfloat16:
+            return 64
+        return self.token_tile(-(-2 * n_tokens // n_experts), gated=True)
+
+    def _gemm_tc(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
+        if plan is not None:
+            bn, splits, E = plan.tile_rows, 1, plan.n_experts
+        else:
+            E = 1
+            bn = self.token_tile(M, gated=w_up is not None)
+            tiles = -(-N // 128) * -(-M // bn)
+            kb = -(-K // 64)
+            splits = 1
+            if w_up is None and tiles < 148 and kb >= 8:
+                splits = max(1, min(-(-296 // tiles), kb // 4, 16))
+        partial = None
+        if splits > 1:
+            partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias),
+                  _ptr(out), c_int(_code(out.dtype)), c_int(out.stride(0)), c_int(1 if accumulate else 0),
+                  c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
+                  _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
+                  c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
+                  c_int(splits), _ptr(partial), _ptr(self.tc_error))
 
     def _gemm_simt(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
-        if plan is not None and plan.tile_rows != 64:
-            raise KernelError("gemm_simt: the plan must use 64-row tiles")
+        if plan is not None and plan.tile_rows > 64:
+            raise KernelError("gemm_simt: the plan's row tiles must not exceed 64 rows")
         self._run("gemm_simt", "flint_gemm_simt", _ptr(x), c_int(_code(x.dtype)), c_int(x.stride(0)), _ptr(w),
                   _ptr(w_up), c_int(_code(w.dtype)), _ptr(bias), _ptr(out), c_int(_code(out.dtype)),
                   c_int(out.stride(0)), c_int(1 if accumulate else 0), c_int(act_code),
                   _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
-                  c_int(plan.max_tiles if plan else 0), c_int(M), c_int(N), c_int(K))
+                  c_int(plan.max_tiles if plan else 0), c_int(plan.tile_rows if plan else 0), c_int(M), c_int(N), c_int(K))
 
     # ------------------------------------------------------------------ attention
     def attention_splits(self, T, nq, nkv, max_kv_len):

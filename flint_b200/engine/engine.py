@@ -85,7 +85,8 @@ class Engine:
         self.seed = int(seed)
         self.stop = tuple(stop)
         self.tokenizer = tokenizer
-        self.scheduler = Scheduler(model.cache, max_step_tokens=max_step_tokens or model.max_step_tokens,
+        self.scheduler = Scheduler(model.cache,
+                                   max_step_tokens=min(max_step_tokens or model.max_step_tokens, model.max_step_tokens),
                                    prefill_chunk=prefill_chunk)
         self.sampler = BatchSampler(model.ops, model.device, max_rows=model.cache.max_slots)
         self.sessions: dict[int, _Session] = {}

@@ -240,6 +240,10 @@ class Model:
         if int(self.staging.status.item()) != 0:
             self.staging.status.zero_()
             raise ModelError("a kernel met a position whose page was not allocated")
+        tc = getattr(self.ops, "tc_error", None)
+        if tc is not None and int(tc.item()) != 0:
+            tc.zero_()
+            raise ModelError("a tensor-core kernel gave up waiting for its operands")
 
 
 # ---------------------------------------------------------------------- loading by config.json

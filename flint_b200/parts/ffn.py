@@ -14,8 +14,6 @@ from ..errors import ConfigError
 from ..registry import FEED_FORWARDS
 from .base import FeedForward, mat, matmul_dtype
 
-TILE_ROWS = 64
-
 
 @FEED_FORWARDS.register("gated_mlp")
 class GatedMLP(FeedForward):
@@ -84,7 +82,7 @@ class SparseMixerMoE(FeedForward):
         ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
         gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
         ops.router_sparsemixer(x32, self.w_router, self.eps, ids, gates)
-        plan = ops.moe_plan(ids, self.E, TILE_ROWS)
+        plan = ops.moe_plan(ids, self.E, ops.moe_tile_rows(T, self.E, self.w1.dtype))
         xs = torch.empty((2 * T, self.hidden), dtype=xa.dtype, device=dev)
         ops.gather_rows(xa, plan.token_of, xs)
         a = torch.empty((2 * T, self.inter), dtype=self.w1.dtype, device=dev)

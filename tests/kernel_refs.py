@@ -134,6 +134,9 @@ class RefOps:
                 res[t, h] = torch.softmax(s, 0) @ v[:, h // G, :]
         out.copy_(res.reshape(T, nq * hd).to(out.dtype))
 
+    def moe_tile_rows(self, n_tokens, n_experts, weight_dtype):
+        return 64
+
     # ------------------------------------------------------------------ routing
     def router_sparsemixer(self, x, wr, eps, expert_ids, gates, logits_out=None):
         s_all = x.to(self.cd) @ wr.to(self.cd).T
