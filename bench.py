@@ -214,6 +214,35 @@ def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
     return {"tok_s": n_tok / dt, "h2d": h2d, "d2h": batch * 4, "ms": dt * 1000 / steps}
 
 
+def profile(model, cfg, args, rng):
+    """Per-kernel device time (CUDA events around every launch, graphs off): one prefill of 2,048
+    tokens and one decode step of the batch.  Launches are serialised by the events, so compare shares."""
+    import torch
+    from flint_b200.engine.step import StepEntry
+    V = cfg["vocab_size"]
+    model.use_graphs = False
+    slots = [model.cache.admit() for _ in range(args.batch)]
+    for i, s in enumerate(slots):
+        model.cache.ensure(s, 0, args.prompt_tokens + 2)
+        if i == len(slots) - 1:
+            model.ops.start_profile()
+        model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(args.prompt_tokens)], [args.prompt_tokens - 1])])
+    table = model.ops.stop_profile()
+
+    def show(title, table):
+        total = sum(ms for _, ms in table.values())
+        print(f"--- {title}: {total:.3f} ms in {sum(n for n, _ in table.values())} launches", file=sys.stderr)
+        for name, (n, ms) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+            print(f"{name:32s} {n:6d} launches {ms:10.3f} ms {100 * ms / total:6.1f} %", file=sys.stderr)
+    show(f"prefill of {args.prompt_tokens} tokens", table)
+    dec = lambda p: model.step([StepEntry(s, p, [rng.randrange(V)], [0]) for s in slots])
+    dec(args.prompt_tokens)
+    model.ops.start_profile()
+    dec(args.prompt_tokens + 1)
+    show(f"decode step, batch {args.batch}, context {args.prompt_tokens}", model.ops.stop_profile())
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -225,6 +254,8 @@ def main():
     ap.add_argument("--ctx-size", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are named)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--profile", action="store_true",
+                    help="print per-kernel device times of one prefill and one decode step to stderr and exit")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -243,6 +274,9 @@ def main():
     rng = random.Random(0)
     max_batch = max(args.batch, 1 if args.no_points else 64)
     model = build_model(cfg, max_batch, args.ctx_size)
+
+    if args.profile:
+        return profile(model, cfg, args, rng)
 
     clocks = ClockSampler()
     clocks.start()

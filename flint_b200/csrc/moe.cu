@@ -13,34 +13,53 @@ using namespace flint;
 namespace {
 constexpr int MAX_E = 256;
 
-// One warp per token.  logits s_e = <x, Wr[e]>, then (all lanes redundantly, on registers
-// read from shared memory):
+// One block per TT tokens.  The tokens' rows are staged in shared memory; each warp takes
+// experts warp, warp+8, ... and computes their logits for all TT tokens while reading the
+// router row once; then one thread per token does the selection:
 //   i1 = argmax s (lowest index on ties), m1 = s[i1]
 //   keep_j = !((m1 - s_j) / max(|s_j|, m1) > 2 eps);  g1 = e^{s_i1 - m1} / sum_{keep} e^{s_j - m1}
 //   the same again over s without i1 for (i2, g2); the gates are not renormalised.
+constexpr int TT = 4;
+constexpr int ROUTER_WARPS = 8;
+
 template <typename TW>
-__global__ void router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr,
-                                          float eps, int* __restrict__ expert_ids,
-                                          float* __restrict__ gates, float* __restrict__ logits_out,
-                                          int T, int H, int E) {
-  extern __shared__ float smem[];   // per warp: E logits
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr, float eps,
+                          int* __restrict__ expert_ids, float* __restrict__ gates,
+                          float* __restrict__ logits_out, int T, int H, int E) {
+  extern __shared__ float smem[];   // TT rows of x, then TT x E logits
+  float* xs = smem;
+  float* s_all = smem + (size_t)TT * H;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-  if (t >= T) return;
-  float* s = smem + warp * E;
-  const float* xr = x + (size_t)t * H;
-  for (int e = 0; e < E; ++e) {
+  const int t0 = blockIdx.x * TT;
+  const int nt = min(TT, T - t0);
+  for (int i = threadIdx.x; i < TT * H; i += blockDim.x) {
+    const int tt = i / H;
+    xs[i] = tt < nt ? x[(size_t)t0 * H + i] : 0.f;
+  }
+  __syncthreads();
+  for (int e = warp; e < E; e += ROUTER_WARPS) {
     const TW* w = wr + (size_t)e * H;
-    float a = 0.f;
-    for (int d = lane; d < H; d += 32) a = fmaf(xr[d], to_f32(w[d]), a);
-    a = warp_sum(a);
-    if (lane == 0) {
-      s[e] = a;
-      if (logits_out) logits_out[(size_t)t * E + e] = a;
+    float a[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) a[tt] = 0.f;
+    for (int d = lane; d < H; d += 32) {
+      const float wv = to_f32(w[d]);
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) a[tt] = fmaf(xs[tt * H + d], wv, a[tt]);
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      const float v = warp_sum(a[tt]);
+      if (lane == 0) s_all[tt * E + e] = v;
     }
   }
-  __syncwarp();
-  if (lane != 0) return;
+  __syncthreads();
+  if (threadIdx.x >= nt) return;
+  const int t = t0 + threadIdx.x;
+  const float* s = s_all + threadIdx.x * E;
+  if (logits_out)
+    for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = s[e];
   int sel[2];
   float gate[2];
   int excluded = -1;
@@ -114,11 +133,19 @@ extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dt
                                         int H, int E, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E < 2 || E > MAX_E) return fail("router: %d experts (supported: 2..%d)", E, MAX_E);
-  const int warps = 4;
-  const size_t smem = (size_t)warps * E * sizeof(float);
-  const int blocks = (T + warps - 1) / warps;
+  const size_t smem = ((size_t)TT * H + (size_t)TT * E) * sizeof(float);
+  if (smem > 200 * 1024) return fail("router: width %d is too large for the staging buffer", H);
+  const int blocks = (T + TT - 1) / TT;
+  static bool configured[2] = {false, false};
+  if (smem > 48 * 1024 && !configured[w_dtype ? 1 : 0]) {
+    cudaError_t e = w_dtype == FLINT_F32
+        ? cudaFuncSetAttribute(router_sparsemixer_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)
+        : cudaFuncSetAttribute(router_sparsemixer_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail("router: cannot raise shared memory: %s", cudaGetErrorString(e));
+    configured[w_dtype ? 1 : 0] = true;
+  }
   FLINT_DISPATCH_DTYPE(w_dtype, TW,
-      (router_sparsemixer_kernel<TW><<<blocks, warps * 32, smem, stream>>>(
+      (router_sparsemixer_kernel<TW><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(
           x, (const TW*)wr, eps, expert_ids, gates, logits_out, T, H, E)));
   return check_launch("router_sparsemixer");
 }

@@ -70,6 +70,7 @@ class CudaOps:
         self.device = torch.device(device)
         self._libs = {}
         self.launches = 0
+        self._profile = None
         self.tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a tensor-core
         # kernel whose bounded wait ran out
 
@@ -84,11 +85,33 @@ class CudaOps:
 
     def _run(self, module, name, *args):
         fn = self._fn(module, name)
-        rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        if self._profile is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+            e1.record()
+            self._profile.append((name, e0, e1))
+        else:
+            rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
         self.launches += 1
         if rc != 0:
             msg = getattr(self._libs[module], f"flint_{module}_last_error")()
             raise KernelError((msg or b"unknown kernel error").decode())
+
+    # Per-kernel device times, like the reference's timestamp profiler
+    # (crates/thuban_profiler/src/lib.rs:173-248): events around every launch, summed by name.
+    def start_profile(self):
+        self._profile = []
+
+    def stop_profile(self):
+        """Returns {kernel name: (launches, total ms)} and stops profiling."""
+        torch.cuda.synchronize(self.device)
+        out = {}
+        for name, e0, e1 in self._profile or []:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + e0.elapsed_time(e1))
+        self._profile = None
+        return out
 
     def preload(self, modules=None):
         """Compile and load modules ahead of their first use."""

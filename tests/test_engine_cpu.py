@@ -1,0 +1,125 @@
+"""The engine's plumbing (batching, block tables, pages used again, scheduler, entry point) on the
+CPU: the kernels are replaced by their plain references, everything else is the product's code."""
+import pytest
+import torch
+
+import plain_phimoe
+import tiny
+import traces
+from flint_b200.engine.engine import Engine
+from flint_b200.engine.model import load_model
+from flint_b200.engine.replay import Replayer
+from flint_b200.errors import ModelError
+from flint_b200.sampling.params import SamplingParams
+from kernel_refs import RefOps
+
+LENGTHS = {"A": (7, 13, 32, 100, 65), "B": (5, 40, 70, 100, 64)}
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def setup(request, tmp_path_factory):
+    which = request.param
+    folder = tiny.write_tiny(tmp_path_factory.mktemp("tiny") / which, which, seed=11, dtype=torch.float32)
+    reqs = traces.make_requests(tiny.CONFIGS[which]["vocab_size"], LENGTHS[which], seed=5)
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    plain = {rid: plain_phimoe.forward(cfg, w, t) for rid, t in reqs.items()}
+    return which, folder, reqs, plain
+
+
+def replay(folder, steps, page_size=16):
+    n = traces.max_tokens_needed(steps)
+    rp = Replayer(folder, dtype="float32", max_tokens=n, page_size=page_size, device="cpu", ops=RefOps())
+    out = {}
+    for s in steps:
+        lg = rp.run_step(s["entries"], s["end"])
+        if lg is not None:
+            out[s["step"]] = lg
+        rp.model.cache.check()
+    assert all(g.pages.pool.used_pages == 0 for g in rp.model.cache.groups)
+    return out, rp
+
+
+def compare(out, steps, plain, tol=2e-5):
+    exp = traces.expected_rows(steps, plain)
+    assert set(out) == set(exp)
+    for k, rows in exp.items():
+        want = torch.stack(rows)
+        assert out[k].shape == want.shape
+        err = (out[k].double() - want).abs().max().item()
+        assert err < tol, f"step {k}: max error {err:.2e}"
+
+
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_replay_matches_plain_under_every_cut(setup, cut, page_size):
+    which, folder, reqs, plain = setup
+    steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[cut](reqs)
+    out, rp = replay(folder, steps, page_size)
+    compare(out, steps, plain)
+    if cut == "mixed" and page_size == 16:
+        assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2, "no page was used again"
+
+
+def test_step_refuses_bad_batches(setup):
+    which, folder, reqs, plain = setup
+    from flint_b200.engine.step import StepEntry
+    m = load_model(folder, dtype="float32", device="cpu", ops=RefOps(), page_size=16, n_pages=8, max_slots=2)
+    s = m.cache.admit()
+    with pytest.raises(ModelError, match="pages do not cover"):
+        m.step([StepEntry(s, 0, [1, 2, 3], [0])])
+    m.cache.ensure(s, 0, 3)
+    with pytest.raises(ModelError, match="outside the vocabulary"):
+        m.step([StepEntry(s, 0, [1, 10 ** 6, 3], [0])])
+    with pytest.raises(ModelError, match="twice"):
+        m.step([StepEntry(s, 0, [1], [0]), StepEntry(s, 1, [2], [0])])
+    with pytest.raises(ModelError, match="wanted place"):
+        m.step([StepEntry(s, 0, [1, 2], [2])])
+    with pytest.raises(ModelError, match="at least one token"):
+        m.step([])
+
+
+def test_greedy_generation_through_the_entry_point(setup):
+    which, folder, reqs, plain = setup
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    prompts = [t[:n] for t, n in zip(reqs.values(), (7, 13, 32))]
+    eos = set(cfg["eos_token_id"] if isinstance(cfg["eos_token_id"], list) else [cfg["eos_token_id"]])
+    expected = []
+    for p in prompts:
+        toks, out = list(p), []
+        for _ in range(10):
+            t = int(torch.argmax(plain_phimoe.forward(cfg, w, toks)[-1]))
+            if t in eos:
+                break
+            out.append(t)
+            toks.append(t)
+        expected.append(out)
+    for n_pages in (16, 4):       # plenty of pages; so few that requests are preempted and recomputed
+        m = load_model(folder, dtype="float32", device="cpu", ops=RefOps(), page_size=16, n_pages=n_pages, max_slots=4,
+                       max_step_tokens=24)
+        eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16)
+        assert eng.generate(prompts, 10) == expected
+        assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
+    assert eng.scheduler.preemptions > 0
+
+
+def test_session_interface(setup):
+    which, folder, reqs, plain = setup
+    m = load_model(folder, dtype="float32", device="cpu", ops=RefOps(), page_size=16, n_pages=16, max_slots=2)
+    eng = Engine(m, SamplingParams.greedy(), seed=42)
+    a = eng.create(list(reqs["r1"]), max_tokens=5)
+    b = eng.create(list(reqs["r0"]), max_tokens=3)
+    got = {a: [], b: []}
+    while not (eng.finished(a) and eng.finished(b)):
+        eng.step()
+        for sid in (a, b):
+            got[sid] += [p.token for p in eng.poll(sid)]
+    assert len(got[a]) <= 5 and len(got[b]) <= 3
+    st = eng.stats(a)
+    assert st.prefill_tokens == len(reqs["r1"]) and st.decode_tokens == max(len(got[a]) - 1, 0)
+    eng.close(a)
+    eng.close(b)
+    with pytest.raises(ModelError, match="empty prompt"):
+        eng.create([], 4)
+    with pytest.raises(ModelError, match="tokenizer"):
+        eng.create("hello", 4)

@@ -1,0 +1,196 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16: each request
+alone and whole; most of it in one step and the last 32 tokens one by one; portions of changing
+size; mixed batches with pages used again; long decoding; the first tokens; generation through the
+entry point; and the replay tool as a program."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_phimoe
+import tiny
+import traces
+from flint_b200.engine.engine import Engine
+from flint_b200.engine.model import load_model
+from flint_b200.engine.replay import Replayer
+from flint_b200.engine.step import StepEntry
+from flint_b200.sampling.params import SamplingParams
+
+pytestmark = pytest.mark.gpu
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LENGTHS = {"A": (7, 13, 32, 100, 65, 200), "B": (5, 40, 70, 100, 64, 300)}
+# float32: the engine's float32 kernels against float64 arithmetic.  bfloat16: activations are rounded
+# to 8 bits of mantissa between kernels (2^-9 relative each), which grows to a few percent of the
+# largest logit over the layers of these tiny models; weights are the same bfloat16 values on both sides.
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+@pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def setup(request, tmp_path_factory):
+    which, dtype = request.param
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = tiny.write_tiny(tmp_path_factory.mktemp("tiny") / f"{which}_{dtype}", which, seed=11, dtype=store)
+    reqs = traces.make_requests(tiny.CONFIGS[which]["vocab_size"], LENGTHS[which], seed=5)
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    plain = {rid: plain_phimoe.forward(cfg, w, t) for rid, t in reqs.items()}
+    return which, dtype, folder, reqs, plain
+
+
+def replay(folder, dtype, steps, page_size):
+    rp = Replayer(folder, dtype=dtype, max_tokens=traces.max_tokens_needed(steps), page_size=page_size)
+    out = {}
+    for s in steps:
+        lg = rp.run_step(s["entries"], s["end"])
+        if lg is not None:
+            out[s["step"]] = lg
+    rp.model.cache.check()
+    assert all(g.pages.pool.used_pages == 0 for g in rp.model.cache.groups)
+    return out, rp
+
+
+def compare(out, steps, plain, dtype):
+    exp = traces.expected_rows(steps, plain)
+    assert set(out) == set(exp)
+    scale = max(float(v.abs().max()) for v in plain.values())
+    worst = 0.0
+    for k, rows in exp.items():
+        want = torch.stack(rows)
+        assert out[k].shape == want.shape
+        assert torch.isfinite(out[k]).all()
+        worst = max(worst, (out[k].double() - want).abs().max().item())
+    assert worst <= TOL[dtype] * scale, f"max error {worst:.3e} against a largest logit of {scale:.3f}"
+    return worst
+
+
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_replay_matches_plain_under_every_cut(setup, cut, page_size):
+    which, dtype, folder, reqs, plain = setup
+    steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
+             "mixed": lambda r: traces.mixed(r, seed=3)}[cut](reqs)
+    out, rp = replay(folder, dtype, steps, page_size)
+    compare(out, steps, plain, dtype)
+    if cut == "mixed":
+        assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2, "no page was used again"
+
+
+def test_cuts_agree_with_each_other(setup):
+    """The logits at a position do not depend on how the tokens were cut into steps or on what else
+    was in the batch, beyond rounding: far tighter than the distance to the plain implementation."""
+    which, dtype, folder, reqs, plain = setup
+    per_cut = {}
+    for name, fn in (("whole", traces.whole), ("tail", traces.tail_decoded), ("mixed", lambda r: traces.mixed(r, seed=9))):
+        steps = fn(reqs)
+        out, _ = replay(folder, dtype, steps, 16)
+        done, got = {}, {}
+        for s in steps:
+            i = 0
+            for e in s["entries"]:
+                base = done.get(e["id"], 0)
+                for w in e["want"]:
+                    got[(e["id"], base + w)] = out[s["step"]][i]
+                    i += 1
+                done[e["id"]] = base + len(e["tokens"])
+        per_cut[name] = got
+    scale = max(float(v.abs().max()) for v in plain.values())
+    tol = (2e-5 if dtype == "float32" else 2e-2) * scale
+    for name in ("tail", "mixed"):
+        common = set(per_cut["whole"]) & set(per_cut[name])
+        assert len(common) > 30
+        worst = max((per_cut["whole"][k] - per_cut[name][k]).abs().max().item() for k in common)
+        assert worst <= tol, f"{name} differs from whole by {worst:.3e}"
+
+
+def test_long_decoding_and_first_tokens(setup):
+    which, dtype, folder, reqs, plain = setup
+    rid = "r5"
+    t = reqs[rid]
+    m = load_model(folder, dtype=dtype, page_size=16, n_pages=32, max_slots=2)
+    s = m.cache.admit()
+    rows = []
+    for i, tok in enumerate(t):                    # the whole sequence one token at a time: the first tokens
+        m.cache.ensure(s, i, i + 1)                # of a sequence and a long run of decoding through the graph path
+        rows.append(m.step([StepEntry(s, i, [tok], [0])]).clone())
+        m.cache.advance(s, i + 1)
+    m.check_status()
+    got = torch.cat(rows).cpu()
+    scale = float(plain[rid].abs().max())
+    err = (got.double() - plain[rid]).abs()
+    assert err[:4].max().item() <= TOL[dtype] * scale        # positions 0..3
+    assert err.max().item() <= TOL[dtype] * scale
+    assert len(m._graphs) >= 1, "decode steps did not go through the captured graph"
+
+
+def test_greedy_generation_through_the_entry_point(setup):
+    which, dtype, folder, reqs, plain = setup
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    eos = cfg["eos_token_id"] if isinstance(cfg["eos_token_id"], list) else [cfg["eos_token_id"]]
+    prompts = [reqs["r0"], reqs["r1"], reqs["r2"]]
+    for n_pages in (16, 4):
+        m = load_model(folder, dtype=dtype, page_size=16, n_pages=n_pages, max_slots=4, max_step_tokens=24)
+        eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16)
+        got = eng.generate(prompts, 16)
+        assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups)
+        for p, g in zip(prompts, got):
+            # teacher-forced check: each generated token is the plain implementation's arg-max given the
+            # engine's own prefix, or (bfloat16) within rounding of it
+            lg = plain_phimoe.forward(cfg, w, list(p) + g)
+            for j, tok in enumerate(g):
+                row = lg[len(p) - 1 + j]
+                best = int(torch.argmax(row))
+                if dtype == "float32":
+                    assert tok == best
+                else:
+                    assert float(row[best] - row[tok]) <= 2 * TOL[dtype] * float(lg.abs().max())
+            assert len(g) == 16 or int(torch.argmax(lg[-1])) in eos or dtype == "bfloat16"
+    assert eng.scheduler.preemptions > 0
+
+
+def test_temperature_sampling_is_reproducible_and_follows_the_host_sampler(setup):
+    which, dtype, folder, reqs, plain = setup
+    m = load_model(folder, dtype=dtype, page_size=16, n_pages=32, max_slots=4)
+    params = SamplingParams(temperature=0.8, top_k=20, top_p=0.8)
+    a = Engine(m, params, seed=5, prefill_chunk=16).generate([reqs["r1"], reqs["r3"]], 24)
+    b = Engine(m, params, seed=5, prefill_chunk=16).generate([reqs["r1"], reqs["r3"]], 24)
+    c = Engine(m, params, seed=6, prefill_chunk=16).generate([reqs["r1"], reqs["r3"]], 24)
+    assert a == b and a != c
+    if dtype == "float32":
+        # replay the first request on the host: same generator, same filters, the plain model's logits
+        cfg, w = plain_phimoe.load_model_dir(folder)
+        hs = plain_phimoe.PlainSampler(0.8, 20, 0.8, seed=6)        # the engine's seed 5 is incremented per request
+        toks = list(reqs["r1"])
+        eos = cfg["eos_token_id"] if isinstance(cfg["eos_token_id"], list) else [cfg["eos_token_id"]]
+        for tok in a[0]:
+            want = hs.sample(plain_phimoe.forward(cfg, w, toks)[-1].float().numpy())
+            assert want == tok
+            toks.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_as_a_program(tmp_path, dtype):
+    """bin/trace_run in a process of its own, fed a mixed trace over standard input."""
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    folder = tiny.write_tiny(tmp_path / "model", "B", seed=4, dtype=store)
+    reqs = traces.make_requests(384, (5, 40, 70, 100, 90), seed=8)
+    steps = traces.mixed(reqs, seed=2)
+    out_dir = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(REPO, "bin", "trace_run"), "--model", str(folder), "--dtype", dtype,
+                           "--out", str(out_dir), "--max-tokens", str(traces.max_tokens_needed(steps))],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l] == [f"done {s['step']}" for s in steps]
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    plain = {rid: plain_phimoe.forward(cfg, w, t) for rid, t in reqs.items()}
+    out = {}
+    for s in steps:
+        f = out_dir / f"{s['step']}.f32"
+        n = sum(len(e["want"]) for e in s["entries"])
+        assert f.exists() == (n > 0)
+        if n:
+            out[s["step"]] = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(n, 384))
+    compare(out, steps, plain, dtype)

@@ -1,0 +1,271 @@
+"""Each part alone on the GPU beside its plain function, and the generality of the composition:
+a toy mixer with state of its own, a dense feed-forward, an RMS norm, a parallel block, a layer
+that runs twice and a layer that reads another layer's cache -- all registered and built from the
+test, without a change to the package."""
+import math
+
+import pytest
+import torch
+
+import plain_phimoe as P
+from flint_b200.cache.manager import CacheManager, KVSpec, StateSpec
+from flint_b200.config.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
+from flint_b200.engine.model import Model
+from flint_b200.engine.step import StepEntry, StepStaging
+from flint_b200.parts.base import BuildContext, Mixer, mat
+from flint_b200.registry import ARCHITECTURES, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
+from flint_b200.weights.sources import RandomSource
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def ctx_for(dtype):
+    from flint_b200.csrc.ops import get_ops
+    return BuildContext(ops=get_ops(DEV), device=torch.device(DEV), compute=dtype)
+
+
+def load_random(part, seed=0, dtype=torch.float32):
+    src = RandomSource(part.weights(), seed, dtype=dtype)
+    from flint_b200.weights.loader import place
+    t = {n: place(src.read(n), ws, part.ctx.compute, DEV) for n, ws in part.weights().items()}
+    part.load(t)
+    return {n: v.double().cpu() for n, v in t.items()}
+
+
+@pytest.mark.parametrize("kind,params", [("layernorm", {"width": 72, "eps": 1e-6, "bias": True}),
+                                         ("layernorm", {"width": 100, "eps": 1e-5, "bias": False}),
+                                         ("rmsnorm", {"width": 72, "eps": 1e-6})])
+def test_norm_part(kind, params):
+    part = NORMS.get(kind)(params, ctx_for("bfloat16"))
+    w = load_random(part)
+    x = torch.randn(9, params["width"]) * 2 + 0.5
+    out = part.forward(x.to(DEV), (torch.float32, torch.bfloat16))
+    if kind == "layernorm":
+        exp = P.layer_norm(x.double(), w["weight"], w.get("bias"), params["eps"])
+    else:
+        exp = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + params["eps"]) * w["weight"]
+    assert (out[torch.float32].double().cpu() - exp).abs().max() < 1e-5
+    assert (out[torch.bfloat16].double().cpu() - exp).abs().max() < 3e-2
+
+
+def test_rope_part_tables():
+    cfg = {"rope_theta": 500000.0, "max_position_embeddings": 512, "original_max_position_embeddings": 64,
+           "rope_scaling": {"type": "longrope", "short_factor": [1.0 + 0.1 * i for i in range(16)],
+                            "long_factor": [2.0 + 0.1 * i for i in range(16)], "short_mscale": 1.1, "long_mscale": 1.3}}
+    part = POSITION_ENCODINGS.get("rope")({"rotary_dim": 32, "theta": 500000.0, "max_positions": 512,
+                                           "short_factor": cfg["rope_scaling"]["short_factor"],
+                                           "long_factor": cfg["rope_scaling"]["long_factor"],
+                                           "original_max_positions": 64, "short_mscale": 1.1, "long_mscale": 1.3},
+                                          ctx_for("float32"))
+    cos, sin = part.tables()
+    ec, es = P.rope_tables(cfg, 32, 512)
+    assert (cos.double().cpu() - ec).abs().max() < 1e-6 and (sin.double().cpu() - es).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_part_alone(dtype):
+    """The attention mixer with a cache of its own, in two portions, beside the plain functions."""
+    H, nq, nkv, hd, T = 80, 5, 5, 16, 50
+    rope = PartSpec("rope", {"rotary_dim": 8, "theta": 10000.0, "max_positions": 128})
+    ctx = ctx_for(dtype)
+    part = MIXERS.get("attention")({"hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": hd, "window": 20,
+                                    "qkv_bias": True, "out_bias": True, "position": rope}, ctx)
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = load_random(part, dtype=store)
+    cm = CacheManager({0: part.cache_spec()}, {}, page_size=16, n_pages=8, max_slots=2, max_context=128,
+                      dtype=store, device=DEV)
+    slot = cm.admit()
+    x = torch.randn(T, H)
+    staging = StepStaging(64, DEV)
+    res = torch.zeros(T, H, device=DEV)
+    for a, b in ((0, 33), (33, 50)):
+        cm.ensure(slot, a, b)
+        cm.sync()
+        step = staging.pack([StepEntry(slot, a, [0] * (b - a), [])], 10, 128)
+        xin = {dt: x[a:b].to(DEV).to(dt) for dt in part.input_dtypes()}
+        part.forward(xin, res[a:b], step, cm.view(0), None)
+        cm.advance(slot, b)
+    xd = x.double() if dtype == "float32" else x.to(torch.bfloat16).double()
+    cos, sin = P.rope_tables({"rope_theta": 10000.0, "partial_rotary_factor": 0.5}, hd, T)
+    q = P.rope_rotate(P.linear(xd, w["q_proj.weight"], w["q_proj.bias"]).view(T, nq, hd), cos, sin)
+    k = P.rope_rotate(P.linear(xd, w["k_proj.weight"], w["k_proj.bias"]).view(T, nkv, hd), cos, sin)
+    v = P.linear(xd, w["v_proj.weight"], w["v_proj.bias"]).view(T, nkv, hd)
+    exp = P.linear(P.attention(q, k, v, 20).reshape(T, nq * hd), w["o_proj.weight"], w["o_proj.bias"])
+    tol = 1e-5 if dtype == "float32" else 2e-2 * float(exp.abs().max())
+    assert (res.double().cpu() - exp).abs().max() < tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("kind", ["sparsemixer_moe", "gated_mlp"])
+def test_feed_forward_parts_alone(kind, dtype):
+    H, I, E, T = 72, 40, 5, 37
+    ctx = ctx_for(dtype)
+    params = {"hidden_size": H, "intermediate_size": I, "act": "silu"}
+    if kind == "sparsemixer_moe":
+        params.update(num_experts=E, jitter_eps=0.05)
+    part = FEED_FORWARDS.get(kind)(params, ctx)
+    store = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = load_random(part, dtype=store)
+    x = torch.randn(T, H)
+    xin = {dt: x.to(DEV).to(dt) for dt in part.input_dtypes()}
+    res = torch.zeros(T, H, device=DEV)
+    step = type("S", (), {"record": {}})()
+    part.forward(xin, res, step)
+    x64 = x.double()
+    xa = x64 if dtype == "float32" else x.to(torch.bfloat16).double()
+    if kind == "gated_mlp":
+        exp = P.expert_mlp(xa, w["gate_proj.weight"], w["up_proj.weight"], w["down_proj.weight"])
+    else:
+        exp = torch.zeros(T, H, dtype=torch.float64)
+        logits = x64 @ w["gate.weight"].T
+        chosen = []
+        for t in range(T):
+            i1, g1, i2, g2 = P.sparsemixer_top2(logits[t], 0.05)
+            chosen.append([i1, i2])
+            ex = lambda e: P.expert_mlp(xa[t:t + 1], w[f"experts.{e}.w1.weight"], w[f"experts.{e}.w3.weight"], w[f"experts.{e}.w2.weight"])[0]
+            exp[t] = g1 * ex(i1) + g2 * ex(i2)
+        assert step.record["experts"][0].cpu().tolist() == chosen       # the same experts, first
+    tol = 1e-5 if dtype == "float32" else 3e-2 * float(exp.abs().max())
+    assert (res.double().cpu() - exp).abs().max() < tol
+
+
+# ------------------------------------------------------------------------------------------------
+# a toy architecture defined here: a mixer with state of its own, parts the engine's model does not use
+
+class RunningSumMixer(Mixer):
+    """out[t] = W (state + x[first..t] summed) * 0.1; the state is the running sum of the request."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width = params["width"]
+
+    def weights(self):
+        return {"mix.weight": mat(self.width, self.width)}
+
+    def load(self, t):
+        self.w = t["mix.weight"].float()
+
+    def input_dtypes(self):
+        return (torch.float32,)
+
+    def state_spec(self):
+        return StateSpec((self.width,), torch.float32)
+
+    def forward(self, x, residual, step, cache, state, writes_cache=True):
+        x32 = x[torch.float32]
+        for e, row0 in zip(step.entries, step.entry_start):
+            n = len(e.tokens)
+            run = state[e.slot] + torch.cumsum(x32[row0:row0 + n], 0)
+            residual[row0:row0 + n] += (run @ self.w.T) * 0.1
+            state[e.slot] = run[-1]
+
+
+def toy_spec(H=48, V=97):
+    rope = PartSpec("rope", {"rotary_dim": 16, "theta": 10000.0, "max_positions": 256})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16, "window": 0,
+                                  "qkv_bias": False, "out_bias": False, "position": rope})
+    rms = PartSpec("rmsnorm", {"width": H, "eps": 1e-6})
+    ln = PartSpec("layernorm", {"width": H, "eps": 1e-5, "bias": True})
+    mlp = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 64, "act": "gelu_pytorch_tanh"})
+    toy = PartSpec("test_running_sum", {"width": H})
+    names = {"norm1": "n1.", "mixer": "mix.", "norm2": "n2.", "ffn": "ff."}
+    layers = (LayerSpec("prenorm", {"norm1": rms, "mixer": toy, "norm2": rms, "ffn": mlp}, "layers.0.", names),
+              LayerSpec("parallel", {"norm1": ln, "mixer": attn, "ffn": mlp}, "layers.1.", names),
+              LayerSpec("prenorm", {"norm1": ln, "mixer": attn, "norm2": rms, "ffn": mlp}, "layers.2.", names))
+    # layer 0 runs twice (shared weights, separate state); the last call reads the cache of call 1
+    order = (LayerCall(0), LayerCall(1), LayerCall(0), LayerCall(2, cache_of=1))
+    return ModelSpec(architecture="ToyStateLM", vocab_size=V, hidden_size=H, max_positions=256, layers=layers,
+                     order=order, final_norm=rms, head_bias=False, tie_word_embeddings=True)
+
+
+def toy_plain(spec, w, tokens):
+    """Whole-sequence computation of the toy model with the plain functions."""
+    T = len(tokens)
+    h = P.embed(tokens, w["embed_tokens.weight"])
+    rms = lambda x, g: x / torch.sqrt((x ** 2).mean(-1, keepdim=True) + 1e-6) * g
+    mlp = lambda x, p: (P.activation(x @ w[p + "gate_proj.weight"].T, "gelu_pytorch_tanh") * (x @ w[p + "up_proj.weight"].T)) @ w[p + "down_proj.weight"].T
+    cos, sin = P.rope_tables({"rope_theta": 10000.0}, 16, T)
+    kv1 = None
+    for call in spec.order:
+        p = f"layers.{call.layer}."
+        if call.layer == 0:
+            x = rms(h, w[p + "n1.weight"])
+            h = h + (torch.cumsum(x, 0) @ w[p + "mix.mix.weight"].T) * 0.1
+            h = h + mlp(rms(h, w[p + "n2.weight"]), p + "ff.")
+            continue
+        x = P.layer_norm(h, w[p + "n1.weight"], w[p + "n1.bias"], 1e-5)
+        q = P.rope_rotate((x @ w[p + "mix.q_proj.weight"].T).view(T, 3, 16), cos, sin)
+        if call.cache_of is None:
+            k = P.rope_rotate((x @ w[p + "mix.k_proj.weight"].T).view(T, 3, 16), cos, sin)
+            v = (x @ w[p + "mix.v_proj.weight"].T).view(T, 3, 16)
+            kv1 = (k, v)
+        a = P.attention(q, kv1[0], kv1[1], 0).reshape(T, 48) @ w[p + "mix.o_proj.weight"].T
+        if call.layer == 1:               # parallel block: both read the same normed input
+            h = h + a + mlp(x, p + "ff.")
+        else:
+            h = h + a
+            h = h + mlp(rms(h, w[p + "n2.weight"]), p + "ff.")
+    return rms(h, w["norm.weight"]) @ w["embed_tokens.weight"].T
+
+
+def test_toy_architecture_with_a_stateful_mixer_is_built_and_stepped():
+    MIXERS.register("test_running_sum", RunningSumMixer, replace=True)
+
+    class ToyArch:
+        @staticmethod
+        def parse_config(d):
+            return d
+
+        @staticmethod
+        def model_spec(cfg):
+            return toy_spec()
+    ARCHITECTURES.register("ToyStateLM", ToyArch, replace=True)
+    try:
+        from flint_b200.engine.model import architecture_of
+        spec = architecture_of({"architectures": ["ToyStateLM"]}).model_spec({})
+        from flint_b200.engine.model import Layer, expected_tensors
+        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers])
+        for n, ws in NORMS.get("rmsnorm")(spec.final_norm.params, ctx_for("float32")).weights().items():
+            expected["norm." + n] = ws
+        src = RandomSource(expected, 3, dtype=torch.float32)
+        model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=12, max_slots=3)
+        assert sorted(model.cache.state) == [0, 2] and len(model.cache.groups) == 1
+        assert model.cache.groups[0].calls == [1]          # call 3 reads call 1's cache and owns none
+        w = {n: src.read(n).double() for n in expected}
+        seqs = {0: [i * 7 % 97 for i in range(60)], 1: [i * 11 % 97 for i in range(41)]}
+        want = {k: toy_plain(spec, w, t) for k, t in seqs.items()}
+        # two requests side by side, in portions of changing size, one decoded token by token at the end
+        slots = {k: model.cache.admit() for k in seqs}
+        done = {k: 0 for k in seqs}
+        got = {k: [] for k in seqs}
+        sizes = [5, 2, 9, 1, 1, 17, 3, 1, 30, 64]
+        i = 0
+        while any(done[k] < len(seqs[k]) for k in seqs):
+            entries, ks = [], []
+            for k in seqs:
+                n = min(sizes[(i + k) % len(sizes)], len(seqs[k]) - done[k])
+                if n <= 0:
+                    continue
+                model.cache.ensure(slots[k], done[k], done[k] + n)
+                entries.append(StepEntry(slots[k], done[k], seqs[k][done[k]:done[k] + n], list(range(n))))
+                ks.append((k, n))
+            out = model.step(entries).cpu()
+            r = 0
+            for k, n in ks:
+                got[k].append(out[r:r + n])
+                r += n
+                done[k] += n
+            i += 1
+        for k in seqs:
+            err = (torch.cat(got[k]).double() - want[k]).abs().max().item()
+            assert err < 1e-4, f"request {k}: {err:.2e}"
+        # a slot that is used again starts from zero state
+        model.cache.release(slots[0])
+        s = model.cache.admit()
+        model.cache.ensure(s, 0, 10)
+        again = model.step([StepEntry(s, 0, seqs[0][:10], list(range(10)))]).cpu()
+        assert (again.double() - want[0][:10]).abs().max().item() < 1e-4
+    finally:
+        MIXERS.unregister("test_running_sum")
+        ARCHITECTURES.unregister("ToyStateLM")

@@ -1,0 +1,145 @@
+"""The scheduler's decisions with a scripted model (no GPU): admission, portions under a token
+budget, decode first, finishing and freeing, and what happens when pages run out."""
+import torch
+
+from flint_b200.cache.manager import CacheManager, KVSpec
+from flint_b200.engine.scheduler import FAILED, FINISHED, RUNNING, WAITING, Request, Scheduler
+from flint_b200.sampling.params import SamplingParams, SplitMix64
+
+
+def setup(n_pages=16, page=16, slots=4, ctx=256, budget=32, chunk=16, window=0):
+    cache = CacheManager({0: KVSpec(1, 16, window)}, {}, page_size=page, n_pages=n_pages, max_slots=slots,
+                         max_context=ctx, dtype=torch.float32, device="cpu")
+    return cache, Scheduler(cache, max_step_tokens=budget, prefill_chunk=chunk)
+
+
+def req(i, n_prompt, max_tokens=4, stop=()):
+    return Request(id=i, prompt=list(range(1, n_prompt + 1)), max_tokens=max_tokens, sampling=SamplingParams.greedy(),
+                   stop=tuple(stop), rng=SplitMix64(i), arrival=i)
+
+
+def next_token(r):
+    """Scripted model: depends only on what the request has run so far."""
+    return (len(r.tokens) * 7 + 3) % 97 + 100
+
+
+def run(sched, reqs, max_steps=500, log=None):
+    for r in reqs:
+        sched.add(r)
+    steps = 0
+    while sched.has_work() and steps < max_steps:
+        portions = sched.plan()
+        if not portions:
+            assert not sched.has_work(), "no progress"
+            break
+        assert sum(p.n_tokens for p in portions) <= sched.max_step_tokens
+        assert len({p.request.id for p in portions}) == len(portions)
+        if log is not None:
+            log.append([(p.request.id, p.start, p.n_tokens, p.wants_logits) for p in portions])
+        sched.commit(portions, [next_token(p.request) for p in portions if p.wants_logits])
+        sched.cache.check()
+        steps += 1
+    return steps
+
+
+def test_prompt_is_cut_into_portions_and_then_decoded():
+    cache, s = setup(budget=32, chunk=16)
+    r = req(0, 40, max_tokens=3)
+    log = []
+    run(s, [r], log=log)
+    assert [e[0][1:3] for e in log[:3]] == [(0, 16), (16, 16), (32, 8)]
+    assert [e[0][3] for e in log[:3]] == [False, False, True]      # logits only where the prompt ends
+    assert all(e[0][2] == 1 and e[0][3] for e in log[3:])
+    assert r.state == FINISHED and r.finish_reason == "length" and len(r.generated) == 3
+    assert (r.prefill_tokens, r.decode_tokens) == (40, 2)
+    assert cache.free_slots == 4 and cache.free_pages() == 16     # freed at finish
+
+
+def test_decodes_go_first_and_the_budget_is_kept():
+    cache, s = setup(budget=20, chunk=16)
+    a, b = req(0, 5, max_tokens=50), req(1, 60, max_tokens=2)
+    log = []
+    s.add(a)
+    for _ in range(2):
+        p = s.plan(); s.commit(p, [next_token(x.request) for x in p if x.wants_logits])
+    s.add(b)
+    p = s.plan()
+    assert [(x.request.id, x.n_tokens) for x in p] == [(0, 1), (1, 16)]   # decode token beside a portion
+    s.commit(p, [next_token(x.request) for x in p if x.wants_logits])
+    p = s.plan()
+    assert [(x.request.id, x.start, x.n_tokens) for x in p] == [(0, 7, 1), (1, 16, 16)]
+
+
+def test_stop_token_is_not_emitted_and_frees_at_once():
+    cache, s = setup()
+    r = req(0, 6, max_tokens=10)
+    r.stop = (next_token(r),)
+    run(s, [r])
+    assert r.generated == [] and r.finish_reason == "stop" and cache.free_pages() == 16
+
+
+def test_waiting_queue_is_first_come_first_served_over_slots():
+    cache, s = setup(slots=2, budget=64, chunk=64)
+    rs = [req(i, 10, max_tokens=3) for i in range(5)]
+    log = []
+    run(s, rs, log=log)
+    first_seen = {}
+    for i, step in enumerate(log):
+        for rid, *_ in step:
+            first_seen.setdefault(rid, i)
+    assert [first_seen[i] for i in range(5)] == sorted(first_seen[i] for i in range(5))
+    assert max(len(step) for step in log) <= 2
+    assert all(r.state == FINISHED for r in rs)
+
+
+def test_pages_run_out_the_youngest_is_preempted_and_recomputed():
+    cache, s = setup(n_pages=4, page=16, slots=3, budget=64, chunk=64)
+    a, b = req(0, 30, max_tokens=20), req(1, 30, max_tokens=20)    # each grows to 50 tokens = 4 pages
+    log = []
+    run(s, [a, b], log=log)
+    assert a.state == b.state == FINISHED
+    assert s.preemptions >= 1 and b.preemptions >= 1 and a.preemptions == 0   # the older one is never the victim
+    # both produce exactly what they would have produced alone
+    for r in (a, b):
+        if r.state == FINISHED:
+            solo = req(r.id, 30, max_tokens=20)
+            c2, s2 = setup(n_pages=16)
+            run(s2, [solo])
+            assert solo.generated == r.generated
+    assert cache.free_pages() == 4 and cache.free_slots == 3
+
+
+def test_a_request_that_can_never_fit_fails_alone():
+    cache, s = setup(n_pages=2, page=16, ctx=256)
+    big, small = req(0, 100), req(1, 10, max_tokens=2)
+    run(s, [big, small])
+    assert big.state == FAILED and "never fit" in big.error
+    assert small.state == FINISHED and len(small.generated) == 2
+    too_long = req(2, 300)
+    s.add(too_long)
+    assert too_long.state == FAILED and "context limit" in too_long.error
+    empty = req(3, 0)
+    s.add(empty)
+    assert empty.state == FAILED and "empty" in empty.error
+
+
+def test_growth_beyond_the_pool_fails_the_lone_request_with_an_error():
+    cache, s = setup(n_pages=2, page=16, budget=64, chunk=64)
+    r = req(0, 20, max_tokens=100)
+    run(s, [r])
+    assert r.state == FAILED and "more pages than the pool has" in r.error
+    assert len(r.generated) == 13 and cache.free_pages() == 2     # 32 positions held; the 33rd token had no page
+
+
+def test_window_lets_a_long_request_run_in_few_pages():
+    cache, s = setup(n_pages=5, page=16, window=32, budget=16, chunk=16, ctx=256)
+    r = req(0, 100, max_tokens=100)
+    run(s, [r])
+    assert r.state == FINISHED and len(r.generated) == 100 and s.preemptions == 0
+
+
+def test_context_limit_ends_a_request():
+    cache, s = setup(ctx=32)
+    r = req(0, 20, max_tokens=100)
+    run(s, [r])
+    assert r.finish_reason == "context" and len(r.tokens) == 32
