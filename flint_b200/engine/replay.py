@@ -25,8 +25,9 @@ class Replayer:
                                          max_step_tokens=max(int(max_tokens), 64))
         self.live = {}      # request id -> [slot, tokens run]
 
-    def run_step(self, entries, end=()):
-        """entries: [{"id", "tokens", "want"}]; returns CPU float32 logits [wanted, vocab] or None."""
+    def run_step(self, entries, end=(), record=None):
+        """entries: [{"id", "tokens", "want"}]; returns CPU float32 logits [wanted, vocab] or None.
+        ``record``: a dict that parts fill with internals of this step (tests)."""
         m = self.model
         batch = []
         for e in entries:
@@ -40,7 +41,7 @@ class Replayer:
             batch.append(StepEntry(slot, done, tokens, list(e.get("want", []))))
         logits = None
         if batch:
-            out = m.step(batch)
+            out = m.step(batch, record=record)
             for b in batch:
                 rec = next(v for v in self.live.values() if v[0] == b.slot)
                 rec[1] += len(b.tokens)

@@ -92,3 +92,4 @@ class SparseMixerMoE(FeedForward):
         ops.moe_combine(residual, y, plan.row_of, gates)
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
+            step.record.setdefault("gates", []).append(gates)

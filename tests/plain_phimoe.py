@@ -151,6 +151,29 @@ def attention(q, k, v, window):
     return out
 
 
+def routing_fragility(scores, jitter_eps):
+    """How close a row of router logits is to a point where the routing changes discontinuously:
+    the smallest of the relative gaps first/second and second/third logit and of the distances of
+    every mask ratio from its threshold.  A small value means that rounding elsewhere in the model
+    may legitimately flip this decision."""
+    s = scores
+    top = torch.sort(s, descending=True).values
+    gaps = [(top[0] - top[1]) / top[0].abs().clamp(min=1e-30), (top[1] - top[2]) / top[1].abs().clamp(min=1e-30)] \
+        if s.numel() > 2 else [(top[0] - top[1]) / top[0].abs().clamp(min=1e-30)]
+    m1, i1 = top[0], int(torch.argmax(s))
+    r1 = (m1 - s) / torch.clamp(s.abs(), min=m1)
+    m2 = top[1]
+    r2 = (m2 - s) / torch.clamp(s.abs(), min=m2)
+    keep = torch.ones_like(s, dtype=torch.bool)
+    keep[i1] = False
+    keep2 = keep.clone()
+    s2 = s.clone()
+    s2[i1] = float("-inf")
+    keep2[int(torch.argmax(s2))] = False
+    d = torch.cat([(r1[keep] - 2 * jitter_eps).abs(), (r2[keep2] - 2 * jitter_eps).abs(), torch.stack(gaps)])
+    return float(d.min())
+
+
 def sparsemixer_top2(scores, jitter_eps):
     """Top-2 sparsemixer routing at inference, one row of router logits at a time.
     Returns (i1, g1, i2, g2); the two gates are not renormalised."""
@@ -193,7 +216,7 @@ def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None):
     for t in range(x.shape[0]):
         i1, g1, i2, g2 = sparsemixer_top2(logits[t], jitter_eps)
         if record is not None:
-            record.append((i1, i2))
+            record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps)))
         y1 = expert_mlp(x[t:t + 1], *experts[i1], act=act)[0]
         y2 = expert_mlp(x[t:t + 1], *experts[i2], act=act)[0]
         out[t] = g1 * y1 + g2 * y2

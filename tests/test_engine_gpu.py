@@ -24,9 +24,14 @@ pytestmark = pytest.mark.gpu
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LENGTHS = {"A": (7, 13, 32, 100, 65, 200), "B": (5, 40, 70, 100, 64, 300)}
 # float32: the engine's float32 kernels against float64 arithmetic.  bfloat16: activations are rounded
-# to 8 bits of mantissa between kernels (2^-9 relative each), which grows to a few percent of the
-# largest logit over the layers of these tiny models; weights are the same bfloat16 values on both sides.
-TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+# to 8 bits of mantissa between kernels (2^-9 relative each); weights are the same bfloat16 values on
+# both sides.  Sparsemixer routing is discontinuous (an arg-max and a mask threshold), so rounding can
+# flip a decision whose margin is within the rounding noise; the logits after such a flip are not
+# comparable.  The tests therefore compare routing first: a difference is accepted only where the plain
+# implementation itself says that the decision was a near-tie (FRAGILE), and logits are compared at all
+# positions before a request's first flip.
+TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+FRAGILE = {"float32": 1e-5, "bfloat16": 2e-2}
 
 
 @pytest.fixture(scope="module", params=[("A", "float32"), ("A", "bfloat16"), ("B", "float32"), ("B", "bfloat16")],
@@ -36,34 +41,97 @@ def setup(request, tmp_path_factory):
     store = torch.float32 if dtype == "float32" else torch.bfloat16
     folder = tiny.write_tiny(tmp_path_factory.mktemp("tiny") / f"{which}_{dtype}", which, seed=11, dtype=store)
     reqs = traces.make_requests(tiny.CONFIGS[which]["vocab_size"], LENGTHS[which], seed=5)
-    cfg, w = plain_phimoe.load_model_dir(folder)
-    plain = {rid: plain_phimoe.forward(cfg, w, t) for rid, t in reqs.items()}
+    plain = plain_all(folder, reqs)
     return which, dtype, folder, reqs, plain
 
 
+class Plain(dict):
+    """request id -> logits [len, vocab]; ``.routing[rid][layer][pos]`` = (i1, i2, g1, g2, fragility)."""
+    routing = None
+
+
+def plain_all(folder, reqs):
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    out = Plain()
+    out.routing = {}
+    for rid, t in reqs.items():
+        rec = []
+        out[rid] = plain_phimoe.forward(cfg, w, t, rec)
+        out.routing[rid] = rec
+    return out
+
+
 def replay(folder, dtype, steps, page_size):
+    """Runs the trace; returns {step: logits}, the replayer, and the engine's routing
+    {(rid, pos): [(i1, i2, g1, g2) per layer]}."""
     rp = Replayer(folder, dtype=dtype, max_tokens=traces.max_tokens_needed(steps), page_size=page_size)
-    out = {}
+    out, routing, done = {}, {}, {}
     for s in steps:
-        lg = rp.run_step(s["entries"], s["end"])
+        rec = {}
+        lg = rp.run_step(s["entries"], s["end"], record=rec)
         if lg is not None:
             out[s["step"]] = lg
+        ids = [t.cpu() for t in rec.get("experts", [])]
+        gates = [t.cpu() for t in rec.get("gates", [])]
+        row = 0
+        for e in s["entries"]:
+            base = done.get(e["id"], 0)
+            for j in range(len(e["tokens"])):
+                routing[(e["id"], base + j)] = [(int(i[row, 0]), int(i[row, 1]), float(g[row, 0]), float(g[row, 1]))
+                                                for i, g in zip(ids, gates)]
+                row += 1
+            done[e["id"]] = base + len(e["tokens"])
     rp.model.cache.check()
     assert all(g.pages.pool.used_pages == 0 for g in rp.model.cache.groups)
+    rp.routing = routing
     return out, rp
 
 
-def compare(out, steps, plain, dtype):
+def first_flips(routing, plain, dtype):
+    """request id -> first position whose routing differs from the plain implementation's.  Every
+    such first difference must be a near-tie by the plain implementation's own margins."""
+    flips = {}
+    for (rid, pos) in sorted(routing, key=lambda k: (k[0], k[1])):
+        if rid in flips:
+            continue
+        for layer, got in enumerate(routing[(rid, pos)]):
+            i1, i2, g1, g2, frag = plain.routing[rid][layer][pos]
+            same = got[:2] == (i1, i2) and abs(got[2] - g1) < 2e-2 and abs(got[3] - g2) < 2e-2
+            if not same:
+                assert frag < FRAGILE[dtype], (f"{rid} position {pos} layer {layer}: engine routed {got}, plain "
+                                               f"({i1}, {i2}, {g1:.4f}, {g2:.4f}) with a margin of {frag:.4f}")
+                flips[rid] = pos
+                break
+    return flips
+
+
+def compare(out, steps, plain, dtype, routing=None):
     exp = traces.expected_rows(steps, plain)
     assert set(out) == set(exp)
+    flips = first_flips(routing, plain, dtype) if routing is not None else {}
     scale = max(float(v.abs().max()) for v in plain.values())
-    worst = 0.0
-    for k, rows in exp.items():
-        want = torch.stack(rows)
-        assert out[k].shape == want.shape
-        assert torch.isfinite(out[k]).all()
-        worst = max(worst, (out[k].double() - want).abs().max().item())
+    worst, compared, total = 0.0, 0, 0
+    done = {}
+    for s in steps:
+        i = 0
+        for e in s["entries"]:
+            base = done.get(e["id"], 0)
+            for w in e["want"]:
+                got = out[s["step"]][i]
+                i += 1
+                total += 1
+                assert torch.isfinite(got).all()
+                if base + w >= flips.get(e["id"], 10 ** 9):
+                    continue
+                compared += 1
+                worst = max(worst, (got.double() - plain[e["id"]][base + w]).abs().max().item())
+            done[e["id"]] = base + len(e["tokens"])
+        if s["step"] in out:
+            assert out[s["step"]].shape[0] == i
     assert worst <= TOL[dtype] * scale, f"max error {worst:.3e} against a largest logit of {scale:.3f}"
+    assert compared >= 0.6 * total, f"only {compared} of {total} rows were comparable (routing flips: {flips})"
+    if dtype == "float32":
+        assert not flips, flips
     return worst
 
 
@@ -74,7 +142,7 @@ def test_replay_matches_plain_under_every_cut(setup, cut, page_size):
     steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
              "mixed": lambda r: traces.mixed(r, seed=3)}[cut](reqs)
     out, rp = replay(folder, dtype, steps, page_size)
-    compare(out, steps, plain, dtype)
+    compare(out, steps, plain, dtype, rp.routing)
     if cut == "mixed":
         assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2, "no page was used again"
 
@@ -83,10 +151,11 @@ def test_cuts_agree_with_each_other(setup):
     """The logits at a position do not depend on how the tokens were cut into steps or on what else
     was in the batch, beyond rounding: far tighter than the distance to the plain implementation."""
     which, dtype, folder, reqs, plain = setup
-    per_cut = {}
+    per_cut, routings = {}, {}
     for name, fn in (("whole", traces.whole), ("tail", traces.tail_decoded), ("mixed", lambda r: traces.mixed(r, seed=9))):
         steps = fn(reqs)
-        out, _ = replay(folder, dtype, steps, 16)
+        out, rp = replay(folder, dtype, steps, 16)
+        routings[name] = rp.routing
         done, got = {}, {}
         for s in steps:
             i = 0
@@ -98,9 +167,18 @@ def test_cuts_agree_with_each_other(setup):
                 done[e["id"]] = base + len(e["tokens"])
         per_cut[name] = got
     scale = max(float(v.abs().max()) for v in plain.values())
-    tol = (2e-5 if dtype == "float32" else 2e-2) * scale
+    tol = (2e-5 if dtype == "float32" else 1e-2) * scale
     for name in ("tail", "mixed"):
-        common = set(per_cut["whole"]) & set(per_cut[name])
+        # positions at or after a routing difference between the two cuts are not comparable
+        first = {}
+        for k in sorted(set(routings["whole"]) & set(routings[name])):
+            a, b = routings["whole"][k], routings[name][k]
+            if k[0] not in first and any(x[:2] != y[:2] or abs(x[2] - y[2]) > 2e-2 or abs(x[3] - y[3]) > 2e-2
+                                         for x, y in zip(a, b)):
+                first[k[0]] = k[1]
+        if dtype == "float32":
+            assert not first, first
+        common = [k for k in set(per_cut["whole"]) & set(per_cut[name]) if k[1] < first.get(k[0], 10 ** 9)]
         assert len(common) > 30
         worst = max((per_cut["whole"][k] - per_cut[name][k]).abs().max().item() for k in common)
         assert worst <= tol, f"{name} differs from whole by {worst:.3e}"
@@ -120,9 +198,15 @@ def test_long_decoding_and_first_tokens(setup):
     m.check_status()
     got = torch.cat(rows).cpu()
     scale = float(plain[rid].abs().max())
-    err = (got.double() - plain[rid]).abs()
+    err = (got.double() - plain[rid]).abs().max(dim=1).values
+    # the graph path records no routing; find where the error jumps and hold the plain margins to it
+    bad = (err > TOL[dtype] * scale).nonzero()
+    end = int(bad[0]) if len(bad) else len(t)
+    if end < len(t):
+        frag = min(plain.routing[rid][layer][end][4] for layer in range(len(plain.routing[rid])))
+        assert dtype == "bfloat16" and frag < FRAGILE[dtype], f"error jumps at position {end}, margin {frag:.4f}"
+    assert end >= 100, f"only {end} positions comparable"
     assert err[:4].max().item() <= TOL[dtype] * scale        # positions 0..3
-    assert err.max().item() <= TOL[dtype] * scale
     assert len(m._graphs) >= 1, "decode steps did not go through the captured graph"
 
 
@@ -139,14 +223,19 @@ def test_greedy_generation_through_the_entry_point(setup):
         for p, g in zip(prompts, got):
             # teacher-forced check: each generated token is the plain implementation's arg-max given the
             # engine's own prefix, or (bfloat16) within rounding of it
-            lg = plain_phimoe.forward(cfg, w, list(p) + g)
+            rec = []
+            lg = plain_phimoe.forward(cfg, w, list(p) + g, rec)
             for j, tok in enumerate(g):
-                row = lg[len(p) - 1 + j]
+                q = len(p) - 1 + j
+                row = lg[q]
                 best = int(torch.argmax(row))
                 if dtype == "float32":
                     assert tok == best
-                else:
-                    assert float(row[best] - row[tok]) <= 2 * TOL[dtype] * float(lg.abs().max())
+                elif float(row[best] - row[tok]) > 2 * TOL[dtype] * float(lg.abs().max()):
+                    # only a routing near-tie at or before this position can explain it
+                    frag = min(rec[layer][k][4] for layer in range(len(rec)) for k in range(q + 1))
+                    assert frag < FRAGILE[dtype], f"token {j}: {tok} instead of {best}, smallest margin {frag:.4f}"
+                    break
             assert len(g) == 16 or int(torch.argmax(lg[-1])) in eos or dtype == "bfloat16"
     assert eng.scheduler.preemptions > 0
 
@@ -184,8 +273,7 @@ def test_trace_run_as_a_program(tmp_path, dtype):
                           input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     assert [l for l in proc.stdout.split("\n") if l] == [f"done {s['step']}" for s in steps]
-    cfg, w = plain_phimoe.load_model_dir(folder)
-    plain = {rid: plain_phimoe.forward(cfg, w, t) for rid, t in reqs.items()}
+    plain = plain_all(folder, reqs)
     out = {}
     for s in steps:
         f = out_dir / f"{s['step']}.f32"
@@ -193,4 +281,7 @@ def test_trace_run_as_a_program(tmp_path, dtype):
         assert f.exists() == (n > 0)
         if n:
             out[s["step"]] = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(n, 384))
-    compare(out, steps, plain, dtype)
+    inproc, rp = replay(folder, dtype, steps, 64)        # the same trace in this process, for its routing
+    compare(out, steps, plain, dtype, rp.routing)
+    for k in out:
+        assert (out[k] - inproc[k]).abs().max().item() <= 1e-2 * float(plain["r3"].abs().max())

@@ -97,7 +97,7 @@ def test_expert_and_moe_by_hand():
     experts = [(w1, w3, w2), (w1 * 0, w3, w2)]
     rec = []
     y = P.moe_feed_forward(x, router, experts, 0.01, record=rec)
-    assert rec == [(0, 1)]
+    assert [r[:2] for r in rec] == [(0, 1)]
     assert torch.allclose(y, torch.tensor([[-3 * silu2, -6 * silu2]], dtype=D))      # g1 = 1 (other masked), expert 1 gives 0
 
 
