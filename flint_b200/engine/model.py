@@ -137,7 +137,8 @@ class Model:
         # decode steps (one token per entry) are captured once per batch size and key-range
         # split, and replayed: their hundreds of small launches would otherwise be bound by
         # the host
-        self.use_graphs = use_graphs and self.device.type == "cuda"
+        self.use_graphs = (use_graphs and self.device.type == "cuda" and self.final_norm.graph_safe
+                           and all(p.graph_safe for layer in self.layers for p in layer.parts.values()))
         self._graphs = {}
         self.graph_max_batch = 256
 
@@ -179,7 +180,7 @@ class Model:
         step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
         step.record = record
         step.attention_splits = attention_splits
-        if (self.use_graphs and record is None and attention_splits is None
+        if (self.use_graphs and attention_splits is None
                 and step.n_tokens == len(entries) <= self.graph_max_batch and step.n_want == step.n_tokens):
             return self._graphed_decode(step)
         return self.forward(step)
@@ -208,13 +209,17 @@ class Model:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = self.ops.launches
-            with torch.cuda.graph(graph):
+            wanted, step.record = step.record, {}     # internals are recorded as references to the
+            with torch.cuda.graph(graph):             # graph's own tensors, refreshed by every replay
                 logits = self.forward(step)
-            entry = (graph, logits, self.ops.launches - before)
+            entry = (graph, logits, self.ops.launches - before, step.record)
+            step.record = wanted
             self._graphs[key] = entry
-        graph, logits, n = entry
+        graph, logits, n, internals = entry
         graph.replay()
         self.ops.launches += n
+        if step.record is not None:
+            step.record.update(internals)
         return logits
 
     def forward(self, step) -> torch.Tensor:

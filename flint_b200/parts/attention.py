@@ -32,6 +32,8 @@ class Attention(Mixer):
     """params: hidden_size, num_heads, num_kv_heads, head_dim, window (0 = none),
     qkv_bias, out_bias, scale (optional), position (PartSpec or None)."""
 
+    graph_safe = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         p = params

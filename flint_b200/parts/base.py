@@ -44,6 +44,11 @@ class BuildContext:
 class Part:
     """Base of all parts: parameters in, tensor specs out, tensors in."""
 
+    # True if ``forward`` only launches work that reads the step's metadata from device memory
+    # (so a decode step can be captured once as a CUDA graph and replayed).  A part that looks at
+    # the host-side entries of the step must leave this False; the model then runs it eagerly.
+    graph_safe = False
+
     def __init__(self, params: dict, ctx: BuildContext):
         self.params = dict(params)
         self.ctx = ctx

@@ -19,6 +19,8 @@ from .base import FeedForward, mat, matmul_dtype
 class GatedMLP(FeedForward):
     """params: hidden_size, intermediate_size, act; tensors gate_proj/up_proj [I,H], down_proj [H,I]."""
 
+    graph_safe = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden, self.inter = int(params["hidden_size"]), int(params["intermediate_size"])
@@ -47,6 +49,8 @@ class GatedMLP(FeedForward):
 class SparseMixerMoE(FeedForward):
     """params: hidden_size, intermediate_size, num_experts, jitter_eps, act.
     tensors: gate.weight [E,H]; experts.{e}.w1 / w3 [I,H] (gate / up), w2 [H,I] (down)."""
+
+    graph_safe = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

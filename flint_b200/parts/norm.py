@@ -15,6 +15,7 @@ from .base import Norm, vec
 
 class _RowNorm(Norm):
     mode = "layer"
+    graph_safe = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

@@ -153,25 +153,30 @@ def attention(q, k, v, window):
 
 def routing_fragility(scores, jitter_eps):
     """How close a row of router logits is to a point where the routing changes discontinuously:
-    the smallest of the relative gaps first/second and second/third logit and of the distances of
-    every mask ratio from its threshold.  A small value means that rounding elsewhere in the model
-    may legitimately flip this decision."""
+    the smallest change of a single logit, as a fraction of the largest logit magnitude of the
+    row, that would swap first and second or second and third place, or move a mask ratio
+    (m - s_j) / max(|s_j|, m) across its threshold 2*eps.  A small value means that rounding
+    elsewhere in the model may legitimately flip this decision."""
     s = scores
+    sigma = s.abs().max().clamp(min=1e-30)
     top = torch.sort(s, descending=True).values
-    gaps = [(top[0] - top[1]) / top[0].abs().clamp(min=1e-30), (top[1] - top[2]) / top[1].abs().clamp(min=1e-30)] \
-        if s.numel() > 2 else [(top[0] - top[1]) / top[0].abs().clamp(min=1e-30)]
-    m1, i1 = top[0], int(torch.argmax(s))
-    r1 = (m1 - s) / torch.clamp(s.abs(), min=m1)
-    m2 = top[1]
-    r2 = (m2 - s) / torch.clamp(s.abs(), min=m2)
-    keep = torch.ones_like(s, dtype=torch.bool)
-    keep[i1] = False
-    keep2 = keep.clone()
+    d = [(top[0] - top[1]) / sigma]
+    if s.numel() > 2:
+        d.append((top[1] - top[2]) / sigma)
+    i1 = int(torch.argmax(s))
     s2 = s.clone()
     s2[i1] = float("-inf")
-    keep2[int(torch.argmax(s2))] = False
-    d = torch.cat([(r1[keep] - 2 * jitter_eps).abs(), (r2[keep2] - 2 * jitter_eps).abs(), torch.stack(gaps)])
-    return float(d.min())
+    i2 = int(torch.argmax(s2))
+    for m, skip in ((top[0], (i1,)), (top[1], (i1, i2))):
+        factor = torch.clamp(s.abs(), min=m)
+        ratio = (m - s) / factor
+        need = (ratio - 2 * jitter_eps).abs() * factor / sigma      # change of s_j that reaches the threshold
+        keep = torch.ones_like(s, dtype=torch.bool)
+        for i in skip:
+            keep[i] = False
+        if keep.any():
+            d.append(need[keep].min())
+    return float(torch.stack(d).min())
 
 
 def sparsemixer_top2(scores, jitter_eps):
@@ -209,14 +214,25 @@ def expert_mlp(x, w1, w3, w2, act="silu"):
     return (activation(x @ w1.T, act) * (x @ w3.T)) @ w2.T
 
 
-def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None):
-    """x [T,H] -> sum over the two selected experts of gate * expert(x)."""
+def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None, forced=None):
+    """x [T,H] -> sum over the two selected experts of gate * expert(x).
+
+    ``forced`` (tests of reduced-precision engines): per token an engine's decision
+    (i1, i2, g1, g2).  Where it differs from this function's own decision, the engine's
+    is used and the record notes the difference with this row's fragility, so that a test
+    can require every difference to be a near-tie."""
     out = torch.zeros_like(x)
     logits = x @ router_w.T
     for t in range(x.shape[0]):
         i1, g1, i2, g2 = sparsemixer_top2(logits[t], jitter_eps)
+        differs = False
+        if forced is not None:
+            f1, f2, fg1, fg2 = forced[t]
+            differs = (f1, f2) != (i1, i2) or abs(fg1 - float(g1)) > 2e-2 or abs(fg2 - float(g2)) > 2e-2
+            if differs:
+                i1, i2, g1, g2 = f1, f2, fg1, fg2
         if record is not None:
-            record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps)))
+            record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps), differs))
         y1 = expert_mlp(x[t:t + 1], *experts[i1], act=act)[0]
         y2 = expert_mlp(x[t:t + 1], *experts[i2], act=act)[0]
         out[t] = g1 * y1 + g2 * y2
@@ -232,7 +248,7 @@ def norm_eps_of(cfg):
     return 1e-5
 
 
-def forward(cfg, w, token_ids, record_experts=None):
+def forward(cfg, w, token_ids, record_experts=None, forced_routing=None):
     """Logits [T, V] of one whole sequence (order of operations as
     crates/thuban_architectures/src/transformer/forward.rs:88-468)."""
     H = cfg["hidden_size"]
@@ -265,7 +281,8 @@ def forward(cfg, w, token_ids, record_experts=None):
                     w[f"{p}block_sparse_moe.experts.{e}.w3.weight"],
                     w[f"{p}block_sparse_moe.experts.{e}.w2.weight"]) for e in range(E)]
         rec = [] if record_experts is not None else None
-        h = h + moe_feed_forward(x, w[p + "block_sparse_moe.gate.weight"], experts, jitter, act, rec)
+        h = h + moe_feed_forward(x, w[p + "block_sparse_moe.gate.weight"], experts, jitter, act, rec,
+                                 forced_routing[l] if forced_routing is not None else None)
         if record_experts is not None:
             record_experts.append(rec)
     x = layer_norm(h, w["norm.weight"], w.get("norm.bias"), eps)
