@@ -15,191 +15,9 @@
 //
 // Reference counterpart: crates/thuban_kernel/wgsl/attn.wgsl (8 query rows x 128 keys,
 // one dispatch per sequence chunk; window and causal mask at :78-90).
-#include <math.h>
-#include <stdarg.h>
-#include "common.cuh"
+#include "attention_kernels.cuh"
 
 using namespace flint;
-
-namespace {
-constexpr int GC = 4;          // query heads handled by one warp
-constexpr int WARPS = 4;       // warps per block
-constexpr int MAX_DPL = 8;     // output dims per lane: head_dim <= 256
-
-template <typename TC>
-__device__ __forceinline__ void load8(const TC* p, float* f);
-template <>
-__device__ __forceinline__ void load8<float>(const float* p, float* f) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
-  const uint4 a = *reinterpret_cast<const uint4*>(p);
-  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[2 * i] = __uint_as_float(w[i] << 16);
-    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-
-template <typename TQ, typename TC, typename TO>
-__global__ void __launch_bounds__(WARPS * 32)
-paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
-                       const TC* __restrict__ v_cache, const int* __restrict__ block_table,
-                       int max_pages, int page_size, const int* __restrict__ pos,
-                       const int* __restrict__ slot, TO* __restrict__ out,
-                       float* __restrict__ scratch, int T, int nq, int nkv, int hd, int window,
-                       float scale, int split_keys, int n_splits, int g_chunks) {
-  extern __shared__ float smem[];  // per warp: GC * hd floats of q
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * WARPS + warp;
-  const long long n_items = (long long)T * nkv * g_chunks * n_splits;
-  if (item >= n_items) return;
-  const int split = (int)(item % n_splits);
-  long long rest = item / n_splits;
-  const int gchunk = (int)(rest % g_chunks);
-  rest /= g_chunks;
-  const int kvh = (int)(rest % nkv);
-  const int t = (int)(rest / nkv);
-
-  const int G = nq / nkv;
-  const int g0 = gchunk * GC;
-  const int ng = min(GC, G - g0);          // query heads of this warp
-  const int h0 = kvh * G + g0;             // first query head
-  const int p = pos[t];
-  const int lo_row = window > 0 ? max(0, p + 1 - window) : 0;
-  const int lo = lo_row + split * split_keys;
-  const int hi = min(p + 1, lo + split_keys);   // keys [lo, hi)
-  const int* bt = block_table + (size_t)slot[t] * max_pages;
-
-  float* qs = smem + warp * GC * hd;
-  for (int i = lane; i < ng * hd; i += 32)
-    qs[i] = to_f32(q[((size_t)t * nq + h0) * hd + i]) * scale;
-  __syncwarp();
-
-  const int dpl = (hd + 31) / 32;
-  float m[GC], l[GC], acc[GC][MAX_DPL];
-#pragma unroll
-  for (int g = 0; g < GC; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAX_DPL; ++i) acc[g][i] = 0.f;
-  }
-
-  for (int j0 = lo; j0 < hi; j0 += 32) {
-    const int j = j0 + lane;
-    const bool valid = j < hi;
-    long long row = -1;   // index of the key's row in [page, kv_head, P] units
-    if (valid) {
-      const int page = bt[j / page_size];
-      if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
-    }
-    float s[GC];
-#pragma unroll
-    for (int g = 0; g < GC; ++g) s[g] = 0.f;
-    if (row >= 0) {
-      const TC* kr = k_cache + row * hd;
-      for (int d = 0; d < hd; d += 8) {   // head_dim is a multiple of 16
-        float kf[8];
-        load8<TC>(kr + d, kf);
-#pragma unroll
-        for (int g = 0; g < GC; ++g)
-          if (g < ng) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) s[g] = fmaf(qs[g * hd + d + e], kf[e], s[g]);
-          }
-      }
-    }
-    float pr[GC];
-#pragma unroll
-    for (int g = 0; g < GC; ++g) {
-      const float sg = row >= 0 ? s[g] : -INFINITY;
-      const float m_new = fmaxf(m[g], warp_max(sg));
-      const bool any = m_new > -INFINITY;               // false only if no key was readable yet
-      const float alpha = any ? expf(m[g] - m_new) : 1.f;   // 0 on the first block (m = -inf)
-      pr[g] = (any && row >= 0) ? expf(sg - m_new) : 0.f;
-      l[g] = l[g] * alpha + warp_sum(pr[g]);
-      m[g] = m_new;
-#pragma unroll
-      for (int i = 0; i < MAX_DPL; ++i) acc[g][i] *= alpha;
-    }
-    const int nk = min(32, hi - j0);
-    for (int jj = 0; jj < nk; ++jj) {
-      const long long vrow = __shfl_sync(0xffffffffu, row, jj);
-      float pj[GC];
-#pragma unroll
-      for (int g = 0; g < GC; ++g) pj[g] = __shfl_sync(0xffffffffu, pr[g], jj);
-      if (vrow < 0) continue;
-      const TC* vr = v_cache + vrow * hd;
-#pragma unroll
-      for (int i = 0; i < MAX_DPL; ++i) {
-        const int d = lane + 32 * i;
-        if (i < dpl && d < hd) {
-          const float vv = to_f32(vr[d]);
-#pragma unroll
-          for (int g = 0; g < GC; ++g) acc[g][i] = fmaf(pj[g], vv, acc[g][i]);
-        }
-      }
-    }
-  }
-
-  if (n_splits == 1) {
-#pragma unroll
-    for (int g = 0; g < GC; ++g)
-      if (g < ng) {
-        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
-#pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i) {
-          const int d = lane + 32 * i;
-          if (i < dpl && d < hd) out[((size_t)t * nq + h0 + g) * hd + d] = from_f32<TO>(acc[g][i] * inv);
-        }
-      }
-  } else {
-    // scratch [T, nq, n_splits, hd + 2]: unnormalised output, then max, then sum
-#pragma unroll
-    for (int g = 0; g < GC; ++g)
-      if (g < ng) {
-        float* dst = scratch + (((size_t)t * nq + h0 + g) * n_splits + split) * (hd + 2);
-#pragma unroll
-        for (int i = 0; i < MAX_DPL; ++i) {
-          const int d = lane + 32 * i;
-          if (i < dpl && d < hd) dst[d] = acc[g][i];
-        }
-        if (lane == 0) {
-          dst[hd] = m[g];
-          dst[hd + 1] = l[g];
-        }
-      }
-  }
-}
-
-// Merge the splits of one (row, head): out = sum_s e^{m_s-M} o_s / sum_s e^{m_s-M} l_s.
-template <typename TO>
-__global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out,
-                                         int hd, int n_splits) {
-  const size_t rh = blockIdx.x;   // row * nq + head
-  const float* base = scratch + rh * n_splits * (hd + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (hd + 2) + hd]);
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = base[(size_t)s * (hd + 2) + hd];
-    if (ms > -INFINITY) L += expf(ms - M) * base[(size_t)s * (hd + 2) + hd + 1];
-  }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float o = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = base[(size_t)s * (hd + 2) + hd];
-      if (ms > -INFINITY) o += expf(ms - M) * base[(size_t)s * (hd + 2) + d];
-    }
-    out[rh * hd + d] = from_f32<TO>(o * inv);
-  }
-}
-}  // namespace
 
 // Number of floats of scratch that flint_paged_attention needs for n_splits > 1.
 extern "C" long long flint_paged_attention_scratch_floats(int T, int nq, int hd, int n_splits) {
@@ -212,32 +30,9 @@ extern "C" int flint_paged_attention(const void* q, int q_dtype, const void* k_c
                                      void* out, int out_dtype, int T, int nq, int nkv, int hd,
                                      int window, float scale, int split_keys, int n_splits,
                                      float* scratch, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (hd <= 0 || hd % 16 || hd > 32 * MAX_DPL)
-    return fail("paged_attention: head size %d is not a multiple of 16 up to %d", hd, 32 * MAX_DPL);
-  if (nkv <= 0 || nq % nkv) return fail("paged_attention: %d query heads do not divide into %d kv heads", nq, nkv);
-  if (n_splits < 1 || split_keys < 1) return fail("paged_attention: bad split (%d keys, %d splits)", split_keys, n_splits);
-  if (n_splits > 1 && !scratch) return fail("paged_attention: splits need scratch memory");
-  if (q_dtype != out_dtype) return fail("paged_attention: output type must equal the query type");
-  const int G = nq / nkv;
-  const int g_chunks = (G + GC - 1) / GC;
-  const long long items = (long long)T * nkv * g_chunks * n_splits;
-  const long long blocks = (items + WARPS - 1) / WARPS;
-  if (blocks > 0x7fffffffLL) return fail("paged_attention: too many work items");
-  const size_t smem = (size_t)WARPS * GC * hd * sizeof(float);
-#define LAUNCH(TQ, TC)                                                                         \
-  paged_attention_kernel<TQ, TC, TQ><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(          \
-      (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, \
-      pos, slot, (TQ*)out, scratch, T, nq, nkv, hd, window, scale, split_keys, n_splits, g_chunks)
-  FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC, LAUNCH(TQ, TC)));
-#undef LAUNCH
-  int rc = check_launch("paged_attention");
-  if (rc || n_splits == 1) return rc;
-  const int threads = hd >= 128 ? 128 : 64;
-  FLINT_DISPATCH_DTYPE(out_dtype, TO,
-      (attention_combine_kernel<TO><<<(unsigned)((long long)T * nq), threads, 0, stream>>>(
-          scratch, (TO*)out, hd, n_splits)));
-  return check_launch("attention_combine");
+  return flint_attn::paged_attention_launch(q, q_dtype, k_cache, v_cache, cache_dtype, block_table, max_pages,
+                                            page_size, pos, slot, out, out_dtype, T, nq, nkv, hd, window, scale,
+                                            split_keys, n_splits, scratch, stream);
 }
 
 extern "C" const char* flint_attention_last_error() { return g_error; }
