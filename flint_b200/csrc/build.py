@@ -64,7 +64,7 @@ def _build_dirs():
 def _writable(d: Path) -> bool:
     try:
         d.mkdir(parents=True, exist_ok=True)
-        probe = d / f".probe_{os.getpid()}"
+        probe = d / f".probe_{os.getpid()}_{threading.get_ident()}"
         probe.write_bytes(b"")
         probe.unlink()
         return True
@@ -94,7 +94,7 @@ def compile_module(name: str, verbose: bool = True) -> Path:
         raise KernelError("no writable folder for the compiled kernels (tried "
                           + ", ".join(str(d) for d in _build_dirs()) + ")")
     out = out_dir / f"flint_{name}_{_source_hash(name)}.so"
-    tmp = out_dir / f".{out.name}.{os.getpid()}.tmp"
+    tmp = out_dir / f".{out.name}.{os.getpid()}_{threading.get_ident()}.tmp"
     cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(SRC_DIR), "-o", str(tmp), str(src)]
     if verbose:
         print(f"[flint_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
