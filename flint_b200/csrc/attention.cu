@@ -1,6 +1,7 @@
 // Attention over the paged cache, for prefill portions and decoded tokens alike.
 //
-// Every query row t has a position pos[t] and a request slot slot[t]; it sees the keys
+// Every query row t has a position pos[t] and a request slot slot[t] (with a row list, T counts
+// the listed rows and t = row_list[i]); it sees the keys
 // of its request at positions lo..pos[t], lo = max(0, pos[t]+1-window) (window 0: all).
 // Key j of a request lives in page block_table[slot, j / P] at row j % P; pages are
 // [page, kv_head, P, head_dim].  Scores, the running maximum, the sum and the output
@@ -29,10 +30,22 @@ extern "C" int flint_paged_attention(const void* q, int q_dtype, const void* k_c
                                      int max_pages, int page_size, const int* pos, const int* slot,
                                      void* out, int out_dtype, int T, int nq, int nkv, int hd,
                                      int window, float scale, int split_keys, int n_splits,
-                                     float* scratch, cudaStream_t stream) {
+                                     float* scratch, const int* row_list, cudaStream_t stream) {
   return flint_attn::paged_attention_launch(q, q_dtype, k_cache, v_cache, cache_dtype, block_table, max_pages,
                                             page_size, pos, slot, out, out_dtype, T, nq, nkv, hd, window, scale,
-                                            split_keys, n_splits, scratch, stream);
+                                            split_keys, n_splits, scratch, stream, row_list);
+}
+
+// The same contract with the block kernel (one block per row, kv head and split): for decode.
+extern "C" int flint_paged_attention_block(const void* q, int q_dtype, const void* k_cache,
+                                           const void* v_cache, int cache_dtype, const int* block_table,
+                                           int max_pages, int page_size, const int* pos, const int* slot,
+                                           void* out, int out_dtype, int T, int nq, int nkv, int hd,
+                                           int window, float scale, int split_keys, int n_splits,
+                                           float* scratch, const int* row_list, cudaStream_t stream) {
+  return flint_attn::paged_attention_block_launch(q, q_dtype, k_cache, v_cache, cache_dtype, block_table, max_pages,
+                                                  page_size, pos, slot, out, out_dtype, T, nq, nkv, hd, window,
+                                                  scale, split_keys, n_splits, scratch, stream, row_list);
 }
 
 extern "C" const char* flint_attention_last_error() { return g_error; }

@@ -37,7 +37,8 @@ paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
                        int max_pages, int page_size, const int* __restrict__ pos,
                        const int* __restrict__ slot, TO* __restrict__ out,
                        float* __restrict__ scratch, int T, int nq, int nkv, int hd, int window,
-                       float scale, int split_keys, int n_splits, int g_chunks) {
+                       float scale, int split_keys, int n_splits, int g_chunks,
+                       const int* __restrict__ row_list) {
   extern __shared__ float smem[];  // per warp: GC * hd floats of q
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -48,7 +49,8 @@ paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
   const int gchunk = (int)(rest % g_chunks);
   rest /= g_chunks;
   const int kvh = (int)(rest % nkv);
-  const int t = (int)(rest / nkv);
+  const int ti = (int)(rest / nkv);                 // index into the rows this launch covers
+  const int t = row_list ? row_list[ti] : ti;       // row of the batch
 
   const int G = nq / nkv;
   const int g0 = gchunk * GC;
@@ -148,7 +150,7 @@ paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
 #pragma unroll
     for (int g = 0; g < GC; ++g)
       if (g < ng) {
-        float* dst = scratch + (((size_t)t * nq + h0 + g) * n_splits + split) * (hd + 2);
+        float* dst = scratch + (((size_t)ti * nq + h0 + g) * n_splits + split) * (hd + 2);
 #pragma unroll
         for (int i = 0; i < MAX_DPL; ++i) {
           const int d = lane + 32 * i;
@@ -165,9 +167,10 @@ paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
 // Merge the splits of one (row, head): out = sum_s e^{m_s-M} o_s / sum_s e^{m_s-M} l_s.
 template <typename TO>
 __global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out,
-                                         int hd, int n_splits) {
-  const size_t rh = blockIdx.x;   // row * nq + head
+                                         int hd, int n_splits, int nq, const int* __restrict__ row_list) {
+  const size_t rh = blockIdx.x;   // (index of the row in this launch) * nq + head
   const float* base = scratch + rh * n_splits * (hd + 2);
+  const size_t out_rh = row_list ? (size_t)row_list[rh / nq] * nq + rh % nq : rh;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (hd + 2) + hd]);
   float L = 0.f;
@@ -182,18 +185,19 @@ __global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* 
       const float ms = base[(size_t)s * (hd + 2) + hd];
       if (ms > -INFINITY) o += expf(ms - M) * base[(size_t)s * (hd + 2) + d];
     }
-    out[rh * hd + d] = from_f32<TO>(o * inv);
+    out[out_rh * hd + d] = from_f32<TO>(o * inv);
   }
 }
 
 // Validates the sizes, launches the attention kernel and, with more than one split, the
 // kernel that merges the splits.  `scratch` must hold T*nq*n_splits*(hd+2) floats then.
+// With a row list, T is the number of listed rows and row_list[i] the batch row of the i-th.
 inline int paged_attention_launch(const void* q, int q_dtype, const void* k_cache,
                                      const void* v_cache, int cache_dtype, const int* block_table,
                                      int max_pages, int page_size, const int* pos, const int* slot,
                                      void* out, int out_dtype, int T, int nq, int nkv, int hd,
                                      int window, float scale, int split_keys, int n_splits,
-                                     float* scratch, cudaStream_t stream) {
+                                     float* scratch, cudaStream_t stream, const int* row_list = nullptr) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 16 || hd > 32 * MAX_DPL)
     return fail("paged_attention: head size %d is not a multiple of 16 up to %d", hd, 32 * MAX_DPL);
@@ -210,7 +214,7 @@ inline int paged_attention_launch(const void* q, int q_dtype, const void* k_cach
 #define LAUNCH(TQ, TC)                                                                         \
   paged_attention_kernel<TQ, TC, TQ><<<(unsigned)blocks, WARPS * 32, smem, stream>>>(          \
       (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size, \
-      pos, slot, (TQ*)out, scratch, T, nq, nkv, hd, window, scale, split_keys, n_splits, g_chunks)
+      pos, slot, (TQ*)out, scratch, T, nq, nkv, hd, window, scale, split_keys, n_splits, g_chunks, row_list)
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC, LAUNCH(TQ, TC)));
 #undef LAUNCH
   int rc = check_launch("paged_attention");
@@ -218,9 +222,197 @@ inline int paged_attention_launch(const void* q, int q_dtype, const void* k_cach
   const int threads = hd >= 128 ? 128 : 64;
   FLINT_DISPATCH_DTYPE(out_dtype, TO,
       (attention_combine_kernel<TO><<<(unsigned)((long long)T * nq), threads, 0, stream>>>(
-          scratch, (TO*)out, hd, n_splits)));
+          scratch, (TO*)out, hd, n_splits, nq, row_list)));
   return check_launch("attention_combine");
 }
 
+
+
+// ---------------------------------------------------------------------------------------------
+// Block kernel for few rows over long contexts (decode).  One block of 128 threads per
+// (split, kv head x chunk of 4 query heads, row).  Per chunk of 128 keys: thread t owns key t
+// in the score phase (its K row is read with 16-byte loads, the 4 query heads share it), the
+// block agrees on the new maximum and sum per head through shared memory, the probabilities
+// are left in shared memory, and in the value phase thread t owns output dim t (and t+128):
+// V rows are read coalesced across the block, unrolled for memory-level parallelism.
+constexpr int BT = 128;        // threads per block = keys per chunk
+
+template <typename TQ, typename TC, typename TO>
+__global__ void __launch_bounds__(BT)
+paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
+                             const TC* __restrict__ v_cache, const int* __restrict__ block_table,
+                             int max_pages, int page_size, const int* __restrict__ pos,
+                             const int* __restrict__ slot, TO* __restrict__ out,
+                             float* __restrict__ scratch, int nq, int nkv, int hd, int window,
+                             float scale, int split_keys, int n_splits, int g_chunks,
+                             const int* __restrict__ row_list) {
+  extern __shared__ float smem[];
+  float* qs = smem;                       // [GC][hd]
+  float* ps = qs + GC * hd;               // [GC][BT] probabilities of the chunk
+  float* red = ps + GC * BT;              // [GC][4] per-warp partials
+  long long* rows = (long long*)(red + GC * 4 + 4);   // [BT] row index of each key (or -1)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int split = blockIdx.x;
+  const int kvh = blockIdx.y / g_chunks, gchunk = blockIdx.y % g_chunks;
+  const int ti = blockIdx.z;                        // index into the rows this launch covers
+  const int t = row_list ? row_list[ti] : ti;       // row of the batch
+  const int G = nq / nkv;
+  const int g0 = gchunk * GC;
+  const int ng = min(GC, G - g0);
+  const int h0 = kvh * G + g0;
+  const int p = pos[t];
+  const int lo_row = window > 0 ? max(0, p + 1 - window) : 0;
+  const int lo = lo_row + split * split_keys;
+  const int hi = min(p + 1, lo + split_keys);
+  const int* bt = block_table + (size_t)slot[t] * max_pages;
+
+  for (int i = tid; i < ng * hd; i += BT) qs[i] = to_f32(q[((size_t)t * nq + h0) * hd + i]) * scale;
+  __syncthreads();
+
+  float m[GC], l[GC], acc[GC][2];
+#pragma unroll
+  for (int g = 0; g < GC; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = 0.f; }
+
+  for (int j0 = lo; j0 < hi; j0 += BT) {
+    const int j = j0 + tid;
+    long long row = -1;
+    if (j < hi) {
+      const int page = bt[j / page_size];
+      if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
+    }
+    rows[tid] = row;
+    float s[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) s[g] = 0.f;
+    if (row >= 0) {
+      const TC* kr = k_cache + row * hd;
+      for (int d = 0; d < hd; d += 8) {
+        float kf[8];
+        load8<TC>(kr + d, kf);
+#pragma unroll
+        for (int g = 0; g < GC; ++g)
+          if (g < ng) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s[g] = fmaf(qs[g * hd + d + e], kf[e], s[g]);
+          }
+      }
+    }
+    // block maximum per head
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      const float v = warp_max(row >= 0 ? s[g] : -INFINITY);
+      if (lane == 0) red[g * 4 + warp] = v;
+    }
+    __syncthreads();
+    float alpha[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      const float mc = fmaxf(fmaxf(red[g * 4], red[g * 4 + 1]), fmaxf(red[g * 4 + 2], red[g * 4 + 3]));
+      const float m_new = fmaxf(m[g], mc);
+      const bool any = m_new > -INFINITY;
+      alpha[g] = any ? expf(m[g] - m_new) : 1.f;
+      const float pr = (any && row >= 0) ? expf(s[g] - m_new) : 0.f;
+      ps[g * BT + tid] = pr;
+      m[g] = m_new;
+      s[g] = pr;
+    }
+    __syncthreads();      // red is read by all, ps written by all
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      const float v = warp_sum(s[g]);
+      if (lane == 0) red[g * 4 + warp] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GC; ++g) {
+      l[g] = l[g] * alpha[g] + (red[g * 4] + red[g * 4 + 1]) + (red[g * 4 + 2] + red[g * 4 + 3]);
+      acc[g][0] *= alpha[g];
+      acc[g][1] *= alpha[g];
+    }
+    // values: thread owns dims tid and tid + BT
+    const int nk = min(BT, hi - j0);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int d = tid + half * BT;
+      if (d < hd) {
+        int jj = 0;
+        for (; jj + 8 <= nk; jj += 8) {
+          float vv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const long long r = rows[jj + e];
+            vv[e] = r >= 0 ? to_f32(v_cache[r * hd + d]) : 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+#pragma unroll
+            for (int g = 0; g < GC; ++g) acc[g][half] = fmaf(ps[g * BT + jj + e], vv[e], acc[g][half]);
+        }
+        for (; jj < nk; ++jj) {
+          const long long r = rows[jj];
+          const float vv = r >= 0 ? to_f32(v_cache[r * hd + d]) : 0.f;
+#pragma unroll
+          for (int g = 0; g < GC; ++g) acc[g][half] = fmaf(ps[g * BT + jj], vv, acc[g][half]);
+        }
+      }
+    }
+    __syncthreads();      // ps, rows and red are rewritten by the next chunk
+  }
+
+#pragma unroll
+  for (int g = 0; g < GC; ++g) {
+    if (g >= ng) continue;
+    if (n_splits == 1) {
+      const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int d = tid + half * BT;
+        if (d < hd) out[((size_t)t * nq + h0 + g) * hd + d] = from_f32<TO>(acc[g][half] * inv);
+      }
+    } else {
+      float* dst = scratch + (((size_t)ti * nq + h0 + g) * n_splits + split) * (hd + 2);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int d = tid + half * BT;
+        if (d < hd) dst[d] = acc[g][half];
+      }
+      if (tid == 0) { dst[hd] = m[g]; dst[hd + 1] = l[g]; }
+    }
+  }
+}
+
+// Same contract as paged_attention_launch, with the block kernel: for few rows and long key ranges.
+inline int paged_attention_block_launch(const void* q, int q_dtype, const void* k_cache,
+                                        const void* v_cache, int cache_dtype, const int* block_table,
+                                        int max_pages, int page_size, const int* pos, const int* slot,
+                                        void* out, int out_dtype, int T, int nq, int nkv, int hd,
+                                        int window, float scale, int split_keys, int n_splits,
+                                        float* scratch, cudaStream_t stream, const int* row_list = nullptr) {
+  if (T <= 0) return 0;
+  if (hd <= 0 || hd % 16 || hd > 2 * BT)
+    return fail("paged_attention: head size %d is not a multiple of 16 up to %d", hd, 2 * BT);
+  if (nkv <= 0 || nq % nkv) return fail("paged_attention: %d query heads do not divide into %d kv heads", nq, nkv);
+  if (n_splits < 1 || split_keys < 1) return fail("paged_attention: bad split (%d keys, %d splits)", split_keys, n_splits);
+  if (n_splits > 1 && !scratch) return fail("paged_attention: splits need scratch memory");
+  if (q_dtype != out_dtype) return fail("paged_attention: output type must equal the query type");
+  const int G = nq / nkv;
+  const int g_chunks = (G + GC - 1) / GC;
+  if (T > 65535 || nkv * g_chunks > 65535) return fail("paged_attention: too many rows or heads for the block kernel");
+  dim3 grid(n_splits, nkv * g_chunks, T);
+  const size_t smem = (size_t)(GC * hd + GC * BT + GC * 4 + 4) * sizeof(float) + BT * sizeof(long long);
+#define LAUNCH(TQ, TC)                                                                          \
+  paged_attention_block_kernel<TQ, TC, TQ><<<grid, BT, smem, stream>>>(                         \
+      (const TQ*)q, (const TC*)k_cache, (const TC*)v_cache, block_table, max_pages, page_size,  \
+      pos, slot, (TQ*)out, scratch, nq, nkv, hd, window, scale, split_keys, n_splits, g_chunks, row_list)
+  FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC, LAUNCH(TQ, TC)));
+#undef LAUNCH
+  int rc = check_launch("paged_attention (block kernel)");
+  if (rc || n_splits == 1) return rc;
+  const int threads = hd >= 128 ? 128 : 64;
+  FLINT_DISPATCH_DTYPE(out_dtype, TO,
+      (attention_combine_kernel<TO><<<(unsigned)((long long)T * nq), threads, 0, stream>>>(
+          scratch, (TO*)out, hd, n_splits, nq, row_list)));
+  return check_launch("attention_combine");
+}
 
 }  // namespace flint_attn

@@ -287,37 +287,80 @@ class CudaOps:
                   c_int(plan.max_tiles if plan else 0), c_int(plan.tile_rows if plan else 0), c_int(M), c_int(N), c_int(K))
 
     # ------------------------------------------------------------------ attention
-    def attention_splits(self, T, nq, nkv, max_kv_len):
-        """How to split the key range so that the device is filled: (keys per split, splits)."""
+    def attention_plan(self, T, nq, nkv, span):
+        """Which kernel and how to split the key range so that the device is filled:
+        (kernel, keys per split, splits).  Few rows (decode): the block kernel, one block per
+        (row, kv head, split) with splits of whole 128-key chunks; many rows: the warp kernel."""
         g_chunks = -(-(nq // nkv) // 4)
         base = T * nkv * g_chunks
-        if base >= 2048 or max_kv_len <= 64:
-            return max(max_kv_len, 1), 1
-        n = min(-(-max_kv_len // 64), -(-2048 // base))
-        keys = -(-max_kv_len // n)
-        keys = -(-keys // 32) * 32
-        return keys, -(-max_kv_len // keys)
+        span = max(span, 1)
+        if T <= 256:
+            n = max(1, min(-(-span // 128), -(-1184 // base)))
+            keys = -(-(-(-span // n)) // 128) * 128
+            return "block", keys, -(-span // keys)
+        if base >= 2048 or span <= 64:
+            return "warp", span, 1
+        n = min(-(-span // 64), -(-2048 // base))
+        keys = -(-(-(-span // n)) // 32) * 32
+        return "warp", keys, -(-span // keys)
 
-    def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None):
+    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale):
+        """Attention of all rows of a step: long portions on the tensor cores (bfloat16, head
+        sizes up to 128), decoded tokens and short portions row by row."""
+        P = cache.page_size
+        tc = (step.n_tiles > 0 and q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and hd <= 128
+              and (64 % P == 0 or P % 64 == 0) and step.attention_splits is None)
+        if not tc:
+            return self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale,
+                                        step.max_kv_len, splits=step.attention_splits)
+        self.attention_prefill_tc(q, cache, step.tiles, step.n_tiles, out, nq, nkv, hd, window, scale)
+        if step.n_other_rows:
+            self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len,
+                                 rows=step.other_rows)
+
+    def attention_prefill_tc(self, q, cache, tiles, n_tiles, out, nq, nkv, hd, window, scale):
+        _check(q, "q", torch.bfloat16, 2)
+        _check(out, "out", torch.bfloat16, 2)
+        _check(tiles, "tiles", torch.int32)
+        T = q.shape[0]
+        if q.shape[1] != nq * hd or tuple(out.shape) != (T, nq * hd):
+            raise KernelError("attention_prefill_tc: q/out width does not match the head counts")
+        if cache.k.dtype != torch.bfloat16 or tuple(cache.k.shape[1:]) != (nkv, cache.page_size, hd):
+            raise KernelError("attention_prefill_tc: cache pages must be bfloat16 [page, kv head, P, head size]")
+        self._run("attention_tc", "flint_attention_prefill_tc", _ptr(q), _ptr(cache.k), _ptr(cache.v),
+                  c_int(cache.k.shape[0]), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
+                  c_int(cache.page_size), _ptr(tiles), c_int(n_tiles), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
+                  c_int(hd), c_int(window), c_float(scale), _ptr(self.tc_error))
+
+    def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,
+                        kernel=None, rows=None):
+        """rows: int32 list of the batch rows to compute (default: all)."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
         if q.shape[1] != nq * hd or tuple(out.shape) != (T, nq * hd):
             raise KernelError("paged_attention: q/out width does not match the head counts")
+        if rows is not None:
+            _check(rows, "rows", torch.int32, 1)
+            T = rows.numel()
         if tuple(cache.k.shape[1:]) != (nkv, cache.page_size, hd):
             raise KernelError("paged_attention: cache pages do not match the head counts")
         span = min(max_kv_len, window) if window else max_kv_len
-        split_keys, n_splits = splits or self.attention_splits(T, nq, nkv, span)
+        auto_kernel, split_keys, n_splits = self.attention_plan(T, nq, nkv, span)
+        kernel = kernel or auto_kernel
+        if splits is not None:
+            split_keys, n_splits = splits
         if split_keys * n_splits < span:
             raise KernelError(f"paged_attention: {n_splits} splits of {split_keys} keys do not cover {span} keys")
         scratch = None
         if n_splits > 1:
             scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
-        self._run("attention", "flint_paged_attention", _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
+        fn = {"warp": "flint_paged_attention", "block": "flint_paged_attention_block"}[kernel]
+        self._run("attention", fn, _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
                   c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(_code(out.dtype)), c_int(T),
                   c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
-                  _ptr(scratch))
+                  _ptr(scratch), _ptr(rows))
 
     # ------------------------------------------------------------------ routing
     def router_sparsemixer(self, x, wr, eps, expert_ids, gates, logits_out=None):

@@ -21,6 +21,10 @@ import torch
 from ..errors import ModelError
 
 
+TILE_ROWS = 128        # query rows per tile of the tensor-core attention
+TILE_MIN_ROWS = 16     # shorter portions go row by row
+
+
 @dataclass
 class StepEntry:
     slot: int              # request slot (row of the block tables, index of state slabs)
@@ -42,6 +46,13 @@ class StepContext:
     status: torch.Tensor       # [1] int32, set non-zero by a kernel that met a missing page
     entries: list              # the host-side StepEntry list
     entry_start: list          # first flattened row of each entry (host)
+    # Rows of long portions, cut into tiles of up to 128 consecutive rows of one request
+    # ([n, 4] int32: first row, rows, slot, position of the first row), for the tensor-core
+    # attention; and the rows that are not in any tile (decoded tokens, short portions).
+    tiles: torch.Tensor = None
+    n_tiles: int = 0
+    other_rows: torch.Tensor = None
+    n_other_rows: int = 0
     attention_splits: tuple | None = None
     record: dict | None = None  # filled by parts when a test asks for internals
 
@@ -52,7 +63,8 @@ class StepStaging:
     def __init__(self, max_tokens: int, device):
         self.max_tokens = int(max_tokens)
         self.device = torch.device(device)
-        n = 4 * self.max_tokens
+        self.max_tiles = self.max_tokens // 8 + 16
+        n = 5 * self.max_tokens + 4 * self.max_tiles
         self.host = torch.zeros(n, dtype=torch.int32)
         if self.device.type == "cuda":
             self.host = self.host.pin_memory()
@@ -69,7 +81,7 @@ class StepStaging:
             raise ModelError("a step needs at least one token")
         if T > self.max_tokens:
             raise ModelError(f"step of {T} tokens exceeds the limit of {self.max_tokens}")
-        ids, pos, slot, want, starts = [], [], [], [], []
+        ids, pos, slot, want, starts, tiles, others = [], [], [], [], [], [], []
         seen = set()
         max_kv = 0
         for e in entries:
@@ -94,6 +106,11 @@ class StepStaging:
                 if not 0 <= w < n:
                     raise ModelError(f"wanted place {w} is outside the entry's {n} tokens")
                 want.append(base + w)
+            if n >= TILE_MIN_ROWS:
+                for r in range(0, n, TILE_ROWS):
+                    tiles += [base + r, min(TILE_ROWS, n - r), e.slot, e.start_pos + r]
+            else:
+                others.extend(range(base, base + n))
             max_kv = max(max_kv, e.start_pos + n)
         R = len(want)
         M = self.max_tokens
@@ -105,6 +122,10 @@ class StepStaging:
         h[2 * M:2 * M + T] = torch.tensor(slot, dtype=torch.int32)
         if R:
             h[3 * M:3 * M + R] = torch.tensor(want, dtype=torch.int32)
+        if others:
+            h[4 * M:4 * M + len(others)] = torch.tensor(others, dtype=torch.int32)
+        if tiles:
+            h[5 * M:5 * M + len(tiles)] = torch.tensor(tiles, dtype=torch.int32)
         self.dev.copy_(h, non_blocking=True)
         if self._copied is not None:
             self._copied.record()
@@ -112,4 +133,6 @@ class StepStaging:
         d = self.dev
         return StepContext(n_tokens=T, ids=d[0:T], pos=d[M:M + T], slot=d[2 * M:2 * M + T],
                            want_rows=d[3 * M:3 * M + R], n_want=R, max_kv_len=max_kv, status=self.status,
-                           entries=list(entries), entry_start=starts)
+                           entries=list(entries), entry_start=starts,
+                           tiles=d[5 * M:5 * M + len(tiles)].view(-1, 4), n_tiles=len(tiles) // 4,
+                           other_rows=d[4 * M:4 * M + len(others)], n_other_rows=len(others))

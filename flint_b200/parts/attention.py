@@ -98,6 +98,5 @@ class Attention(Mixer):
         ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
                           writes_cache, step.status)
         attn = torch.empty_like(q)
-        ops.paged_attention(q, cache, step.pos, step.slot, attn, nq, nkv, hd, self.window, self.scale,
-                            step.max_kv_len, splits=step.attention_splits)
+        ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale)
         ops.gemm(attn, self.w_o, residual, bias=self.b_o, accumulate=True)

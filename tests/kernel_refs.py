@@ -112,16 +112,17 @@ class RefOps:
             out[lo:hi] = (xs[lo:hi] @ w[e].to(self.cd).T).to(out.dtype)
 
     # ------------------------------------------------------------------ attention
-    def attention_splits(self, T, nq, nkv, max_kv_len):
-        return max(max_kv_len, 1), 1
+    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale):
+        self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len)
 
-    def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None):
+    def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,
+                        kernel=None, rows=None):
         T = q.shape[0]
         P = cache.page_size
         G = nq // nkv
         qq = q.to(self.cd).view(T, nq, hd)
-        res = torch.zeros(T, nq, hd, dtype=self.cd)
-        for t in range(T):
+        res = out.to(self.cd).view(T, nq, hd).clone()
+        for t in (range(T) if rows is None else rows.tolist()):
             p = int(pos[t])
             lo = max(0, p + 1 - window) if window else 0
             js = torch.arange(lo, p + 1)

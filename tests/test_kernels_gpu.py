@@ -236,8 +236,12 @@ def test_rope_write_and_attention(ops, ref, qd, cd, nq, nkv, hd, P, window):
     # make one far key stand out for row 0 of slot 0, so that a kernel that skips it is caught
     out_d = torch.empty(T, nq * hd, dtype=qd, device=DEV)
     scale = 1 / math.sqrt(hd)
-    for splits in (None, (32, -(-min(lens[0], window or 10 ** 9) // 32)), (64, -(-min(lens[0], window or 10 ** 9) // 64))):
-        ops.paged_attention(q_d, dv, pos.to(DEV), slot.to(DEV), out_d, nq, nkv, hd, window, scale, max(lens.values()), splits=splits)
+    span = min(lens[0], window or 10 ** 9)
+    for kernel, splits in (("warp", None), ("warp", (32, -(-span // 32))), ("warp", (64, -(-span // 64))), ("block", None),
+                           ("block", (128, -(-span // 128))), ("block", (span, 1)), ("block", (40, -(-span // 40)))):
+        out_d.fill_(float("nan"))
+        ops.paged_attention(q_d, dv, pos.to(DEV), slot.to(DEV), out_d, nq, nkv, hd, window, scale, max(lens.values()),
+                            splits=splits, kernel=kernel)
         out_r = torch.empty(T, nq * hd, dtype=torch.float64)
         # the reference reads the device's cache content (bf16-rounded where it is) and the device's q
         cv2 = CacheView(dv.k.cpu(), dv.v.cpu(), bt, P, dv.spec)
@@ -258,17 +262,69 @@ def test_attention_far_key_stands_out(ops, ref):
     dv, cv = views(k, v, bt, P, nkv, hd, 0)
     pos, slot = torch.tensor([L - 1], dtype=torch.int32), torch.tensor([0], dtype=torch.int32)
     out = torch.empty(1, nq * hd, device=DEV)
-    for splits in (None, (32, 19), (600, 1)):
-        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, 0, 1 / math.sqrt(hd), L, splits=splits)
+    for kernel, splits in (("warp", None), ("warp", (32, 19)), ("warp", (600, 1)), ("block", None), ("block", (256, 3))):
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, 0, 1 / math.sqrt(hd), L,
+                            splits=splits, kernel=kernel)
         exp = torch.empty(1, nq * hd, dtype=torch.float64)
         ref.paged_attention(q, cv, pos, slot, exp, nq, nkv, hd, 0, 1 / math.sqrt(hd), L)
         close(out, exp, 1e-4, 1e-5)
         close(out[0, :hd], v[bt[0, far // P].long(), 0, far % P], 1e-3, 1e-3)
     # with a window that ends just after the far key it must vanish; one position wider and it is back
-    for window, present in ((L - 1 - far, False), (L - far, True)):
-        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, 1 / math.sqrt(hd), L)
-        is_far = torch.allclose(out[0, :hd].cpu(), v[bt[0, far // P].long(), 0, far % P], atol=1e-3)
-        assert is_far == present
+    for kernel in ("warp", "block"):
+        for window, present in ((L - 1 - far, False), (L - far, True)):
+            ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, 1 / math.sqrt(hd), L,
+                                kernel=kernel)
+            is_far = torch.allclose(out[0, :hd].cpu(), v[bt[0, far // P].long(), 0, far % P], atol=1e-3)
+            assert is_far == present
+
+
+@pytest.mark.parametrize("nq,nkv,hd,P,window,lens,portions", [
+    (4, 2, 16, 16, 0, (100, 37), (100, 20)), (3, 1, 32, 16, 48, (300, 90), (200, 50)),
+    (32, 8, 128, 64, 0, (700, 128), (300, 128)), (6, 2, 64, 32, 0, (257, 65), (129, 65)),
+    (5, 5, 80, 64, 20, (150, 40), (100, 40)), (8, 2, 96, 128, 0, (300, 20), (260, 16)),
+    (2, 2, 128, 16, 100, (500, 17), (130, 17))])
+def test_attention_prefill_on_tensor_cores(ops, ref, nq, nkv, hd, P, window, lens, portions):
+    """Tiles of long portions on the tcgen05 kernel, one decoded row of a third request beside them
+    through the row list, all in one output buffer; scattered pages; portions that start deep in a
+    request (keys of earlier portions come from the cache)."""
+    g = torch.Generator().manual_seed(nq * 131 + hd)
+    lens = (*lens, 77)
+    need = [-(-n // P) for n in lens]
+    n_pages = sum(need) + 3
+    k = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    bt = torch.full((3, max(need) + 1), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    o = 0
+    for s_, n in enumerate(need):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    pos, slot, tiles = [], [], []
+    for s_, (n_total, n_rows) in enumerate(zip(lens[:2], portions)):
+        base = len(pos)
+        pos += list(range(n_total - n_rows, n_total))
+        slot += [s_] * n_rows
+        for r in range(0, n_rows, 128):
+            tiles += [base + r, min(128, n_rows - r), s_, n_total - n_rows + r]
+    other = [len(pos)]
+    pos.append(lens[2] - 1)
+    slot.append(2)
+    T = len(pos)
+    pos, slot = torch.tensor(pos, dtype=torch.int32), torch.tensor(slot, dtype=torch.int32)
+    q = torch.randn(T, nq * hd, generator=g).to(torch.bfloat16)
+    spec = KVSpec(nkv, hd, window)
+    dv = CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec)
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_prefill_tc(q.to(DEV), dv, torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 4, out, nq,
+                             nkv, hd, window, scale)
+    assert torch.isnan(out[other[0]]).all() and not torch.isnan(out[:other[0]]).any()    # only its own rows
+    ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens),
+                        rows=torch.tensor(other, dtype=torch.int32, device=DEV))
+    assert int(ops.tc_error.item()) == 0
+    exp = torch.zeros(T, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, window, scale, max(lens))
+    close(out, exp, 2e-2, 2e-2)
 
 
 @pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (3, 32064)])
