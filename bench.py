@@ -243,6 +243,35 @@ def profile(model, cfg, args, rng):
     return 0
 
 
+def one_step(model, cfg, args, rng):
+    """Set-up, one warm step and one more step of the asked kind, eagerly (no graph), for profilers."""
+    import torch
+    from flint_b200.engine.step import StepEntry
+    V = cfg["vocab_size"]
+    model.use_graphs = False
+    n = args.prompt_tokens
+    slots = [model.cache.admit() for _ in range(args.batch)]
+    if args.one_step == "decode":
+        for s in slots:
+            model.cache.ensure(s, 0, n + 2)
+            model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(n)], [])])
+        step = lambda p: model.step([StepEntry(s, p, [rng.randrange(V)], [0]) for s in slots])
+        step(n)
+        torch.cuda.synchronize()
+        before = model.ops.launches
+        step(n + 1)
+    else:
+        run = lambda s: (model.cache.ensure(s, 0, n), model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(n)], [n - 1])]))
+        run(slots[0])
+        torch.cuda.synchronize()
+        before = model.ops.launches
+        run(slots[1 % len(slots)])
+    torch.cuda.synchronize()
+    print(f"launcher calls before the last step: {before}, in it: {model.ops.launches - before} "
+          f"(a call with a split launches two kernels)", file=sys.stderr)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -254,6 +283,9 @@ def main():
     ap.add_argument("--ctx-size", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are named)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--one-step", choices=["decode", "prefill"], default=None,
+                    help="run the set-up, then one warm and one measured eager step of this kind, and exit "
+                         "(for a launch list under ncu: the launch counts to skip and capture go to stderr)")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
     args = ap.parse_args()
@@ -277,6 +309,8 @@ def main():
 
     if args.profile:
         return profile(model, cfg, args, rng)
+    if args.one_step:
+        return one_step(model, cfg, args, rng)
 
     clocks = ClockSampler()
     clocks.start()

@@ -269,9 +269,17 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
   for (int i = tid; i < ng * hd; i += BT) qs[i] = to_f32(q[((size_t)t * nq + h0) * hd + i]) * scale;
   __syncthreads();
 
-  float m[GC], l[GC], acc[GC][2];
+  const int groups = hd / 8;             // 8-dim groups of a value row
+  const int lanes = BT / groups;         // key lanes working side by side in the value phase
+  const int dg = tid % groups, kl = tid / groups;
+  float m[GC], l[GC], acc[GC][8];
 #pragma unroll
-  for (int g = 0; g < GC; ++g) { m[g] = -INFINITY; l[g] = 0.f; acc[g][0] = acc[g][1] = 0.f; }
+  for (int g = 0; g < GC; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
+  }
 
   for (int j0 = lo; j0 < hi; j0 += BT) {
     const int j = j0 + tid;
@@ -326,56 +334,52 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
 #pragma unroll
     for (int g = 0; g < GC; ++g) {
       l[g] = l[g] * alpha[g] + (red[g * 4] + red[g * 4 + 1]) + (red[g * 4 + 2] + red[g * 4 + 3]);
-      acc[g][0] *= alpha[g];
-      acc[g][1] *= alpha[g];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[g][e] *= alpha[g];
     }
-    // values: thread owns dims tid and tid + BT
+    // values: thread (dg, kl) owns 8 output dims (group dg) and the keys kl, kl + lanes, ...;
+    // one 16-byte load per key, partial sums over key lanes are added up at the end
     const int nk = min(BT, hi - j0);
+    if (kl < lanes) {
+      for (int jj = kl; jj < nk; jj += lanes) {
+        const long long r = rows[jj];
+        if (r < 0) continue;
+        float vv[8];
+        load8<TC>(v_cache + r * hd + dg * 8, vv);
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int d = tid + half * BT;
-      if (d < hd) {
-        int jj = 0;
-        for (; jj + 8 <= nk; jj += 8) {
-          float vv[8];
+        for (int g = 0; g < GC; ++g) {
+          const float pj = ps[g * BT + jj];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const long long r = rows[jj + e];
-            vv[e] = r >= 0 ? to_f32(v_cache[r * hd + d]) : 0.f;
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e)
-#pragma unroll
-            for (int g = 0; g < GC; ++g) acc[g][half] = fmaf(ps[g * BT + jj + e], vv[e], acc[g][half]);
-        }
-        for (; jj < nk; ++jj) {
-          const long long r = rows[jj];
-          const float vv = r >= 0 ? to_f32(v_cache[r * hd + d]) : 0.f;
-#pragma unroll
-          for (int g = 0; g < GC; ++g) acc[g][half] = fmaf(ps[g * BT + jj], vv, acc[g][half]);
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vv[e], acc[g][e]);
         }
       }
     }
     __syncthreads();      // ps, rows and red are rewritten by the next chunk
   }
 
+  // add the key lanes' partial sums into osum [GC][hd], which reuses the query staging area
+  float* osum = qs;
+  __syncthreads();
+  for (int i = tid; i < GC * hd; i += BT) osum[i] = 0.f;
+  __syncthreads();
+  for (int lane_k = 0; lane_k < lanes; ++lane_k) {      // fixed order: results do not depend on timing
+    if (kl == lane_k) {
 #pragma unroll
-  for (int g = 0; g < GC; ++g) {
-    if (g >= ng) continue;
+      for (int g = 0; g < GC; ++g)
+        if (g < ng) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) osum[g * hd + dg * 8 + e] += acc[g][e];
+        }
+    }
+    __syncthreads();
+  }
+  for (int g = 0; g < ng; ++g) {
     if (n_splits == 1) {
       const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int d = tid + half * BT;
-        if (d < hd) out[((size_t)t * nq + h0 + g) * hd + d] = from_f32<TO>(acc[g][half] * inv);
-      }
+      for (int d = tid; d < hd; d += BT) out[((size_t)t * nq + h0 + g) * hd + d] = from_f32<TO>(osum[g * hd + d] * inv);
     } else {
       float* dst = scratch + (((size_t)ti * nq + h0 + g) * n_splits + split) * (hd + 2);
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int d = tid + half * BT;
-        if (d < hd) dst[d] = acc[g][half];
-      }
+      for (int d = tid; d < hd; d += BT) dst[d] = osum[g * hd + d];
       if (tid == 0) { dst[hd] = m[g]; dst[hd + 1] = l[g]; }
     }
   }

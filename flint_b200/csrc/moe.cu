@@ -14,19 +14,37 @@ namespace {
 constexpr int MAX_E = 256;
 
 // One block per TT tokens.  The tokens' rows are staged in shared memory; each warp takes
-// experts warp, warp+8, ... and computes their logits for all TT tokens while reading the
-// router row once; then one thread per token does the selection:
+// experts warp, warp+16, ... and computes their logits for all TT tokens while reading the
+// router row once with 16-byte loads; then one thread per token does the selection:
 //   i1 = argmax s (lowest index on ties), m1 = s[i1]
 //   keep_j = !((m1 - s_j) / max(|s_j|, m1) > 2 eps);  g1 = e^{s_i1 - m1} / sum_{keep} e^{s_j - m1}
 //   the same again over s without i1 for (i2, g2); the gates are not renormalised.
 constexpr int TT = 4;
-constexpr int ROUTER_WARPS = 8;
+constexpr int ROUTER_WARPS = 16;
+
+template <typename TW> struct Vec;                       // 16 bytes of a weight row
+template <> struct Vec<float> { static constexpr int N = 4; };
+template <> struct Vec<__nv_bfloat16> { static constexpr int N = 8; };
+
+__device__ __forceinline__ void load_vec(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+}
+__device__ __forceinline__ void load_vec(const __nv_bfloat16* p, float* f) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
 
 template <typename TW>
 __global__ void __launch_bounds__(ROUTER_WARPS * 32)
 router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr, float eps,
                           int* __restrict__ expert_ids, float* __restrict__ gates,
-                          float* __restrict__ logits_out, int T, int H, int E) {
+                          float* __restrict__ logits_out, int T, int H, int E, int vec_ok) {
   extern __shared__ float smem[];   // TT rows of x, then TT x E logits
   float* xs = smem;
   float* s_all = smem + (size_t)TT * H;
@@ -38,15 +56,28 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
     xs[i] = tt < nt ? x[(size_t)t0 * H + i] : 0.f;
   }
   __syncthreads();
+  constexpr int VN = Vec<TW>::N;
   for (int e = warp; e < E; e += ROUTER_WARPS) {
     const TW* w = wr + (size_t)e * H;
     float a[TT];
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) a[tt] = 0.f;
-    for (int d = lane; d < H; d += 32) {
-      const float wv = to_f32(w[d]);
+    if (vec_ok) {
+#pragma unroll 4
+      for (int d = lane * VN; d < H; d += 32 * VN) {
+        float wv[VN];
+        load_vec(w + d, wv);
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) a[tt] = fmaf(xs[tt * H + d], wv, a[tt]);
+        for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+          for (int i = 0; i < VN; ++i) a[tt] = fmaf(xs[tt * H + d + i], wv[i], a[tt]);
+      }
+    } else {
+      for (int d = lane; d < H; d += 32) {
+        const float wv = to_f32(w[d]);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) a[tt] = fmaf(xs[tt * H + d], wv, a[tt]);
+      }
     }
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
@@ -136,6 +167,8 @@ extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dt
   const size_t smem = ((size_t)TT * H + (size_t)TT * E) * sizeof(float);
   if (smem > 200 * 1024) return fail("router: width %d is too large for the staging buffer", H);
   const int blocks = (T + TT - 1) / TT;
+  // 16-byte loads of the router rows need rows that start on 16 bytes
+  const int vec_ok = (H % 8 == 0) && (((uintptr_t)wr & 15) == 0);
   static bool configured[2] = {false, false};
   if (smem > 48 * 1024 && !configured[w_dtype ? 1 : 0]) {
     cudaError_t e = w_dtype == FLINT_F32
@@ -146,7 +179,7 @@ extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dt
   }
   FLINT_DISPATCH_DTYPE(w_dtype, TW,
       (router_sparsemixer_kernel<TW><<<blocks, ROUTER_WARPS * 32, smem, stream>>>(
-          x, (const TW*)wr, eps, expert_ids, gates, logits_out, T, H, E)));
+          x, (const TW*)wr, eps, expert_ids, gates, logits_out, T, H, E, vec_ok)));
   return check_launch("router_sparsemixer");
 }
 
