@@ -281,6 +281,15 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
     for (int e = 0; e < 8; ++e) acc[g][e] = 0.f;
   }
 
+  // score phase: 16 lanes share one key row; each lane keeps its 8 query dims of every head in registers
+  float* ss = ps;                        // raw scores of the chunk share the probabilities' place
+  const int khalf = lane >> 4, kq = lane & 15;
+  float qreg[GC][8];
+#pragma unroll
+  for (int g = 0; g < GC; ++g)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) qreg[g][e] = (g < ng && kq * 8 < hd) ? qs[g * hd + kq * 8 + e] : 0.f;
+
   for (int j0 = lo; j0 < hi; j0 += BT) {
     const int j = j0 + tid;
     long long row = -1;
@@ -289,22 +298,64 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
       if (page >= 0) row = ((long long)page * nkv + kvh) * page_size + (j % page_size);
     }
     rows[tid] = row;
-    float s[GC];
+    __syncthreads();
+    // a warp reads two whole key rows per instruction (16 lanes x 16 bytes each), four such loads in
+    // flight; every lane gets partial dot products over its 8 dims and a butterfly over the 16 lanes
+    // leaves the sum of head 2*bit3+bit2 in each lane.  Rows wider than 128 dims take more passes.
+    constexpr int UK = 4;
+#pragma unroll 1
+    for (int k0 = warp * 2 + khalf; k0 < BT; k0 += 8 * UK) {
+      float kf[UK][8];
+      long long rr[UK];
 #pragma unroll
-    for (int g = 0; g < GC; ++g) s[g] = 0.f;
-    if (row >= 0) {
-      const TC* kr = k_cache + row * hd;
-      for (int d = 0; d < hd; d += 8) {
-        float kf[8];
-        load8<TC>(kr + d, kf);
+      for (int u = 0; u < UK; ++u) {
+        rr[u] = rows[k0 + 8 * u];
+        if (rr[u] >= 0 && kq * 8 < hd) {
+          load8<TC>(k_cache + rr[u] * hd + kq * 8, kf[u]);
+        } else {
 #pragma unroll
-        for (int g = 0; g < GC; ++g)
-          if (g < ng) {
+          for (int e = 0; e < 8; ++e) kf[u][e] = 0.f;
+        }
+      }
 #pragma unroll
-            for (int e = 0; e < 8; ++e) s[g] = fmaf(qs[g * hd + d + e], kf[e], s[g]);
+      for (int u = 0; u < UK; ++u) {
+        float s[GC];
+#pragma unroll
+        for (int g = 0; g < GC; ++g) {
+          s[g] = 0.f;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) s[g] = fmaf(qreg[g][e], kf[u][e], s[g]);
+        }
+        if (hd > 128 && rr[u] >= 0) {
+          for (int d = kq * 8 + 128; d < hd; d += 128) {
+            float k2[8];
+            load8<TC>(k_cache + rr[u] * hd + d, k2);
+#pragma unroll
+            for (int g = 0; g < GC; ++g)
+              if (g < ng) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) s[g] = fmaf(qs[g * hd + d + e], k2[e], s[g]);
+              }
           }
+        }
+        const bool b3 = lane & 8, b2 = lane & 4;
+        float a0 = b3 ? s[2] : s[0], a1 = b3 ? s[3] : s[1];
+        const float x0 = b3 ? s[0] : s[2], x1 = b3 ? s[1] : s[3];
+        a0 += __shfl_xor_sync(0xffffffffu, x0, 8);
+        a1 += __shfl_xor_sync(0xffffffffu, x1, 8);
+        float c = b2 ? a1 : a0;
+        const float x2 = b2 ? a0 : a1;
+        c += __shfl_xor_sync(0xffffffffu, x2, 4);
+        c += __shfl_xor_sync(0xffffffffu, c, 2);
+        c += __shfl_xor_sync(0xffffffffu, c, 1);
+        if ((lane & 3) == 0) ss[((b3 ? 2 : 0) + (b2 ? 1 : 0)) * BT + k0 + 8 * u] = c;
       }
     }
+    __syncthreads();
+    float s[GC];
+#pragma unroll
+    for (int g = 0; g < GC; ++g) s[g] = ss[g * BT + tid];
+    __syncthreads();      // ss is overwritten by the probabilities below
     // block maximum per head
 #pragma unroll
     for (int g = 0; g < GC; ++g) {
@@ -341,16 +392,30 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
     // one 16-byte load per key, partial sums over key lanes are added up at the end
     const int nk = min(BT, hi - j0);
     if (kl < lanes) {
-      for (int jj = kl; jj < nk; jj += lanes) {
-        const long long r = rows[jj];
-        if (r < 0) continue;
-        float vv[8];
-        load8<TC>(v_cache + r * hd + dg * 8, vv);
+      constexpr int U = 4;      // rows in flight per thread
+#pragma unroll 1
+      for (int j1 = kl; j1 < nk; j1 += lanes * U) {
+        float vv[U][8];
 #pragma unroll
-        for (int g = 0; g < GC; ++g) {
-          const float pj = ps[g * BT + jj];
+        for (int u = 0; u < U; ++u) {
+          const int jj = j1 + u * lanes;
+          const long long r = jj < nk ? rows[jj] : -1;
+          if (r >= 0) {
+            load8<TC>(v_cache + r * hd + dg * 8, vv[u]);
+          } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vv[e], acc[g][e]);
+            for (int e = 0; e < 8; ++e) vv[u][e] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int jj = min(j1 + u * lanes, BT - 1);     // beyond nk the values are zero
+#pragma unroll
+          for (int g = 0; g < GC; ++g) {
+            const float pj = ps[g * BT + jj];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(pj, vv[u][e], acc[g][e]);
+          }
         }
       }
     }

@@ -27,7 +27,7 @@ from pathlib import Path
 from ..errors import KernelError
 
 SRC_DIR = Path(__file__).resolve().parent
-MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention", "attention_tc", "moe", "sampling", "noalloc")
+MODULES = ("elementwise", "row_fused", "gemm_simt", "gemm_tc", "attention", "attention_tc", "moe", "sampling", "noalloc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
 _LOCK = threading.Lock()

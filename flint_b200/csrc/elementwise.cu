@@ -80,7 +80,8 @@ extern "C" int flint_norm(const float* x, const int* row_index, const float* gam
 }
 
 // --------------------------------------------------------------------------- rope + kv write
-// qkv [T, (nq+2*nkv)*hd] float32: q heads, then k heads, then v heads.
+// qkv [n_partials][T, (nq+2*nkv)*hd] float32: q heads, then k heads, then v heads; the partials
+// (pieces of a split K range, partial_stride floats apart) and the bias are added on the way in.
 // q and k are rotated (NeoX half-split over the first `rot` dims of each head) by the row of
 // the cos/sin tables that belongs to the token's position; q goes to q_out, k and v go to
 // the token's place in the paged cache: page = block_table[slot, pos / P], row pos % P.
@@ -90,12 +91,21 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
                                const float* __restrict__ sin_t, int rot, TQ* __restrict__ q_out,
                                TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                const int* __restrict__ block_table, int max_pages, int page_size,
-                               int nq, int nkv, int hd, int write_kv, int* __restrict__ status) {
+                               int nq, int nkv, int hd, int write_kv, int* __restrict__ status,
+                               int n_partials, long long partial_stride, const float* __restrict__ bias) {
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0..nq-1 q, nq..nq+nkv-1 k, then v
   const int p = pos[t];
   const int half = rot >> 1;
-  const float* src = qkv + ((size_t)t * (nq + 2 * nkv) + head) * hd;
+  const size_t src_off = ((size_t)t * (nq + 2 * nkv) + head) * hd;
+  const float* bias_h = bias ? bias + (size_t)head * hd : nullptr;
+  // the projection may arrive as partial sums over pieces of its K range, and without its bias:
+  // they are added here in a fixed order
+  auto rd = [&](int d) {
+    float v = qkv[src_off + d];
+    for (int z = 1; z < n_partials; ++z) v += qkv[(size_t)z * partial_stride + src_off + d];
+    return bias_h ? v + bias_h[d] : v;
+  };
   const bool is_q = head < nq;
   const bool is_v = head >= nq + nkv;
   if (!is_q && !write_kv) return;
@@ -112,11 +122,11 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float y;
     if (is_v || d >= rot) {
-      y = src[d];
+      y = rd(d);
     } else {
       const int i = d < half ? d : d - half;
       const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
-      y = d < half ? src[d] * c - src[d + half] * s : src[d] * c + src[d - half] * s;
+      y = d < half ? rd(d) * c - rd(d + half) * s : rd(d) * c + rd(d - half) * s;
     }
     if (is_q) q_out[((size_t)t * nq + head) * hd + d] = from_f32<TQ>(y);
     else if (is_v) v_cache[cache_row + d] = from_f32<TC>(y);
@@ -129,8 +139,10 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
                                    int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                    const int* block_table, int max_pages, int page_size, int T,
                                    int nq, int nkv, int hd, int write_kv, int* status,
+                                   int n_partials, long long partial_stride, const float* bias,
                                    cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (n_partials < 1) return fail("rope: needs at least one partial");
   if (rot < 0 || rot > hd || (rot & 1)) return fail("rope: rotary size %d does not fit head size %d", rot, hd);
   if (page_size <= 0) return fail("rope: bad page size %d", page_size);
   dim3 grid(T, nq + 2 * nkv);
@@ -138,7 +150,7 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
       (rope_kv_kernel<TQ, TC><<<grid, threads, 0, stream>>>(
           qkv, pos, slot, cos_t, sin_t, rot, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,
-          max_pages, page_size, nq, nkv, hd, write_kv, status))));
+          max_pages, page_size, nq, nkv, hd, write_kv, status, n_partials, partial_stride, bias))));
   return check_launch("rope_kv_write");
 }
 
@@ -181,6 +193,25 @@ extern "C" int flint_moe_combine(float* h, const float* y, const int* row_of, co
   if (T <= 0) return 0;
   moe_combine_kernel<<<T, 256, 0, stream>>>(h, y, row_of, gates, H);
   return check_launch("moe_combine");
+}
+
+// x[r, c] += sum_z partials[z][r, c] (+ bias[c]): the fallback for widths the fused row kernel refuses.
+__global__ void add_partials_kernel(float* __restrict__ x, const float* __restrict__ partials, int n_partials,
+                                    long long stride, const float* __restrict__ bias, long long n, int H) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = x[i];
+  for (int z = 0; z < n_partials; ++z) v += partials[(size_t)z * stride + i];
+  if (bias) v += bias[i % H];
+  x[i] = v;
+}
+
+extern "C" int flint_add_partials(float* x, const float* partials, int n_partials, long long stride,
+                                  const float* bias, int rows, int H, cudaStream_t stream) {
+  const long long n = (long long)rows * H;
+  if (n <= 0) return 0;
+  add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(x, partials, n_partials, stride, bias, n, H);
+  return check_launch("add_partials");
 }
 
 extern "C" const char* flint_elementwise_last_error() { return g_error; }

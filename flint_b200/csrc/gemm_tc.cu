@@ -57,6 +57,7 @@ struct Params {
   int out_dtype, ldo, accumulate, act;
   int rows, N, K;
   int kb_per_split, splits, stages;
+  int defer;                   // write raw partial tiles even for a single split; the consumer sums them
 };
 
 // Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = bn.
@@ -158,7 +159,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const int q = warp & 3;                       // this warp's quarter of the 128 lanes
       const int f = f0 + q * 32 + lane;             // output feature of this thread
       const bool f_ok = f < p.N;
-      const float bias = (p.bias && f_ok && p.splits == 1) ? p.bias[f] : 0.f;
+      const bool raw = p.splits > 1 || p.defer;       // partial tile: no bias, no accumulate
+      const float bias = (p.bias && f_ok && !raw) ? p.bias[f] : 0.f;
       const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 8) {
@@ -172,7 +174,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (r >= row_end || !f_ok) continue;
           float y = v[c];
           if (GATED) y = act_fn(y, p.act) * u[c];
-          if (p.splits > 1) {
+          if (raw) {
             p.partial[((size_t)blockIdx.z * p.rows + r) * p.N + f] = y;
             continue;
           }
@@ -298,12 +300,15 @@ extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
 // x [rows, K] bf16 with row stride ldx; w / w_up [E, N, K] bf16 (E = 1 when dense); out [rows, N].
 // bn: token rows per tile (16, 32, 64, 128 or 256); with a tile map it must equal the plan's tile size.
 // splits > 1 divides the K blocks over several CTAs and needs `partial` (not with a gated product).
+// defer: leave the raw partial sums [splits, rows, N] in `partial` (no bias, nothing added to out);
+// the caller's next kernel adds them up.  The number of splits used is ceil(kb / ceil(kb / splits))
+// with kb = ceil(K / 64).
 // error_flag: device int, set to 1 if a bounded wait ran out.
 extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* w_up, const float* bias, void* out,
                              int out_dtype, int ldo, int accumulate, int act, const int* tile_expert,
                              const int* tile_row0, const int* n_tiles, const int* offsets, int max_tiles,
                              int n_experts, int rows, int N, int K, int bn, int splits, float* partial,
-                             int* error_flag, cudaStream_t stream) {
+                             int defer, int* error_flag, cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
@@ -311,7 +316,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
     return fail("gemm_tc: operands must be 16-byte aligned");
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("gemm_tc: bad token tile %d", bn);
   if (splits < 1) return fail("gemm_tc: bad split %d", splits);
-  if (splits > 1 && (w_up || !partial)) return fail("gemm_tc: a K split needs scratch and cannot be gated");
+  if ((splits > 1 || defer) && (w_up || !partial)) return fail("gemm_tc: partial sums need scratch and cannot be gated");
   if (!error_flag) return fail("gemm_tc: needs an error flag");
   const int total_kb = (K + BK - 1) / BK;
   if (splits > total_kb) splits = total_kb;
@@ -333,7 +338,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
   p.error_flag = error_flag;
   p.out_dtype = out_dtype; p.ldo = ldo; p.accumulate = accumulate; p.act = act;
   p.rows = rows; p.N = N; p.K = K;
-  p.kb_per_split = kbps; p.splits = splits;
+  p.kb_per_split = kbps; p.splits = splits; p.defer = defer;
   p.stages = flint_gemm_tc_stages(bn, w_up != nullptr);
   if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;
   dim3 grid((N + BM - 1) / BM, tiles_n, splits);
@@ -351,7 +356,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
     default: rc = fail("gemm_tc: bad token tile %d", bn);
   }
 #undef CASE
-  if (rc || splits == 1) return rc;
+  if (rc || splits == 1 || defer) return rc;
   const size_t n = (size_t)rows * N;
   splitk_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(partial, splits, rows, N, bias, out,
                                                                         out_dtype, ldo, accumulate);

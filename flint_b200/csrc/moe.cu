@@ -51,9 +51,15 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TT;
   const int nt = min(TT, T - t0);
-  for (int i = threadIdx.x; i < TT * H; i += blockDim.x) {
-    const int tt = i / H;
-    xs[i] = tt < nt ? x[(size_t)t0 * H + i] : 0.f;
+  if (vec_ok) {        // rows are staged with 16-byte loads, several in flight per thread
+    const int n4 = TT * H / 4, live4 = nt * H / 4;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)t0 * H);
+    float4* dst = reinterpret_cast<float4*>(xs);
+#pragma unroll 8
+    for (int i = threadIdx.x; i < n4; i += blockDim.x)
+      dst[i] = i < live4 ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  } else {
+    for (int i = threadIdx.x; i < TT * H; i += blockDim.x) xs[i] = i < nt * H ? x[(size_t)t0 * H + i] : 0.f;
   }
   __syncthreads();
   constexpr int VN = Vec<TW>::N;
@@ -68,9 +74,13 @@ router_sparsemixer_kernel(const float* __restrict__ x, const TW* __restrict__ wr
         float wv[VN];
         load_vec(w + d, wv);
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt)
+        for (int tt = 0; tt < TT; ++tt) {
+          float xv[VN];                       // 16-byte reads of the staged row: no bank conflicts
 #pragma unroll
-          for (int i = 0; i < VN; ++i) a[tt] = fmaf(xs[tt * H + d + i], wv[i], a[tt]);
+          for (int i = 0; i < VN; i += 4) load_vec(xs + tt * H + d + i, xv + i);
+#pragma unroll
+          for (int i = 0; i < VN; ++i) a[tt] = fmaf(xv[i], wv[i], a[tt]);
+        }
       }
     } else {
       for (int d = lane; d < H; d += 32) {

@@ -149,11 +149,80 @@ class CudaOps:
         self._run("elementwise", "flint_norm", _ptr(x), _ptr(row_index), _ptr(gamma), _ptr(beta), c_float(eps),
                   c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), c_int(rows), c_int(H))
 
-    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status):
-        _check(qkv, "qkv", torch.float32, 2)
-        T = qkv.shape[0]
-        if qkv.shape[1] != (nq + 2 * nkv) * hd:
+    def row_norm(self, x, gamma, beta, eps, mode, out_f32=None, out_bf16=None, row_index=None, pending=None,
+                 router=None):
+        """Norm of the residual rows with what is pending applied first (x is updated in place) and,
+        on request, the routing of every row.  Falls back to separate kernels for widths that the
+        fused kernel does not take."""
+        _check(x, "x", torch.float32, 2)
+        T, H = x.shape
+        if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 40000)):
+            if pending is not None:
+                self.apply_pending(x, pending)
+            tmp = out_f32
+            if router is not None and tmp is None:
+                tmp = torch.empty((T, H), dtype=torch.float32, device=x.device)
+            self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
+            if router is not None:
+                self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates)
+            return
+        rows = row_index.numel() if row_index is not None else T
+        for o, dt in ((out_f32, torch.float32), (out_bf16, torch.bfloat16)):
+            if o is not None:
+                _check(o, "norm output", dt, 2)
+                if tuple(o.shape) != (rows, H):
+                    raise KernelError(f"row_norm: output must be [{rows}, {H}]")
+        if gamma is not None and (gamma.dtype != torch.float32 or gamma.numel() != H):
+            raise KernelError("row_norm: scale must be float32 of the row width")
+        partials = bias = y = row_of = gts = None
+        S, stride = 0, 0
+        if pending is not None:
+            if pending.partials is not None:
+                partials = pending.partials
+                _check(partials, "pending partials", torch.float32, 3)
+                if tuple(partials.shape[1:]) != (T, H):
+                    raise KernelError("row_norm: pending partial sums do not match the residual")
+                S, stride, bias = partials.shape[0], partials.stride(0), pending.bias
+            if pending.y is not None:
+                y, row_of, gts = pending.y, pending.row_of, pending.gates
+                _check(y, "pending expert rows", torch.float32, 2)
+                if y.shape[1] != H or row_of.numel() != 2 * T or gts.numel() != 2 * T:
+                    raise KernelError("row_norm: pending expert rows do not match the residual")
+        wr = wcode = None
+        E, jit, ids, gates = 0, 0.0, None, None
+        if router is not None:
+            wr, E, jit, ids, gates = router.weight, router.weight.shape[0], router.jitter_eps, router.expert_ids, router.gates
+            _check(wr, "router weight", dims=2)
+            if wr.shape[1] != H or ids.numel() != 2 * T or gates.numel() != 2 * T:
+                raise KernelError("row_norm: router shapes do not match")
+        self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
+                  c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), _ptr(gamma), _ptr(beta),
+                  c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
+                  c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates))
+
+    def apply_pending(self, x, pending):
+        """x += what a part left pending (for a norm that cannot take it along)."""
+        _check(x, "x", torch.float32, 2)
+        T, H = x.shape
+        if H % 4 == 0 and H <= 16384:
+            return self.row_norm(x, None, None, 0.0, "layer", pending=pending)
+        if pending.partials is not None:
+            p = pending.partials
+            self._run("elementwise", "flint_add_partials", _ptr(x), _ptr(p), c_int(p.shape[0]), c_longlong(p.stride(0)),
+                      _ptr(pending.bias), c_int(T), c_int(H))
+        if pending.y is not None:
+            self.moe_combine(x, pending.y, pending.row_of, pending.gates)
+
+    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None):
+        """qkv [T, W] or [S, T, W] float32 (S partial sums that are added here, with the bias)."""
+        if qkv.dim() == 2:
+            qkv = qkv.unsqueeze(0)
+        _check(qkv, "qkv", torch.float32, 3)
+        S, T = qkv.shape[0], qkv.shape[1]
+        if qkv.shape[2] != (nq + 2 * nkv) * hd:
             raise KernelError("rope_kv_write: qkv width does not match the head counts")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != qkv.shape[2]):
+            raise KernelError("rope_kv_write: bias must be float32 of the qkv width")
         _check(q_out, "q_out", dims=2)
         _check(cos, "cos", torch.float32, 2)
         _check(sin, "sin", torch.float32, 2)
@@ -173,7 +242,7 @@ class CudaOps:
         self._run("elementwise", "flint_rope_kv_write", _ptr(qkv), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin),
                   c_int(rot), _ptr(q_out), c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(cdt), _ptr(bt),
                   c_int(max_pages), c_int(P), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write_kv else 0),
-                  _ptr(status))
+                  _ptr(status), c_int(S), c_longlong(qkv.stride(0)), _ptr(bias))
 
     def gather_rows(self, x, index, out):
         _check(x, "x", dims=2)
@@ -205,6 +274,40 @@ class CudaOps:
     def grouped_gemm(self, x, w, out, plan: MoePlan):
         """out[r] = x[r] @ w[expert of row r].T; w [E, N, K]."""
         self._gemm(x, w, None, out, None, False, "silu", plan)
+
+    def gemm_partials(self, x, w):
+        """x @ w.T left as S partial sums over pieces of the K range: float32 [S, M, N], no bias.
+        The next kernel (rotary write, row norm) adds them up; S is 1 when nothing was split."""
+        _check(x, "x", dims=2)
+        _check(w, "w", dims=2)
+        M, K = x.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError("gemm_partials: shapes do not match")
+        if not self.tensor_core_ok(x, w):
+            out = torch.empty((1, M, N), dtype=torch.float32, device=x.device)
+            self._gemm_simt(x, w, None, out[0], None, False, 0, None, M, N, K)
+            return out
+        bn = self.token_tile(M)
+        splits = self._k_splits(M, N, K, bn)
+        kb = -(-K // 64)
+        kbps = -(-kb // splits)
+        splits = -(-kb // kbps)
+        out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), _ptr(None), _ptr(None),
+                  _ptr(out), c_int(F32), c_int(N), c_int(0), c_int(0), _ptr(None), _ptr(None), _ptr(None), _ptr(None),
+                  c_int(0), c_int(1), c_int(M), c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1),
+                  _ptr(self.tc_error))
+        return out
+
+    @staticmethod
+    def _k_splits(M, N, K, bn):
+        """Pieces of the K range so that a product with few tiles still fills the device."""
+        tiles = -(-N // 128) * -(-M // bn)
+        kb = -(-K // 64)
+        if tiles >= 148 or kb < 8:
+            return 1
+        return max(1, min(-(-296 // tiles), kb // 4, 16))
 
     def _gemm(self, x, w, w_up, out, bias, accumulate, act, plan):
         _check(x, "x", dims=2, contiguous=False)
@@ -261,11 +364,7 @@ class CudaOps:
         else:
             E = 1
             bn = self.token_tile(M, gated=w_up is not None)
-            tiles = -(-N // 128) * -(-M // bn)
-            kb = -(-K // 64)
-            splits = 1
-            if w_up is None and tiles < 148 and kb >= 8:
-                splits = max(1, min(-(-296 // tiles), kb // 4, 16))
+            splits = 1 if w_up is not None else self._k_splits(M, N, K, bn)
         partial = None
         if splits > 1:
             partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
@@ -274,7 +373,7 @@ class CudaOps:
                   c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
                   c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
-                  c_int(splits), _ptr(partial), _ptr(self.tc_error))
+                  c_int(splits), _ptr(partial), c_int(0), _ptr(self.tc_error))
 
     def _gemm_simt(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None and plan.tile_rows > 64:

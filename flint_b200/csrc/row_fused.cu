@@ -1,0 +1,258 @@
+// The row kernel of the residual stream: apply what earlier kernels left pending, normalise,
+// and (optionally) route -- one block per row, the row held in registers.
+//
+//   x[row] += sum_z partials[z][row] + bias          (a product whose K range was split)
+//   x[row] += g0 * y[r0] + g1 * y[r1]                 (the two selected experts' outputs)
+//   y = LayerNorm(x[row]) or RMSNorm(x[row])          float32 statistics, two passes over registers
+//   out_f32 / out_bf16 <- y
+//   logits_e = <y, Wr[e]>, sparsemixer top-2          (float32; same selection as moe.cu)
+//
+// Fusing these saves, per layer of a decode step, the kernels that would only add to the
+// residual stream and one pass over it.  Widths that are not a multiple of 4 or exceed 16384
+// are refused; the caller then uses the separate kernels.
+// Reference counterparts: crates/thuban_kernel/wgsl/norm.wgsl (mode 3), add.wgsl, merge_gemm.wgsl.
+#include <math.h>
+#include <stdarg.h>
+#include "common.cuh"
+
+using namespace flint;
+
+namespace {
+constexpr int MAX_VPT = 4;
+constexpr int MAX_E = 256;
+
+struct RowArgs {
+  float* x;
+  const int* row_index;
+  const float* partials; int n_partials; long long partial_stride; const float* add_bias;
+  const float* comb_y; const int* comb_row_of; const float* comb_gates;
+  const float* gamma; const float* beta; float eps; int mode;
+  float* out_f32; __nv_bfloat16* out_bf16;
+  const void* wr; int E; float jitter_eps; int* expert_ids; float* gates;
+  int H;
+};
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void add4(float4& a, const float4 b) { a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w; }
+__device__ __forceinline__ void fma4(float4& a, float g, const float4 b) {
+  a.x = fmaf(g, b.x, a.x); a.y = fmaf(g, b.y, a.y); a.z = fmaf(g, b.z, a.z); a.w = fmaf(g, b.w, a.w);
+}
+
+__device__ __forceinline__ void load_w8(const float* p, float* f) {
+  const float4 a = ld4(p), b = ld4(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ void load_w8(const __nv_bfloat16* p, float* f) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <int VPT, typename TW>
+__global__ void __launch_bounds__(1024)
+row_norm_kernel(const RowArgs a) {
+  extern __shared__ float smem[];          // router only: H floats of the normalised row, then partial logits
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = a.row_index ? a.row_index[r] : r;
+  const int H = a.H, n4 = H >> 2;
+  float* xr = a.x + (size_t)src * H;
+  float4 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    v[i] = c < n4 ? ld4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  const bool pending = a.partials || a.comb_y;
+  if (a.partials) {
+    for (int z = 0; z < a.n_partials; ++z) {          // fixed order
+      const float* pr = a.partials + (size_t)z * a.partial_stride + (size_t)src * H;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) add4(v[i], ld4(pr + 4 * c));
+      }
+    }
+    if (a.add_bias) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) add4(v[i], ld4(a.add_bias + 4 * c));
+      }
+    }
+  }
+  if (a.comb_y) {
+    const int r0 = a.comb_row_of[2 * src], r1 = a.comb_row_of[2 * src + 1];
+    const float g0 = a.comb_gates[2 * src], g1 = a.comb_gates[2 * src + 1];
+    const float* y0 = a.comb_y + (size_t)r0 * H;
+    const float* y1 = a.comb_y + (size_t)r1 * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < n4) {
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);   // g0*y0 + g1*y1 first, then added: the order of moe_combine
+        fma4(t, g0, ld4(y0 + 4 * c));
+        fma4(t, g1, ld4(y1 + 4 * c));
+        add4(v[i], t);
+      }
+    }
+  }
+  if (pending) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      if (c < n4) *reinterpret_cast<float4*>(xr + 4 * c) = v[i];
+    }
+  }
+  if (!a.gamma) return;                     // only the additions were wanted
+  // statistics
+  float mean = 0.f;
+  if (a.mode == 0) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);   // zeros beyond the row
+    mean = block_sum(s, red) / (float)H;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4) {
+      const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+      ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+    }
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)H + a.eps);
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * blockDim.x;
+    if (c < n4) {
+      const float4 g = ld4(a.gamma + 4 * c);
+      float4 y = make_float4((v[i].x - mean) * inv * g.x, (v[i].y - mean) * inv * g.y,
+                             (v[i].z - mean) * inv * g.z, (v[i].w - mean) * inv * g.w);
+      if (a.beta) add4(y, ld4(a.beta + 4 * c));
+      if (a.out_f32) *reinterpret_cast<float4*>(a.out_f32 + (size_t)r * H + 4 * c) = y;
+      if (a.out_bf16) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(a.out_bf16 + (size_t)r * H + 4 * c) = pk;
+      }
+      if (a.wr) *reinterpret_cast<float4*>(smem + 4 * c) = y;
+    }
+  }
+  if (!a.wr) return;
+  // ---- router: k warps per expert, each a strided share of the row; partial sums meet in shared memory
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int E = a.E;
+  const int k = n_warps >= E ? n_warps / E : 1;          // warps per expert
+  float* part = smem + H;                                 // [E][k]
+  const TW* wr = (const TW*)a.wr;
+  const bool vec = (H & 7) == 0;
+  for (int job = warp; job < E * k; job += n_warps) {
+    const int e = job / k, sl = job % k;
+    const TW* w = wr + (size_t)e * H;
+    float acc = 0.f;
+    if (vec) {
+#pragma unroll 4
+      for (int d = (sl * 32 + lane) * 8; d < H; d += k * 256) {
+        float wv[8];
+        load_w8(w + d, wv);
+        const float4 x0 = ld4(smem + d), x1 = ld4(smem + d + 4);
+        acc = fmaf(x0.x, wv[0], acc); acc = fmaf(x0.y, wv[1], acc); acc = fmaf(x0.z, wv[2], acc); acc = fmaf(x0.w, wv[3], acc);
+        acc = fmaf(x1.x, wv[4], acc); acc = fmaf(x1.y, wv[5], acc); acc = fmaf(x1.z, wv[6], acc); acc = fmaf(x1.w, wv[7], acc);
+      }
+    } else {
+      for (int d = sl * 32 + lane; d < H; d += k * 32) acc = fmaf(smem[d], to_f32(w[d]), acc);
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) part[e * k + sl] = acc;
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  float* s = smem;                                        // the row is no longer needed
+  for (int e = 0; e < E; ++e) {
+    float t = 0.f;
+    for (int i = 0; i < k; ++i) t += part[e * k + i];    // fixed order
+    s[e] = t;
+  }
+  int excluded = -1;
+  for (int round = 0; round < 2; ++round) {
+    float m = -INFINITY;
+    int im = 0;
+    for (int e = 0; e < E; ++e)
+      if (e != excluded && s[e] > m) { m = s[e]; im = e; }
+    float denom = 0.f;
+    for (int e = 0; e < E; ++e) {
+      if (e == excluded) continue;
+      const float factor = fmaxf(fabsf(s[e]), m);
+      if (!(((m - s[e]) / factor) > 2.0f * a.jitter_eps)) denom += expf(s[e] - m);
+    }
+    a.expert_ids[2 * r + round] = im;
+    a.gates[2 * r + round] = 1.0f / denom;
+    excluded = im;
+  }
+}
+
+template <int VPT, typename TW>
+int launch_row(const RowArgs& a, int rows, int threads, size_t smem, cudaStream_t stream) {
+  row_norm_kernel<VPT, TW><<<rows, threads, smem, stream>>>(a);
+  return check_launch("row_norm");
+}
+}  // namespace
+
+// x [T, H] float32 residual stream, updated in place if anything is pending.
+// rows: number of output rows (T, or the length of row_index if given; then x rows are gathered).
+// pending: partials [n_partials][T][H] (stride partial_stride floats) + add_bias [H]; and/or
+//          comb_y [2T, H] with comb_row_of [T, 2] and comb_gates [T, 2].
+// gamma NULL: only apply the pending additions.  wr != NULL (router weights [E, H], bf16 or f32):
+// also fill expert_ids [rows, 2] and gates [rows, 2]; then row_index must be NULL.
+extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, const float* partials,
+                              int n_partials, long long partial_stride, const float* add_bias,
+                              const float* comb_y, const int* comb_row_of, const float* comb_gates,
+                              const float* gamma, const float* beta, float eps, int mode, float* out_f32,
+                              void* out_bf16, const void* wr, int w_dtype, int E, float jitter_eps,
+                              int* expert_ids, float* gates, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || (H & 3) || H > 4 * 1024 * MAX_VPT) return fail("row_norm: width %d (multiples of 4 up to %d)", H, 4096 * MAX_VPT);
+  if (gamma && !out_f32 && !out_bf16 && !wr) return fail("row_norm: no output given");
+  if (mode != 0 && mode != 1) return fail("row_norm: unknown mode %d", mode);
+  if (wr && (E < 2 || E > MAX_E)) return fail("row_norm: %d experts (2..%d)", E, MAX_E);
+  if (wr && (row_index || !gamma || !expert_ids || !gates)) return fail("row_norm: the router needs a norm and all rows");
+  if (wr && (((uintptr_t)wr & 15) != 0)) return fail("row_norm: router weights must be 16-byte aligned");
+  RowArgs a;
+  a.x = x; a.row_index = row_index;
+  a.partials = partials; a.n_partials = n_partials; a.partial_stride = partial_stride; a.add_bias = add_bias;
+  a.comb_y = comb_y; a.comb_row_of = comb_row_of; a.comb_gates = comb_gates;
+  a.gamma = gamma; a.beta = beta; a.eps = eps; a.mode = mode;
+  a.out_f32 = out_f32; a.out_bf16 = (__nv_bfloat16*)out_bf16;
+  a.wr = wr; a.E = E; a.jitter_eps = jitter_eps; a.expert_ids = expert_ids; a.gates = gates;
+  a.H = H;
+  const int n4 = H / 4;
+  int threads = ((n4 + 31) / 32) * 32;
+  if (threads > 1024) threads = 1024;
+  if (wr && threads < 128) threads = 128;               // a few warps for the router's dot products
+  const int vpt = (n4 + threads - 1) / threads;
+  const int n_warps = threads / 32;
+  const int k = wr ? (n_warps >= E ? n_warps / E : 1) : 0;
+  const size_t smem = wr ? (size_t)(H + E * k) * sizeof(float) : 0;
+#define GO(V)                                                                                             \
+  (wr && w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16>(a, rows, threads, smem, stream)             \
+                               : launch_row<V, float>(a, rows, threads, smem, stream))
+  if (smem > 48 * 1024) return fail("row_norm: width %d is too large for the fused router", H);
+  switch (vpt) {
+    case 1: return GO(1);
+    case 2: return GO(2);
+    case 3: case 4: return GO(4);
+    default: return fail("row_norm: width %d is too large", H);
+  }
+#undef GO
+}
+
+extern "C" const char* flint_row_fused_last_error() { return g_error; }

@@ -21,6 +21,7 @@ from ..cache.manager import CacheManager
 from ..config.spec import ModelSpec
 from ..errors import ConfigError, ModelError
 from ..parts.base import BuildContext, matmul_dtype
+from ..parts.block import run_norm
 from ..registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
 from ..weights.loader import load_tensors
 from ..weights.sources import SafetensorsSource, WeightSpec
@@ -227,17 +228,18 @@ class Model:
         T = step.n_tokens
         h = torch.empty((T, spec.hidden_size), dtype=torch.float32, device=self.device)
         ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
+        carry = None     # an addition to h that a layer left for the next norm to apply
         for i, call in enumerate(self.order):
             layer = self.layers[call.layer]
             owner = i if call.cache_of is None else call.cache_of
-            layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),
-                                writes_cache=call.cache_of is None)
+            carry = layer.block.forward(h, step, self.cache.view(owner), self.cache.state_of(i),
+                                        writes_cache=call.cache_of is None, carry=carry)
         R = step.n_want
         logits = torch.empty((R, spec.vocab_size), dtype=torch.float32, device=self.device)
         if R:
             wdt = self.head_weight.dtype
-            x = self.final_norm.forward(h, (wdt,), row_index=step.want_rows)[wdt]
-            ops.gemm(x, self.head_weight, logits, bias=self.head_bias)
+            x, _ = run_norm(self.final_norm, h, (wdt,), carry, row_index=step.want_rows)
+            ops.gemm(x[wdt], self.head_weight, logits, bias=self.head_bias)
         return logits
 
     def check_status(self):

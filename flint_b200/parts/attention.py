@@ -16,7 +16,7 @@ import torch
 from ..cache.manager import KVSpec
 from ..errors import ConfigError, ModelError
 from ..registry import MIXERS, POSITION_ENCODINGS
-from .base import Mixer, mat, matmul_dtype, vec
+from .base import Mixer, Pending, mat, matmul_dtype, vec
 
 
 def shared_position_encoding(spec, ctx):
@@ -86,17 +86,20 @@ class Attention(Mixer):
         ops, nq, nkv, hd = self.ops, self.nq, self.nkv, self.hd
         xin = x[self.w_qkv.dtype]
         T = xin.shape[0]
-        width = (nq + 2 * nkv) * hd
-        qkv = torch.empty((T, width), dtype=torch.float32, device=xin.device)
-        if writes_cache:
-            ops.gemm(xin, self.w_qkv, qkv, bias=self.b_qkv)
-        else:   # reads another call's cache: only the queries are needed
-            nqd = nq * hd
-            ops.gemm(xin, self.w_qkv[:nqd], qkv[:, :nqd], bias=self.b_qkv[:nqd] if self.b_qkv is not None else None)
         act = self.ctx.act_dtype
         q = torch.empty((T, nq * hd), dtype=act, device=xin.device)
-        ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
-                          writes_cache, step.status)
+        if writes_cache:
+            # the projection is left as partial sums over pieces of K; the rotary kernel adds them and the bias
+            qkv = ops.gemm_partials(xin, self.w_qkv)
+            ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
+                              True, step.status, bias=self.b_qkv)
+        else:   # reads another call's cache: only the queries are needed
+            width, nqd = (nq + 2 * nkv) * hd, nq * hd
+            qkv = torch.empty((1, T, width), dtype=torch.float32, device=xin.device)
+            ops.gemm(xin, self.w_qkv[:nqd], qkv[0, :, :nqd], bias=self.b_qkv[:nqd] if self.b_qkv is not None else None)
+            ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
+                              False, step.status)
         attn = torch.empty_like(q)
         ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale)
-        ops.gemm(attn, self.w_o, residual, bias=self.b_o, accumulate=True)
+        # the output projection is handed to the next norm as partial sums (and its bias)
+        return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)

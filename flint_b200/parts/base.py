@@ -8,13 +8,18 @@ crates/thuban_model/src/ops/*.rs).
 
 Interfaces
 ----------
-Norm          ``forward(x, want, row_index=None) -> {dtype: tensor}``
+Norm          ``forward(x, want, row_index=None, pending=None, router=None) -> {dtype: tensor}``
               x is the float32 residual stream [T, H]; ``want`` is the set of element
-              types the next part asked for.
+              types the next part asked for.  A norm with ``supports_pending`` applies a
+              ``Pending`` addition to x first; one with ``supports_router`` can fill a
+              ``RouterRequest``.  Both are optional abilities; the block works without them.
 Mixer         ``input_dtypes()``, ``cache_spec()``, ``state_spec()``,
               ``forward(x, residual, step, cache, state, writes_cache=True)``:
-              adds its output into ``residual`` (float32 [T, H]) in place.
-FeedForward   ``input_dtypes()``, ``forward(x, residual, step)``: adds into ``residual``.
+              adds its output into ``residual`` (float32 [T, H]) in place and returns None,
+              or returns a ``Pending`` that the block hands to the next norm.
+FeedForward   ``input_dtypes()``, ``forward(x, residual, step)``: adds into ``residual`` or
+              returns a ``Pending``.  A feed-forward with ``router_request(n_rows)`` gets the
+              filled request back as ``forward(..., routed=request)``.
 PositionEncoding  ``rotary_dim``, ``tables() -> (cos, sin)`` float32 [positions, rotary_dim/2].
 Block         ``forward(residual, step, cache, state, writes_cache)``: the arrangement of
               the parts of one layer.
@@ -26,6 +31,31 @@ from dataclasses import dataclass, field
 import torch
 
 from ..weights.sources import WeightSpec
+
+
+@dataclass
+class Pending:
+    """An addition to the residual stream that its producer has not applied: the next norm's
+    kernel applies it while it reads the row anyway (or ``ops.apply_pending`` does, for a norm
+    that cannot).  Either partial sums of a product whose K range was split
+    (``partials`` [S, T, H] float32, plus an optional ``bias`` [H]), or the two selected experts'
+    outputs (``y`` [2T, H] with ``row_of`` [T, 2] and ``gates`` [T, 2]), or both."""
+    partials: torch.Tensor | None = None
+    bias: torch.Tensor | None = None
+    y: torch.Tensor | None = None
+    row_of: torch.Tensor | None = None
+    gates: torch.Tensor | None = None
+
+
+@dataclass
+class RouterRequest:
+    """What a feed-forward asks a norm to compute while the normalised row is at hand: router
+    logits over ``weight`` [E, H], sparsemixer top-2 with ``jitter_eps``, into ``expert_ids`` and
+    ``gates`` ([T, 2] each)."""
+    weight: torch.Tensor
+    jitter_eps: float
+    expert_ids: torch.Tensor
+    gates: torch.Tensor
 
 
 @dataclass
@@ -83,7 +113,10 @@ class FeedForward(Part):
 
 
 class Norm(Part):
-    def forward(self, x, want, row_index=None):
+    supports_pending = False
+    supports_router = False
+
+    def forward(self, x, want, row_index=None, pending=None, router=None):
         raise NotImplementedError
 
 

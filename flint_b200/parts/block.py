@@ -10,13 +10,39 @@ from __future__ import annotations
 from ..registry import BLOCKS
 
 
+def run_norm(norm, residual, want, pending=None, router=None, row_index=None):
+    """Run a norm; a pending addition or a routing request that the norm cannot take is served
+    by separate kernels instead.  Returns (outputs, router or None if it still has to be done)."""
+    if pending is not None and not norm.supports_pending:
+        norm.ops.apply_pending(residual, pending)
+        pending = None
+    if router is not None and not norm.supports_router:
+        router = None
+    kw = {}
+    if pending is not None:
+        kw["pending"] = pending
+    if router is not None:
+        kw["router"] = router
+    if row_index is not None:
+        kw["row_index"] = row_index
+    return norm.forward(residual, want, **kw), router
+
+
+def settle(part, residual, pending):
+    """Apply a pending addition right away (for arrangements that cannot carry it)."""
+    if pending is not None:
+        part.ops.apply_pending(residual, pending)
+
+
 class Block:
     roles = ()
 
     def __init__(self, parts: dict):
         self.parts = parts
 
-    def forward(self, residual, step, cache, state, writes_cache=True):
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
+        """Runs the layer on ``residual`` in place.  ``carry``: a Pending addition left by the
+        previous layer; returns the Pending addition this layer leaves (or None)."""
         raise NotImplementedError
 
 
@@ -24,21 +50,25 @@ class Block:
 class PreNormBlock(Block):
     roles = ("norm1", "mixer", "norm2", "ffn")
 
-    def forward(self, residual, step, cache, state, writes_cache=True):
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
         p = self.parts
-        x = p["norm1"].forward(residual, p["mixer"].input_dtypes())
-        p["mixer"].forward(x, residual, step, cache, state, writes_cache)
-        x = p["norm2"].forward(residual, p["ffn"].input_dtypes())
-        p["ffn"].forward(x, residual, step)
+        mixer, ffn = p["mixer"], p["ffn"]
+        x, _ = run_norm(p["norm1"], residual, mixer.input_dtypes(), carry)
+        pend = mixer.forward(x, residual, step, cache, state, writes_cache)
+        request = ffn.router_request(residual.shape[0]) if hasattr(ffn, "router_request") else None
+        want = ffn.input_dtypes_when_routed() if request is not None and p["norm2"].supports_router \
+            else ffn.input_dtypes()
+        x, routed = run_norm(p["norm2"], residual, want, pend, request)
+        return ffn.forward(x, residual, step, routed=routed) if routed is not None else ffn.forward(x, residual, step)
 
 
 @BLOCKS.register("parallel")
 class ParallelBlock(Block):
     roles = ("norm1", "mixer", "ffn")
 
-    def forward(self, residual, step, cache, state, writes_cache=True):
+    def forward(self, residual, step, cache, state, writes_cache=True, carry=None):
         p = self.parts
         want = tuple(set(p["mixer"].input_dtypes()) | set(p["ffn"].input_dtypes()))
-        x = p["norm1"].forward(residual, want)
-        p["mixer"].forward(x, residual, step, cache, state, writes_cache)
-        p["ffn"].forward(x, residual, step)
+        x, _ = run_norm(p["norm1"], residual, want, carry)
+        settle(p["mixer"], residual, p["mixer"].forward(x, residual, step, cache, state, writes_cache))
+        return p["ffn"].forward(x, residual, step)

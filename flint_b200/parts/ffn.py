@@ -12,7 +12,7 @@ import torch
 
 from ..errors import ConfigError
 from ..registry import FEED_FORWARDS
-from .base import FeedForward, mat, matmul_dtype
+from .base import FeedForward, Pending, RouterRequest, mat, matmul_dtype
 
 
 @FEED_FORWARDS.register("gated_mlp")
@@ -78,14 +78,26 @@ class SparseMixerMoE(FeedForward):
     def input_dtypes(self):
         return (torch.float32, self.w1.dtype)
 
-    def forward(self, x, residual, step):
+    def router_request(self, n_rows):
+        """Routing can ride on the norm before this part (the normalised row is in registers there)."""
+        dev = self.w_router.device
+        return RouterRequest(self.w_router, self.eps, torch.empty((n_rows, 2), dtype=torch.int32, device=dev),
+                             torch.empty((n_rows, 2), dtype=torch.float32, device=dev))
+
+    def input_dtypes_when_routed(self):
+        return (self.w1.dtype,)
+
+    def forward(self, x, residual, step, routed=None):
         ops = self.ops
-        x32, xa = x[torch.float32], x[self.w1.dtype]
-        T = x32.shape[0]
-        dev = x32.device
-        ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
-        gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
-        ops.router_sparsemixer(x32, self.w_router, self.eps, ids, gates)
+        xa = x[self.w1.dtype]
+        T = xa.shape[0]
+        dev = xa.device
+        if routed is not None:
+            ids, gates = routed.expert_ids, routed.gates
+        else:
+            ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
+            gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
+            ops.router_sparsemixer(x[torch.float32], self.w_router, self.eps, ids, gates)
         plan = ops.moe_plan(ids, self.E, ops.moe_tile_rows(T, self.E, self.w1.dtype))
         xs = torch.empty((2 * T, self.hidden), dtype=xa.dtype, device=dev)
         ops.gather_rows(xa, plan.token_of, xs)
@@ -93,7 +105,8 @@ class SparseMixerMoE(FeedForward):
         ops.gated_gemm(xs, self.w1, self.w3, a, self.act, plan)
         y = torch.empty((2 * T, self.hidden), dtype=torch.float32, device=dev)
         ops.grouped_gemm(a, self.w2, y, plan)
-        ops.moe_combine(residual, y, plan.row_of, gates)
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
             step.record.setdefault("gates", []).append(gates)
+        # the gated sum of the two experts' rows is added by the next norm's kernel
+        return Pending(y=y, row_of=plan.row_of, gates=gates)

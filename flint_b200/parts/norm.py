@@ -34,13 +34,16 @@ class _RowNorm(Norm):
         self.gamma = tensors["weight"]
         self.beta = tensors.get("bias")
 
-    def forward(self, x, want, row_index=None):
+    supports_pending = True
+    supports_router = True
+
+    def forward(self, x, want, row_index=None, pending=None, router=None):
         rows = row_index.numel() if row_index is not None else x.shape[0]
         out = {}
         for dt in set(want):
             out[dt] = torch.empty((rows, self.width), dtype=dt, device=x.device)
-        self.ops.norm(x, self.gamma, self.beta, self.eps, self.mode,
-                      out_f32=out.get(torch.float32), out_bf16=out.get(torch.bfloat16), row_index=row_index)
+        self.ops.row_norm(x, self.gamma, self.beta, self.eps, self.mode, out_f32=out.get(torch.float32),
+                          out_bf16=out.get(torch.bfloat16), row_index=row_index, pending=pending, router=router)
         return out
 
 

@@ -47,7 +47,38 @@ class RefOps:
         if out_bf16 is not None:
             out_bf16.copy_(y.to(torch.float32).to(torch.bfloat16))
 
-    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status):
+    def row_norm(self, x, gamma, beta, eps, mode, out_f32=None, out_bf16=None, row_index=None, pending=None,
+                 router=None):
+        if pending is not None:
+            self.apply_pending(x, pending)
+        if gamma is None:
+            return
+        tmp = out_f32
+        if router is not None and tmp is None:
+            tmp = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32)
+        self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
+        if router is not None:
+            self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates)
+
+    def apply_pending(self, x, pending):
+        if pending.partials is not None:
+            add = pending.partials.to(self.cd).sum(0)
+            if pending.bias is not None:
+                add = add + pending.bias.to(self.cd)
+            x.add_(add.to(x.dtype))
+        if pending.y is not None:
+            self.moe_combine(x, pending.y, pending.row_of, pending.gates)
+
+    def gemm_partials(self, x, w):
+        out = torch.empty((1, x.shape[0], w.shape[0]), dtype=torch.float32)
+        self.gemm(x, w, out[0])
+        return out
+
+    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None):
+        if qkv.dim() == 3:
+            qkv = qkv.to(self.cd).sum(0)
+        if bias is not None:
+            qkv = qkv.to(self.cd) + bias.to(self.cd)
         T = qkv.shape[0]
         x = qkv.to(self.cd).view(T, nq + 2 * nkv, hd)
         half = rot // 2

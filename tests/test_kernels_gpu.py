@@ -64,6 +64,88 @@ def test_norm(ops, ref, mode, bias, T, H):
     close(o, e32[idx.long()], 1e-5, 1e-5)
 
 
+@pytest.mark.parametrize("T,H,E,wd", [(1, 4096, 16, torch.bfloat16), (9, 96, 6, torch.float32), (33, 64, 4, torch.bfloat16),
+                                      (5, 1000, 7, torch.float32), (3, 8192, 16, torch.bfloat16), (2, 2052, 3, torch.float32)])
+@pytest.mark.parametrize("mode", ["layer", "rms"])
+def test_row_norm_with_pending_additions_and_router(ops, ref, T, H, E, wd, mode):
+    """The fused row kernel beside the separate references: split-K partial sums + bias, the gated sum
+    of two expert rows, the norm, and the routing of the normalised row."""
+    from flint_b200.parts.base import Pending, RouterRequest
+    x0 = rnd(T, H, scale=2.0) + 0.5
+    gamma, beta = 1 + rnd(H, seed=1) * 0.1, (rnd(H, seed=2) * 0.1 if mode == "layer" else None)
+    partials, bias = rnd(3, T, H, seed=3), rnd(H, seed=4)
+    y = rnd(2 * T, H, seed=5)
+    row_of = torch.randperm(2 * T, generator=torch.Generator().manual_seed(6)).to(torch.int32).view(T, 2)
+    gts = torch.rand(T, 2)
+    wr = rnd(E, H, dtype=wd, seed=7, scale=0.05)
+    dev = lambda t: t.to(DEV) if t is not None else None
+    for use_partials, use_comb, use_router in ((True, False, False), (False, True, True), (True, True, True), (False, False, True)):
+        pend_d = Pending(partials=dev(partials) if use_partials else None, bias=dev(bias) if use_partials else None,
+                         y=dev(y) if use_comb else None, row_of=dev(row_of) if use_comb else None,
+                         gates=dev(gts) if use_comb else None) if (use_partials or use_comb) else None
+        pend_r = Pending(partials=partials if use_partials else None, bias=bias if use_partials else None,
+                         y=y if use_comb else None, row_of=row_of if use_comb else None,
+                         gates=gts if use_comb else None) if (use_partials or use_comb) else None
+        xd, xr = x0.clone().to(DEV), x0.clone().double()
+        o32, o16 = torch.empty(T, H, device=DEV), torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+        req = RouterRequest(dev(wr), 0.05, torch.empty(T, 2, dtype=torch.int32, device=DEV),
+                            torch.empty(T, 2, device=DEV)) if use_router else None
+        ops.row_norm(xd, dev(gamma), dev(beta), 1e-5, mode, out_f32=o32, out_bf16=o16, pending=pend_d, router=req)
+        e32 = torch.empty(T, H, dtype=torch.float64)
+        rreq = RouterRequest(wr, 0.05, torch.empty(T, 2, dtype=torch.int32), torch.empty(T, 2, dtype=torch.float64)) \
+            if use_router else None
+        RefOps(torch.float64).row_norm(xr, gamma, beta, 1e-5, mode, out_f32=None, pending=pend_r)
+        RefOps(torch.float64).norm(xr, gamma, beta, 1e-5, mode, out_f32=e32)
+        close(xd, xr, 1e-6, 1e-5)                       # the residual stream was updated in place
+        close(o32, e32, 1e-5, 1e-5)
+        close(o16, e32, 1e-2, 1e-2)
+        if use_router:
+            RefOps(torch.float64).router_sparsemixer(e32, wr, 0.05, rreq.expert_ids, rreq.gates)
+            assert torch.equal(req.expert_ids.cpu(), rreq.expert_ids)
+            close(req.gates, rreq.gates, 1e-4, 1e-5)
+    # gathered rows with a pending sum, and the additions alone
+    idx = torch.tensor([T - 1, 0], dtype=torch.int32)
+    xd, xr = x0.clone().to(DEV), x0.clone().double()
+    o = torch.empty(2, H, device=DEV)
+    ops.row_norm(xd, dev(gamma), dev(beta), 1e-5, mode, out_f32=o, row_index=idx.to(DEV),
+                 pending=Pending(partials=dev(partials), bias=dev(bias)))
+    xr += partials.double().sum(0) + bias.double()
+    e = torch.empty(T, H, dtype=torch.float64)
+    RefOps(torch.float64).norm(xr, gamma, beta, 1e-5, mode, out_f32=e)
+    close(o, e[idx.long()], 1e-5, 1e-5)
+    xd = x0.clone().to(DEV)
+    ops.apply_pending(xd, Pending(y=dev(y), row_of=dev(row_of), gates=dev(gts)))
+    xr = x0.clone().double()
+    RefOps(torch.float64).moe_combine(xr, y, row_of, gts)
+    close(xd, xr, 1e-6, 1e-5)
+
+
+def test_gemm_partials_and_rope_sum_them(ops, ref):
+    """A product left as partial sums over pieces of K, summed by the rotary kernel with the bias."""
+    T, nq, nkv, hd, H = 5, 4, 2, 32, 4096
+    x, w, b = rnd(T, H, dtype=torch.bfloat16), rnd((nq + 2 * nkv) * hd, H, dtype=torch.bfloat16, seed=1, scale=0.05), rnd((nq + 2 * nkv) * hd, seed=2)
+    parts = ops.gemm_partials(x.to(DEV), w.to(DEV))
+    assert parts.shape[0] > 1 and parts.shape[1:] == (T, (nq + 2 * nkv) * hd)
+    exp = x.double() @ w.double().T
+    close(parts.sum(0), exp, 1e-5, 1e-3)
+    P = 16
+    k, v, bt = make_cache(4, nkv, P, hd, torch.bfloat16, 1, 4)
+    bt[0, :2] = torch.tensor([2, 1], dtype=torch.int32)
+    dv, cv = views(k, v, bt, P, nkv, hd, 0)
+    pos, slot = torch.arange(3, 3 + T, dtype=torch.int32), torch.zeros(T, dtype=torch.int32)
+    ang = torch.arange(64, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    q_d = torch.empty(T, nq * hd, dtype=torch.bfloat16, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(parts, pos.to(DEV), slot.to(DEV), cos.to(DEV), sin.to(DEV), hd, q_d, dv, nq, nkv, hd, True, status,
+                      bias=b.to(DEV))
+    q_r = torch.empty(T, nq * hd, dtype=torch.float64)
+    ref.rope_kv_write(exp + b.double(), pos, slot, cos, sin, hd, q_r, cv, nq, nkv, hd, True, None)
+    close(q_d, q_r, 1e-2, 1e-2)
+    close(dv.k, cv.k, 1e-2, 1e-2)
+    close(dv.v, cv.v, 1e-2, 1e-2)
+
+
 GEMM_SHAPES = [(1, 16, 64), (3, 17, 33), (64, 64, 64), (65, 130, 100), (200, 96, 80), (7, 384, 96), (130, 250, 1000)]
 
 
