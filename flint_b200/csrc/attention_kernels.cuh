@@ -450,6 +450,31 @@ paged_attention_block_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Warp-level tensor-core helpers (mma.sync m16n8k16, bf16 in, float32 out) for the decode
+// kernel in attention_tc.cu.  A decoded token brings only nq/nkv (typically 4) query rows per
+// key/value head, far below the 128 rows of a tcgen05 tile, and the float32-pipe kernels here
+// are bound by instruction issue; the warp-level MMA with 16 rows (the group's heads, zero
+// padded) cuts the instruction count per byte of cache about tenfold:
+//   S = Q K^T    ldmatrix (K rows are already the "col" operand), 2 x hd/16 MMAs per 16 keys
+//   softmax      on the accumulator fragment: 4 lanes share a row; float32 max, sum, exp
+//   O += P V     P re-packed from the S fragment as the A operand, V through ldmatrix.trans
+__device__ __forceinline__ void ldsm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float* d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 // Same contract as paged_attention_launch, with the block kernel: for few rows and long key ranges.
 inline int paged_attention_block_launch(const void* q, int q_dtype, const void* k_cache,
                                         const void* v_cache, int cache_dtype, const int* block_table,

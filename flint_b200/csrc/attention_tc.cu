@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "tc_common.cuh"
+#include "attention_kernels.cuh"
 
 using namespace flint;
 using namespace flint_tc;
@@ -289,6 +290,197 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention: the warp-level tensor-core kernel of attention_kernels.cuh with its key and
+// value tiles brought by TMA instead of per-thread copies.  Per-thread loads (and cp.async)
+// cannot keep enough bytes in flight per SM to fill HBM3e; a bulk tensor copy of a whole
+// 16-key tile per instruction can.  One warp per (row, kv head x up to 8 query heads, split); each
+// warp owns a ring of DSTAGES stages of 16 keys (K and V, two 64-dim chunks each, 128-byte
+// swizzle) with one mbarrier per stage; lane 0 issues the copies, all lanes wait (bounded).
+constexpr int DK = 16;            // keys per stage
+constexpr int DSTAGES = 3;
+constexpr int DSTAGE_BYTES = 2 * 2 * DK * 128;      // K and V, two chunks of 64 dims
+
+struct DecodeParams {
+  const __nv_bfloat16* q;
+  const int* block_table;
+  const int* pos;
+  const int* slot;
+  const int* row_list;
+  __nv_bfloat16* out;
+  float* scratch;
+  int* error_flag;
+  int n_rows, max_pages, page_size, nq, nkv, hd, window, split_keys, n_splits, g_chunks;
+  float scale;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                           const DecodeParams p) {
+  using flint_attn::ldsm4;
+  using flint_attn::ldsm4t;
+  using flint_attn::mma16816;
+  constexpr int MG = 8;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  const long long n_items = (long long)p.n_rows * p.nkv * p.g_chunks * p.n_splits;
+  if (item >= n_items) return;
+  const int split = (int)(item % p.n_splits);
+  long long rest = item / p.n_splits;
+  const int gchunk = (int)(rest % p.g_chunks);
+  rest /= p.g_chunks;
+  const int kvh = (int)(rest % p.nkv);
+  const int ti = (int)(rest / p.nkv);
+  const int t = p.row_list ? p.row_list[ti] : ti;
+  const int hd = p.hd, nq = p.nq;
+  const int G = nq / p.nkv;
+  const int g0 = gchunk * MG;
+  const int ng = min(MG, G - g0);
+  const int h0 = kvh * G + g0;
+  const int pq = p.pos[t];
+  const int lo_row = p.window > 0 ? max(0, pq + 1 - p.window) : 0;
+  const int lo = lo_row + split * p.split_keys;
+  const int hi = min(pq + 1, lo + p.split_keys);
+  const int* bt = p.block_table + (size_t)p.slot[t] * p.max_pages;
+  const int gid = lane >> 2, tid4 = lane & 3;
+  constexpr int KB = HD / 16, DB = HD / 8;
+  const int kb_n = hd / 16, db_n = hd / 8, chunks = (hd + 63) / 64;
+
+  const uint32_t ring = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * (DSTAGES * DSTAGE_BYTES);
+  const uint32_t bar0 = smem_u32(&bars[warp * DSTAGES]);
+  if (lane == 0) {
+    for (int s = 0; s < DSTAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  uint32_t qa[KB][2];
+#pragma unroll
+  for (int kb = 0; kb < KB; ++kb) {
+    qa[kb][0] = qa[kb][1] = 0u;
+    if (gid < ng && kb < kb_n) {
+      const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
+      qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  float o[DB][4];
+#pragma unroll
+  for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+  float m = -INFINITY, l = 0.f;
+
+  // stages cover absolute key positions [first + step*16, +16): tiles never straddle a page
+  const int first = lo & ~(DK - 1);
+  const int n_steps = hi > lo ? (hi - first + DK - 1) / DK : 0;
+  auto issue = [&](int step, int stage) {      // lane 0 only
+    const int j0 = first + step * DK;
+    const int lp = j0 / p.page_size;
+    int page = lp < p.max_pages ? bt[lp] : -1;
+    if (page < 0) page = 0;                    // never visible (masked): any finite page will do
+    const int row = (page * p.nkv + kvh) * p.page_size + j0 % p.page_size;
+    const uint32_t dst = ring + stage * DSTAGE_BYTES, bar = bar0 + 8 * stage;
+    mbar_expect_tx(bar, 2 * chunks * DK * 128);
+    for (int c = 0; c < chunks; ++c) {
+      tma_load_2d(dst + c * DK * 128, &map_k, c * 64, row, bar);
+      tma_load_2d(dst + 2 * DK * 128 + c * DK * 128, &map_v, c * 64, row, bar);
+    }
+  };
+  if (lane == 0)
+    for (int s0 = 0; s0 < DSTAGES - 1 && s0 < n_steps; ++s0) issue(s0, s0);
+
+  int failed = 0;
+#pragma unroll 1
+  for (int step = 0; step < n_steps; ++step) {
+    const int stage = step % DSTAGES;
+    __syncwarp();        // every lane is done reading the stage that is refilled next
+    if (lane == 0 && step + DSTAGES - 1 < n_steps) issue(step + DSTAGES - 1, (step + DSTAGES - 1) % DSTAGES);
+    {   // bounded wait for this stage's tile
+      const uint32_t bar = bar0 + 8 * stage, parity = (step / DSTAGES) & 1;
+      if (!mbar_try_wait(bar, parity)) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(bar, parity))
+          if (clock64() - t0 > WAIT_CYCLES) { failed = 1; break; }
+      }
+    }
+    if (__any_sync(0xffffffffu, failed)) break;
+    const uint32_t ks = ring + stage * DSTAGE_BYTES, vs = ks + 2 * DK * 128;
+    const int j0 = first + step * DK;
+    float sacc[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb) {
+      sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+#pragma unroll
+      for (int kb = 0; kb < KB; kb += 2) {
+        if (kb < kb_n) {
+          // matrices: this block's 8 keys x dims [kb*16, +8), [+8, +16), [(kb+1)*16, +8), [+8, +16)
+          const int r = nb * 8 + (lane & 7);
+          const int unit = kb * 2 + (lane >> 3);              // 16-byte unit along the head dimension
+          uint32_t b0, b1, b2, b3;
+          ldsm4(ks + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma16816(sacc[nb], qa[kb][0], 0u, qa[kb][1], 0u, b0, b1);
+          if (kb + 1 < kb_n) mma16816(sacc[nb], qa[kb + 1][0], 0u, qa[kb + 1][1], 0u, b2, b3);
+        }
+      }
+    }
+    float sv[4];
+    float mx = m;
+#pragma unroll
+    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = j0 + nb * 8 + tid4 * 2 + e;
+        sv[nb * 2 + e] = (j >= lo && j < hi) ? sacc[nb][e] * p.scale : -INFINITY;
+        mx = fmaxf(mx, sv[nb * 2 + e]);
+      }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float alpha = mx > -INFINITY ? expf(m - mx) : 1.f;
+    m = mx;
+    float pv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pv[i] = sv[i] > -INFINITY ? expf(sv[i] - mx) : 0.f;
+    const __nv_bfloat162 p01 = __floats2bfloat162_rn(pv[0], pv[1]), p23 = __floats2bfloat162_rn(pv[2], pv[3]);
+    l = l * alpha + ((__bfloat162float(p01.x) + __bfloat162float(p01.y)) + (__bfloat162float(p23.x) + __bfloat162float(p23.y)));
+    const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p01), pa2 = *reinterpret_cast<const uint32_t*>(&p23);
+#pragma unroll
+    for (int db = 0; db < DB; db += 2) {
+      if (db < db_n) {
+        o[db][0] *= alpha; o[db][1] *= alpha; o[db + 1][0] *= alpha; o[db + 1][1] *= alpha;
+        const int r = (lane & 7) + ((lane >> 3) & 1) * 8;      // key row
+        const int unit = db + (lane >> 4);                      // 16-byte unit = 8 dims
+        uint32_t b0, b1, b2, b3;
+        ldsm4t(vs + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+        mma16816(o[db], pa0, 0u, pa2, 0u, b0, b1);
+        mma16816(o[db + 1], pa0, 0u, pa2, 0u, b2, b3);
+      }
+    }
+  }
+  if (failed) {
+    if (lane == 0) atomicExch(p.error_flag, 1);
+    return;
+  }
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (gid >= ng) return;
+  if (p.n_splits == 1) {
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    __nv_bfloat16* dst = p.out + ((size_t)t * nq + h0 + gid) * hd + tid4 * 2;
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+      if (db < db_n) *reinterpret_cast<__nv_bfloat162*>(dst + db * 8) = __floats2bfloat162_rn(o[db][0] * inv, o[db][1] * inv);
+  } else {
+    float* dst = p.scratch + (((size_t)ti * nq + h0 + gid) * p.n_splits + split) * (hd + 2);
+#pragma unroll
+    for (int db = 0; db < DB; ++db)
+      if (db < db_n) { dst[db * 8 + tid4 * 2] = o[db][0]; dst[db * 8 + tid4 * 2 + 1] = o[db][1]; }
+    if (tid4 == 0) { dst[hd] = m; dst[hd + 1] = l; }
+  }
+}
+
 }  // namespace
 
 // q, out [T, nq*hd] bf16; k_cache, v_cache pages [n_pages, nkv, page_size, hd] bf16;
@@ -336,6 +528,51 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
     attention_prefill_tc_kernel<128><<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
   }
   return check_launch("attention_prefill_tc");
+}
+
+// Decode rows (or any rows, one at a time) over the paged bfloat16 cache: the contract of
+// flint_paged_attention with bfloat16 q/out, page sizes that are multiples of 16, head sizes up to 128.
+extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                         const int* block_table, int max_pages, int page_size, const int* pos,
+                                         const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
+                                         float scale, int split_keys, int n_splits, float* scratch,
+                                         const int* row_list, int* error_flag, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_tc: head size %d (multiples of 16 up to 128)", hd);
+  if (nkv <= 0 || nq % nkv) return fail("attention_decode_tc: %d query heads do not divide into %d kv heads", nq, nkv);
+  if (page_size <= 0 || page_size % DK) return fail("attention_decode_tc: page size %d must be a multiple of %d", page_size, DK);
+  if (n_splits < 1 || split_keys < 1) return fail("attention_decode_tc: bad split (%d keys, %d splits)", split_keys, n_splits);
+  if (n_splits > 1 && !scratch) return fail("attention_decode_tc: splits need scratch memory");
+  if (!error_flag) return fail("attention_decode_tc: needs an error flag");
+  CUtensorMap mk, mv;
+  const long long kv_rows = (long long)n_pages * nkv * page_size;
+  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, DK);
+  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, DK);
+  if (rc) return fail("attention_decode_tc: cuTensorMapEncodeTiled failed (%d)", rc);
+  DecodeParams p;
+  p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot; p.row_list = row_list;
+  p.out = (__nv_bfloat16*)out; p.scratch = scratch; p.error_flag = error_flag;
+  p.n_rows = T; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd;
+  p.window = window; p.split_keys = split_keys; p.n_splits = n_splits;
+  p.g_chunks = (nq / nkv + 7) / 8;
+  p.scale = scale;
+  const long long items = (long long)T * nkv * p.g_chunks * n_splits;
+  const long long blocks = (items + 3) / 4;
+  if (blocks > 0x7fffffffLL) return fail("attention_decode_tc: too many work items");
+  const size_t smem = 4 * DSTAGES * DSTAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = true;
+  }
+  if (hd <= 64) attention_decode_tc_kernel<64><<<(unsigned)blocks, 128, smem, stream>>>(mk, mv, p);
+  else attention_decode_tc_kernel<128><<<(unsigned)blocks, 128, smem, stream>>>(mk, mv, p);
+  rc = check_launch("attention_decode_tc");
+  if (rc || n_splits == 1) return rc;
+  flint_attn::attention_combine_kernel<__nv_bfloat16><<<(unsigned)((long long)T * nq), hd >= 128 ? 128 : 64, 0, stream>>>(
+      scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
+  return check_launch("attention_combine");
 }
 
 extern "C" const char* flint_attention_tc_last_error() { return g_error; }

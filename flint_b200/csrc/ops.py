@@ -386,13 +386,21 @@ class CudaOps:
                   c_int(plan.max_tiles if plan else 0), c_int(plan.tile_rows if plan else 0), c_int(M), c_int(N), c_int(K))
 
     # ------------------------------------------------------------------ attention
-    def attention_plan(self, T, nq, nkv, span):
+    def attention_plan(self, T, nq, nkv, span, hd=128, bf16=True):
         """Which kernel and how to split the key range so that the device is filled:
-        (kernel, keys per split, splits).  Few rows (decode): the block kernel, one block per
-        (row, kv head, split) with splits of whole 128-key chunks; many rows: the warp kernel."""
+        (kernel, keys per split, splits).  Few rows (decode), bfloat16, head sizes up to 128: the
+        TMA-fed tensor-core kernel, one warp per (row, kv head, split); few rows otherwise: one block
+        each on the float32 pipes; many rows: the warp-per-row kernel."""
         g_chunks = -(-(nq // nkv) // 4)
         base = T * nkv * g_chunks
         span = max(span, 1)
+        if T <= 256 and hd <= 128 and bf16:
+            # tensor-core decode kernel fed by TMA: 8 query heads per warp, about one wave of 8 warps
+            # per SM, at least 128 keys per warp
+            base8 = T * nkv * -(-(nq // nkv) // 8)
+            n = max(1, min(span // 128, -(-1184 // base8)))
+            keys = -(-(-(-span // n)) // 16) * 16
+            return "tma", keys, -(-span // keys)
         if T <= 256:
             n = max(1, min(-(-span // 128), -(-1184 // base)))
             keys = -(-(-(-span // n)) // 128) * 128
@@ -445,7 +453,8 @@ class CudaOps:
         if tuple(cache.k.shape[1:]) != (nkv, cache.page_size, hd):
             raise KernelError("paged_attention: cache pages do not match the head counts")
         span = min(max_kv_len, window) if window else max_kv_len
-        auto_kernel, split_keys, n_splits = self.attention_plan(T, nq, nkv, span)
+        auto_kernel, split_keys, n_splits = self.attention_plan(
+            T, nq, nkv, span, hd, q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16)
         kernel = kernel or auto_kernel
         if splits is not None:
             split_keys, n_splits = splits
@@ -454,6 +463,14 @@ class CudaOps:
         scratch = None
         if n_splits > 1:
             scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+        if kernel == "tma":
+            if rows is not None and rows.numel() != T:
+                raise KernelError("paged_attention: bad row list")
+            return self._run("attention_tc", "flint_attention_decode_tc", _ptr(q), _ptr(cache.k), _ptr(cache.v),
+                             c_int(cache.k.shape[0]), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
+                             c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
+                             c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
+                             _ptr(scratch), _ptr(rows), _ptr(self.tc_error))
         fn = {"warp": "flint_paged_attention", "block": "flint_paged_attention_block"}[kernel]
         self._run("attention", fn, _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),

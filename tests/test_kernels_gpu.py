@@ -320,7 +320,10 @@ def test_rope_write_and_attention(ops, ref, qd, cd, nq, nkv, hd, P, window):
     scale = 1 / math.sqrt(hd)
     span = min(lens[0], window or 10 ** 9)
     for kernel, splits in (("warp", None), ("warp", (32, -(-span // 32))), ("warp", (64, -(-span // 64))), ("block", None),
-                           ("block", (128, -(-span // 128))), ("block", (span, 1)), ("block", (40, -(-span // 40)))):
+                           ("block", (128, -(-span // 128))), ("block", (span, 1)), ("block", (40, -(-span // 40))),
+                           ("tma", None), ("tma", (span, 1)), ("tma", (48, -(-span // 48))), ("tma", (23, -(-span // 23)))):
+        if kernel == "tma" and (hd > 128 or qd != torch.bfloat16):
+            continue
         out_d.fill_(float("nan"))
         ops.paged_attention(q_d, dv, pos.to(DEV), slot.to(DEV), out_d, nq, nkv, hd, window, scale, max(lens.values()),
                             splits=splits, kernel=kernel)
