@@ -196,7 +196,9 @@ def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
     from flint_b200.sampling.params import SamplingParams
     eng = Engine(model, SamplingParams.greedy(), seed=1, prefill_chunk=2048, max_step_tokens=2048 + batch)
     V = cfg["vocab_size"]
-    ids = [eng.create([rng.randrange(V) for _ in range(prompt_len)], steps + warmup + 8) for _ in range(batch)]
+    # requests are admitted one prompt per step, so the first has decoded `batch` tokens before the last is
+    # in: give all of them room to keep decoding through the timed region
+    ids = [eng.create([rng.randrange(V) for _ in range(prompt_len)], steps + warmup + 2 * batch + 8) for _ in range(batch)]
     while any(r.remaining > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
         eng.step()
     for _ in range(warmup):

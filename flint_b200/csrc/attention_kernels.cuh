@@ -168,6 +168,8 @@ paged_attention_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache,
 template <typename TO>
 __global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* __restrict__ out,
                                          int hd, int n_splits, int nq, const int* __restrict__ row_list) {
+  pdl_launch();
+  pdl_wait();
   const size_t rh = blockIdx.x;   // (index of the row in this launch) * nq + head
   const float* base = scratch + rh * n_splits * (hd + 2);
   const size_t out_rh = row_list ? (size_t)row_list[rh / nq] * nq + rh % nq : rh;

@@ -325,6 +325,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   constexpr int MG = 8;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
+  pdl_launch();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * 4 + warp;
   const long long n_items = (long long)p.n_rows * p.nkv * p.g_chunks * p.n_splits;
@@ -566,12 +568,12 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
     cudaFuncSetAttribute(attention_decode_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     configured = true;
   }
-  if (hd <= 64) attention_decode_tc_kernel<64><<<(unsigned)blocks, 128, smem, stream>>>(mk, mv, p);
-  else attention_decode_tc_kernel<128><<<(unsigned)blocks, 128, smem, stream>>>(mk, mv, p);
+  if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+  else launch_pdl(attention_decode_tc_kernel<128>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
   rc = check_launch("attention_decode_tc");
   if (rc || n_splits == 1) return rc;
-  flint_attn::attention_combine_kernel<__nv_bfloat16><<<(unsigned)((long long)T * nq), hd >= 128 ? 128 : 64, 0, stream>>>(
-      scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
+  launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
+             dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
   return check_launch("attention_combine");
 }
 

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define FLINT_F32 0
 #define FLINT_BF16 1
@@ -30,6 +31,40 @@ inline int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
   return 0;
+}
+
+// Programmatic dependent launch.  A kernel launched through launch_pdl may begin (its blocks are
+// scheduled, run their prologue, even fetch data that no earlier kernel writes) while the kernel
+// before it in the stream is still finishing.  Every such kernel must call pdl_wait() before it
+// reads anything an earlier kernel wrote and before it writes anything at all; pdl_launch() at its
+// top lets the kernel after it start early in turn.  With FLINT_PDL=0 launches are ordinary and
+// both calls do nothing.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLINT_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 __device__ __forceinline__ float to_f32(float v) { return v; }

@@ -14,6 +14,8 @@ using namespace flint;
 template <typename TT>
 __global__ void embed_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
                              float* __restrict__ out, int T, int H, int V, float scale) {
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   int id = ids[r];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);  // ids are validated on the host; never read outside
@@ -28,7 +30,7 @@ extern "C" int flint_embed(const int* ids, const void* table, int table_dtype, f
   if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   FLINT_DISPATCH_DTYPE(table_dtype, TT,
-      embed_kernel<TT><<<T, threads, 0, stream>>>(ids, (const TT*)table, out, T, H, V, scale));
+      launch_pdl(embed_kernel<TT>, dim3(T), dim3(threads), 0, stream, ids, (const TT*)table, out, T, H, V, scale));
   return check_launch("embed");
 }
 
@@ -93,6 +95,8 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
                                const int* __restrict__ block_table, int max_pages, int page_size,
                                int nq, int nkv, int hd, int write_kv, int* __restrict__ status,
                                int n_partials, long long partial_stride, const float* __restrict__ bias) {
+  pdl_launch();
+  pdl_wait();
   const int t = blockIdx.x;
   const int head = blockIdx.y;  // 0..nq-1 q, nq..nq+nkv-1 k, then v
   const int p = pos[t];
@@ -148,7 +152,7 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
   dim3 grid(T, nq + 2 * nkv);
   const int threads = hd >= 128 ? 128 : (hd > 32 ? 64 : 32);
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
-      (rope_kv_kernel<TQ, TC><<<grid, threads, 0, stream>>>(
+      (launch_pdl(rope_kv_kernel<TQ, TC>, grid, dim3(threads), 0, stream,
           qkv, pos, slot, cos_t, sin_t, rot, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,
           max_pages, page_size, nq, nkv, hd, write_kv, status, n_partials, partial_stride, bias))));
   return check_launch("rope_kv_write");
@@ -159,6 +163,8 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
 // index gives a row of zeros.
 __global__ void gather_rows_kernel(const uint32_t* __restrict__ x, const int* __restrict__ index,
                                    uint32_t* __restrict__ out, int words) {
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = index[r];
   for (int d = threadIdx.x; d < words; d += blockDim.x)
@@ -169,7 +175,7 @@ extern "C" int flint_gather_rows(const void* x, const int* index, void* out, int
                                  int row_bytes, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (row_bytes <= 0 || (row_bytes & 3)) return fail("gather_rows: row size %d bytes is not a multiple of 4", row_bytes);
-  gather_rows_kernel<<<rows, 256, 0, stream>>>((const uint32_t*)x, index, (uint32_t*)out, row_bytes / 4);
+  launch_pdl(gather_rows_kernel, dim3(rows), dim3(256), 0, stream, (const uint32_t*)x, index, (uint32_t*)out, row_bytes / 4);
   return check_launch("gather_rows");
 }
 

@@ -79,10 +79,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
+  pdl_launch();
   if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
   // ---- which tile
   int expert = 0, row0 = blockIdx.y * BN, row_end = p.rows;
   if (p.tile_expert) {
+    pdl_wait();        // the tile map comes from the routing plan of an earlier kernel
     if ((int)blockIdx.y >= *p.n_tiles) return;
     expert = p.tile_expert[blockIdx.y];
     row0 = p.tile_row0[blockIdx.y];
@@ -120,7 +122,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
-    for (int i = 0; i < nkb; ++i) {
+    // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+    // requested at once, and only the activation tiles wait for that kernel to finish.
+    const int head = nkb < stages ? nkb : stages;
+    for (int i = 0; i < head; ++i) {
+      const uint32_t a = tiles + i * STAGE_BYTES, bar = full0 + 8 * i;
+      mbar_expect_tx(bar, STAGE_BYTES);
+      const int kx = (kb0 + i) * BK;
+      tma_load_2d(a, &map_w, kx, w_row, bar);
+      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w_row, bar);
+    }
+    pdl_wait();
+    for (int i = 0; i < head; ++i)
+      tma_load_2d(tiles + i * STAGE_BYTES + A_BYTES * (GATED ? 2 : 1), &map_x, (kb0 + i) * BK, row0, full0 + 8 * i);
+    for (int i = head; i < nkb; ++i) {
       const int s = i % stages;
       if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, ab)) break;
       const uint32_t a = tiles + s * STAGE_BYTES;
@@ -156,6 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---------------------------------------------------------------- epilogue
     if (mbar_wait(accum_bar, 0, ab)) {
       tc_fence_after();
+      pdl_wait();                                   // before reading or writing what earlier kernels touch
       const int q = warp & 3;                       // this warp's quarter of the 128 lanes
       const int f = f0 + q * 32 + lane;             // output feature of this thread
       const bool f_ok = f < p.N;
@@ -276,7 +292,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, 
     if (e != cudaSuccess) return fail("gemm_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
     configured = true;
   }
-  gemm_tc_kernel<BN, GATED><<<grid, THREADS, smem, stream>>>(mw, mu, mx, p);
+  launch_pdl(gemm_tc_kernel<BN, GATED>, grid, dim3(THREADS), smem, stream, mw, mu, mx, p);
   return check_launch("gemm_tc");
 }
 
@@ -284,7 +300,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, 
 
 // Stages of the K ring for a token tile of bn rows: as many as fit about 100 KB (two blocks
 // per SM), at least 3, at most 8 (wide tiles take up to 192 KB and run one block per SM).
+static int g_stage_override = 0;
+// For tuning: force the number of stages (0 = choose by tile size).
+extern "C" void flint_gemm_tc_set_stages(int stages) { g_stage_override = stages; }
+
 extern "C" int flint_gemm_tc_stages(int bn, int gated) {
+  if (g_stage_override > 0) return g_stage_override;
   const int stage = BM * BK * 2 * (gated ? 2 : 1) + bn * BK * 2;
   int s = (bn >= 128 ? 192 * 1024 : 100 * 1024) / stage;
   if (s < 3) s = 3;

@@ -135,6 +135,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ expert_ids, int n_assign
                                 int* __restrict__ n_tiles, int max_tiles) {
   __shared__ int cnt[MAX_E];
   __shared__ int off[MAX_E + 1];
+  pdl_launch();
+  pdl_wait();
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
   // rank of each assignment inside its expert (the order inside an expert has no effect on
@@ -206,7 +208,7 @@ extern "C" int flint_moe_plan(const int* expert_ids, int n_assign, int E, int ti
   if (tile_rows <= 0) return fail("moe_plan: bad tile size %d", tile_rows);
   if (max_tiles < flint_moe_max_tiles(n_assign, E, tile_rows))
     return fail("moe_plan: tile map of %d entries is too small", max_tiles);
-  moe_plan_kernel<<<1, 1024, 0, stream>>>(expert_ids, n_assign, E, tile_rows, counts, offsets, row_of,
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, expert_ids, n_assign, E, tile_rows, counts, offsets, row_of,
                                           token_of, tile_expert, tile_row0, n_tiles, max_tiles);
   return check_launch("moe_plan");
 }

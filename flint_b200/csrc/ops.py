@@ -275,7 +275,7 @@ class CudaOps:
         """out[r] = x[r] @ w[expert of row r].T; w [E, N, K]."""
         self._gemm(x, w, None, out, None, False, "silu", plan)
 
-    def gemm_partials(self, x, w):
+    def gemm_partials(self, x, w, splits=None):
         """x @ w.T left as S partial sums over pieces of the K range: float32 [S, M, N], no bias.
         The next kernel (rotary write, row norm) adds them up; S is 1 when nothing was split."""
         _check(x, "x", dims=2)
@@ -289,7 +289,7 @@ class CudaOps:
             self._gemm_simt(x, w, None, out[0], None, False, 0, None, M, N, K)
             return out
         bn = self.token_tile(M)
-        splits = self._k_splits(M, N, K, bn)
+        splits = splits or self._k_splits(M, N, K, bn)
         kb = -(-K // 64)
         kbps = -(-kb // splits)
         splits = -(-kb // kbps)

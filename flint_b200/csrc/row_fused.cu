@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(1024)
 row_norm_kernel(const RowArgs a) {
   extern __shared__ float smem[];          // router only: H floats of the normalised row, then partial logits
   __shared__ float red[32];
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = a.row_index ? a.row_index[r] : r;
   const int H = a.H, n4 = H >> 2;
@@ -202,7 +204,7 @@ row_norm_kernel(const RowArgs a) {
 
 template <int VPT, typename TW>
 int launch_row(const RowArgs& a, int rows, int threads, size_t smem, cudaStream_t stream) {
-  row_norm_kernel<VPT, TW><<<rows, threads, smem, stream>>>(a);
+  launch_pdl(row_norm_kernel<VPT, TW>, dim3(rows), dim3(threads), smem, stream, a);
   return check_launch("row_norm");
 }
 }  // namespace

@@ -91,6 +91,8 @@ __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
   __shared__ float red[33];
   __shared__ int redi[32];
+  pdl_launch();
+  pdl_wait();
   const int r = blockIdx.x;
   const int tok = block_argmax(logits + (size_t)r * V, V, red, redi);
   if (threadIdx.x == 0) out[r] = tok;
@@ -261,7 +263,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ params
 extern "C" int flint_argmax(const float* logits, int* out, int rows, int V, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return fail("argmax: bad vocabulary %d", V);
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, out, V);
+  launch_pdl(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, out, V);
   return check_launch("argmax");
 }
 

@@ -189,9 +189,11 @@ class Model:
     def _decode_splits(self, step):
         """Key-range split for a decode batch, from a bucketed context length so that
         few graphs are needed as requests grow."""
-        bucket = 256
-        while bucket < step.max_kv_len:
-            bucket *= 2
+        # four buckets per doubling of the context, at least 256 apart: a graph serves a range of
+        # lengths, and the key-range split it was captured with is never much longer than needed
+        kv = max(step.max_kv_len, 1)
+        gran = max(256, 1 << max(kv.bit_length() - 3, 0))
+        bucket = -(-kv // gran) * gran
         spans = [bucket]
         for i, call in enumerate(self.order):
             mixer = self.layers[call.layer].parts.get("mixer")
