@@ -64,6 +64,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 2^x on the special-function unit (float32 in and out, about 2 ulp)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -72,13 +79,13 @@ template <int HDM>   // HDM: 64 or 128, the largest head size this instantiation
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const Params p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];   // tiles need 1024-byte alignment (128-byte swizzle)
   __shared__ __align__(8) uint64_t bars[8];   // q, kv_full[2], kv_empty[2], s_full, p_full, o_full
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
   if (*(volatile int*)p.error_flag) return;
-  const int* tile = p.tiles + 4 * blockIdx.x;
+  const int* tile = p.tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
   const int row0 = tile[0], n_rows = tile[1], slot = tile[2], pos0 = tile[3];
   const int head = blockIdx.y;
   const int hd = p.hd;
@@ -94,7 +101,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int tile_lo = k_lo / BKV;
   const int n_kv_tiles = (k_hi + BKV - 1) / BKV - tile_lo;
 
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t base = smem_u32(smem_raw);
+  if (base & 1023u) {           // would corrupt the swizzle: refuse rather than compute garbage
+    if (threadIdx.x == 0) atomicExch(p.error_flag, 2);
+    return;
+  }
   const uint32_t q_smem = base;                                       // chunks x [128 rows][128 B]
   const uint32_t kv_smem = q_smem + chunks * BQ * 128;                // per stage: K chunks, then V chunks
   const uint32_t kv_stage_bytes = 2u * chunks * BKV * 128;
@@ -193,19 +204,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) break;
       tc_fence_after();
       const int kv0 = (tile_lo + i) * BKV;
-      // pass 1: the row's maximum over this tile
-      float mx = m;
+      // only tiles that touch the diagonal or the window's edge need the mask (uniform in the block)
+      const bool need_mask = (kv0 + BKV - 1 > pos0) || (p.window > 0 && kv0 < pos0 + n_rows - p.window);
+      // pass 1: the row's maximum over this tile (of the raw scores; the scale is positive)
+      float mraw = -INFINITY;
 #pragma unroll
       for (int c0 = 0; c0 < BKV; c0 += 16) {
         float v[16];
         tmem_ld16(tmem_s + lane_addr + c0, v);
+        if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const int kj = kv0 + c0 + c;
-          if (kj <= q_pos && kj >= first) mx = fmaxf(mx, v[c] * p.scale_log2);
+          for (int c = 0; c < 16; ++c) {
+            const int kj = kv0 + c0 + c;
+            if (kj <= q_pos && kj >= first) mraw = fmaxf(mraw, v[c]);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < 16; ++c) mraw = fmaxf(mraw, v[c]);
         }
       }
-      const float alpha = exp2f(m - mx);
+      const float mx = fmaxf(m, mraw * p.scale_log2);
+      const float alpha = ex2(m - mx);
       m = mx;
       // pass 2: probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
       float sum = 0.f;
@@ -219,8 +238,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           float pr[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            const int kj = kv0 + c0 + c + e;
-            pr[e] = (kj <= q_pos && kj >= first) ? exp2f(v[c + e] * p.scale_log2 - m) : 0.f;
+            pr[e] = ex2(fmaf(v[c + e], p.scale_log2, -m));
+            if (need_mask) {
+              const int kj = kv0 + c0 + c + e;
+              if (!(kj <= q_pos && kj >= first)) pr[e] = 0.f;
+            }
           }
           const __nv_bfloat162 b = __floats2bfloat162_rn(pr[0], pr[1]);
           // the sum uses the rounded values that the MMA will see
@@ -513,7 +535,7 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   const int chunks = (hd + 63) / 64;
-  const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128 + 1024;
+  const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128;
   dim3 grid(n_tiles, nq);
   static bool configured[2] = {false, false};
   if (hd <= 64) {

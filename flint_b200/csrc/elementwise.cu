@@ -88,7 +88,8 @@ extern "C" int flint_norm(const float* x, const int* row_index, const float* gam
 // the cos/sin tables that belongs to the token's position; q goes to q_out, k and v go to
 // the token's place in the paged cache: page = block_table[slot, pos / P], row pos % P.
 template <typename TQ, typename TC>
-__global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
+__global__ void __launch_bounds__(256)
+rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                                const int* __restrict__ slot, const float* __restrict__ cos_t,
                                const float* __restrict__ sin_t, int rot, TQ* __restrict__ q_out,
                                TC* __restrict__ k_cache, TC* __restrict__ v_cache,
@@ -97,44 +98,62 @@ __global__ void rope_kv_kernel(const float* __restrict__ qkv, const int* __restr
                                int n_partials, long long partial_stride, const float* __restrict__ bias) {
   pdl_launch();
   pdl_wait();
+  // One block per token.  A work item is a pair of dims (d, d + rot/2) of one head (or two
+  // neighbouring dims beyond the rotary part, or of a value head), so that every input element
+  // is read exactly once; consecutive threads take consecutive pairs.
   const int t = blockIdx.x;
-  const int head = blockIdx.y;  // 0..nq-1 q, nq..nq+nkv-1 k, then v
   const int p = pos[t];
   const int half = rot >> 1;
-  const size_t src_off = ((size_t)t * (nq + 2 * nkv) + head) * hd;
-  const float* bias_h = bias ? bias + (size_t)head * hd : nullptr;
+  const int pairs = hd >> 1;                 // per head
+  const int heads = nq + (write_kv ? 2 * nkv : 0);
+  const size_t row_off = (size_t)t * (nq + 2 * nkv) * hd;
+  long long cache_tok = -1;                  // row of this token in [page, kv_head, P] units, head 0
+  if (write_kv) {
+    const int page = block_table[(size_t)slot[t] * max_pages + p / page_size];
+    if (page < 0) {                          // the host must have allocated the page; record and skip
+      if (threadIdx.x == 0) atomicExch(status, 1);
+    } else {
+      cache_tok = (long long)page * nkv * page_size + (p % page_size);
+    }
+  }
   // the projection may arrive as partial sums over pieces of its K range, and without its bias:
   // they are added here in a fixed order
-  auto rd = [&](int d) {
-    float v = qkv[src_off + d];
-    for (int z = 1; z < n_partials; ++z) v += qkv[(size_t)z * partial_stride + src_off + d];
-    return bias_h ? v + bias_h[d] : v;
+  auto rd = [&](size_t off, int col) {
+    float v = qkv[row_off + off];
+    for (int z = 1; z < n_partials; ++z) v += qkv[(size_t)z * partial_stride + row_off + off];
+    return bias ? v + bias[col] : v;
   };
-  const bool is_q = head < nq;
-  const bool is_v = head >= nq + nkv;
-  if (!is_q && !write_kv) return;
-  size_t cache_row = 0;
-  if (!is_q) {
-    const int page = block_table[(size_t)slot[t] * max_pages + p / page_size];
-    if (page < 0) {  // the host must have allocated the page; record and skip
-      if (threadIdx.x == 0) atomicExch(status, 1);
-      return;
-    }
-    const int kvh = is_v ? head - nq - nkv : head - nq;
-    cache_row = (((size_t)page * nkv + kvh) * page_size + (p % page_size)) * hd;
-  }
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
-    float y;
-    if (is_v || d >= rot) {
-      y = rd(d);
-    } else {
-      const int i = d < half ? d : d - half;
+  // with few tokens several blocks share a token (gridDim.y), each a contiguous range of items
+  const int n_items = heads * pairs;
+  const int per_block = (n_items + gridDim.y - 1) / gridDim.y;
+  const int item_end = min(n_items, (int)(blockIdx.y + 1) * per_block);
+  for (int item = blockIdx.y * per_block + threadIdx.x; item < item_end; item += blockDim.x) {
+    const int head = item / pairs, i = item % pairs;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
+    // dims of this item: inside the rotary part (d, d + half); beyond it (rot + 2j, rot + 2j + 1)
+    int d0, d1;
+    bool rotate = false;
+    if (!is_v && i < half) { d0 = i; d1 = i + half; rotate = true; }
+    else if (is_v) { d0 = 2 * i; d1 = 2 * i + 1; }
+    else { d0 = rot + 2 * (i - half); d1 = d0 + 1; }
+    const size_t base = (size_t)head * hd;
+    float x0 = rd(base + d0, head * hd + d0), x1 = rd(base + d1, head * hd + d1);
+    if (rotate) {
       const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
-      y = d < half ? rd(d) * c - rd(d + half) * s : rd(d) * c + rd(d - half) * s;
+      const float y0 = x0 * c - x1 * s, y1 = x1 * c + x0 * s;
+      x0 = y0;
+      x1 = y1;
     }
-    if (is_q) q_out[((size_t)t * nq + head) * hd + d] = from_f32<TQ>(y);
-    else if (is_v) v_cache[cache_row + d] = from_f32<TC>(y);
-    else k_cache[cache_row + d] = from_f32<TC>(y);
+    if (is_q) {
+      TQ* dst = q_out + ((size_t)t * nq + head) * hd;
+      dst[d0] = from_f32<TQ>(x0);
+      dst[d1] = from_f32<TQ>(x1);
+    } else if (cache_tok >= 0) {
+      const int kvh = is_v ? head - nq - nkv : head - nq;
+      TC* dst = (is_v ? v_cache : k_cache) + (cache_tok + (long long)kvh * page_size) * hd;
+      dst[d0] = from_f32<TC>(x0);
+      dst[d1] = from_f32<TC>(x1);
+    }
   }
 }
 
@@ -149,8 +168,13 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
   if (n_partials < 1) return fail("rope: needs at least one partial");
   if (rot < 0 || rot > hd || (rot & 1)) return fail("rope: rotary size %d does not fit head size %d", rot, hd);
   if (page_size <= 0) return fail("rope: bad page size %d", page_size);
-  dim3 grid(T, nq + 2 * nkv);
-  const int threads = hd >= 128 ? 128 : (hd > 32 ? 64 : 32);
+  const int items = (nq + 2 * nkv) * (hd / 2);
+  int per_token = T >= 296 ? 1 : (296 + T - 1) / T;            // enough blocks to fill the device
+  if (per_token > (items + 63) / 64) per_token = (items + 63) / 64;
+  if (per_token < 1) per_token = 1;
+  dim3 grid(T, per_token);
+  const int share = (items + per_token - 1) / per_token;
+  const int threads = share >= 256 ? 256 : ((share + 31) / 32) * 32;
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
       (launch_pdl(rope_kv_kernel<TQ, TC>, grid, dim3(threads), 0, stream,
           qkv, pos, slot, cos_t, sin_t, rot, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,

@@ -156,7 +156,7 @@ class CudaOps:
         fused kernel does not take."""
         _check(x, "x", torch.float32, 2)
         T, H = x.shape
-        if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 40000)):
+        if H % 4 or H > 16384 or (router is not None and (row_index is not None or H * 4 > 160000)):
             if pending is not None:
                 self.apply_pending(x, pending)
             tmp = out_f32

@@ -52,136 +52,196 @@ __device__ __forceinline__ void load_w8(const __nv_bfloat16* p, float* f) {
   }
 }
 
-template <int VPT, typename TW>
+// ROWS rows per block (1, or 4 for long batches with a router, so that each router row read from L2
+// serves four tokens).
+template <int VPT, typename TW, int ROWS>
 __global__ void __launch_bounds__(1024)
-row_norm_kernel(const RowArgs a) {
-  extern __shared__ float smem[];          // router only: H floats of the normalised row, then partial logits
+row_norm_kernel(const RowArgs a, int n_rows) {
+  extern __shared__ float smem[];          // router only: ROWS x H floats of normalised rows, then partial logits
   __shared__ float red[32];
   pdl_launch();
   pdl_wait();
-  const int r = blockIdx.x;
-  const int src = a.row_index ? a.row_index[r] : r;
   const int H = a.H, n4 = H >> 2;
-  float* xr = a.x + (size_t)src * H;
-  float4 v[VPT];
+  const int rows_here = min(ROWS, n_rows - (int)blockIdx.x * ROWS);
+  for (int rr = 0; rr < rows_here; ++rr) {
+    const int r = blockIdx.x * ROWS + rr;
+    const int src = a.row_index ? a.row_index[r] : r;
+    float* xr = a.x + (size_t)src * H;
+    float4 v[VPT];
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    v[i] = c < n4 ? ld4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  const bool pending = a.partials || a.comb_y;
-  if (a.partials) {
-    for (int z = 0; z < a.n_partials; ++z) {          // fixed order
-      const float* pr = a.partials + (size_t)z * a.partial_stride + (size_t)src * H;
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      v[i] = c < n4 ? ld4(xr + 4 * c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const bool pending = a.partials || a.comb_y;
+    if (a.partials) {
+      for (int z = 0; z < a.n_partials; ++z) {          // fixed order
+        const float* pr = a.partials + (size_t)z * a.partial_stride + (size_t)src * H;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          if (c < n4) add4(v[i], ld4(pr + 4 * c));
+        }
+      }
+      if (a.add_bias) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int c = threadIdx.x + i * blockDim.x;
+          if (c < n4) add4(v[i], ld4(a.add_bias + 4 * c));
+        }
+      }
+    }
+    if (a.comb_y) {
+      const int r0 = a.comb_row_of[2 * src], r1 = a.comb_row_of[2 * src + 1];
+      const float g0 = a.comb_gates[2 * src], g1 = a.comb_gates[2 * src + 1];
+      const float* y0 = a.comb_y + (size_t)r0 * H;
+      const float* y1 = a.comb_y + (size_t)r1 * H;
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        if (c < n4) add4(v[i], ld4(pr + 4 * c));
+        if (c < n4) {
+          float4 t = make_float4(0.f, 0.f, 0.f, 0.f);   // g0*y0 + g1*y1 first, then added: the order of moe_combine
+          fma4(t, g0, ld4(y0 + 4 * c));
+          fma4(t, g1, ld4(y1 + 4 * c));
+          add4(v[i], t);
+        }
       }
     }
-    if (a.add_bias) {
+    if (pending) {
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        if (c < n4) add4(v[i], ld4(a.add_bias + 4 * c));
+        if (c < n4) *reinterpret_cast<float4*>(xr + 4 * c) = v[i];
       }
     }
-  }
-  if (a.comb_y) {
-    const int r0 = a.comb_row_of[2 * src], r1 = a.comb_row_of[2 * src + 1];
-    const float g0 = a.comb_gates[2 * src], g1 = a.comb_gates[2 * src + 1];
-    const float* y0 = a.comb_y + (size_t)r0 * H;
-    const float* y1 = a.comb_y + (size_t)r1 * H;
+    if (!a.gamma) continue;                   // only the additions were wanted
+    // statistics
+    float mean = 0.f;
+    if (a.mode == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);   // zeros beyond the row
+      mean = block_sum(s, red) / (float)H;
+    }
+    float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
       if (c < n4) {
-        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);   // g0*y0 + g1*y1 first, then added: the order of moe_combine
-        fma4(t, g0, ld4(y0 + 4 * c));
-        fma4(t, g1, ld4(y1 + 4 * c));
-        add4(v[i], t);
+        const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
+        ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
       }
     }
-  }
-  if (pending) {
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)H + a.eps);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * blockDim.x;
-      if (c < n4) *reinterpret_cast<float4*>(xr + 4 * c) = v[i];
-    }
-  }
-  if (!a.gamma) return;                     // only the additions were wanted
-  // statistics
-  float mean = 0.f;
-  if (a.mode == 0) {
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);   // zeros beyond the row
-    mean = block_sum(s, red) / (float)H;
-  }
-  float ss = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    if (c < n4) {
-      const float d0 = v[i].x - mean, d1 = v[i].y - mean, d2 = v[i].z - mean, d3 = v[i].w - mean;
-      ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
-    }
-  }
-  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)H + a.eps);
-#pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int c = threadIdx.x + i * blockDim.x;
-    if (c < n4) {
-      const float4 g = ld4(a.gamma + 4 * c);
-      float4 y = make_float4((v[i].x - mean) * inv * g.x, (v[i].y - mean) * inv * g.y,
-                             (v[i].z - mean) * inv * g.z, (v[i].w - mean) * inv * g.w);
-      if (a.beta) add4(y, ld4(a.beta + 4 * c));
-      if (a.out_f32) *reinterpret_cast<float4*>(a.out_f32 + (size_t)r * H + 4 * c) = y;
-      if (a.out_bf16) {
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
-        uint2 pk;
-        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
-        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(a.out_bf16 + (size_t)r * H + 4 * c) = pk;
+      if (c < n4) {
+        const float4 g = ld4(a.gamma + 4 * c);
+        float4 y = make_float4((v[i].x - mean) * inv * g.x, (v[i].y - mean) * inv * g.y,
+                               (v[i].z - mean) * inv * g.z, (v[i].w - mean) * inv * g.w);
+        if (a.beta) add4(y, ld4(a.beta + 4 * c));
+        if (a.out_f32) *reinterpret_cast<float4*>(a.out_f32 + (size_t)r * H + 4 * c) = y;
+        if (a.out_bf16) {
+          const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+          uint2 pk;
+          pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+          pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(a.out_bf16 + (size_t)r * H + 4 * c) = pk;
+        }
+        if (a.wr) *reinterpret_cast<float4*>(smem + (size_t)rr * H + 4 * c) = y;
       }
-      if (a.wr) *reinterpret_cast<float4*>(smem + 4 * c) = y;
     }
   }
-  if (!a.wr) return;
-  // ---- router: k warps per expert, each a strided share of the row; partial sums meet in shared memory
+  if (!a.wr || !a.gamma) return;
+  // ---- router: k warps per expert, each a strided share of the rows; partial sums meet in shared memory
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int E = a.E;
   const int k = n_warps >= E ? n_warps / E : 1;          // warps per expert
-  float* part = smem + H;                                 // [E][k]
+  float* part = smem + (size_t)ROWS * H;                  // [ROWS][E][k]
   const TW* wr = (const TW*)a.wr;
   const bool vec = (H & 7) == 0;
   for (int job = warp; job < E * k; job += n_warps) {
     const int e = job / k, sl = job % k;
     const TW* w = wr + (size_t)e * H;
-    float acc = 0.f;
+    float acc[ROWS];
+#pragma unroll
+    for (int rr = 0; rr < ROWS; ++rr) acc[rr] = 0.f;
     if (vec) {
-#pragma unroll 4
+#pragma unroll 8
       for (int d = (sl * 32 + lane) * 8; d < H; d += k * 256) {
         float wv[8];
         load_w8(w + d, wv);
-        const float4 x0 = ld4(smem + d), x1 = ld4(smem + d + 4);
-        acc = fmaf(x0.x, wv[0], acc); acc = fmaf(x0.y, wv[1], acc); acc = fmaf(x0.z, wv[2], acc); acc = fmaf(x0.w, wv[3], acc);
-        acc = fmaf(x1.x, wv[4], acc); acc = fmaf(x1.y, wv[5], acc); acc = fmaf(x1.z, wv[6], acc); acc = fmaf(x1.w, wv[7], acc);
+#pragma unroll
+        for (int rr = 0; rr < ROWS; ++rr) {
+          if (rr < rows_here) {
+            const float4 x0 = ld4(smem + (size_t)rr * H + d), x1 = ld4(smem + (size_t)rr * H + d + 4);
+            float t = acc[rr];
+            t = fmaf(x0.x, wv[0], t); t = fmaf(x0.y, wv[1], t); t = fmaf(x0.z, wv[2], t); t = fmaf(x0.w, wv[3], t);
+            t = fmaf(x1.x, wv[4], t); t = fmaf(x1.y, wv[5], t); t = fmaf(x1.z, wv[6], t); t = fmaf(x1.w, wv[7], t);
+            acc[rr] = t;
+          }
+        }
       }
     } else {
-      for (int d = sl * 32 + lane; d < H; d += k * 32) acc = fmaf(smem[d], to_f32(w[d]), acc);
+      for (int d = sl * 32 + lane; d < H; d += k * 32) {
+        const float wv = to_f32(w[d]);
+#pragma unroll
+        for (int rr = 0; rr < ROWS; ++rr)
+          if (rr < rows_here) acc[rr] = fmaf(smem[(size_t)rr * H + d], wv, acc[rr]);
+      }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) part[e * k + sl] = acc;
+#pragma unroll
+    for (int rr = 0; rr < ROWS; ++rr) {
+      const float t = warp_sum(acc[rr]);
+      if (lane == 0) part[(rr * E + e) * k + sl] = t;
+    }
   }
   __syncthreads();
-  if (threadIdx.x != 0) return;
-  float* s = smem;                                        // the row is no longer needed
+  // selection: one warp per row.  Up to 32 experts sit one per lane (argmax and the masked sums by
+  // shuffle); more experts are handled by lane 0 alone.
+  if (warp >= rows_here) return;
+  const int rr = warp;
+  const int r = blockIdx.x * ROWS + rr;
+  if (E <= 32) {
+    float sv = -INFINITY;
+    if (lane < E) {
+      sv = 0.f;
+      for (int i = 0; i < k; ++i) sv += part[(rr * E + lane) * k + i];    // fixed order
+    }
+    int excluded = -1;
+    for (int round = 0; round < 2; ++round) {
+      // arg-max over lanes, lowest index on ties
+      float m = (lane < E && lane != excluded) ? sv : -INFINITY;
+      int im = lane;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, im, o);
+        if (om > m || (om == m && oi < im)) { m = om; im = oi; }
+      }
+      float term = 0.f;
+      if (lane < E && lane != excluded) {
+        const float factor = fmaxf(fabsf(sv), m);
+        if (!(((m - sv) / factor) > 2.0f * a.jitter_eps)) term = expf(sv - m);
+      }
+      // the sum in lane order, so that it does not depend on the shuffle tree
+      float denom = 0.f;
+      for (int e = 0; e < E; ++e) denom += __shfl_sync(0xffffffffu, term, e);
+      if (lane == 0) {
+        a.expert_ids[2 * r + round] = im;
+        a.gates[2 * r + round] = 1.0f / denom;
+      }
+      excluded = im;
+    }
+    return;
+  }
+  if (lane != 0) return;
+  float* s = smem + (size_t)rr * H;                       // the rows are no longer needed
   for (int e = 0; e < E; ++e) {
     float t = 0.f;
-    for (int i = 0; i < k; ++i) t += part[e * k + i];    // fixed order
+    for (int i = 0; i < k; ++i) t += part[(rr * E + e) * k + i];    // fixed order
     s[e] = t;
   }
   int excluded = -1;
@@ -202,9 +262,18 @@ row_norm_kernel(const RowArgs a) {
   }
 }
 
-template <int VPT, typename TW>
+template <int VPT, typename TW, int ROWS>
 int launch_row(const RowArgs& a, int rows, int threads, size_t smem, cudaStream_t stream) {
-  launch_pdl(row_norm_kernel<VPT, TW>, dim3(rows), dim3(threads), smem, stream, a);
+  if (smem > 48 * 1024) {
+    static bool configured = false;   // per instantiation
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(row_norm_kernel<VPT, TW, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           200 * 1024);
+      if (e != cudaSuccess) return fail("row_norm: cannot raise shared memory: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+  }
+  launch_pdl(row_norm_kernel<VPT, TW, ROWS>, dim3((rows + ROWS - 1) / ROWS), dim3(threads), smem, stream, a, rows);
   return check_launch("row_norm");
 }
 }  // namespace
@@ -237,17 +306,25 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   a.wr = wr; a.E = E; a.jitter_eps = jitter_eps; a.expert_ids = expert_ids; a.gates = gates;
   a.H = H;
   const int n4 = H / 4;
-  int threads = ((n4 + 31) / 32) * 32;
+  // few rows: a wide block per row (more warps share the router's rows); many rows: narrow blocks
+  // with four vectors per thread, so that several blocks fit an SM and hide each other's latency
+  int threads = rows < 148 ? ((n4 + 31) / 32) * 32 : ((n4 / 4 + 31) / 32) * 32;
   if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
   if (wr && threads < 128) threads = 128;               // a few warps for the router's dot products
   const int vpt = (n4 + threads - 1) / threads;
   const int n_warps = threads / 32;
   const int k = wr ? (n_warps >= E ? n_warps / E : 1) : 0;
-  const size_t smem = wr ? (size_t)(H + E * k) * sizeof(float) : 0;
+  // long batches with a router: four rows per block share each read of the router's rows
+  const int rpb = (wr && rows >= 256 && (size_t)(4 * H + 4 * E * k) * sizeof(float) <= 160 * 1024) ? 4 : 1;
+  const size_t smem = wr ? (size_t)(rpb * H + rpb * E * k) * sizeof(float) : 0;
 #define GO(V)                                                                                             \
-  (wr && w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16>(a, rows, threads, smem, stream)             \
-                               : launch_row<V, float>(a, rows, threads, smem, stream))
-  if (smem > 48 * 1024) return fail("row_norm: width %d is too large for the fused router", H);
+  (rpb == 4 ? (w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16, 4>(a, rows, threads, smem, stream)    \
+                                     : launch_row<V, float, 4>(a, rows, threads, smem, stream))           \
+            : (wr && w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16, 1>(a, rows, threads, smem, stream) \
+                                           : launch_row<V, float, 1>(a, rows, threads, smem, stream)))
+  if (smem > 200 * 1024) return fail("row_norm: width %d is too large for the fused router", H);
+  if (rpb > threads / 32) return fail("row_norm: too few warps for %d rows per block", rpb);
   switch (vpt) {
     case 1: return GO(1);
     case 2: return GO(2);

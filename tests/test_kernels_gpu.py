@@ -65,7 +65,8 @@ def test_norm(ops, ref, mode, bias, T, H):
 
 
 @pytest.mark.parametrize("T,H,E,wd", [(1, 4096, 16, torch.bfloat16), (9, 96, 6, torch.float32), (33, 64, 4, torch.bfloat16),
-                                      (5, 1000, 7, torch.float32), (3, 8192, 16, torch.bfloat16), (2, 2052, 3, torch.float32)])
+                                      (5, 1000, 7, torch.float32), (3, 8192, 16, torch.bfloat16), (2, 2052, 3, torch.float32),
+                                      (301, 4096, 16, torch.bfloat16), (258, 96, 6, torch.float32)])
 @pytest.mark.parametrize("mode", ["layer", "rms"])
 def test_row_norm_with_pending_additions_and_router(ops, ref, T, H, E, wd, mode):
     """The fused row kernel beside the separate references: split-K partial sums + bias, the gated sum
