@@ -244,4 +244,36 @@ extern "C" int flint_add_partials(float* x, const float* partials, int n_partial
   return check_launch("add_partials");
 }
 
+// out[r, i] = act(sum_z p[z][r, i]) * sum_z p[z][r, I + i]: the epilogue of a gated product whose K range
+// was split (p: [S, rows, 2I] float32 partial sums, gate columns before up columns).
+template <typename TO>
+__global__ void gated_act_kernel(const float* __restrict__ p, int S, long long stride, TO* __restrict__ out,
+                                 int rows, int I, int act) {
+  pdl_launch();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * I) return;
+  const int r = (int)(i / I), c = (int)(i % I);
+  float g = 0.f, u = 0.f;
+  for (int z = 0; z < S; ++z) {
+    const float* row = p + (size_t)z * stride + (size_t)r * 2 * I;
+    g += row[c];
+    u += row[I + c];
+  }
+  const float a = act == 0 ? g / (1.0f + expf(-g))
+                           : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  out[i] = from_f32<TO>(a * u);
+}
+
+extern "C" int flint_gated_act(const float* partials, int S, long long stride, void* out, int out_dtype, int rows,
+                               int I, int act, cudaStream_t stream) {
+  const long long n = (long long)rows * I;
+  if (n <= 0) return 0;
+  if (S < 1) return fail("gated_act: needs at least one partial");
+  FLINT_DISPATCH_DTYPE(out_dtype, TO,
+      launch_pdl(gated_act_kernel<TO>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, partials, S, stride,
+                 (TO*)out, rows, I, act));
+  return check_launch("gated_act");
+}
+
 extern "C" const char* flint_elementwise_last_error() { return g_error; }

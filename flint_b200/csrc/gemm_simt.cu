@@ -30,7 +30,7 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
                  TO* __restrict__ out, int ldo, int accumulate, int act,
                  const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                  const int* __restrict__ n_tiles, const int* __restrict__ offsets, int tile_rows,
-                 int M, int N, int K) {
+                 long long expert_stride, int M, int N, int K) {
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   __shared__ float us[GATED ? BK : 1][BN + 4];
@@ -43,8 +43,8 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
     row_end = min(offsets[expert + 1], row0 + tile_rows);
   }
   const int col0 = blockIdx.x * BN;
-  const TW* we = w + (size_t)expert * N * K;
-  const TW* ue = GATED ? w_up + (size_t)expert * N * K : nullptr;
+  const TW* we = w + (size_t)expert * expert_stride;
+  const TW* ue = GATED ? w_up + (size_t)expert * expert_stride : nullptr;
 
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
   float acc[4][4] = {}, acc_u[GATED ? 4 : 1][4] = {};
@@ -101,17 +101,21 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
 }
 }  // namespace
 
-// x [rows, K] (row stride ldx), w / w_up [E, N, K], out [rows, N] (row stride ldo).
+// x [rows, K] (row stride ldx), w [E, N, K] (gated: [E, 2N, K], gate rows then up rows), out [rows, N].
 // Dense: tile_expert == NULL, rows = M, one "expert".  Grouped: rows of expert e are
 // offsets[e] .. offsets[e+1]-1, and tile i covers up to tile_rows (<= 64) rows from tile_row0[i] of
 // expert tile_expert[i]; only the first *n_tiles tiles exist (max_tiles bounds the grid).
-extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* w, const void* w_up,
+extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* w, int gated,
                                int w_dtype, const float* bias, void* out, int out_dtype, int ldo,
                                int accumulate, int act, const int* tile_expert,
                                const int* tile_row0, const int* n_tiles, const int* offsets,
                                int max_tiles, int tile_rows, int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return fail("gemm_simt: K=%d", K);
+  // gated: each expert's block of w is N gate rows followed by N up rows
+  const size_t esize = w_dtype == FLINT_F32 ? 4 : 2;
+  const void* w_up = gated ? (const void*)((const char*)w + (size_t)N * K * esize) : nullptr;
+  const long long expert_stride = (long long)(gated ? 2 : 1) * N * K;
   if (w_up && accumulate) return fail("gemm_simt: a gated product cannot accumulate");
   if (tile_expert && (tile_rows < 1 || tile_rows > BM)) return fail("gemm_simt: row tiles of %d rows (1..%d)", tile_rows, BM);
   const int tiles_m = tile_expert ? max_tiles : (M + BM - 1) / BM;
@@ -123,11 +127,11 @@ extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* 
     if (w_up)                                                                                     \
       gemm_simt_kernel<TX, TW, TO, true><<<grid, THREADS, 0, stream>>>(                           \
           (const TX*)x, ldx, (const TW*)w, (const TW*)w_up, bias, (TO*)out, ldo, accumulate, act, \
-          tile_expert, tile_row0, n_tiles, offsets, tile_rows, M, N, K);                                     \
+          tile_expert, tile_row0, n_tiles, offsets, tile_rows, expert_stride, M, N, K);                                     \
     else                                                                                          \
       gemm_simt_kernel<TX, TW, TO, false><<<grid, THREADS, 0, stream>>>(                          \
           (const TX*)x, ldx, (const TW*)w, nullptr, bias, (TO*)out, ldo, accumulate, act,         \
-          tile_expert, tile_row0, n_tiles, offsets, tile_rows, M, N, K);                                     \
+          tile_expert, tile_row0, n_tiles, offsets, tile_rows, expert_stride, M, N, K);                                     \
   } while (0)
   FLINT_DISPATCH_DTYPE(x_dtype, TX, FLINT_DISPATCH_DTYPE(w_dtype, TW,
       FLINT_DISPATCH_DTYPE(out_dtype, TO, LAUNCH(TX, TW, TO))));

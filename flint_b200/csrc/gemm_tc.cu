@@ -58,6 +58,8 @@ struct Params {
   int rows, N, K;
   int kb_per_split, splits, stages;
   int defer;                   // write raw partial tiles even for a single split; the consumer sums them
+  int w_expert_rows;           // rows between two experts in the stacked weight tensor
+  int up_row_offset;           // gated: rows from an expert's gate rows to its up rows
 };
 
 // Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = bn.
@@ -91,7 +93,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     row_end = p.offsets[expert + 1];
   }
   const int f0 = blockIdx.x * BM;                 // first feature of the tile inside the expert
-  const int w_row = expert * p.N + f0;            // row in the stacked weight tensor
+  const int w_row = expert * p.w_expert_rows + f0;   // row in the stacked weight tensor
+  const int u_row = w_row + p.up_row_offset;
   const int total_kb = (p.K + BK - 1) / BK;
   const int kb0 = blockIdx.z * p.kb_per_split;
   const int nkb = min(total_kb, kb0 + p.kb_per_split) - kb0;
@@ -130,7 +133,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_expect_tx(bar, STAGE_BYTES);
       const int kx = (kb0 + i) * BK;
       tma_load_2d(a, &map_w, kx, w_row, bar);
-      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w_row, bar);
+      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, u_row, bar);
     }
     pdl_wait();
     for (int i = 0; i < head; ++i)
@@ -143,7 +146,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_expect_tx(bar, STAGE_BYTES);
       const int kx = (kb0 + i) * BK;
       tma_load_2d(a, &map_w, kx, w_row, bar);
-      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w_row, bar);
+      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, u_row, bar);
       tma_load_2d(a + A_BYTES * (GATED ? 2 : 1), &map_x, kx, row0, bar);
     }
   } else if (warp == 1 && lane == 0) {
@@ -318,14 +321,15 @@ extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
   return splits > 1 ? (long long)splits * rows * N : 0;
 }
 
-// x [rows, K] bf16 with row stride ldx; w / w_up [E, N, K] bf16 (E = 1 when dense); out [rows, N].
+// x [rows, K] bf16 with row stride ldx; w [E, N, K] bf16 (E = 1 when dense), or, gated, [E, 2N, K] with each
+// expert's N gate rows before its N up rows; out [rows, N].
 // bn: token rows per tile (16, 32, 64, 128 or 256); with a tile map it must equal the plan's tile size.
 // splits > 1 divides the K blocks over several CTAs and needs `partial` (not with a gated product).
 // defer: leave the raw partial sums [splits, rows, N] in `partial` (no bias, nothing added to out);
 // the caller's next kernel adds them up.  The number of splits used is ceil(kb / ceil(kb / splits))
 // with kb = ceil(K / 64).
 // error_flag: device int, set to 1 if a bounded wait ran out.
-extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* w_up, const float* bias, void* out,
+extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, const float* bias, void* out,
                              int out_dtype, int ldo, int accumulate, int act, const int* tile_expert,
                              const int* tile_row0, const int* n_tiles, const int* offsets, int max_tiles,
                              int n_experts, int rows, int N, int K, int bn, int splits, float* partial,
@@ -333,8 +337,9 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
   if (rows <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
-  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || (w_up && ((uintptr_t)w_up & 15)))
-    return fail("gemm_tc: operands must be 16-byte aligned");
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
+  const bool w_up = gated != 0;            // gated: each expert's block is N gate rows, then N up rows
+  const int w_expert_rows = gated ? 2 * N : N;
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("gemm_tc: bad token tile %d", bn);
   if (splits < 1) return fail("gemm_tc: bad split %d", splits);
   if ((splits > 1 || defer) && (w_up || !partial)) return fail("gemm_tc: partial sums need scratch and cannot be gated");
@@ -348,9 +353,8 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
   if (tiles_n > 65535) return fail("gemm_tc: %d row tiles exceed the grid limit", tiles_n);
 
   CUtensorMap mw, mu, mx;
-  if (int rc = weight_map(&mw, w, (long long)n_experts * N, K)) return rc;
-  if (w_up) { if (int rc = weight_map(&mu, w_up, (long long)n_experts * N, K)) return rc; }
-  else mu = mw;
+  if (int rc = weight_map(&mw, w, (long long)n_experts * w_expert_rows, K)) return rc;
+  mu = mw;
   if (int rc = make_map(&mx, x, rows, K, ldx, bn)) return rc;
 
   Params p;
@@ -360,7 +364,8 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, const void* 
   p.out_dtype = out_dtype; p.ldo = ldo; p.accumulate = accumulate; p.act = act;
   p.rows = rows; p.N = N; p.K = K;
   p.kb_per_split = kbps; p.splits = splits; p.defer = defer;
-  p.stages = flint_gemm_tc_stages(bn, w_up != nullptr);
+  p.w_expert_rows = w_expert_rows; p.up_row_offset = gated ? N : 0;
+  p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
   if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;
   dim3 grid((N + BM - 1) / BM, tiles_n, splits);
   int rc;

@@ -264,40 +264,49 @@ class CudaOps:
     # ------------------------------------------------------------------ matrix products
     def gemm(self, x, w, out, bias=None, accumulate=False):
         """out = x @ w.T (+ bias) (+ out).  x [M,K], w [N,K], out [M,N]."""
-        self._gemm(x, w, None, out, bias, accumulate, "silu", None)
+        self._gemm(x, w, False, out, bias, accumulate, "silu", None)
 
-    def gated_gemm(self, x, w_gate, w_up, out, act="silu", plan: MoePlan | None = None):
-        """out = act(x @ w_gate.T) * (x @ w_up.T); with a plan, rows are grouped by expert
-        and the weights are [E, N, K]."""
-        self._gemm(x, w_gate, w_up, out, None, False, act, plan)
+    def gated_gemm(self, x, w13, out, act="silu", plan: MoePlan | None = None):
+        """out = act(x @ Wg.T) * (x @ Wu.T) with the gate rows Wg stacked before the up rows Wu:
+        w13 [2N, K], or with a plan (rows grouped by expert) [E, 2N, K]."""
+        self._gemm(x, w13, True, out, None, False, act, plan)
 
     def grouped_gemm(self, x, w, out, plan: MoePlan):
         """out[r] = x[r] @ w[expert of row r].T; w [E, N, K]."""
-        self._gemm(x, w, None, out, None, False, "silu", plan)
+        self._gemm(x, w, False, out, None, False, "silu", plan)
 
-    def gemm_partials(self, x, w, splits=None):
+    def gemm_partials(self, x, w, splits=None, plan: MoePlan | None = None):
         """x @ w.T left as S partial sums over pieces of the K range: float32 [S, M, N], no bias.
-        The next kernel (rotary write, row norm) adds them up; S is 1 when nothing was split."""
+        The next kernel (rotary write, row norm, gated activation) adds them up; S is 1 when nothing
+        was split.  With a plan, rows are grouped by expert and w is [E, N, K]."""
         _check(x, "x", dims=2)
-        _check(w, "w", dims=2)
+        _check(w, "w")
         M, K = x.shape
-        N = w.shape[0]
-        if w.shape[1] != K:
+        N = w.shape[-2]
+        if w.shape[-1] != K or (plan is None) != (w.dim() == 2):
             raise KernelError("gemm_partials: shapes do not match")
-        if not self.tensor_core_ok(x, w):
+        if not self.tensor_core_ok(x, w, plan):
             out = torch.empty((1, M, N), dtype=torch.float32, device=x.device)
-            self._gemm_simt(x, w, None, out[0], None, False, 0, None, M, N, K)
+            self._gemm_simt(x, w, False, out[0], None, False, 0, plan, M, N, K)
             return out
-        bn = self.token_tile(M)
-        splits = splits or self._k_splits(M, N, K, bn)
         kb = -(-K // 64)
+        if plan is None:
+            bn, E = self.token_tile(M), 1
+            splits = splits or self._k_splits(M, N, K, bn)
+        else:
+            bn, E = plan.tile_rows, plan.n_experts
+            # the number of row tiles is known on the device only: assume the rows spread over
+            # min(rows, experts) experts
+            tiles = -(-N // 128) * max(1, min(M, E))
+            splits = splits or (1 if tiles >= 148 or kb < 8 else max(1, min(296 // tiles, kb // 4, 16)))
         kbps = -(-kb // splits)
         splits = -(-kb // kbps)
         out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
-        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), _ptr(None), _ptr(None),
-                  _ptr(out), c_int(F32), c_int(N), c_int(0), c_int(0), _ptr(None), _ptr(None), _ptr(None), _ptr(None),
-                  c_int(0), c_int(1), c_int(M), c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1),
-                  _ptr(self.tc_error))
+        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(0), _ptr(None),
+                  _ptr(out), c_int(F32), c_int(N), c_int(0), c_int(0), _ptr(plan.tile_expert if plan else None),
+                  _ptr(plan.tile_row0 if plan else None), _ptr(plan.n_tiles if plan else None),
+                  _ptr(plan.offsets if plan else None), c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M),
+                  c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1), _ptr(self.tc_error))
         return out
 
     @staticmethod
@@ -307,9 +316,11 @@ class CudaOps:
         kb = -(-K // 64)
         if tiles >= 148 or kb < 8:
             return 1
-        return max(1, min(-(-296 // tiles), kb // 4, 16))
+        # as many pieces as still fit one wave of two blocks per SM (a second, partial wave would
+        # cost as much as a full one)
+        return max(1, min(296 // tiles, kb // 4, 16))
 
-    def _gemm(self, x, w, w_up, out, bias, accumulate, act, plan):
+    def _gemm(self, x, w, gated, out, bias, accumulate, act, plan):
         _check(x, "x", dims=2, contiguous=False)
         _check(out, "out", dims=2, contiguous=False)
         if x.stride(1) != 1 or out.stride(1) != 1:
@@ -319,24 +330,31 @@ class CudaOps:
         if plan is None:
             if w.dim() != 2:
                 raise KernelError("gemm: dense weights must be [N, K]")
-            N = w.shape[0]
-        else:
-            if w.dim() != 3 or w.shape[0] != plan.n_experts:
-                raise KernelError("gemm: grouped weights must be [E, N, K]")
-            N = w.shape[1]
+        elif w.dim() != 3 or w.shape[0] != plan.n_experts:
+            raise KernelError("gemm: grouped weights must be [E, N, K]")
+        N = w.shape[-2] // 2 if gated else w.shape[-2]
+        if gated and w.shape[-2] % 2:
+            raise KernelError("gemm: stacked gate/up weights need an even number of rows")
         if w.shape[-1] != K or tuple(out.shape) != (M, N):
             raise KernelError(f"gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
-        if w_up is not None and (w_up.shape != w.shape or w_up.dtype != w.dtype):
-            raise KernelError("gemm: gate and up weights must match")
         if bias is not None:
             _check(bias, "bias", torch.float32, 1)
             if bias.numel() != N:
                 raise KernelError("gemm: bias length does not match")
         act_code = {"silu": 0, "gelu_pytorch_tanh": 1}[act]
         if self.tensor_core_ok(x, w, plan):
-            self._gemm_tc(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+            if gated and M <= 128:
+                # few rows: the product is bound by streaming the weights, and a gated tile cannot split
+                # its K range; run it as a plain product over the 2N stacked rows, split over K, and apply
+                # the activation to the summed partial tiles
+                parts = self.gemm_partials(x, w, plan=plan)
+                self._run("elementwise", "flint_gated_act", _ptr(parts), c_int(parts.shape[0]),
+                          c_longlong(parts.stride(0)), _ptr(out), c_int(_code(out.dtype)), c_int(M), c_int(N),
+                          c_int(act_code))
+                return
+            self._gemm_tc(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K)
         else:
-            self._gemm_simt(x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K)
+            self._gemm_simt(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K)
 
     # bfloat16 x bfloat16 with 16-byte aligned rows goes to the tensor cores; everything else
     # (float32 operands: the true 32-bit path; odd K) to the float32 pipes
@@ -358,28 +376,28 @@ class CudaOps:
             return 64
         return self.token_tile(-(-2 * n_tokens // n_experts), gated=True)
 
-    def _gemm_tc(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
+    def _gemm_tc(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None:
             bn, splits, E = plan.tile_rows, 1, plan.n_experts
         else:
             E = 1
-            bn = self.token_tile(M, gated=w_up is not None)
-            splits = 1 if w_up is not None else self._k_splits(M, N, K, bn)
+            bn = self.token_tile(M, gated=gated)
+            splits = 1 if gated else self._k_splits(M, N, K, bn)
         partial = None
         if splits > 1:
             partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
-        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), _ptr(w_up), _ptr(bias),
+        self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(1 if gated else 0), _ptr(bias),
                   _ptr(out), c_int(_code(out.dtype)), c_int(out.stride(0)), c_int(1 if accumulate else 0),
                   c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
                   c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
                   c_int(splits), _ptr(partial), c_int(0), _ptr(self.tc_error))
 
-    def _gemm_simt(self, x, w, w_up, out, bias, accumulate, act_code, plan, M, N, K):
+    def _gemm_simt(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None and plan.tile_rows > 64:
             raise KernelError("gemm_simt: the plan's row tiles must not exceed 64 rows")
         self._run("gemm_simt", "flint_gemm_simt", _ptr(x), c_int(_code(x.dtype)), c_int(x.stride(0)), _ptr(w),
-                  _ptr(w_up), c_int(_code(w.dtype)), _ptr(bias), _ptr(out), c_int(_code(out.dtype)),
+                  c_int(1 if gated else 0), c_int(_code(w.dtype)), _ptr(bias), _ptr(out), c_int(_code(out.dtype)),
                   c_int(out.stride(0)), c_int(1 if accumulate else 0), c_int(act_code),
                   _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),

@@ -32,16 +32,17 @@ class GatedMLP(FeedForward):
 
     def load(self, t):
         dt = matmul_dtype(*t.values())
-        self.w_gate, self.w_up, self.w_down = (t[k].to(dt) for k in
-                                               ("gate_proj.weight", "up_proj.weight", "down_proj.weight"))
+        # the gate rows are stacked before the up rows: one product gives both
+        self.w_gate_up = torch.cat([t["gate_proj.weight"].to(dt), t["up_proj.weight"].to(dt)], 0).contiguous()
+        self.w_down = t["down_proj.weight"].to(dt)
 
     def input_dtypes(self):
-        return (self.w_gate.dtype,)
+        return (self.w_gate_up.dtype,)
 
     def forward(self, x, residual, step):
-        xin = x[self.w_gate.dtype]
-        a = torch.empty((xin.shape[0], self.inter), dtype=self.w_gate.dtype, device=xin.device)
-        self.ops.gated_gemm(xin, self.w_gate, self.w_up, a, self.act)
+        xin = x[self.w_gate_up.dtype]
+        a = torch.empty((xin.shape[0], self.inter), dtype=self.w_gate_up.dtype, device=xin.device)
+        self.ops.gated_gemm(xin, self.w_gate_up, a, self.act)
         self.ops.gemm(a, self.w_down, residual, accumulate=True)
 
 
@@ -72,11 +73,13 @@ class SparseMixerMoE(FeedForward):
     def load(self, t):
         self.w_router = t["gate.weight"]
         dt = matmul_dtype(*(t[k] for k in t if k.startswith("experts.")))
-        stack = lambda n: torch.stack([t[f"experts.{e}.{n}.weight"].to(dt) for e in range(self.E)], 0).contiguous()
-        self.w1, self.w3, self.w2 = stack("w1"), stack("w3"), stack("w2")
+        # per expert the gate rows (w1) are stacked before the up rows (w3): [E, 2I, H]
+        self.w13 = torch.stack([torch.cat([t[f"experts.{e}.w1.weight"].to(dt), t[f"experts.{e}.w3.weight"].to(dt)], 0)
+                                for e in range(self.E)], 0).contiguous()
+        self.w2 = torch.stack([t[f"experts.{e}.w2.weight"].to(dt) for e in range(self.E)], 0).contiguous()
 
     def input_dtypes(self):
-        return (torch.float32, self.w1.dtype)
+        return (torch.float32, self.w13.dtype)
 
     def router_request(self, n_rows):
         """Routing can ride on the norm before this part (the normalised row is in registers there)."""
@@ -85,11 +88,11 @@ class SparseMixerMoE(FeedForward):
                              torch.empty((n_rows, 2), dtype=torch.float32, device=dev))
 
     def input_dtypes_when_routed(self):
-        return (self.w1.dtype,)
+        return (self.w13.dtype,)
 
     def forward(self, x, residual, step, routed=None):
         ops = self.ops
-        xa = x[self.w1.dtype]
+        xa = x[self.w13.dtype]
         T = xa.shape[0]
         dev = xa.device
         if routed is not None:
@@ -98,11 +101,11 @@ class SparseMixerMoE(FeedForward):
             ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
             gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
             ops.router_sparsemixer(x[torch.float32], self.w_router, self.eps, ids, gates)
-        plan = ops.moe_plan(ids, self.E, ops.moe_tile_rows(T, self.E, self.w1.dtype))
+        plan = ops.moe_plan(ids, self.E, ops.moe_tile_rows(T, self.E, self.w13.dtype))
         xs = torch.empty((2 * T, self.hidden), dtype=xa.dtype, device=dev)
         ops.gather_rows(xa, plan.token_of, xs)
-        a = torch.empty((2 * T, self.inter), dtype=self.w1.dtype, device=dev)
-        ops.gated_gemm(xs, self.w1, self.w3, a, self.act, plan)
+        a = torch.empty((2 * T, self.inter), dtype=self.w13.dtype, device=dev)
+        ops.gated_gemm(xs, self.w13, a, self.act, plan)
         y = torch.empty((2 * T, self.hidden), dtype=torch.float32, device=dev)
         ops.grouped_gemm(a, self.w2, y, plan)
         if step.record is not None:

@@ -127,14 +127,16 @@ class RefOps:
         off = plan.offsets.tolist()
         return [(e, off[e], off[e + 1]) for e in range(plan.n_experts) if off[e + 1] > off[e]]
 
-    def gated_gemm(self, x, w_gate, w_up, out, act="silu", plan=None):
+    def gated_gemm(self, x, w13, out, act="silu", plan=None):
+        """w13: the gate rows stacked before the up rows, [2N, K] or [E, 2N, K]."""
         xs = x.to(self.cd)
+        n = w13.shape[-2] // 2
         if plan is None:
-            out.copy_((_act(xs @ w_gate.to(self.cd).T, act) * (xs @ w_up.to(self.cd).T)).to(out.dtype))
+            out.copy_((_act(xs @ w13[:n].to(self.cd).T, act) * (xs @ w13[n:].to(self.cd).T)).to(out.dtype))
             return
         for e, lo, hi in self._rows_by_expert(plan):
-            g = xs[lo:hi] @ w_gate[e].to(self.cd).T
-            u = xs[lo:hi] @ w_up[e].to(self.cd).T
+            g = xs[lo:hi] @ w13[e, :n].to(self.cd).T
+            u = xs[lo:hi] @ w13[e, n:].to(self.cd).T
             out[lo:hi] = (_act(g, act) * u).to(out.dtype)
 
     def grouped_gemm(self, x, w, out, plan):

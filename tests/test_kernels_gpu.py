@@ -205,14 +205,15 @@ def test_gated_and_grouped(ops, ref, act, dtype):
     assert torch.equal(xs.cpu(), x[token_of])
     w1, w3, w2 = (rnd(E, I, H, dtype=dtype, seed=1, scale=0.1), rnd(E, I, H, dtype=dtype, seed=2, scale=0.1),
                   rnd(E, H, I, dtype=dtype, seed=3, scale=0.1))
+    w13 = torch.cat([w1, w3], 1).contiguous()          # per expert: gate rows, then up rows
     a = torch.empty(2 * T, I, dtype=dtype, device=DEV)
-    ops.gated_gemm(xs, w1.to(DEV), w3.to(DEV), a, act, plan)
+    ops.gated_gemm(xs, w13.to(DEV), a, act, plan)
     # the reference works on the same row order
     from flint_b200.csrc.ops import MoePlan
     cplan = MoePlan(E, 64, plan.max_tiles, *(t.cpu() for t in (plan.counts, plan.offsets, plan.row_of, plan.token_of,
                                                              plan.tile_expert, plan.tile_row0, plan.n_tiles)))
     ea = torch.zeros(2 * T, I, dtype=torch.float64)
-    ref.gated_gemm(xs.cpu(), w1, w3, ea, act, cplan)
+    ref.gated_gemm(xs.cpu(), w13, ea, act, cplan)
     tol = (1e-5, 1e-4) if dtype == torch.float32 else (2e-2, 2e-2)
     close(a, ea, *tol)
     y = torch.empty(2 * T, H, device=DEV)
@@ -229,10 +230,23 @@ def test_gated_and_grouped(ops, ref, act, dtype):
     close(h, eh, 1e-5, 1e-5)
     # dense gated product (one "expert")
     d = torch.empty(T, I, dtype=dtype, device=DEV)
-    ops.gated_gemm(x.to(DEV), w1[0].to(DEV), w3[0].to(DEV), d, act)
+    ops.gated_gemm(x.to(DEV), w13[0].to(DEV), d, act)
     ed = torch.zeros(T, I, dtype=torch.float64)
-    ref.gated_gemm(x, w1[0], w3[0], ed, act)
+    ref.gated_gemm(x, w13[0], ed, act)
     close(d, ed, *tol)
+    # few rows: the split path (plain product over the stacked rows, then the activation)
+    for rows in (1, 9):
+        ids_s = ids[:rows].contiguous()
+        plan_s = ops.moe_plan(ids_s.to(DEV), E, ops.moe_tile_rows(rows, E, dtype))
+        xs_s = torch.empty(2 * rows, H, dtype=dtype, device=DEV)
+        ops.gather_rows(x.to(DEV), plan_s.token_of, xs_s)
+        a_s = torch.empty(2 * rows, I, dtype=dtype, device=DEV)
+        ops.gated_gemm(xs_s, w13.to(DEV), a_s, act, plan_s)
+        cp = MoePlan(E, plan_s.tile_rows, plan_s.max_tiles, *(t.cpu() for t in (plan_s.counts, plan_s.offsets, plan_s.row_of,
+                     plan_s.token_of, plan_s.tile_expert, plan_s.tile_row0, plan_s.n_tiles)))
+        ea_s = torch.zeros(2 * rows, I, dtype=torch.float64)
+        ref.gated_gemm(xs_s.cpu(), w13, ea_s, act, cp)
+        close(a_s, ea_s, *tol)
 
 
 @pytest.mark.parametrize("wd", [torch.float32, torch.bfloat16])
