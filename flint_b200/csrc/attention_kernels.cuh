@@ -173,6 +173,38 @@ __global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* 
   const size_t rh = blockIdx.x;   // (index of the row in this launch) * nq + head
   const float* base = scratch + rh * n_splits * (hd + 2);
   const size_t out_rh = row_list ? (size_t)row_list[rh / nq] * nq + rh % nq : rh;
+  // up to 256 splits: the (max, sum) records are fetched side by side, and the weights
+  // e^{m_s-M} are then shared by every output dim
+  __shared__ float w_s[256];
+  __shared__ float l_s[256];
+  if (n_splits <= 256) {
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) {
+      w_s[s] = base[(size_t)s * (hd + 2) + hd];
+      l_s[s] = base[(size_t)s * (hd + 2) + hd + 1];
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int i = 0; i < n_splits; ++i) M = fmaxf(M, w_s[i]);
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_splits; s += blockDim.x) w_s[s] = w_s[s] > -INFINITY ? expf(w_s[s] - M) : 0.f;
+    __syncthreads();
+    float L = 0.f;
+    for (int i = 0; i < n_splits; ++i) L += w_s[i] * l_s[i];     // fixed order, the same in every thread
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+      float o = 0.f;
+      for (int s0 = 0; s0 < n_splits; s0 += 8) {          // eight loads in flight, added in order
+        float t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u] = s0 + u < n_splits ? base[(size_t)(s0 + u) * (hd + 2) + d] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (s0 + u < n_splits) o += w_s[s0 + u] * t[u];
+      }
+      out[out_rh * hd + d] = from_f32<TO>(o * inv);
+    }
+    return;
+  }
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, base[(size_t)s * (hd + 2) + hd]);
   float L = 0.f;

@@ -119,8 +119,15 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
   // the projection may arrive as partial sums over pieces of its K range, and without its bias:
   // they are added here in a fixed order
   auto rd = [&](size_t off, int col) {
-    float v = qkv[row_off + off];
-    for (int z = 1; z < n_partials; ++z) v += qkv[(size_t)z * partial_stride + row_off + off];
+    const float* src = qkv + row_off + off;
+    float v = 0.f;
+    for (int z0 = 0; z0 < n_partials; z0 += 8) {      // eight loads in flight, added in order
+      float t[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) t[u] = z0 + u < n_partials ? src[(size_t)(z0 + u) * partial_stride] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v += t[u];
+    }
     return bias ? v + bias[col] : v;
   };
   // with few tokens several blocks share a token (gridDim.y), each a contiguous range of items

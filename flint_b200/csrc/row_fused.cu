@@ -75,12 +75,20 @@ row_norm_kernel(const RowArgs a, int n_rows) {
     }
     const bool pending = a.partials || a.comb_y;
     if (a.partials) {
-      for (int z = 0; z < a.n_partials; ++z) {          // fixed order
-        const float* pr = a.partials + (size_t)z * a.partial_stride + (size_t)src * H;
+      const float* pr = a.partials + (size_t)src * H;
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-          const int c = threadIdx.x + i * blockDim.x;
-          if (c < n4) add4(v[i], ld4(pr + 4 * c));
+      for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n4) {
+          for (int z0 = 0; z0 < a.n_partials; z0 += 4) {      // four loads in flight, added in a fixed order
+            float4 t[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              t[u] = z0 + u < a.n_partials ? ld4(pr + (size_t)(z0 + u) * a.partial_stride + 4 * c)
+                                           : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) add4(v[i], t[u]);
+          }
         }
       }
       if (a.add_bias) {
