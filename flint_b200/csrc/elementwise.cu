@@ -120,6 +120,7 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
   // they are added here in a fixed order
   auto rd = [&](size_t off, int col) {
     const float* src = qkv + row_off + off;
+    if (n_partials == 1) return bias ? src[0] + bias[col] : src[0];
     float v = 0.f;
     for (int z0 = 0; z0 < n_partials; z0 += 8) {      // eight loads in flight, added in order
       float t[8];

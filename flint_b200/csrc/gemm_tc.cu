@@ -72,39 +72,36 @@ __device__ __forceinline__ float act_fn(float g, int act) {
   return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
 }
 
+// Persistent: a block walks over work items (feature tile, row tile, piece of K) with a stride of the
+// grid.  The TMA ring runs on across items, and the accumulator is double-buffered in tensor memory, so
+// the epilogue of one item overlaps the main loop of the next.
 template <int BN, bool GATED>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u,
                const __grid_constant__ CUtensorMap map_x, const Params p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * 16 + 1];   // full[stages], empty[stages], accumulator
+  __shared__ __align__(8) uint64_t bars[2 * 16 + 4];   // full[stages], empty[stages], acc_full[2], acc_empty[2]
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
   pdl_launch();
   if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
-  // ---- which tile
-  int expert = 0, row0 = blockIdx.y * BN, row_end = p.rows;
-  if (p.tile_expert) {
-    pdl_wait();        // the tile map comes from the routing plan of an earlier kernel
-    if ((int)blockIdx.y >= *p.n_tiles) return;
-    expert = p.tile_expert[blockIdx.y];
-    row0 = p.tile_row0[blockIdx.y];
-    row_end = p.offsets[expert + 1];
-  }
-  const int f0 = blockIdx.x * BM;                 // first feature of the tile inside the expert
-  const int w_row = expert * p.w_expert_rows + f0;   // row in the stacked weight tensor
-  const int u_row = w_row + p.up_row_offset;
+  const bool grouped = p.tile_expert != nullptr;
+  if (grouped) pdl_wait();                    // the tile map comes from the routing plan of an earlier kernel
+  const int tiles_m = (p.N + BM - 1) / BM;
+  const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
+  const int n_items = tiles_m * tiles_n * p.splits;
+  if ((int)blockIdx.x >= n_items) return;
   const int total_kb = (p.K + BK - 1) / BK;
-  const int kb0 = blockIdx.z * p.kb_per_split;
-  const int nkb = min(total_kb, kb0 + p.kb_per_split) - kb0;
 
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (GATED ? 2 * BN : BN) < 32 ? 32 : (GATED ? 2 * BN : BN);
+  constexpr uint32_t ACC_COLS = GATED ? 2 * BN : BN;                     // columns of one accumulator set
+  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // two sets; a power of two
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = p.stages;
-  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]), accum_bar = smem_u32(&bars[32]);
+  const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[16]);
+  const uint32_t acc_full0 = smem_u32(&bars[32]), acc_empty0 = smem_u32(&bars[34]);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -113,7 +110,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 128);     // every epilogue thread arrives
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), TMEM_COLS);
@@ -123,78 +123,125 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const uint32_t tmem = tmem_holder;
   volatile int* ab = &abort_flag;
 
+  // item -> (piece of K, feature tile, row tile): pieces of one tile and neighbouring feature tiles go
+  // to neighbouring blocks, which then share the activation tile in L2
+  struct Item { int kb0, nkb, f0, w_row, row0, row_end, z; };
+  auto item_of = [&](int it) {
+    Item r;
+    r.z = it % p.splits;
+    const int t = it / p.splits;
+    const int tm = t % tiles_m, tn = t / tiles_m;
+    int expert = 0;
+    r.row0 = tn * BN;
+    r.row_end = p.rows;
+    if (grouped) {
+      expert = p.tile_expert[tn];
+      r.row0 = p.tile_row0[tn];
+      r.row_end = p.offsets[expert + 1];
+    }
+    r.f0 = tm * BM;
+    r.w_row = expert * p.w_expert_rows + r.f0;
+    r.kb0 = r.z * p.kb_per_split;
+    r.nkb = min(total_kb, r.kb0 + p.kb_per_split) - r.kb0;
+    return r;
+  };
+
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- TMA producer
-    // The weights do not depend on the kernel before this one: the first ring of weight tiles is
-    // requested at once, and only the activation tiles wait for that kernel to finish.
-    const int head = nkb < stages ? nkb : stages;
-    for (int i = 0; i < head; ++i) {
-      const uint32_t a = tiles + i * STAGE_BYTES, bar = full0 + 8 * i;
-      mbar_expect_tx(bar, STAGE_BYTES);
-      const int kx = (kb0 + i) * BK;
-      tma_load_2d(a, &map_w, kx, w_row, bar);
-      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, u_row, bar);
-    }
-    pdl_wait();
-    for (int i = 0; i < head; ++i)
-      tma_load_2d(tiles + i * STAGE_BYTES + A_BYTES * (GATED ? 2 : 1), &map_x, (kb0 + i) * BK, row0, full0 + 8 * i);
-    for (int i = head; i < nkb; ++i) {
-      const int s = i % stages;
-      if (!mbar_wait(empty0 + 8 * s, ((i / stages) & 1) ^ 1, ab)) break;
-      const uint32_t a = tiles + s * STAGE_BYTES;
-      const uint32_t bar = full0 + 8 * s;
-      mbar_expect_tx(bar, STAGE_BYTES);
-      const int kx = (kb0 + i) * BK;
-      tma_load_2d(a, &map_w, kx, w_row, bar);
-      if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, u_row, bar);
-      tma_load_2d(a + A_BYTES * (GATED ? 2 : 1), &map_x, kx, row0, bar);
+    int kc = 0;                      // K blocks issued so far, over all items
+    bool first = true, ok = true;
+    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
+      const Item w = item_of(it);
+      int i = 0;
+      if (first) {
+        // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+        // requested at once, and only the activation tiles wait for that kernel to finish.
+        const int head = w.nkb < stages ? w.nkb : stages;
+        for (; i < head; ++i) {
+          const uint32_t a = tiles + i * STAGE_BYTES, bar = full0 + 8 * i;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const int kx = (w.kb0 + i) * BK;
+          tma_load_2d(a, &map_w, kx, w.w_row, bar);
+          if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w.w_row + p.up_row_offset, bar);
+        }
+        pdl_wait();
+        for (int j = 0; j < head; ++j)
+          tma_load_2d(tiles + j * STAGE_BYTES + A_BYTES * (GATED ? 2 : 1), &map_x, (w.kb0 + j) * BK, w.row0,
+                      full0 + 8 * j);
+        kc = head;
+        first = false;
+      }
+      for (; i < w.nkb; ++i, ++kc) {
+        const int s = kc % stages;
+        if (!mbar_wait(empty0 + 8 * s, ((kc / stages) & 1) ^ 1, ab)) { ok = false; break; }
+        const uint32_t a = tiles + s * STAGE_BYTES, bar = full0 + 8 * s;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int kx = (w.kb0 + i) * BK;
+        tma_load_2d(a, &map_w, kx, w.w_row, bar);
+        if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w.w_row + p.up_row_offset, bar);
+        tma_load_2d(a + A_BYTES * (GATED ? 2 : 1), &map_x, kx, w.row0, bar);
+      }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
     const uint32_t idesc = instr_desc(BN);
+    int kc = 0, j = 0;
     bool ok = true;
-    for (int i = 0; i < nkb && ok; ++i) {
-      const int s = i % stages;
-      ok = mbar_wait(full0 + 8 * s, (i / stages) & 1, ab);
+    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++j) {
+      const Item w = item_of(it);
+      const int buf = j & 1;
+      ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, ab);     // the epilogue has drained this set
       if (!ok) break;
       tc_fence_after();
-      const uint32_t a = tiles + s * STAGE_BYTES;
-      const uint32_t b = a + A_BYTES * (GATED ? 2 : 1);
+      const uint32_t acc_addr = tmem + buf * ACC_COLS;
+      for (int i = 0; i < w.nkb; ++i, ++kc) {
+        const int s = kc % stages;
+        ok = mbar_wait(full0 + 8 * s, (kc / stages) & 1, ab);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a = tiles + s * STAGE_BYTES;
+        const uint32_t b = a + A_BYTES * (GATED ? 2 : 1);
 #pragma unroll
-      for (int k = 0; k < BK / 16; ++k) {
-        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-        const uint64_t bd = smem_desc(b + k * 32);
-        umma_bf16(tmem, smem_desc(a + k * 32), bd, idesc, acc);
-        if (GATED) umma_bf16(tmem + BN, smem_desc(a + A_BYTES + k * 32), bd, idesc, acc);
+        for (int k = 0; k < BK / 16; ++k) {
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          const uint64_t bd = smem_desc(b + k * 32);
+          umma_bf16(acc_addr, smem_desc(a + k * 32), bd, idesc, acc);
+          if (GATED) umma_bf16(acc_addr + BN, smem_desc(a + A_BYTES + k * 32), bd, idesc, acc);
+        }
+        umma_commit(empty0 + 8 * s);   // frees the stage when these MMAs have read it
       }
-      umma_commit(empty0 + 8 * s);   // frees the stage when these MMAs have read it
+      if (ok) umma_commit(acc_full0 + 8 * buf);
     }
-    if (ok) umma_commit(accum_bar);
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- epilogue
-    if (mbar_wait(accum_bar, 0, ab)) {
+    const int q = warp & 3;                       // this warp's quarter of the 128 lanes
+    const bool raw = p.splits > 1 || p.defer;     // partial tile: no bias, no accumulate
+    bool waited = false;
+    int j = 0;
+    for (int it = blockIdx.x; it < n_items; it += gridDim.x, ++j) {
+      const Item w = item_of(it);
+      const int buf = j & 1;
+      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, ab)) break;
       tc_fence_after();
-      pdl_wait();                                   // before reading or writing what earlier kernels touch
-      const int q = warp & 3;                       // this warp's quarter of the 128 lanes
-      const int f = f0 + q * 32 + lane;             // output feature of this thread
+      if (!waited) { pdl_wait(); waited = true; }   // before reading or writing what earlier kernels touch
+      const int f = w.f0 + q * 32 + lane;           // output feature of this thread
       const bool f_ok = f < p.N;
-      const bool raw = p.splits > 1 || p.defer;       // partial tile: no bias, no accumulate
       const float bias = (p.bias && f_ok && !raw) ? p.bias[f] : 0.f;
-      const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
+      const uint32_t lane_addr = tmem + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 8) {
-        if (row0 + c0 >= row_end) break;            // uniform in the warp
+        if (w.row0 + c0 >= w.row_end) break;        // uniform in the warp
         float v[8], u[8];
         tmem_ld8(lane_addr + c0, v);
         if (GATED) tmem_ld8(lane_addr + BN + c0, u);
 #pragma unroll
         for (int c = 0; c < 8; ++c) {
-          const int r = row0 + c0 + c;
-          if (r >= row_end || !f_ok) continue;
+          const int r = w.row0 + c0 + c;
+          if (r >= w.row_end || !f_ok) continue;
           float y = v[c];
           if (GATED) y = act_fn(y, p.act) * u[c];
           if (raw) {
-            p.partial[((size_t)blockIdx.z * p.rows + r) * p.N + f] = y;
+            p.partial[((size_t)w.z * p.rows + r) * p.N + f] = y;
             continue;
           }
           y += bias;
@@ -208,6 +255,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
+      tc_fence_before();
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
     }
   }
   // ---- teardown: everyone meets, tensor memory is freed by the warp that took it
@@ -295,7 +344,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, 
     if (e != cudaSuccess) return fail("gemm_tc: cannot raise shared memory: %s", cudaGetErrorString(e));
     configured = true;
   }
-  launch_pdl(gemm_tc_kernel<BN, GATED>, grid, dim3(THREADS), smem, stream, mw, mu, mx, p);
+  // persistent grid: at most as many blocks as stay resident (two per SM if shared memory and tensor
+  // memory allow it), each walking over its share of the items
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  constexpr int acc_cols = 2 * (GATED ? 2 * BN : BN);
+  const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
+  const long long items = (long long)grid.x * grid.y * grid.z;
+  const unsigned blocks = (unsigned)(items < (long long)sm_count * per_sm ? items : (long long)sm_count * per_sm);
+  launch_pdl(gemm_tc_kernel<BN, GATED>, dim3(blocks), dim3(THREADS), smem, stream, mw, mu, mx, p);
   return check_launch("gemm_tc");
 }
 
@@ -350,7 +412,6 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   splits = (total_kb + kbps - 1) / kbps;            // no empty split
   const int tiles_n = tile_expert ? max_tiles : (rows + bn - 1) / bn;
   if (tiles_n <= 0) return 0;
-  if (tiles_n > 65535) return fail("gemm_tc: %d row tiles exceed the grid limit", tiles_n);
 
   CUtensorMap mw, mu, mx;
   if (int rc = weight_map(&mw, w, (long long)n_experts * w_expert_rows, K)) return rc;

@@ -55,7 +55,7 @@ __device__ __forceinline__ void load_w8(const __nv_bfloat16* p, float* f) {
 // ROWS rows per block (1, or 4 for long batches with a router, so that each router row read from L2
 // serves four tokens).
 template <int VPT, typename TW, int ROWS>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(ROWS == 4 ? 256 : 1024)
 row_norm_kernel(const RowArgs a, int n_rows) {
   extern __shared__ float smem[];          // router only: ROWS x H floats of normalised rows, then partial logits
   __shared__ float red[32];
@@ -162,49 +162,68 @@ row_norm_kernel(const RowArgs a, int n_rows) {
     }
   }
   if (!a.wr || !a.gamma) return;
-  // ---- router: k warps per expert, each a strided share of the rows; partial sums meet in shared memory
+  // ---- router: a job is (group of 4 experts, strided share of the row); a warp keeps ROWS x 4 sums, so
+  // that every value read from shared memory or from the router's rows feeds 4 multiply-adds; partial
+  // sums meet in shared memory
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int E = a.E;
-  const int k = n_warps >= E ? n_warps / E : 1;          // warps per expert
-  float* part = smem + (size_t)ROWS * H;                  // [ROWS][E][k]
+  constexpr int EG = 4;
+  const int groups = (E + EG - 1) / EG;
+  const int k = n_warps >= groups ? n_warps / groups : 1;   // warps per expert group
+  float* part = smem + (size_t)ROWS * H;                     // [ROWS][E][k]
   const TW* wr = (const TW*)a.wr;
   const bool vec = (H & 7) == 0;
-  for (int job = warp; job < E * k; job += n_warps) {
-    const int e = job / k, sl = job % k;
-    const TW* w = wr + (size_t)e * H;
-    float acc[ROWS];
+  for (int job = warp; job < groups * k; job += n_warps) {
+    const int e0 = (job / k) * EG, sl = job % k;
+    float acc[ROWS][EG];
 #pragma unroll
-    for (int rr = 0; rr < ROWS; ++rr) acc[rr] = 0.f;
+    for (int rr = 0; rr < ROWS; ++rr)
+#pragma unroll
+      for (int j = 0; j < EG; ++j) acc[rr][j] = 0.f;
     if (vec) {
-#pragma unroll 8
+#pragma unroll 2
       for (int d = (sl * 32 + lane) * 8; d < H; d += k * 256) {
-        float wv[8];
-        load_w8(w + d, wv);
+        float wv[EG][8];
+#pragma unroll
+        for (int j = 0; j < EG; ++j) {
+          if (e0 + j < E) {
+            load_w8(wr + (size_t)(e0 + j) * H + d, wv[j]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) wv[j][i] = 0.f;
+          }
+        }
 #pragma unroll
         for (int rr = 0; rr < ROWS; ++rr) {
           if (rr < rows_here) {
             const float4 x0 = ld4(smem + (size_t)rr * H + d), x1 = ld4(smem + (size_t)rr * H + d + 4);
-            float t = acc[rr];
-            t = fmaf(x0.x, wv[0], t); t = fmaf(x0.y, wv[1], t); t = fmaf(x0.z, wv[2], t); t = fmaf(x0.w, wv[3], t);
-            t = fmaf(x1.x, wv[4], t); t = fmaf(x1.y, wv[5], t); t = fmaf(x1.z, wv[6], t); t = fmaf(x1.w, wv[7], t);
-            acc[rr] = t;
+            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int j = 0; j < EG; ++j)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[rr][j] = fmaf(xv[i], wv[j][i], acc[rr][j]);
           }
         }
       }
     } else {
       for (int d = sl * 32 + lane; d < H; d += k * 32) {
-        const float wv = to_f32(w[d]);
 #pragma unroll
-        for (int rr = 0; rr < ROWS; ++rr)
-          if (rr < rows_here) acc[rr] = fmaf(smem[(size_t)rr * H + d], wv, acc[rr]);
+        for (int j = 0; j < EG; ++j) {
+          const float wv = e0 + j < E ? to_f32(wr[(size_t)(e0 + j) * H + d]) : 0.f;
+#pragma unroll
+          for (int rr = 0; rr < ROWS; ++rr)
+            if (rr < rows_here) acc[rr][j] = fmaf(smem[(size_t)rr * H + d], wv, acc[rr][j]);
+        }
       }
     }
 #pragma unroll
-    for (int rr = 0; rr < ROWS; ++rr) {
-      const float t = warp_sum(acc[rr]);
-      if (lane == 0) part[(rr * E + e) * k + sl] = t;
-    }
+    for (int rr = 0; rr < ROWS; ++rr)
+#pragma unroll
+      for (int j = 0; j < EG; ++j) {
+        const float t = warp_sum(acc[rr][j]);
+        if (lane == 0 && e0 + j < E) part[(rr * E + e0 + j) * k + sl] = t;
+      }
   }
   __syncthreads();
   // selection: one warp per row.  Up to 32 experts sit one per lane (argmax and the masked sums by
@@ -322,9 +341,10 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   if (wr && threads < 128) threads = 128;               // a few warps for the router's dot products
   const int vpt = (n4 + threads - 1) / threads;
   const int n_warps = threads / 32;
-  const int k = wr ? (n_warps >= E ? n_warps / E : 1) : 0;
+  const int groups = (E + 3) / 4;
+  const int k = wr ? (n_warps >= groups ? n_warps / groups : 1) : 0;
   // long batches with a router: four rows per block share each read of the router's rows
-  const int rpb = (wr && rows >= 256 && (size_t)(4 * H + 4 * E * k) * sizeof(float) <= 160 * 1024) ? 4 : 1;
+  const int rpb = (wr && rows >= 256 && threads <= 256 && (size_t)(4 * H + 4 * E * k) * sizeof(float) <= 160 * 1024) ? 4 : 1;
   const size_t smem = wr ? (size_t)(rpb * H + rpb * E * k) * sizeof(float) : 0;
 #define GO(V)                                                                                             \
   (rpb == 4 ? (w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16, 4>(a, rows, threads, smem, stream)    \
