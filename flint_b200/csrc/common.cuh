@@ -16,6 +16,13 @@
 
 namespace flint {
 
+// Gate and up weights of a gated feed-forward are kept paired: blocks of GATE_BLOCK gate rows alternate with
+// the GATE_BLOCK up rows of the same features, and the feature count is padded to a multiple of GATE_BLOCK with
+// zero rows.  Feature f has its gate row at paired_gate_row(f) and its up row GATE_BLOCK rows further.
+constexpr int GATE_BLOCK = 16;
+__host__ __device__ inline int paired_rows(int features) { return 2 * ((features + GATE_BLOCK - 1) / GATE_BLOCK) * GATE_BLOCK; }
+__host__ __device__ inline int paired_gate_row(int f) { return (f / GATE_BLOCK) * 2 * GATE_BLOCK + f % GATE_BLOCK; }
+
 static thread_local char g_error[512];
 
 inline int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));

@@ -81,6 +81,16 @@ extern "C" int flint_norm(const float* x, const int* row_index, const float* gam
   return check_launch("norm");
 }
 
+// four neighbouring values written with one store
+__device__ __forceinline__ void store4(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  uint2 w;
+  w.x = *reinterpret_cast<const uint32_t*>(&lo);
+  w.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(dst) = w;
+}
+
 // --------------------------------------------------------------------------- rope + kv write
 // qkv [n_partials][T, (nq+2*nkv)*hd] float32: q heads, then k heads, then v heads; the partials
 // (pieces of a split K range, partial_stride floats apart) and the bias are added on the way in.
@@ -135,6 +145,54 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
   const int n_items = heads * pairs;
   const int per_block = (n_items + gridDim.y - 1) / gridDim.y;
   const int item_end = min(n_items, (int)(blockIdx.y + 1) * per_block);
+  // fast path (one partial, head size and rotary size multiples of 8, 16-byte aligned pointers): a thread
+  // takes 4 neighbouring pairs with 16-byte loads
+  const bool aligned16 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(cos_t) |
+                           reinterpret_cast<uintptr_t>(sin_t) | reinterpret_cast<uintptr_t>(bias) |
+                           reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+                           reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
+  if (n_partials == 1 && (half & 3) == 0 && (hd & 7) == 0 && gridDim.y == 1 && aligned16) {
+    const int quads = pairs >> 2;
+    for (int item = threadIdx.x; item < heads * quads; item += blockDim.x) {
+      const int head = item / quads, i = (item % quads) * 4;      // first pair of the four
+      const bool is_q = head < nq, is_v = head >= nq + nkv;
+      int d0, d1;
+      bool rotate = false;
+      if (!is_v && i < half) { d0 = i; d1 = i + half; rotate = true; }
+      else if (is_v) { d0 = 2 * i; d1 = 2 * i + 4; }               // eight neighbouring dims
+      else { d0 = rot + 2 * (i - half); d1 = d0 + 4; }
+      const size_t base = row_off + (size_t)head * hd;
+      float4 x0 = *reinterpret_cast<const float4*>(qkv + base + d0);
+      float4 x1 = *reinterpret_cast<const float4*>(qkv + base + d1);
+      if (bias) {
+        const float4 b0 = *reinterpret_cast<const float4*>(bias + head * hd + d0);
+        const float4 b1 = *reinterpret_cast<const float4*>(bias + head * hd + d1);
+        x0.x += b0.x; x0.y += b0.y; x0.z += b0.z; x0.w += b0.w;
+        x1.x += b1.x; x1.y += b1.y; x1.z += b1.z; x1.w += b1.w;
+      }
+      if (rotate) {
+        const float4 c = *reinterpret_cast<const float4*>(cos_t + (size_t)p * half + i);
+        const float4 sn = *reinterpret_cast<const float4*>(sin_t + (size_t)p * half + i);
+        const float4 y0 = make_float4(x0.x * c.x - x1.x * sn.x, x0.y * c.y - x1.y * sn.y, x0.z * c.z - x1.z * sn.z,
+                                      x0.w * c.w - x1.w * sn.w);
+        const float4 y1 = make_float4(x1.x * c.x + x0.x * sn.x, x1.y * c.y + x0.y * sn.y, x1.z * c.z + x0.z * sn.z,
+                                      x1.w * c.w + x0.w * sn.w);
+        x0 = y0;
+        x1 = y1;
+      }
+      if (is_q) {
+        TQ* dst = q_out + ((size_t)t * nq + head) * hd;
+        store4(dst + d0, x0);
+        store4(dst + d1, x1);
+      } else if (cache_tok >= 0) {
+        const int kvh = is_v ? head - nq - nkv : head - nq;
+        TC* dst = (is_v ? v_cache : k_cache) + (cache_tok + (long long)kvh * page_size) * hd;
+        store4(dst + d0, x0);
+        store4(dst + d1, x1);
+      }
+    }
+    return;
+  }
   for (int item = blockIdx.y * per_block + threadIdx.x; item < item_end; item += blockDim.x) {
     const int head = item / pairs, i = item % pairs;
     const bool is_q = head < nq, is_v = head >= nq + nkv;
@@ -252,8 +310,9 @@ extern "C" int flint_add_partials(float* x, const float* partials, int n_partial
   return check_launch("add_partials");
 }
 
-// out[r, i] = act(sum_z p[z][r, i]) * sum_z p[z][r, I + i]: the epilogue of a gated product whose K range
-// was split (p: [S, rows, 2I] float32 partial sums, gate columns before up columns).
+// out[r, i] = act(sum_z gate[z][r, i]) * sum_z up[z][r, i]: the epilogue of a gated product whose K range was
+// split (p: [S, rows, paired_rows(I)] float32 partial sums, gate and up columns paired in blocks like the weight
+// rows that made them).
 template <typename TO>
 __global__ void gated_act_kernel(const float* __restrict__ p, int S, long long stride, TO* __restrict__ out,
                                  int rows, int I, int act) {
@@ -264,9 +323,9 @@ __global__ void gated_act_kernel(const float* __restrict__ p, int S, long long s
   const int r = (int)(i / I), c = (int)(i % I);
   float g = 0.f, u = 0.f;
   for (int z = 0; z < S; ++z) {
-    const float* row = p + (size_t)z * stride + (size_t)r * 2 * I;
-    g += row[c];
-    u += row[I + c];
+    const float* row = p + (size_t)z * stride + (size_t)r * paired_rows(I) + paired_gate_row(c);
+    g += row[0];
+    u += row[GATE_BLOCK];
   }
   const float a = act == 0 ? g / (1.0f + expf(-g))
                            : 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));

@@ -25,8 +25,7 @@ __device__ __forceinline__ float act_fn(float g, int act) {
 
 template <typename TX, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(THREADS)
-gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
-                 const TW* __restrict__ w_up, const float* __restrict__ bias,
+gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w, const float* __restrict__ bias,
                  TO* __restrict__ out, int ldo, int accumulate, int act,
                  const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
                  const int* __restrict__ n_tiles, const int* __restrict__ offsets, int tile_rows,
@@ -44,7 +43,6 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
   }
   const int col0 = blockIdx.x * BN;
   const TW* we = w + (size_t)expert * expert_stride;
-  const TW* ue = GATED ? w_up + (size_t)expert * expert_stride : nullptr;
 
   const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
   float acc[4][4] = {}, acc_u[GATED ? 4 : 1][4] = {};
@@ -57,8 +55,9 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
       xs[k][r] = (gr < row_end && gk < K) ? to_f32(x[(size_t)gr * ldx + gk]) : 0.f;
       const int gc = col0 + r;
       const bool ok = gc < N && gk < K;
-      ws[k][r] = ok ? to_f32(we[(size_t)gc * K + gk]) : 0.f;
-      if (GATED) us[k][r] = ok ? to_f32(ue[(size_t)gc * K + gk]) : 0.f;
+      const size_t wr = GATED ? paired_gate_row(gc) : gc;      // gated: the up row lies GATE_BLOCK rows further
+      ws[k][r] = ok ? to_f32(we[wr * K + gk]) : 0.f;
+      if (GATED) us[k][r] = ok ? to_f32(we[(wr + GATE_BLOCK) * K + gk]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -101,7 +100,8 @@ gemm_simt_kernel(const TX* __restrict__ x, int ldx, const TW* __restrict__ w,
 }
 }  // namespace
 
-// x [rows, K] (row stride ldx), w [E, N, K] (gated: [E, 2N, K], gate rows then up rows), out [rows, N].
+// x [rows, K] (row stride ldx), w [E, N, K] (gated: [E, paired_rows(N), K], gate and up rows paired in blocks),
+// out [rows, N].
 // Dense: tile_expert == NULL, rows = M, one "expert".  Grouped: rows of expert e are
 // offsets[e] .. offsets[e+1]-1, and tile i covers up to tile_rows (<= 64) rows from tile_row0[i] of
 // expert tile_expert[i]; only the first *n_tiles tiles exist (max_tiles bounds the grid).
@@ -112,11 +112,8 @@ extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* 
                                int max_tiles, int tile_rows, int M, int N, int K, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0) return fail("gemm_simt: K=%d", K);
-  // gated: each expert's block of w is N gate rows followed by N up rows
-  const size_t esize = w_dtype == FLINT_F32 ? 4 : 2;
-  const void* w_up = gated ? (const void*)((const char*)w + (size_t)N * K * esize) : nullptr;
-  const long long expert_stride = (long long)(gated ? 2 : 1) * N * K;
-  if (w_up && accumulate) return fail("gemm_simt: a gated product cannot accumulate");
+  const long long expert_stride = (long long)(gated ? paired_rows(N) : N) * K;
+  if (gated && accumulate) return fail("gemm_simt: a gated product cannot accumulate");
   if (tile_expert && (tile_rows < 1 || tile_rows > BM)) return fail("gemm_simt: row tiles of %d rows (1..%d)", tile_rows, BM);
   const int tiles_m = tile_expert ? max_tiles : (M + BM - 1) / BM;
   if (tiles_m <= 0) return 0;
@@ -124,13 +121,13 @@ extern "C" int flint_gemm_simt(const void* x, int x_dtype, int ldx, const void* 
   dim3 grid((N + BN - 1) / BN, tiles_m);
 #define LAUNCH(TX, TW, TO)                                                                        \
   do {                                                                                            \
-    if (w_up)                                                                                     \
+    if (gated)                                                                                    \
       gemm_simt_kernel<TX, TW, TO, true><<<grid, THREADS, 0, stream>>>(                           \
-          (const TX*)x, ldx, (const TW*)w, (const TW*)w_up, bias, (TO*)out, ldo, accumulate, act, \
+          (const TX*)x, ldx, (const TW*)w, bias, (TO*)out, ldo, accumulate, act,                  \
           tile_expert, tile_row0, n_tiles, offsets, tile_rows, expert_stride, M, N, K);                                     \
     else                                                                                          \
       gemm_simt_kernel<TX, TW, TO, false><<<grid, THREADS, 0, stream>>>(                          \
-          (const TX*)x, ldx, (const TW*)w, nullptr, bias, (TO*)out, ldo, accumulate, act,         \
+          (const TX*)x, ldx, (const TW*)w, bias, (TO*)out, ldo, accumulate, act,                  \
           tile_expert, tile_row0, n_tiles, offsets, tile_rows, expert_stride, M, N, K);                                     \
   } while (0)
   FLINT_DISPATCH_DTYPE(x_dtype, TX, FLINT_DISPATCH_DTYPE(w_dtype, TW,

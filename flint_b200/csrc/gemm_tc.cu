@@ -12,9 +12,14 @@
 // Roles (192 threads): warp 0 lane 0 issues TMA loads; warp 1 allocates tensor memory and
 // its lane 0 issues tcgen05.mma (4 of K=16 per 64-wide block) and tcgen05.commit; warps
 // 2..5 wait for the accumulator, read it with tcgen05.ld (each warp its own 32 lanes) and
-// run the epilogue: bias, SiLU/GELU gate times up (two accumulators), add to the output
-// (residual stream), narrowing to bf16, or a float32 partial tile when the K range is
-// split over several CTAs (then a second kernel sums the partials in a fixed order).
+// run the epilogue: bias, SiLU/GELU gate times up, add to the output (residual stream),
+// narrowing to bf16, or a float32 partial tile when the K range is split over several CTAs
+// (then a second kernel sums the partials in a fixed order).
+// A gated product (act(x Wg^T) * (x Wu^T)) takes its weights paired (blocks of 16 gate rows
+// alternating with the 16 up rows of the same features), so a 128-row tile holds 64 features:
+// one MMA per K step fills one accumulator whose lanes 0-15 of each warp's 32 hold gate values
+// and lanes 16-31 the up values of the same 16 features, the epilogue pairs them with one
+// shuffle, and the token tile can be as wide as for a plain product.
 // Grouped products (experts) use the same kernel: rows are sorted by expert and a tile
 // map names the expert and first row of each row tile; the experts' weights are one
 // stacked [E*N, K] tensor, so a tile that hangs over the end of an expert reads rows
@@ -41,7 +46,9 @@ using namespace flint_tc;
 
 namespace {
 
-constexpr int BM = 128;          // output features per tile (MMA M)
+constexpr int BM = 128;          // weight rows per tile (MMA M)
+constexpr int GATED_FEATURES = BM / 2;   // gated: output features per tile (their gate rows and up rows)
+static_assert(GATE_BLOCK == 16, "the gated epilogue pairs lanes l and l + 16 of a warp");
 constexpr int BK = 64;           // bf16 per K block = one 128-byte swizzle row
 constexpr int THREADS = 192;
 
@@ -59,7 +66,6 @@ struct Params {
   int kb_per_split, splits, stages;
   int defer;                   // write raw partial tiles even for a single split; the consumer sums them
   int w_expert_rows;           // rows between two experts in the stacked weight tensor
-  int up_row_offset;           // gated: rows from an expert's gate rows to its up rows
 };
 
 // Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = bn.
@@ -77,8 +83,7 @@ __device__ __forceinline__ float act_fn(float g, int act) {
 // the epilogue of one item overlaps the main loop of the next.
 template <int BN, bool GATED>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_u,
-               const __grid_constant__ CUtensorMap map_x, const Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[2 * 16 + 4];   // full[stages], empty[stages], acc_full[2], acc_empty[2]
   __shared__ uint32_t tmem_holder;
@@ -88,15 +93,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
   const bool grouped = p.tile_expert != nullptr;
   if (grouped) pdl_wait();                    // the tile map comes from the routing plan of an earlier kernel
-  const int tiles_m = (p.N + BM - 1) / BM;
+  constexpr int FM = GATED ? GATED_FEATURES : BM;      // output features per tile
+  const int tiles_m = (p.N + FM - 1) / FM;
   const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
   const int n_items = tiles_m * tiles_n * p.splits;
   if ((int)blockIdx.x >= n_items) return;
   const int total_kb = (p.K + BK - 1) / BK;
 
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
-  constexpr uint32_t STAGE_BYTES = A_BYTES * (GATED ? 2 : 1) + B_BYTES;
-  constexpr uint32_t ACC_COLS = GATED ? 2 * BN : BN;                     // columns of one accumulator set
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t ACC_COLS = BN;                                      // columns of one accumulator set
   constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // two sets; a power of two
   const uint32_t tiles = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int stages = p.stages;
@@ -125,7 +131,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   // item -> (piece of K, feature tile, row tile): pieces of one tile and neighbouring feature tiles go
   // to neighbouring blocks, which then share the activation tile in L2
-  struct Item { int kb0, nkb, f0, w_row, row0, row_end, z; };
+  // A tile that holds fewer than BN token rows (the end of an expert's rows, or of the batch) runs its MMAs
+  // with N = its rows rounded up to 16.
+  struct Item { int kb0, nkb, f0, w_row, row0, row_end, z, mma_n; };
   auto item_of = [&](int it) {
     Item r;
     r.z = it % p.splits;
@@ -139,10 +147,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       r.row0 = p.tile_row0[tn];
       r.row_end = p.offsets[expert + 1];
     }
-    r.f0 = tm * BM;
-    r.w_row = expert * p.w_expert_rows + r.f0;
+    r.f0 = tm * FM;
+    r.w_row = expert * p.w_expert_rows + tm * BM;
     r.kb0 = r.z * p.kb_per_split;
     r.nkb = min(total_kb, r.kb0 + p.kb_per_split) - r.kb0;
+    const int valid = max(1, min(BN, r.row_end - r.row0));
+    r.mma_n = (valid + 15) & ~15;
     return r;
   };
 
@@ -160,14 +170,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (; i < head; ++i) {
           const uint32_t a = tiles + i * STAGE_BYTES, bar = full0 + 8 * i;
           mbar_expect_tx(bar, STAGE_BYTES);
-          const int kx = (w.kb0 + i) * BK;
-          tma_load_2d(a, &map_w, kx, w.w_row, bar);
-          if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w.w_row + p.up_row_offset, bar);
+          tma_load_2d(a, &map_w, (w.kb0 + i) * BK, w.w_row, bar);
         }
         pdl_wait();
         for (int j = 0; j < head; ++j)
-          tma_load_2d(tiles + j * STAGE_BYTES + A_BYTES * (GATED ? 2 : 1), &map_x, (w.kb0 + j) * BK, w.row0,
-                      full0 + 8 * j);
+          tma_load_2d(tiles + j * STAGE_BYTES + A_BYTES, &map_x, (w.kb0 + j) * BK, w.row0, full0 + 8 * j);
         kc = head;
         first = false;
       }
@@ -178,13 +185,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (w.kb0 + i) * BK;
         tma_load_2d(a, &map_w, kx, w.w_row, bar);
-        if (GATED) tma_load_2d(a + A_BYTES, &map_u, kx, w.w_row + p.up_row_offset, bar);
-        tma_load_2d(a + A_BYTES * (GATED ? 2 : 1), &map_x, kx, w.row0, bar);
+        tma_load_2d(a + A_BYTES, &map_x, kx, w.row0, bar);
       }
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issuer
-    const uint32_t idesc = instr_desc(BN);
     int kc = 0, j = 0;
     bool ok = true;
     for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++j) {
@@ -194,20 +199,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc_addr = tmem + buf * ACC_COLS;
+      const uint32_t idesc = instr_desc(w.mma_n);
       for (int i = 0; i < w.nkb; ++i, ++kc) {
         const int s = kc % stages;
         ok = mbar_wait(full0 + 8 * s, (kc / stages) & 1, ab);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a = tiles + s * STAGE_BYTES;
-        const uint32_t b = a + A_BYTES * (GATED ? 2 : 1);
+        const uint32_t b = a + A_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {
-          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          const uint64_t bd = smem_desc(b + k * 32);
-          umma_bf16(acc_addr, smem_desc(a + k * 32), bd, idesc, acc);
-          if (GATED) umma_bf16(acc_addr + BN, smem_desc(a + A_BYTES + k * 32), bd, idesc, acc);
-        }
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(acc_addr, smem_desc(a + k * 32), smem_desc(b + k * 32), idesc, (i > 0 || k > 0) ? 1u : 0u);
         umma_commit(empty0 + 8 * s);   // frees the stage when these MMAs have read it
       }
       if (ok) umma_commit(acc_full0 + 8 * buf);
@@ -224,22 +226,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, ab)) break;
       tc_fence_after();
       if (!waited) { pdl_wait(); waited = true; }   // before reading or writing what earlier kernels touch
-      const int f = w.f0 + q * 32 + lane;           // output feature of this thread
+      // output feature of this thread: its lane of the accumulator, or, gated, one of the warp's 16
+      // features (lanes 0-15 hold its gate values, lanes 16-31 its up values)
+      const int f = GATED ? w.f0 + q * GATE_BLOCK + (lane & 15) : w.f0 + q * 32 + lane;
       const bool f_ok = f < p.N;
       const float bias = (p.bias && f_ok && !raw) ? p.bias[f] : 0.f;
       const uint32_t lane_addr = tmem + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 8) {
         if (w.row0 + c0 >= w.row_end) break;        // uniform in the warp
-        float v[8], u[8];
+        float v[8];
         tmem_ld8(lane_addr + c0, v);
-        if (GATED) tmem_ld8(lane_addr + BN + c0, u);
+        if (GATED) {
+          // the low half-warp takes token columns 0-3 and needs their up values, the high half takes
+          // columns 4-7 and needs their gate values: one exchange of four values each
+          const bool low = lane < 16;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int r = w.row0 + c0 + c;
+          for (int c = 0; c < 4; ++c) {
+            const float got = __shfl_xor_sync(0xffffffffu, low ? v[4 + c] : v[c], 16);
+            const float gate = low ? v[c] : got, up = low ? got : v[4 + c];
+            v[c] = act_fn(gate, p.act) * up;
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < (GATED ? 4 : 8); ++c) {
+          const int r = w.row0 + c0 + (GATED && lane >= 16 ? 4 + c : c);
           if (r >= w.row_end || !f_ok) continue;
           float y = v[c];
-          if (GATED) y = act_fn(y, p.act) * u[c];
           if (raw) {
             p.partial[((size_t)w.z * p.rows + r) * p.N + f] = y;
             continue;
@@ -318,13 +331,13 @@ struct MapKeyHash {
 std::mutex g_map_mutex;
 std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_weight_maps;   // weights never move: encode once
 
-int weight_map(CUtensorMap* m, const void* ptr, long long rows, int K) {
+int weight_map(CUtensorMap* m, const void* ptr, long long rows, int K, int box_rows = BM) {
   std::lock_guard<std::mutex> lock(g_map_mutex);
-  MapKey key{ptr, rows, K, BM};
+  MapKey key{ptr, rows, K, box_rows};
   auto it = g_weight_maps.find(key);
   if (it == g_weight_maps.end()) {
     CUtensorMap fresh;
-    if (int rc = make_map(&fresh, ptr, rows, K, K, BM)) return rc;
+    if (int rc = make_map(&fresh, ptr, rows, K, K, box_rows)) return rc;
     if (g_weight_maps.size() > 4096) g_weight_maps.clear();
     it = g_weight_maps.emplace(key, fresh).first;
   }
@@ -333,9 +346,8 @@ int weight_map(CUtensorMap* m, const void* ptr, long long rows, int K) {
 }
 
 template <int BN, bool GATED>
-int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, const Params& p, dim3 grid,
-           cudaStream_t stream) {
-  constexpr int stage_bytes = BM * BK * 2 * (GATED ? 2 : 1) + BN * BK * 2;
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+  constexpr int stage_bytes = BM * BK * 2 + BN * BK * 2;
   const size_t smem = (size_t)p.stages * stage_bytes + 1024;
   static bool configured = false;   // per instantiation
   if (!configured) {
@@ -353,11 +365,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mu, const CUtensorMap& mx, 
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  constexpr int acc_cols = 2 * (GATED ? 2 * BN : BN);
+  constexpr int acc_cols = 2 * BN;
   const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
   const long long items = (long long)grid.x * grid.y * grid.z;
   const unsigned blocks = (unsigned)(items < (long long)sm_count * per_sm ? items : (long long)sm_count * per_sm);
-  launch_pdl(gemm_tc_kernel<BN, GATED>, dim3(blocks), dim3(THREADS), smem, stream, mw, mu, mx, p);
+  launch_pdl(gemm_tc_kernel<BN, GATED>, dim3(blocks), dim3(THREADS), smem, stream, mw, mx, p);
   return check_launch("gemm_tc");
 }
 
@@ -370,8 +382,9 @@ static int g_stage_override = 0;
 extern "C" void flint_gemm_tc_set_stages(int stages) { g_stage_override = stages; }
 
 extern "C" int flint_gemm_tc_stages(int bn, int gated) {
+  (void)gated;   // a gated tile has the same footprint: 64 gate and 64 up rows on the M side
   if (g_stage_override > 0) return g_stage_override;
-  const int stage = BM * BK * 2 * (gated ? 2 : 1) + bn * BK * 2;
+  const int stage = BM * BK * 2 + bn * BK * 2;
   int s = (bn >= 128 ? 192 * 1024 : 100 * 1024) / stage;
   if (s < 3) s = 3;
   while (s * stage > 192 * 1024) --s;
@@ -383,8 +396,8 @@ extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
   return splits > 1 ? (long long)splits * rows * N : 0;
 }
 
-// x [rows, K] bf16 with row stride ldx; w [E, N, K] bf16 (E = 1 when dense), or, gated, [E, 2N, K] with each
-// expert's N gate rows before its N up rows; out [rows, N].
+// x [rows, K] bf16 with row stride ldx; w [E, N, K] bf16 (E = 1 when dense), or, gated, [E, paired_rows(N), K]
+// with each expert's gate and up rows paired in blocks; out [rows, N].
 // bn: token rows per tile (16, 32, 64, 128 or 256); with a tile map it must equal the plan's tile size.
 // splits > 1 divides the K blocks over several CTAs and needs `partial` (not with a gated product).
 // defer: leave the raw partial sums [splits, rows, N] in `partial` (no bias, nothing added to out);
@@ -400,8 +413,8 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
-  const bool w_up = gated != 0;            // gated: each expert's block is N gate rows, then N up rows
-  const int w_expert_rows = gated ? 2 * N : N;
+  const bool w_up = gated != 0;
+  const int w_expert_rows = gated ? paired_rows(N) : N;
   if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return fail("gemm_tc: bad token tile %d", bn);
   if (splits < 1) return fail("gemm_tc: bad split %d", splits);
   if ((splits > 1 || defer) && (w_up || !partial)) return fail("gemm_tc: partial sums need scratch and cannot be gated");
@@ -413,9 +426,8 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   const int tiles_n = tile_expert ? max_tiles : (rows + bn - 1) / bn;
   if (tiles_n <= 0) return 0;
 
-  CUtensorMap mw, mu, mx;
+  CUtensorMap mw, mx;
   if (int rc = weight_map(&mw, w, (long long)n_experts * w_expert_rows, K)) return rc;
-  mu = mw;
   if (int rc = make_map(&mx, x, rows, K, ldx, bn)) return rc;
 
   Params p;
@@ -425,21 +437,17 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   p.out_dtype = out_dtype; p.ldo = ldo; p.accumulate = accumulate; p.act = act;
   p.rows = rows; p.N = N; p.K = K;
   p.kb_per_split = kbps; p.splits = splits; p.defer = defer;
-  p.w_expert_rows = w_expert_rows; p.up_row_offset = gated ? N : 0;
+  p.w_expert_rows = w_expert_rows;
   p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
   if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;
-  dim3 grid((N + BM - 1) / BM, tiles_n, splits);
+  dim3 grid(w_up ? (N + GATED_FEATURES - 1) / GATED_FEATURES : (N + BM - 1) / BM, tiles_n, splits);
   int rc;
 #define CASE(B)                                                                             \
   case B:                                                                                   \
-    rc = w_up ? launch<B, true>(mw, mu, mx, p, grid, stream) : launch<B, false>(mw, mu, mx, p, grid, stream); \
+    rc = w_up ? launch<B, true>(mw, mx, p, grid, stream) : launch<B, false>(mw, mx, p, grid, stream); \
     break;
   switch (bn) {
-    CASE(16) CASE(32) CASE(64) CASE(128)
-    case 256:
-      if (w_up) return fail("gemm_tc: a gated product takes token tiles up to 128");
-      rc = launch<256, false>(mw, mu, mx, p, grid, stream);
-      break;
+    CASE(16) CASE(32) CASE(64) CASE(128) CASE(256)
     default: rc = fail("gemm_tc: bad token tile %d", bn);
   }
 #undef CASE

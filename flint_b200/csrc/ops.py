@@ -266,9 +266,34 @@ class CudaOps:
         """out = x @ w.T (+ bias) (+ out).  x [M,K], w [N,K], out [M,N]."""
         self._gemm(x, w, False, out, bias, accumulate, "silu", None)
 
+    GATE_BLOCK = 16     # rows per block of the paired gate/up layout (GATE_BLOCK in common.cuh)
+
+    @classmethod
+    def paired_rows(cls, features):
+        return 2 * -(-features // cls.GATE_BLOCK) * cls.GATE_BLOCK
+
+    @classmethod
+    def pair_gate_up(cls, w_gate, w_up):
+        """The layout ``gated_gemm`` takes its weights in: blocks of 16 gate rows alternate with the 16 up
+        rows of the same features; the feature count is padded to a multiple of 16 with zero rows.
+        [..., N, K] twice -> [..., paired_rows(N), K]."""
+        if w_gate.shape != w_up.shape:
+            raise KernelError("pair_gate_up: gate and up weights differ in shape")
+        *lead, n, k = w_gate.shape
+        b = cls.GATE_BLOCK
+        blocks = -(-n // b)
+        out = w_gate.new_zeros((*lead, blocks, 2, b, k))
+        flat = out.view(*lead, blocks, 2, b, k)
+        pad = blocks * b - n
+        for half, w in enumerate((w_gate, w_up)):
+            if pad:
+                w = torch.cat([w, w.new_zeros((*lead, pad, k))], -2)
+            flat[..., half, :, :] = w.reshape(*lead, blocks, b, k)
+        return out.view(*lead, 2 * blocks * b, k)
+
     def gated_gemm(self, x, w13, out, act="silu", plan: MoePlan | None = None):
-        """out = act(x @ Wg.T) * (x @ Wu.T) with the gate rows Wg stacked before the up rows Wu:
-        w13 [2N, K], or with a plan (rows grouped by expert) [E, 2N, K]."""
+        """out = act(x @ Wg.T) * (x @ Wu.T); w13 = pair_gate_up(Wg, Wu): [paired_rows(N), K], or with a
+        plan (rows grouped by expert) [E, paired_rows(N), K]."""
         self._gemm(x, w13, True, out, None, False, act, plan)
 
     def grouped_gemm(self, x, w, out, plan: MoePlan):
@@ -332,9 +357,10 @@ class CudaOps:
                 raise KernelError("gemm: dense weights must be [N, K]")
         elif w.dim() != 3 or w.shape[0] != plan.n_experts:
             raise KernelError("gemm: grouped weights must be [E, N, K]")
-        N = w.shape[-2] // 2 if gated else w.shape[-2]
-        if gated and w.shape[-2] % 2:
-            raise KernelError("gemm: stacked gate/up weights need an even number of rows")
+        N = out.shape[1] if gated else w.shape[-2]
+        if gated and w.shape[-2] != self.paired_rows(N):
+            raise KernelError(f"gemm: paired gate/up weights for {N} features have {self.paired_rows(N)} rows, "
+                              f"not {w.shape[-2]}")
         if w.shape[-1] != K or tuple(out.shape) != (M, N):
             raise KernelError(f"gemm: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} do not match")
         if bias is not None:
@@ -345,7 +371,7 @@ class CudaOps:
         if self.tensor_core_ok(x, w, plan):
             if gated and M <= 128:
                 # few rows: the product is bound by streaming the weights, and a gated tile cannot split
-                # its K range; run it as a plain product over the 2N stacked rows, split over K, and apply
+                # its K range; run it as a plain product over the paired rows, split over K, and apply
                 # the activation to the summed partial tiles
                 parts = self.gemm_partials(x, w, plan=plan)
                 self._run("elementwise", "flint_gated_act", _ptr(parts), c_int(parts.shape[0]),
@@ -361,27 +387,27 @@ class CudaOps:
     def tensor_core_ok(self, x, w, plan=None):
         return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
                 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
-                and (plan is None or plan.tile_rows in (16, 32, 64, 128)))
+                and (plan is None or plan.tile_rows in (16, 32, 64, 128, 256)))
 
     @staticmethod
-    def token_tile(rows, gated=False):
+    def token_tile(rows):
         for bn in (16, 32, 64, 128):
             if rows <= bn:
                 return bn
-        return 128 if gated else 256
+        return 256
 
     def moe_tile_rows(self, n_tokens, n_experts, weight_dtype):
         """Row-tile size the plan should use for grouped products over these weights."""
         if weight_dtype != torch.bfloat16:
             return 64
-        return self.token_tile(-(-2 * n_tokens // n_experts), gated=True)
+        return self.token_tile(-(-2 * n_tokens // n_experts))
 
     def _gemm_tc(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None:
             bn, splits, E = plan.tile_rows, 1, plan.n_experts
         else:
             E = 1
-            bn = self.token_tile(M, gated=gated)
+            bn = self.token_tile(M)
             splits = 1 if gated else self._k_splits(M, N, K, bn)
         partial = None
         if splits > 1:

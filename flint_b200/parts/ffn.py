@@ -32,8 +32,8 @@ class GatedMLP(FeedForward):
 
     def load(self, t):
         dt = matmul_dtype(*t.values())
-        # the gate rows are stacked before the up rows: one product gives both
-        self.w_gate_up = torch.cat([t["gate_proj.weight"].to(dt), t["up_proj.weight"].to(dt)], 0).contiguous()
+        # gate and up rows in the layout the kernels want: one product gives both
+        self.w_gate_up = self.ops.pair_gate_up(t["gate_proj.weight"].to(dt), t["up_proj.weight"].to(dt)).contiguous()
         self.w_down = t["down_proj.weight"].to(dt)
 
     def input_dtypes(self):
@@ -73,8 +73,8 @@ class SparseMixerMoE(FeedForward):
     def load(self, t):
         self.w_router = t["gate.weight"]
         dt = matmul_dtype(*(t[k] for k in t if k.startswith("experts.")))
-        # per expert the gate rows (w1) are stacked before the up rows (w3): [E, 2I, H]
-        self.w13 = torch.stack([torch.cat([t[f"experts.{e}.w1.weight"].to(dt), t[f"experts.{e}.w3.weight"].to(dt)], 0)
+        # per expert the gate rows (w1) and the up rows (w3) in the layout the kernels want: [E, rows, H]
+        self.w13 = torch.stack([self.ops.pair_gate_up(t[f"experts.{e}.w1.weight"].to(dt), t[f"experts.{e}.w3.weight"].to(dt))
                                 for e in range(self.E)], 0).contiguous()
         self.w2 = torch.stack([t[f"experts.{e}.w2.weight"].to(dt) for e in range(self.E)], 0).contiguous()
 

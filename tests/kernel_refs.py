@@ -127,8 +127,13 @@ class RefOps:
         off = plan.offsets.tolist()
         return [(e, off[e], off[e + 1]) for e in range(plan.n_experts) if off[e + 1] > off[e]]
 
+    @staticmethod
+    def pair_gate_up(w_gate, w_up):
+        """This implementation keeps the gate rows before the up rows."""
+        return torch.cat([w_gate, w_up], -2)
+
     def gated_gemm(self, x, w13, out, act="silu", plan=None):
-        """w13: the gate rows stacked before the up rows, [2N, K] or [E, 2N, K]."""
+        """w13 = pair_gate_up(gate, up): [2N, K] or [E, 2N, K]."""
         xs = x.to(self.cd)
         n = w13.shape[-2] // 2
         if plan is None:

@@ -178,8 +178,9 @@ def test_gemm_strided_output(ops, ref):
 
 @pytest.mark.parametrize("act", ["silu", "gelu_pytorch_tanh"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gated_and_grouped(ops, ref, act, dtype):
-    T, H, I, E = 75, 96, 80, 6
+@pytest.mark.parametrize("I", [80, 72])          # a multiple of the pairing block of 16, and not
+def test_gated_and_grouped(ops, ref, act, dtype, I):
+    T, H, E = 75, 96, 6
     ids = torch.randint(0, E, (T, 2), dtype=torch.int32)
     ids[:, 1] = (ids[:, 0] + 1 + ids[:, 1] % (E - 1)) % E
     ids[ids == 4] = 0                      # expert 4 gets no rows
@@ -205,7 +206,8 @@ def test_gated_and_grouped(ops, ref, act, dtype):
     assert torch.equal(xs.cpu(), x[token_of])
     w1, w3, w2 = (rnd(E, I, H, dtype=dtype, seed=1, scale=0.1), rnd(E, I, H, dtype=dtype, seed=2, scale=0.1),
                   rnd(E, H, I, dtype=dtype, seed=3, scale=0.1))
-    w13 = torch.cat([w1, w3], 1).contiguous()          # per expert: gate rows, then up rows
+    w13 = ops.pair_gate_up(w1, w3).contiguous()        # the kernels' layout; the reference keeps its own
+    r13 = ref.pair_gate_up(w1, w3)
     a = torch.empty(2 * T, I, dtype=dtype, device=DEV)
     ops.gated_gemm(xs, w13.to(DEV), a, act, plan)
     # the reference works on the same row order
@@ -213,7 +215,7 @@ def test_gated_and_grouped(ops, ref, act, dtype):
     cplan = MoePlan(E, 64, plan.max_tiles, *(t.cpu() for t in (plan.counts, plan.offsets, plan.row_of, plan.token_of,
                                                              plan.tile_expert, plan.tile_row0, plan.n_tiles)))
     ea = torch.zeros(2 * T, I, dtype=torch.float64)
-    ref.gated_gemm(xs.cpu(), w13, ea, act, cplan)
+    ref.gated_gemm(xs.cpu(), r13, ea, act, cplan)
     tol = (1e-5, 1e-4) if dtype == torch.float32 else (2e-2, 2e-2)
     close(a, ea, *tol)
     y = torch.empty(2 * T, H, device=DEV)
@@ -232,9 +234,9 @@ def test_gated_and_grouped(ops, ref, act, dtype):
     d = torch.empty(T, I, dtype=dtype, device=DEV)
     ops.gated_gemm(x.to(DEV), w13[0].to(DEV), d, act)
     ed = torch.zeros(T, I, dtype=torch.float64)
-    ref.gated_gemm(x, w13[0], ed, act)
+    ref.gated_gemm(x, r13[0], ed, act)
     close(d, ed, *tol)
-    # few rows: the split path (plain product over the stacked rows, then the activation)
+    # few rows: the split path (plain product over the paired rows, then the activation)
     for rows in (1, 9):
         ids_s = ids[:rows].contiguous()
         plan_s = ops.moe_plan(ids_s.to(DEV), E, ops.moe_tile_rows(rows, E, dtype))
@@ -245,8 +247,36 @@ def test_gated_and_grouped(ops, ref, act, dtype):
         cp = MoePlan(E, plan_s.tile_rows, plan_s.max_tiles, *(t.cpu() for t in (plan_s.counts, plan_s.offsets, plan_s.row_of,
                      plan_s.token_of, plan_s.tile_expert, plan_s.tile_row0, plan_s.n_tiles)))
         ea_s = torch.zeros(2 * rows, I, dtype=torch.float64)
-        ref.gated_gemm(xs_s.cpu(), w13, ea_s, act, cp)
+        ref.gated_gemm(xs_s.cpu(), r13, ea_s, act, cp)
         close(a_s, ea_s, *tol)
+
+
+@pytest.mark.parametrize("tile", [128, 256])
+def test_gated_and_grouped_wide_tiles(ops, ref, tile):
+    """Many rows per expert: full tiles, tiles cut short by the end of an expert's rows, an expert with few rows."""
+    from flint_b200.csrc.ops import MoePlan
+    T, H, I, E = 900, 192, 136, 3
+    ids = torch.zeros(T, 2, dtype=torch.int32)
+    ids[:, 0] = torch.randint(0, 2, (T,), dtype=torch.int32)       # experts 0 and 1 share most rows
+    ids[:, 1] = torch.where(torch.arange(T) % 90 == 0, 2, 1 - ids[:, 0]).to(torch.int32)   # expert 2: ten rows
+    plan = ops.moe_plan(ids.to(DEV), E, tile)
+    x = rnd(T, H, dtype=torch.bfloat16)
+    xs = torch.empty(2 * T, H, dtype=torch.bfloat16, device=DEV)
+    ops.gather_rows(x.to(DEV), plan.token_of, xs)
+    w1, w3, w2 = (rnd(E, I, H, dtype=torch.bfloat16, seed=1, scale=0.1), rnd(E, I, H, dtype=torch.bfloat16, seed=2, scale=0.1),
+                  rnd(E, H, I, dtype=torch.bfloat16, seed=3, scale=0.1))
+    a = torch.full((2 * T, I), 7.0, dtype=torch.bfloat16, device=DEV)
+    ops.gated_gemm(xs, ops.pair_gate_up(w1, w3).contiguous().to(DEV), a, "silu", plan)
+    cplan = MoePlan(E, tile, plan.max_tiles, *(t.cpu() for t in (plan.counts, plan.offsets, plan.row_of, plan.token_of,
+                                                               plan.tile_expert, plan.tile_row0, plan.n_tiles)))
+    ea = torch.zeros(2 * T, I, dtype=torch.float64)
+    ref.gated_gemm(xs.cpu(), ref.pair_gate_up(w1, w3), ea, "silu", cplan)
+    close(a, ea, 2e-2, 2e-2)
+    y = torch.empty(2 * T, H, device=DEV)
+    ops.grouped_gemm(a, w2.to(DEV), y, plan)
+    ey = torch.zeros(2 * T, H, dtype=torch.float64)
+    ref.grouped_gemm(a.cpu(), w2, ey, cplan)
+    close(y, ey, 1e-4, 1e-4)
 
 
 @pytest.mark.parametrize("wd", [torch.float32, torch.bfloat16])
