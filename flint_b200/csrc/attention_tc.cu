@@ -11,6 +11,10 @@
 //   O_tile = P V     tcgen05.mma with V [64 keys, hd] as an MN-major B operand, fresh accumulator;
 //                    the row's thread then folds it into its float32 output registers:
 //                    o = o * alpha + O_tile
+// The steps of neighbouring key tiles overlap: S has two buffers in tensor memory, and the MMA thread
+// issues S of tile i+1 before it waits for P of tile i, so the tensor core computes the next scores
+// while the rows' threads are busy with the softmax; and a row folds O of tile i into its registers only
+// after the first pass over the scores of tile i+1, while P V of tile i is still running.
 // Q, K and V tiles come by TMA (128-byte swizzle, no multicast); K/V tiles are double-buffered.
 // Roles (192 threads): warp 0 lane 0 loads, warp 1 owns tensor memory and its lane 0 issues MMAs,
 // warps 2..5 are the 128 softmax rows.  Every mbarrier wait is bounded; on a timeout the block
@@ -80,7 +84,7 @@ __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];   // tiles need 1024-byte alignment (128-byte swizzle)
-  __shared__ __align__(8) uint64_t bars[8];   // q, kv_full[2], kv_empty[2], s_full, p_full, o_full
+  __shared__ __align__(8) uint64_t bars[9];   // q, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -111,8 +115,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t kv_stage_bytes = 2u * chunks * BKV * 128;
   const uint32_t p_smem = kv_smem + STAGES * kv_stage_bytes;          // [128 rows][128 B]
   const uint32_t bar_q = smem_u32(&bars[0]), bar_full0 = smem_u32(&bars[1]), bar_empty0 = smem_u32(&bars[3]);
-  const uint32_t bar_s = smem_u32(&bars[5]), bar_p = smem_u32(&bars[6]), bar_o = smem_u32(&bars[7]);
-  const uint32_t tmem_cols = HDM <= 64 ? 128 : 256;
+  const uint32_t bar_s0 = smem_u32(&bars[5]), bar_p = smem_u32(&bars[7]), bar_o = smem_u32(&bars[8]);
+  const uint32_t tmem_cols = 256;             // two score buffers of 64 columns, then up to 128 of output
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -122,7 +126,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(bar_full0 + 8 * s, 1);
       mbar_init(bar_empty0 + 8 * s, 1);
     }
-    mbar_init(bar_s, 1);
+    mbar_init(bar_s0, 1);
+    mbar_init(bar_s0 + 8, 1);
     mbar_init(bar_p, BQ);       // every softmax row arrives itself
     mbar_init(bar_o, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -132,7 +137,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + BKV;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 2 * BKV;   // scores of tile i at tmem_s + (i & 1) * BKV
   volatile int* ab = &abort_flag;
 
   if (warp == 0 && lane == 0) {
@@ -163,21 +168,30 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // ---------------------------------------------------------------- MMA issue
     const uint32_t idesc_s = idesc_f16(BKV, 0), idesc_o = idesc_f16(hd, 1);
     bool ok = mbar_wait(bar_q, 0, ab);
-    for (int i = 0; i < n_kv_tiles && ok; ++i) {
+    // S_i = Q K_i^T into score buffer i & 1, as soon as the keys of tile i have landed
+    auto issue_scores = [&](int i) -> bool {
       const int s = i % STAGES;
-      ok = mbar_wait(bar_full0 + 8 * s, (i / STAGES) & 1, ab);
-      if (!ok) break;
+      if (!mbar_wait(bar_full0 + 8 * s, (i / STAGES) & 1, ab)) return false;
       tc_fence_after();
-      const uint32_t k_src = kv_smem + s * kv_stage_bytes, v_src = k_src + chunks * BKV * 128;
-      for (int k = 0; k < hd / 16; ++k) {      // S = Q K^T over the head dimension
+      const uint32_t k_src = kv_smem + s * kv_stage_bytes;
+      for (int k = 0; k < hd / 16; ++k) {
         const uint32_t off = (k >> 2) * 128 * 128 + (k & 3) * 32;          // Q: 128 rows per chunk
         const uint32_t koff = (k >> 2) * BKV * 128 + (k & 3) * 32;         // K: 64 rows per chunk
-        umma_bf16(tmem_s, smem_desc(q_smem + off), smem_desc(k_src + koff), idesc_s, k > 0 ? 1u : 0u);
+        umma_bf16(tmem_s + (i & 1) * BKV, smem_desc(q_smem + off), smem_desc(k_src + koff), idesc_s, k > 0 ? 1u : 0u);
       }
-      umma_commit(bar_s);
-      ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read
+      umma_commit(bar_s0 + 8 * (i & 1));
+      return true;
+    };
+    if (ok) ok = issue_scores(0);
+    for (int i = 0; i < n_kv_tiles && ok; ++i) {
+      // the next tile's scores first: their buffer was last read for tile i-1, whose P has been handed over
+      if (i + 1 < n_kv_tiles) ok = issue_scores(i + 1);
+      if (!ok) break;
+      ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read, O of tile i-1 too
       if (!ok) break;
       tc_fence_after();
+      const int s = i % STAGES;
+      const uint32_t v_src = kv_smem + s * kv_stage_bytes + chunks * BKV * 128;
       for (int k = 0; k < BKV / 16; ++k) {      // O_tile = P V over the 64 keys
         // V [keys, hd] is MN-major for B: 16 keys down = 2048 bytes; 64-wide chunks of hd are BKV*128 apart
         const uint64_t vd = smem_desc_mn(v_src + k * 16 * 128, BKV * 128, 1024);
@@ -197,12 +211,29 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float o[HDM];
 #pragma unroll
     for (int d = 0; d < HDM; ++d) o[d] = 0.f;
-    float m = -1e30f, l = 0.f;
+    float m = -1e30f, l = 0.f, alpha_prev = 1.f;
     bool ok = true;
+    // o = o * alpha + O_tile for the tile whose P V has just finished
+    auto fold_output = [&](int i, float alpha) -> bool {
+      if (!mbar_wait(bar_o, i & 1, ab)) return false;
+      tc_fence_after();
+#pragma unroll
+      for (int d0 = 0; d0 < HDM; d0 += 16) {
+        if (d0 < hd) {
+          float v[16];
+          tmem_ld16(tmem_o + lane_addr + d0, v);
+#pragma unroll
+          for (int d = 0; d < 16; ++d) o[d0 + d] = fmaf(o[d0 + d], alpha, v[d]);
+        }
+      }
+      tc_fence_before();
+      return true;
+    };
     for (int i = 0; i < n_kv_tiles && ok; ++i) {
-      ok = mbar_wait(bar_s, i & 1, ab);
+      ok = mbar_wait(bar_s0 + 8 * (i & 1), (i >> 1) & 1, ab);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t s_addr = tmem_s + (i & 1) * BKV + lane_addr;
       const int kv0 = (tile_lo + i) * BKV;
       // only tiles that touch the diagonal or the window's edge need the mask (uniform in the block)
       const bool need_mask = (kv0 + BKV - 1 > pos0) || (p.window > 0 && kv0 < pos0 + n_rows - p.window);
@@ -211,7 +242,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
       for (int c0 = 0; c0 < BKV; c0 += 16) {
         float v[16];
-        tmem_ld16(tmem_s + lane_addr + c0, v);
+        tmem_ld16(s_addr + c0, v);
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 16; ++c) {
@@ -226,12 +257,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float mx = fmaxf(m, mraw * p.scale_log2);
       const float alpha = ex2(m - mx);
       m = mx;
+      // the previous tile's output, whose P V ran during the pass above; P's buffer is free after it
+      if (i > 0) {
+        ok = fold_output(i - 1, alpha_prev);
+        if (!ok) break;
+      }
+      alpha_prev = alpha;
       // pass 2: probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
       float sum = 0.f;
 #pragma unroll
       for (int c0 = 0; c0 < BKV; c0 += 16) {
         float v[16];
-        tmem_ld16(tmem_s + lane_addr + c0, v);
+        tmem_ld16(s_addr + c0, v);
         uint32_t packed[8];
 #pragma unroll
         for (int c = 0; c < 16; c += 2) {
@@ -263,20 +300,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(bar_p);
-      ok = mbar_wait(bar_o, i & 1, ab);
-      if (!ok) break;
-      tc_fence_after();
-#pragma unroll
-      for (int d0 = 0; d0 < HDM; d0 += 16) {
-        if (d0 < hd) {
-          float v[16];
-          tmem_ld16(tmem_o + lane_addr + d0, v);
-#pragma unroll
-          for (int d = 0; d < 16; ++d) o[d0 + d] = fmaf(o[d0 + d], alpha, v[d]);
-        }
-      }
-      tc_fence_before();
     }
+    if (ok) ok = fold_output(n_kv_tiles - 1, alpha_prev);
     if (ok && row_ok) {
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.nq + head) * hd;

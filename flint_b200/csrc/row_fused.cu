@@ -52,19 +52,17 @@ __device__ __forceinline__ void load_w8(const __nv_bfloat16* p, float* f) {
   }
 }
 
-// ROWS rows per block (1, or 4 for long batches with a router, so that each router row read from L2
-// serves four tokens).
-template <int VPT, typename TW, int ROWS>
-__global__ void __launch_bounds__(ROWS == 4 ? 256 : 1024)
-row_norm_kernel(const RowArgs a, int n_rows) {
-  extern __shared__ float smem[];          // router only: ROWS x H floats of normalised rows, then partial logits
+// One block per row; a thread holds VPT vectors of four values of its row.
+template <int VPT, typename TW>
+__global__ void __launch_bounds__(1024)
+row_norm_kernel(const RowArgs a) {
+  extern __shared__ float smem[];          // router only: H floats of the normalised row, then partial logits
   __shared__ float red[32];
   pdl_launch();
   pdl_wait();
   const int H = a.H, n4 = H >> 2;
-  const int rows_here = min(ROWS, n_rows - (int)blockIdx.x * ROWS);
-  for (int rr = 0; rr < rows_here; ++rr) {
-    const int r = blockIdx.x * ROWS + rr;
+  {
+    const int r = blockIdx.x;
     const int src = a.row_index ? a.row_index[r] : r;
     float* xr = a.x + (size_t)src * H;
     float4 v[VPT];
@@ -122,7 +120,7 @@ row_norm_kernel(const RowArgs a, int n_rows) {
         if (c < n4) *reinterpret_cast<float4*>(xr + 4 * c) = v[i];
       }
     }
-    if (!a.gamma) continue;                   // only the additions were wanted
+    if (!a.gamma) return;                     // only the additions were wanted
     // statistics
     float mean = 0.f;
     if (a.mode == 0) {
@@ -157,30 +155,27 @@ row_norm_kernel(const RowArgs a, int n_rows) {
           pk.y = *reinterpret_cast<const uint32_t*>(&hi);
           *reinterpret_cast<uint2*>(a.out_bf16 + (size_t)r * H + 4 * c) = pk;
         }
-        if (a.wr) *reinterpret_cast<float4*>(smem + (size_t)rr * H + 4 * c) = y;
+        if (a.wr) *reinterpret_cast<float4*>(smem + 4 * c) = y;
       }
     }
   }
-  if (!a.wr || !a.gamma) return;
-  // ---- router: a job is (group of 4 experts, strided share of the row); a warp keeps ROWS x 4 sums, so
-  // that every value read from shared memory or from the router's rows feeds 4 multiply-adds; partial
-  // sums meet in shared memory
+  if (!a.wr) return;
+  // ---- router: a job is (group of 4 experts, strided share of the row); a warp keeps 4 sums, so that
+  // every value read from shared memory feeds 4 multiply-adds; partial sums meet in shared memory
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   const int E = a.E;
   constexpr int EG = 4;
   const int groups = (E + EG - 1) / EG;
   const int k = n_warps >= groups ? n_warps / groups : 1;   // warps per expert group
-  float* part = smem + (size_t)ROWS * H;                     // [ROWS][E][k]
+  float* part = smem + H;                                    // [E][k]
   const TW* wr = (const TW*)a.wr;
   const bool vec = (H & 7) == 0;
   for (int job = warp; job < groups * k; job += n_warps) {
     const int e0 = (job / k) * EG, sl = job % k;
-    float acc[ROWS][EG];
+    float acc[EG];
 #pragma unroll
-    for (int rr = 0; rr < ROWS; ++rr)
-#pragma unroll
-      for (int j = 0; j < EG; ++j) acc[rr][j] = 0.f;
+    for (int j = 0; j < EG; ++j) acc[j] = 0.f;
     if (vec) {
 #pragma unroll 2
       for (int d = (sl * 32 + lane) * 8; d < H; d += k * 256) {
@@ -194,48 +189,37 @@ row_norm_kernel(const RowArgs a, int n_rows) {
             for (int i = 0; i < 8; ++i) wv[j][i] = 0.f;
           }
         }
+        const float4 x0 = ld4(smem + d), x1 = ld4(smem + d + 4);
+        const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-        for (int rr = 0; rr < ROWS; ++rr) {
-          if (rr < rows_here) {
-            const float4 x0 = ld4(smem + (size_t)rr * H + d), x1 = ld4(smem + (size_t)rr * H + d + 4);
-            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        for (int j = 0; j < EG; ++j)
 #pragma unroll
-            for (int j = 0; j < EG; ++j)
-#pragma unroll
-              for (int i = 0; i < 8; ++i) acc[rr][j] = fmaf(xv[i], wv[j][i], acc[rr][j]);
-          }
-        }
+          for (int i = 0; i < 8; ++i) acc[j] = fmaf(xv[i], wv[j][i], acc[j]);
       }
     } else {
       for (int d = sl * 32 + lane; d < H; d += k * 32) {
+        const float xv = smem[d];
 #pragma unroll
-        for (int j = 0; j < EG; ++j) {
-          const float wv = e0 + j < E ? to_f32(wr[(size_t)(e0 + j) * H + d]) : 0.f;
-#pragma unroll
-          for (int rr = 0; rr < ROWS; ++rr)
-            if (rr < rows_here) acc[rr][j] = fmaf(smem[(size_t)rr * H + d], wv, acc[rr][j]);
-        }
+        for (int j = 0; j < EG; ++j)
+          acc[j] = fmaf(xv, e0 + j < E ? to_f32(wr[(size_t)(e0 + j) * H + d]) : 0.f, acc[j]);
       }
     }
 #pragma unroll
-    for (int rr = 0; rr < ROWS; ++rr)
-#pragma unroll
-      for (int j = 0; j < EG; ++j) {
-        const float t = warp_sum(acc[rr][j]);
-        if (lane == 0 && e0 + j < E) part[(rr * E + e0 + j) * k + sl] = t;
-      }
+    for (int j = 0; j < EG; ++j) {
+      const float t = warp_sum(acc[j]);
+      if (lane == 0 && e0 + j < E) part[(e0 + j) * k + sl] = t;
+    }
   }
   __syncthreads();
-  // selection: one warp per row.  Up to 32 experts sit one per lane (argmax and the masked sums by
+  // selection by the first warp.  Up to 32 experts sit one per lane (argmax and the masked sums by
   // shuffle); more experts are handled by lane 0 alone.
-  if (warp >= rows_here) return;
-  const int rr = warp;
-  const int r = blockIdx.x * ROWS + rr;
+  if (warp != 0) return;
+  const int r = blockIdx.x;
   if (E <= 32) {
     float sv = -INFINITY;
     if (lane < E) {
       sv = 0.f;
-      for (int i = 0; i < k; ++i) sv += part[(rr * E + lane) * k + i];    // fixed order
+      for (int i = 0; i < k; ++i) sv += part[lane * k + i];    // fixed order
     }
     int excluded = -1;
     for (int round = 0; round < 2; ++round) {
@@ -265,10 +249,10 @@ row_norm_kernel(const RowArgs a, int n_rows) {
     return;
   }
   if (lane != 0) return;
-  float* s = smem + (size_t)rr * H;                       // the rows are no longer needed
+  float* s = smem;                                         // the row is no longer needed
   for (int e = 0; e < E; ++e) {
     float t = 0.f;
-    for (int i = 0; i < k; ++i) t += part[(rr * E + e) * k + i];    // fixed order
+    for (int i = 0; i < k; ++i) t += part[e * k + i];    // fixed order
     s[e] = t;
   }
   int excluded = -1;
@@ -289,18 +273,18 @@ row_norm_kernel(const RowArgs a, int n_rows) {
   }
 }
 
-template <int VPT, typename TW, int ROWS>
+template <int VPT, typename TW>
 int launch_row(const RowArgs& a, int rows, int threads, size_t smem, cudaStream_t stream) {
   if (smem > 48 * 1024) {
     static bool configured = false;   // per instantiation
     if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(row_norm_kernel<VPT, TW, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      cudaError_t e = cudaFuncSetAttribute(row_norm_kernel<VPT, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            200 * 1024);
       if (e != cudaSuccess) return fail("row_norm: cannot raise shared memory: %s", cudaGetErrorString(e));
       configured = true;
     }
   }
-  launch_pdl(row_norm_kernel<VPT, TW, ROWS>, dim3((rows + ROWS - 1) / ROWS), dim3(threads), smem, stream, a, rows);
+  launch_pdl(row_norm_kernel<VPT, TW>, dim3(rows), dim3(threads), smem, stream, a);
   return check_launch("row_norm");
 }
 }  // namespace
@@ -343,16 +327,10 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   const int n_warps = threads / 32;
   const int groups = (E + 3) / 4;
   const int k = wr ? (n_warps >= groups ? n_warps / groups : 1) : 0;
-  // long batches with a router: four rows per block share each read of the router's rows
-  const int rpb = (wr && rows >= 256 && threads <= 256 && (size_t)(4 * H + 4 * E * k) * sizeof(float) <= 160 * 1024) ? 4 : 1;
-  const size_t smem = wr ? (size_t)(rpb * H + rpb * E * k) * sizeof(float) : 0;
-#define GO(V)                                                                                             \
-  (rpb == 4 ? (w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16, 4>(a, rows, threads, smem, stream)    \
-                                     : launch_row<V, float, 4>(a, rows, threads, smem, stream))           \
-            : (wr && w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16, 1>(a, rows, threads, smem, stream) \
-                                           : launch_row<V, float, 1>(a, rows, threads, smem, stream)))
+  const size_t smem = wr ? (size_t)(H + E * k) * sizeof(float) : 0;
+#define GO(V) (wr && w_dtype == FLINT_BF16 ? launch_row<V, __nv_bfloat16>(a, rows, threads, smem, stream) \
+                                           : launch_row<V, float>(a, rows, threads, smem, stream))
   if (smem > 200 * 1024) return fail("row_norm: width %d is too large for the fused router", H);
-  if (rpb > threads / 32) return fail("row_norm: too few warps for %d rows per block", rpb);
   switch (vpt) {
     case 1: return GO(1);
     case 2: return GO(2);
