@@ -6,15 +6,18 @@
 //   S = Q K^T        tcgen05.mma, Q [128, hd] and K [64, hd] both K-major in shared memory, S in
 //                    tensor memory (128 lanes = query rows, 64 columns = keys)
 //   softmax          one thread per query row reads its row of S with tcgen05.ld, applies scale,
-//                    the causal and window mask, keeps the running maximum and sum in float32,
-//                    and writes P = exp2(..) as bfloat16 into shared memory (K-major, swizzled)
-//   O_tile = P V     tcgen05.mma with V [64 keys, hd] as an MN-major B operand, fresh accumulator;
-//                    the row's thread then folds it into its float32 output registers:
-//                    o = o * alpha + O_tile
+//                    the causal and window mask, keeps the running reference and sum in float32,
+//                    and writes P = exp2(s - reference) as bfloat16 into shared memory (K-major, swizzled)
+//   O += P V         tcgen05.mma with V [64 keys, hd] as an MN-major B operand; O stays in tensor
+//                    memory over all key tiles of the block
+// The reference of a row is its running maximum, but it only moves when the maximum has grown by more
+// than 8 (a factor of 256 in P; any reference gives the same softmax as long as the sum and O use the
+// same one).  Only then does the row's warp rescale its rows of O in tensor memory (load, multiply,
+// store), which after the first few tiles is rare; otherwise a tile costs a thread one read of its 64
+// scores, 64 exponentials and the store of P.
 // The steps of neighbouring key tiles overlap: S has two buffers in tensor memory, and the MMA thread
 // issues S of tile i+1 before it waits for P of tile i, so the tensor core computes the next scores
-// while the rows' threads are busy with the softmax; and a row folds O of tile i into its registers only
-// after the first pass over the scores of tile i+1, while P V of tile i is still running.
+// while the rows' threads are busy with the softmax.
 // Q, K and V tiles come by TMA (128-byte swizzle, no multicast); K/V tiles are double-buffered.
 // Roles (192 threads): warp 0 lane 0 loads, warp 1 owns tensor memory and its lane 0 issues MMAs,
 // warps 2..5 are the 128 softmax rows.  Every mbarrier wait is bounded; on a timeout the block
@@ -68,6 +71,26 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 64 consecutive columns of this thread's lane, then the wait, in one statement: nothing that uses the
+// values can be scheduled before the wait
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+  uint32_t r[64];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr) : "memory");
+#pragma unroll
+  for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :: "r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // 2^x on the special-function unit (float32 in and out, about 2 ulp)
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -79,7 +102,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int HDM>   // HDM: 64 or 128, the largest head size this instantiation holds in registers
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -187,7 +209,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // the next tile's scores first: their buffer was last read for tile i-1, whose P has been handed over
       if (i + 1 < n_kv_tiles) ok = issue_scores(i + 1);
       if (!ok) break;
-      ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read, O of tile i-1 too
+      ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read, O is rescaled
       if (!ok) break;
       tc_fence_after();
       const int s = i % STAGES;
@@ -195,7 +217,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int k = 0; k < BKV / 16; ++k) {      // O_tile = P V over the 64 keys
         // V [keys, hd] is MN-major for B: 16 keys down = 2048 bytes; 64-wide chunks of hd are BKV*128 apart
         const uint64_t vd = smem_desc_mn(v_src + k * 16 * 128, BKV * 128, 1024);
-        umma_bf16(tmem_o, smem_desc(p_smem + k * 32), vd, idesc_o, k > 0 ? 1u : 0u);
+        umma_bf16(tmem_o, smem_desc(p_smem + k * 32), vd, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(bar_o);
       umma_commit(bar_empty0 + 8 * s);
@@ -208,74 +230,62 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int q_pos = pos0 + (row_ok ? r : n_rows - 1);
     const int first = p.window > 0 ? max(0, q_pos + 1 - p.window) : 0;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float o[HDM];
-#pragma unroll
-    for (int d = 0; d < HDM; ++d) o[d] = 0.f;
-    float m = -1e30f, l = 0.f, alpha_prev = 1.f;
+    constexpr float kRescaleStep = 8.0f;            // in log2 units
+    float ref = -1e30f, l = 0.f;                    // reference of the exponentials, sum of P
     bool ok = true;
-    // o = o * alpha + O_tile for the tile whose P V has just finished
-    auto fold_output = [&](int i, float alpha) -> bool {
-      if (!mbar_wait(bar_o, i & 1, ab)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int d0 = 0; d0 < HDM; d0 += 16) {
-        if (d0 < hd) {
-          float v[16];
-          tmem_ld16(tmem_o + lane_addr + d0, v);
-#pragma unroll
-          for (int d = 0; d < 16; ++d) o[d0 + d] = fmaf(o[d0 + d], alpha, v[d]);
-        }
-      }
-      tc_fence_before();
-      return true;
-    };
     for (int i = 0; i < n_kv_tiles && ok; ++i) {
       ok = mbar_wait(bar_s0 + 8 * (i & 1), (i >> 1) & 1, ab);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t s_addr = tmem_s + (i & 1) * BKV + lane_addr;
       const int kv0 = (tile_lo + i) * BKV;
       // only tiles that touch the diagonal or the window's edge need the mask (uniform in the block)
       const bool need_mask = (kv0 + BKV - 1 > pos0) || (p.window > 0 && kv0 < pos0 + n_rows - p.window);
-      // pass 1: the row's maximum over this tile (of the raw scores; the scale is positive)
-      float mraw = -INFINITY;
+      float sc[BKV];
+      tmem_ld64(tmem_s + (i & 1) * BKV + lane_addr, sc);
+      float mraw = -INFINITY;                       // of the raw scores; the scale is positive
+      if (need_mask) {
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 16) {
-        float v[16];
-        tmem_ld16(s_addr + c0, v);
-        if (need_mask) {
+        for (int c = 0; c < BKV; ++c) {
+          const int kj = kv0 + c;
+          if (kj <= q_pos && kj >= first) mraw = fmaxf(mraw, sc[c]);
+        }
+      } else {
 #pragma unroll
-          for (int c = 0; c < 16; ++c) {
-            const int kj = kv0 + c0 + c;
-            if (kj <= q_pos && kj >= first) mraw = fmaxf(mraw, v[c]);
+        for (int c = 0; c < BKV; ++c) mraw = fmaxf(mraw, sc[c]);
+      }
+      const float mx = fmaxf(ref, mraw * p.scale_log2);
+      // P V of the previous tile must be done before O is touched or P's buffer is written again
+      if (i > 0) {
+        ok = mbar_wait(bar_o, (i - 1) & 1, ab);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, mx - ref > kRescaleStep)) {      // uniform in the warp: tcgen05.ld/st are
+        const float alpha = ex2(ref - mx);                          // warp-wide; every row of the warp moves
+        ref = mx;
+        l *= alpha;
+        if (i > 0) {
+          for (int d0 = 0; d0 < hd; d0 += 16) {
+            float v[16];
+            tmem_ld16(tmem_o + lane_addr + d0, v);
+#pragma unroll
+            for (int d = 0; d < 16; ++d) v[d] *= alpha;
+            tmem_st16(tmem_o + lane_addr + d0, v);
           }
-        } else {
-#pragma unroll
-          for (int c = 0; c < 16; ++c) mraw = fmaxf(mraw, v[c]);
+          tmem_st_wait();
         }
       }
-      const float mx = fmaxf(m, mraw * p.scale_log2);
-      const float alpha = ex2(m - mx);
-      m = mx;
-      // the previous tile's output, whose P V ran during the pass above; P's buffer is free after it
-      if (i > 0) {
-        ok = fold_output(i - 1, alpha_prev);
-        if (!ok) break;
-      }
-      alpha_prev = alpha;
-      // pass 2: probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
+      // probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
       float sum = 0.f;
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 16) {
-        float v[16];
-        tmem_ld16(s_addr + c0, v);
-        uint32_t packed[8];
+      for (int c0 = 0; c0 < BKV; c0 += 8) {
+        uint32_t packed[4];
 #pragma unroll
-        for (int c = 0; c < 16; c += 2) {
+        for (int c = 0; c < 8; c += 2) {
           float pr[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            pr[e] = ex2(fmaf(v[c + e], p.scale_log2, -m));
+            pr[e] = ex2(fmaf(sc[c0 + c + e], p.scale_log2, -ref));
             if (need_mask) {
               const int kj = kv0 + c0 + c + e;
               if (!(kj <= q_pos && kj >= first)) pr[e] = 0.f;
@@ -286,37 +296,37 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           sum += __bfloat162float(b.x) + __bfloat162float(b.y);
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
         }
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int unit = (c0 >> 3) + u;
-          const uint32_t addr = p_smem + r * 128 + ((unit ^ (r & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[4 * u]), "r"(packed[4 * u + 1]),
-                       "r"(packed[4 * u + 2]), "r"(packed[4 * u + 3]) : "memory");
-        }
+        const uint32_t addr = p_smem + r * 128 + (((c0 >> 3) ^ (r & 7)) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[0]), "r"(packed[1]),
+                     "r"(packed[2]), "r"(packed[3]) : "memory");
       }
-      l = l * alpha + sum;
-      // hand P to the tensor core: make this row's writes visible to the async proxy, then arrive
-      // (the barrier counts all 128 rows; no thread waits on another here)
+      l += sum;
+      // hand P (and the rescaled O) to the tensor core: make this row's shared-memory writes visible to
+      // the async proxy, then arrive (the barrier counts all 128 rows; no thread waits on another here)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(bar_p);
     }
-    if (ok) ok = fold_output(n_kv_tiles - 1, alpha_prev);
-    if (ok && row_ok) {
+    if (ok) ok = mbar_wait(bar_o, (n_kv_tiles - 1) & 1, ab);
+    if (ok) {
+      tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.nq + head) * hd;
+      for (int d0 = 0; d0 < hd; d0 += 16) {           // the loads are warp-wide: rows beyond the tile join in
+        float v[16];
+        tmem_ld16(tmem_o + lane_addr + d0, v);
+        if (row_ok) {
+          uint32_t w[8];
 #pragma unroll
-      for (int d0 = 0; d0 < HDM; d0 += 8) {
-        if (d0 < hd) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 b = __floats2bfloat162_rn(o[d0 + 2 * e] * inv, o[d0 + 2 * e + 1] * inv);
+          for (int e = 0; e < 8; ++e) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * e] * inv, v[2 * e + 1] * inv);
             w[e] = *reinterpret_cast<const uint32_t*>(&b);
           }
           *reinterpret_cast<uint4*>(dst + d0) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(dst + d0 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
         }
       }
+      tc_fence_before();
     }
   }
   // ---- teardown
@@ -562,20 +572,12 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   const int chunks = (hd + 63) / 64;
   const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128;
   dim3 grid(n_tiles, nq);
-  static bool configured[2] = {false, false};
-  if (hd <= 64) {
-    if (!configured[0]) {
-      cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      configured[0] = true;
-    }
-    attention_prefill_tc_kernel<64><<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
-  } else {
-    if (!configured[1]) {
-      cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-      configured[1] = true;
-    }
-    attention_prefill_tc_kernel<128><<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    configured = true;
   }
+  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
   return check_launch("attention_prefill_tc");
 }
 
