@@ -457,6 +457,45 @@ def test_attention_prefill_on_tensor_cores(ops, ref, nq, nkv, hd, P, window, len
     close(out, exp, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("ramp", [0.02, 0.3])
+def test_attention_prefill_growing_scores(ops, ref, ramp):
+    """Keys aligned with the queries and growing with their position: a row's maximum keeps rising, slowly
+    (the softmax reference stays behind it for many tiles) or fast (it moves at every tile, and the output
+    kept on the chip is rescaled); and one late key that stands out for the rows after it."""
+    nq, nkv, hd, P, L = 2, 1, 64, 64, 640
+    g = torch.Generator().manual_seed(5)
+    n_pages = L // P
+    direction = torch.randn(hd, generator=g)
+    direction /= direction.norm()
+    k = (torch.randn(n_pages, nkv, P, hd, generator=g) * 0.3)
+    key_pos = torch.arange(L).view(n_pages, 1, P, 1)
+    k += direction * ramp * key_pos                      # score of key j grows like ramp * j * |q . direction|
+    v = torch.randn(n_pages, nkv, P, hd, generator=g)
+    q = torch.randn(L, nq * hd, generator=g) * 0.3
+    q[:, :hd] += direction * 4.0
+    q[:, hd:] += direction * 4.0
+    late = 500
+    k.view(-1, hd)[late] = direction * 400.0 * (1 if ramp < 0.1 else 3)
+    k, v, q = k.to(torch.bfloat16), v.to(torch.bfloat16), q.to(torch.bfloat16)
+    bt = torch.arange(n_pages, dtype=torch.int32).flip(0).view(1, -1).contiguous()
+    k_paged, v_paged = k.flip(0).contiguous(), v.flip(0).contiguous()      # logical page i sits in page n-1-i
+    pos, slot = torch.arange(L, dtype=torch.int32), torch.zeros(L, dtype=torch.int32)
+    tiles = []
+    for r in range(0, L, 128):
+        tiles += [r, min(128, L - r), 0, r]
+    spec = KVSpec(nkv, hd, 0)
+    out = torch.empty(L, nq * hd, dtype=torch.bfloat16, device=DEV)
+    scale = 1 / math.sqrt(hd)
+    ops.attention_prefill_tc(q.to(DEV), CacheView(k_paged.to(DEV), v_paged.to(DEV), bt.to(DEV), P, spec),
+                             torch.tensor(tiles, dtype=torch.int32, device=DEV), len(tiles) // 4, out, nq, nkv, hd, 0, scale)
+    assert int(ops.tc_error.item()) == 0
+    exp = torch.zeros(L, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q, CacheView(k_paged, v_paged, bt, P, spec), pos, slot, exp, nq, nkv, hd, 0, scale, L)
+    close(out, exp, 2e-2, 2e-2)
+    # rows after the late key see (almost) only its value
+    close(out[late + 1, :hd], v.view(-1, hd)[late].double(), 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("R,V", [(1, 17), (5, 1000), (3, 32064)])
 def test_argmax(ops, R, V):
     lg = rnd(R, V)
