@@ -402,8 +402,12 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int h0 = kvh * G + g0;
   const int pq = p.pos[t];
   const int lo_row = p.window > 0 ? max(0, pq + 1 - p.window) : 0;
-  const int lo = lo_row + split * p.split_keys;
-  const int hi = min(pq + 1, lo + p.split_keys);
+  // the row's keys are divided evenly over the splits (in steps of 16), so that a row shorter than the
+  // launch was sized for still keeps every split busy; split_keys is the upper bound
+  const int even = ((pq + 1 - lo_row + p.n_splits - 1) / p.n_splits + DK - 1) & ~(DK - 1);
+  const int sk = min(p.split_keys, max(even, DK));
+  const int lo = lo_row + split * sk;
+  const int hi = min(pq + 1, lo + sk);
   const int* bt = p.block_table + (size_t)p.slot[t] * p.max_pages;
   const int gid = lane >> 2, tid4 = lane & 3;
   constexpr int KB = HD / 16, DB = HD / 8;

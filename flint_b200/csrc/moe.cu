@@ -169,6 +169,73 @@ __global__ void moe_plan_kernel(const int* __restrict__ expert_ids, int n_assign
     token_of[row] = a >> 1;
   }
 }
+
+// Few assignments (decode): the plan and the gather of the rows in one launch.  Every block works the
+// (tiny) plan out again in shared memory, with ranks by position so that all blocks agree; block r then
+// copies the row of its token to sorted row r, and block 0 also writes the plan out.
+constexpr int DISPATCH_MAX = 256;      // assignments
+__global__ void __launch_bounds__(256)
+moe_dispatch_kernel(const int* __restrict__ expert_ids, int n_assign, int E, int tile_rows,
+                    int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_of,
+                    int* __restrict__ token_of, int* __restrict__ tile_expert, int* __restrict__ tile_row0,
+                    int* __restrict__ n_tiles, int max_tiles, const uint4* __restrict__ x,
+                    uint4* __restrict__ xs, int row_vecs) {
+  __shared__ int ids[DISPATCH_MAX];
+  __shared__ int cnt[MAX_E];
+  __shared__ int off[MAX_E + 1];
+  __shared__ int my_token;
+  pdl_launch();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  if (tid < n_assign) ids[tid] = expert_ids[tid];
+  __syncthreads();
+  if (tid < E) {
+    int c = 0;
+    for (int a = 0; a < n_assign; ++a) c += ids[a] == tid;
+    cnt[tid] = c;
+  }
+  int rank = 0;                       // assignments before this one that chose the same expert
+  if (tid < n_assign)
+    for (int a = 0; a < tid; ++a) rank += ids[a] == ids[tid];
+  __syncthreads();
+  if (tid == 0) {
+    const bool out = blockIdx.x == 0;
+    int run = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      off[e] = run;
+      if (out) {
+        counts[e] = cnt[e];
+        offsets[e] = run;
+        for (int r = 0; r < cnt[e]; r += tile_rows) {
+          if (tiles < max_tiles) {
+            tile_expert[tiles] = e;
+            tile_row0[tiles] = run + r;
+          }
+          ++tiles;
+        }
+      }
+      run += cnt[e];
+    }
+    off[E] = run;
+    if (out) {
+      offsets[E] = run;
+      *n_tiles = tiles < max_tiles ? tiles : max_tiles;
+    }
+  }
+  __syncthreads();
+  if (tid < n_assign) {
+    const int row = off[ids[tid]] + rank;
+    if (blockIdx.x == 0) {
+      row_of[tid] = row;
+      token_of[row] = tid >> 1;
+    }
+    if (row == (int)blockIdx.x) my_token = tid >> 1;
+  }
+  __syncthreads();
+  const uint4* src = x + (size_t)my_token * row_vecs;
+  uint4* dst = xs + (size_t)blockIdx.x * row_vecs;
+  for (int i = tid; i < row_vecs; i += blockDim.x) dst[i] = src[i];
+}
 }  // namespace
 
 extern "C" int flint_router_sparsemixer(const float* x, const void* wr, int w_dtype, float eps,
@@ -211,6 +278,26 @@ extern "C" int flint_moe_plan(const int* expert_ids, int n_assign, int E, int ti
   launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, expert_ids, n_assign, E, tile_rows, counts, offsets, row_of,
                                           token_of, tile_expert, tile_row0, n_tiles, max_tiles);
   return check_launch("moe_plan");
+}
+
+// The plan of flint_moe_plan and xs[r, :] = x[token_of[r], :] in one launch, for up to 256 assignments and rows
+// of a multiple of 16 bytes (x and xs 16-byte aligned).
+extern "C" int flint_moe_dispatch(const int* expert_ids, int n_assign, int E, int tile_rows, int* counts,
+                                  int* offsets, int* row_of, int* token_of, int* tile_expert, int* tile_row0,
+                                  int* n_tiles, int max_tiles, const void* x, void* xs, int row_bytes,
+                                  cudaStream_t stream) {
+  if (n_assign <= 0) return 0;
+  if (n_assign > DISPATCH_MAX) return fail("moe_dispatch: %d assignments (up to %d)", n_assign, DISPATCH_MAX);
+  if (E < 1 || E > MAX_E) return fail("moe_dispatch: %d experts (supported: 1..%d)", E, MAX_E);
+  if (tile_rows <= 0) return fail("moe_dispatch: bad tile size %d", tile_rows);
+  if (max_tiles < flint_moe_max_tiles(n_assign, E, tile_rows))
+    return fail("moe_dispatch: tile map of %d entries is too small", max_tiles);
+  if (row_bytes <= 0 || (row_bytes & 15) || ((uintptr_t)x & 15) || ((uintptr_t)xs & 15))
+    return fail("moe_dispatch: rows must be a multiple of 16 bytes and 16-byte aligned");
+  launch_pdl(moe_dispatch_kernel, dim3(n_assign), dim3(256), 0, stream, expert_ids, n_assign, E, tile_rows, counts,
+             offsets, row_of, token_of, tile_expert, tile_row0, n_tiles, max_tiles, (const uint4*)x, (uint4*)xs,
+             row_bytes / 16);
+  return check_launch("moe_dispatch");
 }
 
 extern "C" const char* flint_moe_last_error() { return g_error; }

@@ -439,10 +439,10 @@ class CudaOps:
         base = T * nkv * g_chunks
         span = max(span, 1)
         if T <= 256 and hd <= 128 and bf16:
-            # tensor-core decode kernel fed by TMA: 8 query heads per warp, about one wave of 8 warps
-            # per SM, at least 128 keys per warp
+            # tensor-core decode kernel fed by TMA: 8 query heads per warp, at most one wave of 8 warps
+            # per SM (a second, nearly empty wave would cost as much as a full one), at least 64 keys per warp
             base8 = T * nkv * -(-(nq // nkv) // 8)
-            n = max(1, min(span // 128, -(-1184 // base8)))
+            n = max(1, min(span // 64, 1184 // base8))
             keys = -(-(-(-span // n)) // 16) * 16
             return "tma", keys, -(-span // keys)
         if T <= 256:
@@ -535,7 +535,7 @@ class CudaOps:
         self._run("moe", "flint_router_sparsemixer", _ptr(x), _ptr(wr), c_int(_code(wr.dtype)), c_float(eps),
                   _ptr(expert_ids), _ptr(gates), _ptr(logits_out), c_int(T), c_int(H), c_int(E))
 
-    def moe_plan(self, expert_ids, n_experts, tile_rows) -> MoePlan:
+    def _plan_buffers(self, expert_ids, n_experts, tile_rows):
         _check(expert_ids, "expert_ids", torch.int32)
         n = expert_ids.numel()
         dev = expert_ids.device
@@ -547,11 +547,31 @@ class CudaOps:
             parts.append(ints[o:o + size])
             o += size
         counts, offsets, row_of, token_of, tile_expert, tile_row0, n_tiles = parts
-        self._run("moe", "flint_moe_plan", _ptr(expert_ids), c_int(n), c_int(n_experts), c_int(tile_rows),
-                  _ptr(counts), _ptr(offsets), _ptr(row_of), _ptr(token_of), _ptr(tile_expert), _ptr(tile_row0),
-                  _ptr(n_tiles), c_int(max_tiles))
-        return MoePlan(n_experts, tile_rows, max_tiles, counts, offsets, row_of.view(-1, 2), token_of,
+        plan = MoePlan(n_experts, tile_rows, max_tiles, counts, offsets, row_of.view(-1, 2), token_of,
                        tile_expert, tile_row0, n_tiles)
+        return plan, [_ptr(t) for t in parts]
+
+    def moe_plan(self, expert_ids, n_experts, tile_rows) -> MoePlan:
+        plan, ptrs = self._plan_buffers(expert_ids, n_experts, tile_rows)
+        self._run("moe", "flint_moe_plan", _ptr(expert_ids), c_int(expert_ids.numel()), c_int(n_experts),
+                  c_int(tile_rows), *ptrs, c_int(plan.max_tiles))
+        return plan
+
+    def moe_dispatch(self, expert_ids, n_experts, tile_rows, x):
+        """The plan for these choices and the rows of x in its order: (plan, xs) with
+        xs[r] = x[plan.token_of[r]].  Few rows take one fused launch."""
+        _check(x, "x", dims=2)
+        n = expert_ids.numel()
+        xs = torch.empty((n, x.shape[1]), dtype=x.dtype, device=x.device)
+        row_bytes = x.shape[1] * x.element_size()
+        if n > 256 or row_bytes % 16 or x.data_ptr() % 16:
+            plan = self.moe_plan(expert_ids, n_experts, tile_rows)
+            self.gather_rows(x, plan.token_of, xs)
+            return plan, xs
+        plan, ptrs = self._plan_buffers(expert_ids, n_experts, tile_rows)
+        self._run("moe", "flint_moe_dispatch", _ptr(expert_ids), c_int(n), c_int(n_experts), c_int(tile_rows), *ptrs,
+                  c_int(plan.max_tiles), _ptr(x), _ptr(xs), c_int(row_bytes))
+        return plan, xs
 
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):

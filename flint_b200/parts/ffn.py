@@ -101,9 +101,7 @@ class SparseMixerMoE(FeedForward):
             ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
             gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
             ops.router_sparsemixer(x[torch.float32], self.w_router, self.eps, ids, gates)
-        plan = ops.moe_plan(ids, self.E, ops.moe_tile_rows(T, self.E, self.w13.dtype))
-        xs = torch.empty((2 * T, self.hidden), dtype=xa.dtype, device=dev)
-        ops.gather_rows(xa, plan.token_of, xs)
+        plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w13.dtype), xa)
         a = torch.empty((2 * T, self.inter), dtype=self.w13.dtype, device=dev)
         ops.gated_gemm(xs, self.w13, a, self.act, plan)
         y = torch.empty((2 * T, self.hidden), dtype=torch.float32, device=dev)

@@ -218,6 +218,10 @@ class RefOps:
         return MoePlan(n_experts, tile_rows, max_tiles, i32(counts), i32(offsets), i32(row_of).view(-1, 2),
                        i32(token_of), pad(tiles_e), pad(tiles_r), i32([len(tiles_e)]))
 
+    def moe_dispatch(self, expert_ids, n_experts, tile_rows, x):
+        plan = self.moe_plan(expert_ids, n_experts, tile_rows)
+        return plan, x[plan.token_of.long()].clone()
+
     # ------------------------------------------------------------------ sampling
     def argmax(self, logits, out):
         out.copy_(torch.argmax(logits, dim=-1).to(torch.int32))

@@ -204,6 +204,20 @@ def test_gated_and_grouped(ops, ref, act, dtype, I):
     xs = torch.empty(2 * T, H, dtype=dtype, device=DEV)
     ops.gather_rows(x.to(DEV), plan.token_of, xs)
     assert torch.equal(xs.cpu(), x[token_of])
+    # plan and gather in one launch (few rows), with ranks by position: the same counts and tiles, a valid order
+    for n_tok in (T, 1, 9):
+        sub = ids[:n_tok].contiguous()
+        rp = ref.moe_plan(sub, E, 64)
+        dplan, dxs = ops.moe_dispatch(sub.to(DEV), E, 64, x[:n_tok].to(DEV))
+        assert torch.equal(dplan.counts.cpu(), rp.counts) and torch.equal(dplan.offsets.cpu(), rp.offsets)
+        nt2 = int(dplan.n_tiles.item())
+        assert nt2 == int(rp.n_tiles.item())
+        assert torch.equal(dplan.tile_expert.cpu()[:nt2], rp.tile_expert[:nt2])
+        assert torch.equal(dplan.tile_row0.cpu()[:nt2], rp.tile_row0[:nt2])
+        d_row, d_tok = dplan.row_of.cpu().long(), dplan.token_of.cpu().long()
+        assert torch.equal(d_row, rp.row_of.long())            # both rank by position
+        assert torch.equal(d_tok[d_row], torch.arange(n_tok)[:, None].expand(n_tok, 2))
+        assert torch.equal(dxs.cpu(), x[:n_tok][d_tok])
     w1, w3, w2 = (rnd(E, I, H, dtype=dtype, seed=1, scale=0.1), rnd(E, I, H, dtype=dtype, seed=2, scale=0.1),
                   rnd(E, H, I, dtype=dtype, seed=3, scale=0.1))
     w13 = ops.pair_gate_up(w1, w3).contiguous()        # the kernels' layout; the reference keeps its own
