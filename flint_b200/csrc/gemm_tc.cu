@@ -65,6 +65,7 @@ struct Params {
   int rows, N, K;
   int kb_per_split, splits, stages;
   int defer;                   // write raw partial tiles even for a single split; the consumer sums them
+  int stream_k;                // cut the K blocks of all tiles, laid end to end, into equal runs, one per block
   int w_expert_rows;           // rows between two experts in the stacked weight tensor
 };
 
@@ -96,9 +97,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   constexpr int FM = GATED ? GATED_FEATURES : BM;      // output features per tile
   const int tiles_m = (p.N + FM - 1) / FM;
   const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
-  const int n_items = tiles_m * tiles_n * p.splits;
-  if ((int)blockIdx.x >= n_items) return;
   const int total_kb = (p.K + BK - 1) / BK;
+  const int n_items = tiles_m * tiles_n * p.splits;
+  // Stream-K (few rows, partial sums deferred to the consumer): the K blocks of all tiles are laid end to end
+  // and cut into runs of `run` blocks, one run per block of the grid, so that every block streams the same
+  // number of weight bytes however many tiles there are (with experts, the number of tiles is only known
+  // here).  A tile is then covered by up to p.splits pieces (run is kept long enough for that); piece i
+  // of a tile goes to partial slice i, and the first piece also clears the slices the tile does not use.
+  int run = 0, unit0 = 0, unit1 = 0;
+  if (p.stream_k) {
+    const long long units = (long long)tiles_m * tiles_n * total_kb;
+    const int run_min = p.splits > 1 ? (total_kb - 1 + p.splits - 2) / (p.splits - 1) : total_kb;
+    run = max(max((int)((units + gridDim.x - 1) / gridDim.x), run_min), 1);
+    if (p.splits == 1) run = ((run + total_kb - 1) / total_kb) * total_kb;     // whole tiles only
+    const long long u0 = (long long)blockIdx.x * run;
+    if (u0 >= units) return;
+    unit0 = (int)u0;
+    unit1 = (int)min(units, u0 + run);
+  } else if ((int)blockIdx.x >= n_items) {
+    return;
+  }
 
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -133,11 +151,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // to neighbouring blocks, which then share the activation tile in L2
   // A tile that holds fewer than BN token rows (the end of an expert's rows, or of the batch) runs its MMAs
   // with N = its rows rounded up to 16.
-  struct Item { int kb0, nkb, f0, w_row, row0, row_end, z, mma_n; };
-  auto item_of = [&](int it) {
+  struct Item { int kb0, nkb, f0, w_row, row0, row_end, z, mma_n, pieces; bool valid; };
+  // the j-th item of this block; not valid when it has no more
+  auto item_at = [&](int j) -> Item {
     Item r;
-    r.z = it % p.splits;
-    const int t = it / p.splits;
+    r.valid = false;
+    int t;
+    if (p.stream_k) {
+      t = unit0 / total_kb + j;
+      const int t_begin = t * total_kb;
+      if (t_begin >= unit1) return r;
+      r.kb0 = max(unit0, t_begin) - t_begin;
+      r.nkb = min(unit1, t_begin + total_kb) - t_begin - r.kb0;
+      const int first_block = t_begin / run;
+      r.z = (int)blockIdx.x - first_block;
+      r.pieces = (t_begin + total_kb - 1) / run - first_block + 1;
+    } else {
+      const int it = blockIdx.x + j * gridDim.x;
+      if (it >= n_items) return r;
+      r.z = it % p.splits;
+      t = it / p.splits;
+      r.kb0 = r.z * p.kb_per_split;
+      r.nkb = min(total_kb, r.kb0 + p.kb_per_split) - r.kb0;
+      r.pieces = p.splits;
+    }
     const int tm = t % tiles_m, tn = t / tiles_m;
     int expert = 0;
     r.row0 = tn * BN;
@@ -149,10 +186,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     r.f0 = tm * FM;
     r.w_row = expert * p.w_expert_rows + tm * BM;
-    r.kb0 = r.z * p.kb_per_split;
-    r.nkb = min(total_kb, r.kb0 + p.kb_per_split) - r.kb0;
     const int valid = max(1, min(BN, r.row_end - r.row0));
     r.mma_n = (valid + 15) & ~15;
+    r.valid = true;
     return r;
   };
 
@@ -160,8 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---------------------------------------------------------------- TMA producer
     int kc = 0;                      // K blocks issued so far, over all items
     bool first = true, ok = true;
-    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x) {
-      const Item w = item_of(it);
+    for (int j = 0; ok; ++j) {
+      const Item w = item_at(j);
+      if (!w.valid) break;
       int i = 0;
       if (first) {
         // The weights do not depend on the kernel before this one: the first ring of weight tiles is
@@ -192,8 +229,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer
     int kc = 0, j = 0;
     bool ok = true;
-    for (int it = blockIdx.x; it < n_items && ok; it += gridDim.x, ++j) {
-      const Item w = item_of(it);
+    for (; ok; ++j) {
+      const Item w = item_at(j);
+      if (!w.valid) break;
       const int buf = j & 1;
       ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, ab);     // the epilogue has drained this set
       if (!ok) break;
@@ -220,8 +258,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const bool raw = p.splits > 1 || p.defer;     // partial tile: no bias, no accumulate
     bool waited = false;
     int j = 0;
-    for (int it = blockIdx.x; it < n_items; it += gridDim.x, ++j) {
-      const Item w = item_of(it);
+    for (;; ++j) {
+      const Item w = item_at(j);
+      if (!w.valid) break;
       const int buf = j & 1;
       if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, ab)) break;
       tc_fence_after();
@@ -232,42 +271,52 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const bool f_ok = f < p.N;
       const float bias = (p.bias && f_ok && !raw) ? p.bias[f] : 0.f;
       const uint32_t lane_addr = tmem + buf * ACC_COLS + ((uint32_t)(q * 32) << 16);
+      constexpr int CH = BN < 32 ? 16 : 32;         // columns fetched from tensor memory at a time
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 8) {
-        if (w.row0 + c0 >= w.row_end) break;        // uniform in the warp
-        float v[8];
-        tmem_ld8(lane_addr + c0, v);
-        if (GATED) {
-          // the low half-warp takes token columns 0-3 and needs their up values, the high half takes
-          // columns 4-7 and needs their gate values: one exchange of four values each
-          const bool low = lane < 16;
+      for (int c1 = 0; c1 < BN; c1 += CH) {
+        if (w.row0 + c1 >= w.row_end) break;        // uniform in the warp
+        float vv[CH];
+        if (CH == 16) tmem_ld16(lane_addr + c1, vv); else tmem_ld32(lane_addr + c1, vv);
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float got = __shfl_xor_sync(0xffffffffu, low ? v[4 + c] : v[c], 16);
-            const float gate = low ? v[c] : got, up = low ? got : v[4 + c];
-            v[c] = act_fn(gate, p.act) * up;
-          }
-        }
+        for (int g = 0; g < CH; g += 8) {
+          const int c0 = c1 + g;
+          float* v = vv + g;
+          if (GATED) {
+            // the low half-warp takes token columns 0-3 and needs their up values, the high half takes
+            // columns 4-7 and needs their gate values: one exchange of four values each
+            const bool low = lane < 16;
 #pragma unroll
-        for (int c = 0; c < (GATED ? 4 : 8); ++c) {
-          const int r = w.row0 + c0 + (GATED && lane >= 16 ? 4 + c : c);
-          if (r >= w.row_end || !f_ok) continue;
-          float y = v[c];
-          if (raw) {
-            p.partial[((size_t)w.z * p.rows + r) * p.N + f] = y;
-            continue;
+            for (int c = 0; c < 4; ++c) {
+              const float got = __shfl_xor_sync(0xffffffffu, low ? v[4 + c] : v[c], 16);
+              const float gate = low ? v[c] : got, up = low ? got : v[4 + c];
+              v[c] = act_fn(gate, p.act) * up;
+            }
           }
-          y += bias;
-          const size_t o = (size_t)r * p.ldo + f;
-          if (p.out_dtype == FLINT_F32) {
-            float* out = (float*)p.out;
-            out[o] = p.accumulate ? out[o] + y : y;
-          } else {
-            __nv_bfloat16* out = (__nv_bfloat16*)p.out;
-            out[o] = __float2bfloat16_rn(p.accumulate ? __bfloat162float(out[o]) + y : y);
+#pragma unroll
+          for (int c = 0; c < (GATED ? 4 : 8); ++c) {
+            const int r = w.row0 + c0 + (GATED && lane >= 16 ? 4 + c : c);
+            if (r >= w.row_end || !f_ok) continue;
+            float y = v[c];
+            if (raw) {
+              p.partial[((size_t)w.z * p.rows + r) * p.N + f] = y;
+              continue;
+            }
+            y += bias;
+            const size_t o = (size_t)r * p.ldo + f;
+            if (p.out_dtype == FLINT_F32) {
+              float* out = (float*)p.out;
+              out[o] = p.accumulate ? out[o] + y : y;
+            } else {
+              __nv_bfloat16* out = (__nv_bfloat16*)p.out;
+              out[o] = __float2bfloat16_rn(p.accumulate ? __bfloat162float(out[o]) + y : y);
+            }
           }
         }
       }
+      // stream-K: the first piece of a tile clears the partial slices that the tile has no piece for
+      if (raw && w.z == 0 && w.pieces < p.splits && f_ok)
+        for (int r = w.row0; r < min(w.row_end, w.row0 + BN); ++r)
+          for (int z = w.pieces; z < p.splits; ++z) p.partial[((size_t)z * p.rows + r) * p.N + f] = 0.f;
       tc_fence_before();
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
     }
@@ -367,7 +416,9 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
   }
   constexpr int acc_cols = 2 * BN;
   const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
-  const long long items = (long long)grid.x * grid.y * grid.z;
+  // stream-K: the work is cut into as many runs as blocks stay resident (at least one K block each)
+  const long long items = p.stream_k ? (long long)grid.x * grid.y * ((p.K + BK - 1) / BK)
+                                     : (long long)grid.x * grid.y * grid.z;
   const unsigned blocks = (unsigned)(items < (long long)sm_count * per_sm ? items : (long long)sm_count * per_sm);
   launch_pdl(gemm_tc_kernel<BN, GATED>, dim3(blocks), dim3(THREADS), smem, stream, mw, mx, p);
   return check_launch("gemm_tc");
@@ -383,7 +434,7 @@ extern "C" void flint_gemm_tc_set_stages(int stages) { g_stage_override = stages
 
 extern "C" int flint_gemm_tc_stages(int bn, int gated) {
   (void)gated;   // a gated tile has the same footprint: 64 gate and 64 up rows on the M side
-  if (g_stage_override > 0) return g_stage_override;
+  if (g_stage_override > 0 && bn < 128) return g_stage_override;   // tuning applies to the few-row tiles
   const int stage = BM * BK * 2 + bn * BK * 2;
   int s = (bn >= 128 ? 192 * 1024 : 100 * 1024) / stage;
   if (s < 3) s = 3;
@@ -401,14 +452,17 @@ extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
 // bn: token rows per tile (16, 32, 64, 128 or 256); with a tile map it must equal the plan's tile size.
 // splits > 1 divides the K blocks over several CTAs and needs `partial` (not with a gated product).
 // defer: leave the raw partial sums [splits, rows, N] in `partial` (no bias, nothing added to out);
-// the caller's next kernel adds them up.  The number of splits used is ceil(kb / ceil(kb / splits))
+// the caller's next kernel adds them up.
+// stream_k (with defer): instead of splits equal pieces per tile, the K blocks of all tiles laid end to end are
+// cut into equal runs, one per resident block; a tile gets at most `splits` pieces and every one of the
+// `splits` slices of `partial` is written (pieces that do not exist as zeros).  The number of splits used is ceil(kb / ceil(kb / splits))
 // with kb = ceil(K / 64).
 // error_flag: device int, set to 1 if a bounded wait ran out.
 extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, const float* bias, void* out,
                              int out_dtype, int ldo, int accumulate, int act, const int* tile_expert,
                              const int* tile_row0, const int* n_tiles, const int* offsets, int max_tiles,
                              int n_experts, int rows, int N, int K, int bn, int splits, float* partial,
-                             int defer, int* error_flag, cudaStream_t stream) {
+                             int defer, int stream_k, int* error_flag, cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
@@ -419,10 +473,11 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   if (splits < 1) return fail("gemm_tc: bad split %d", splits);
   if ((splits > 1 || defer) && (w_up || !partial)) return fail("gemm_tc: partial sums need scratch and cannot be gated");
   if (!error_flag) return fail("gemm_tc: needs an error flag");
+  if (stream_k && !defer) return fail("gemm_tc: stream-K leaves partial sums and needs defer");
   const int total_kb = (K + BK - 1) / BK;
   if (splits > total_kb) splits = total_kb;
   const int kbps = (total_kb + splits - 1) / splits;
-  splits = (total_kb + kbps - 1) / kbps;            // no empty split
+  if (!stream_k) splits = (total_kb + kbps - 1) / kbps;            // no empty split
   const int tiles_n = tile_expert ? max_tiles : (rows + bn - 1) / bn;
   if (tiles_n <= 0) return 0;
 
@@ -436,7 +491,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   p.error_flag = error_flag;
   p.out_dtype = out_dtype; p.ldo = ldo; p.accumulate = accumulate; p.act = act;
   p.rows = rows; p.N = N; p.K = K;
-  p.kb_per_split = kbps; p.splits = splits; p.defer = defer;
+  p.kb_per_split = kbps; p.splits = splits; p.defer = defer; p.stream_k = stream_k;
   p.w_expert_rows = w_expert_rows;
   p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
   if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;

@@ -315,23 +315,27 @@ class CudaOps:
             self._gemm_simt(x, w, False, out[0], None, False, 0, plan, M, N, K)
             return out
         kb = -(-K // 64)
+        stream_k = 0
         if plan is None:
             bn, E = self.token_tile(M), 1
             splits = splits or self._k_splits(M, N, K, bn)
         else:
             bn, E = plan.tile_rows, plan.n_experts
-            # the number of row tiles is known on the device only: assume the rows spread over
-            # min(rows, experts) experts
-            tiles = -(-N // 128) * max(1, min(M, E))
-            splits = splits or (1 if tiles >= 148 or kb < 8 else max(1, min(296 // tiles, kb // 4, 16)))
-        kbps = -(-kb // splits)
-        splits = -(-kb // kbps)
+            if splits is None and bn <= 128 and kb >= 2:
+                # few rows per expert: how many tiles there are is known on the device only, so the kernel
+                # cuts the K blocks of all tiles into equal runs itself; a tile gets at most `splits` pieces
+                stream_k, splits = 1, min(12, kb)
+            splits = splits or 1
+        if not stream_k:
+            kbps = -(-kb // splits)
+            splits = -(-kb // kbps)
         out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
         self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(0), _ptr(None),
                   _ptr(out), c_int(F32), c_int(N), c_int(0), c_int(0), _ptr(plan.tile_expert if plan else None),
                   _ptr(plan.tile_row0 if plan else None), _ptr(plan.n_tiles if plan else None),
                   _ptr(plan.offsets if plan else None), c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M),
-                  c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1), _ptr(self.tc_error))
+                  c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1), c_int(stream_k),
+                  _ptr(self.tc_error))
         return out
 
     @staticmethod
@@ -417,7 +421,7 @@ class CudaOps:
                   c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
                   c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
-                  c_int(splits), _ptr(partial), c_int(0), _ptr(self.tc_error))
+                  c_int(splits), _ptr(partial), c_int(0), c_int(0), _ptr(self.tc_error))
 
     def _gemm_simt(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None and plan.tile_rows > 64:

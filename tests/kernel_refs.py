@@ -69,9 +69,12 @@ class RefOps:
         if pending.y is not None:
             self.moe_combine(x, pending.y, pending.row_of, pending.gates)
 
-    def gemm_partials(self, x, w):
-        out = torch.empty((1, x.shape[0], w.shape[0]), dtype=torch.float32)
-        self.gemm(x, w, out[0])
+    def gemm_partials(self, x, w, splits=None, plan=None):
+        out = torch.empty((1, x.shape[0], w.shape[-2]), dtype=torch.float32)
+        if plan is None:
+            self.gemm(x, w, out[0])
+        else:
+            self.grouped_gemm(x, w, out[0], plan)
         return out
 
     def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None):

@@ -263,6 +263,12 @@ def test_gated_and_grouped(ops, ref, act, dtype, I):
         ea_s = torch.zeros(2 * rows, I, dtype=torch.float64)
         ref.gated_gemm(xs_s.cpu(), r13, ea_s, act, cp)
         close(a_s, ea_s, *tol)
+        # the down product left as partial slices (the K blocks of all tiles cut into equal runs)
+        yp = ops.gemm_partials(a_s, w2.to(DEV), plan=plan_s)
+        assert yp.dim() == 3 and tuple(yp.shape[1:]) == (2 * rows, H)
+        ey_s = torch.zeros(2 * rows, H, dtype=torch.float64)
+        ref.grouped_gemm(a_s.cpu(), w2, ey_s, cp)
+        close(yp.sum(0), ey_s, 1e-5, 1e-5)
 
 
 @pytest.mark.parametrize("tile", [128, 256])
