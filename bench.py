@@ -130,9 +130,10 @@ def run_decode(model, cfg, batch, prompt_len, steps, warmup, rng, count_experts=
     V = cfg["vocab_size"]
     slots = [model.cache.admit() for _ in range(batch)]
     for s in slots:
-        toks = [rng.randrange(V) for _ in range(prompt_len)]
         model.cache.ensure(s, 0, prompt_len)
-        model.step([StepEntry(s, 0, toks, [])])
+        for p0 in range(0, prompt_len, 2048):          # in portions, as the scheduler would
+            n = min(2048, prompt_len - p0)
+            model.step([StepEntry(s, p0, [rng.randrange(V) for _ in range(n)], [])])
     pos = prompt_len
     distinct = None
     if count_experts:
@@ -196,9 +197,11 @@ def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
     from flint_b200.sampling.params import SamplingParams
     eng = Engine(model, SamplingParams.greedy(), seed=1, prefill_chunk=2048, max_step_tokens=2048 + batch)
     V = cfg["vocab_size"]
-    # requests are admitted one prompt per step, so the first has decoded `batch` tokens before the last is
-    # in: give all of them room to keep decoding through the timed region
-    ids = [eng.create([rng.randrange(V) for _ in range(prompt_len)], steps + warmup + 2 * batch + 8) for _ in range(batch)]
+    # prompts go in one portion per step, so the first request has decoded batch * portions tokens before the
+    # last one is in: give all of them room to keep decoding through the timed region
+    portions = -(-prompt_len // 2048)
+    ids = [eng.create([rng.randrange(V) for _ in range(prompt_len)], steps + warmup + batch * (portions + 1) + 8)
+           for _ in range(batch)]
     while any(r.remaining > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
         eng.step()
     for _ in range(warmup):
