@@ -123,7 +123,7 @@ class Engine:
         portions = self.scheduler.plan()
         if not portions:
             return 0
-        entries = [StepEntry(p.request.slot, p.start, p.request.tokens[p.start:p.start + p.n_tokens],
+        entries = [StepEntry(p.request.slot, p.start, p.request.span(p.start, p.n_tokens),
                              [p.n_tokens - 1] if p.wants_logits else []) for p in portions]
         logits = self.model.step(entries)
         rows = [(p.request.sampling, p.request.rng, p.request.generated) for p in portions if p.wants_logits]

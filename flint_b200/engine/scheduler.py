@@ -54,6 +54,19 @@ class Request:
         return self.prompt + self.generated
 
     @property
+    def n_tokens(self):
+        return len(self.prompt) + len(self.generated)
+
+    def span(self, start, n):
+        """Tokens [start, start + n) of prompt and generated text, without joining the two lists."""
+        np_ = len(self.prompt)
+        if start + n <= np_:
+            return self.prompt[start:start + n]
+        if start >= np_:
+            return self.generated[start - np_:start - np_ + n]
+        return self.prompt[start:] + self.generated[:start + n - np_]
+
+    @property
     def remaining(self):
         return len(self.prompt) + len(self.generated) - self.n_cached
 
@@ -128,7 +141,7 @@ class Scheduler:
                 self.running.remove(req)
                 self.cache.release(req.slot)
                 req.slot = -1
-                self._fail(req, f"request of {len(req.tokens)} tokens needs more pages than the pool has")
+                self._fail(req, f"request of {req.n_tokens} tokens needs more pages than the pool has")
                 break
             else:
                 victim = req
@@ -167,10 +180,10 @@ class Scheduler:
         # 3. admit waiting requests, first come first served; never preempts
         while self.waiting and budget > 0 and self.cache.free_slots > 0:
             req = self.waiting[0]
-            need_pages = -(-len(req.tokens) // self.page_size)
-            if len(req.tokens) + 1 > self.max_context or (need_pages > self.total_pages and not self._windowed()):
+            need_pages = -(-req.n_tokens // self.page_size)
+            if req.n_tokens + 1 > self.max_context or (need_pages > self.total_pages and not self._windowed()):
                 self.waiting.popleft()
-                self._fail(req, f"request of {len(req.tokens)} tokens can never fit "
+                self._fail(req, f"request of {req.n_tokens} tokens can never fit "
                                 f"({self.total_pages} pages of {self.page_size}, context limit {self.max_context})")
                 continue
             slot = self.cache.admit()
@@ -217,7 +230,7 @@ class Scheduler:
             emitted.append((req, token))
             if len(req.generated) >= req.max_tokens:
                 self._finish(req, "length")
-            elif len(req.tokens) + 1 > self.max_context:
+            elif req.n_tokens + 1 > self.max_context:
                 self._finish(req, "context")
         return emitted
 
