@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const Params p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];   // tiles need 1024-byte alignment (128-byte swizzle)
-  __shared__ __align__(8) uint64_t bars[9];   // q, kv_full[2], kv_empty[2], s_full[2], p_full, o_full
+  __shared__ __align__(8) uint64_t bars[13];  // q, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_full
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -136,8 +136,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t kv_smem = q_smem + chunks * BQ * 128;                // per stage: K chunks, then V chunks
   const uint32_t kv_stage_bytes = 2u * chunks * BKV * 128;
   const uint32_t p_smem = kv_smem + STAGES * kv_stage_bytes;          // [128 rows][128 B]
-  const uint32_t bar_q = smem_u32(&bars[0]), bar_full0 = smem_u32(&bars[1]), bar_empty0 = smem_u32(&bars[3]);
-  const uint32_t bar_s0 = smem_u32(&bars[5]), bar_p = smem_u32(&bars[7]), bar_o = smem_u32(&bars[8]);
+  // Keys and values have rings of their own: a key tile is free as soon as its scores are computed, well
+  // before the values of the same tile are, so the next keys are on their way while the softmax still runs
+  const uint32_t bar_q = smem_u32(&bars[0]), bar_kfull0 = smem_u32(&bars[1]), bar_kempty0 = smem_u32(&bars[3]);
+  const uint32_t bar_vfull0 = smem_u32(&bars[5]), bar_vempty0 = smem_u32(&bars[7]);
+  const uint32_t bar_s0 = smem_u32(&bars[9]), bar_p = smem_u32(&bars[11]), bar_o = smem_u32(&bars[12]);
   const uint32_t tmem_cols = 256;             // two score buffers of 64 columns, then up to 128 of output
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -145,8 +148,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     abort_flag = 0;
     mbar_init(bar_q, 1);
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full0 + 8 * s, 1);
-      mbar_init(bar_empty0 + 8 * s, 1);
+      mbar_init(bar_kfull0 + 8 * s, 1);
+      mbar_init(bar_kempty0 + 8 * s, 1);
+      mbar_init(bar_vfull0 + 8 * s, 1);
+      mbar_init(bar_vempty0 + 8 * s, 1);
     }
     mbar_init(bar_s0, 1);
     mbar_init(bar_s0 + 8, 1);
@@ -167,12 +172,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_expect_tx(bar_q, chunks * BQ * 128);
     for (int c = 0; c < chunks; ++c) tma_load_2d(q_smem + c * BQ * 128, &map_q, head * hd + c * 64, row0, bar_q);
     const int* bt = p.block_table + (size_t)slot * p.max_pages;
-    for (int i = 0; i < n_kv_tiles; ++i) {
+    // one operand (keys or values) of tile i into its half of stage i % STAGES
+    auto load_tile = [&](int i, bool values) -> bool {
       const int s = i % STAGES;
-      if (!mbar_wait(bar_empty0 + 8 * s, ((i / STAGES) & 1) ^ 1, ab)) break;
-      const uint32_t bar = bar_full0 + 8 * s;
-      mbar_expect_tx(bar, kv_stage_bytes);
-      const uint32_t k_dst = kv_smem + s * kv_stage_bytes, v_dst = k_dst + chunks * BKV * 128;
+      if (!mbar_wait((values ? bar_vempty0 : bar_kempty0) + 8 * s, ((i / STAGES) & 1) ^ 1, ab)) return false;
+      const uint32_t bar = (values ? bar_vfull0 : bar_kfull0) + 8 * s;
+      mbar_expect_tx(bar, kv_stage_bytes / 2);
+      const uint32_t dst = kv_smem + s * kv_stage_bytes + (values ? chunks * BKV * 128 : 0);
       const int kv0 = (tile_lo + i) * BKV;
       for (int pc = 0; pc < pieces; ++pc) {
         const int key = kv0 + pc * piece;
@@ -180,11 +186,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         int page = lp < p.max_pages ? bt[lp] : -1;
         if (page < 0) page = 0;   // never visible to these queries (masked): any finite page will do
         const int row = (page * p.nkv + kvh) * P + key % P;
-        for (int c = 0; c < chunks; ++c) {
-          tma_load_2d(k_dst + c * BKV * 128 + pc * piece * 128, &map_k, c * 64, row, bar);
-          tma_load_2d(v_dst + c * BKV * 128 + pc * piece * 128, &map_v, c * 64, row, bar);
-        }
+        for (int c = 0; c < chunks; ++c)
+          tma_load_2d(dst + c * BKV * 128 + pc * piece * 128, values ? &map_v : &map_k, c * 64, row, bar);
       }
+      return true;
+    };
+    // in the order in which the stages come free: K_0, K_1, V_0, then K_{i+2} (after S_i) and V_{i+1} (after P V of i-1)
+    bool ok = load_tile(0, false);
+    if (ok && n_kv_tiles > 1) ok = load_tile(1, false);
+    if (ok) ok = load_tile(0, true);
+    for (int i = 0; ok && i < n_kv_tiles; ++i) {
+      if (i + 2 < n_kv_tiles) ok = load_tile(i + 2, false);
+      if (ok && i + 1 < n_kv_tiles) ok = load_tile(i + 1, true);
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issue
@@ -193,7 +206,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // S_i = Q K_i^T into score buffer i & 1, as soon as the keys of tile i have landed
     auto issue_scores = [&](int i) -> bool {
       const int s = i % STAGES;
-      if (!mbar_wait(bar_full0 + 8 * s, (i / STAGES) & 1, ab)) return false;
+      if (!mbar_wait(bar_kfull0 + 8 * s, (i / STAGES) & 1, ab)) return false;
       tc_fence_after();
       const uint32_t k_src = kv_smem + s * kv_stage_bytes;
       for (int k = 0; k < hd / 16; ++k) {
@@ -202,6 +215,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_bf16(tmem_s + (i & 1) * BKV, smem_desc(q_smem + off), smem_desc(k_src + koff), idesc_s, k > 0 ? 1u : 0u);
       }
       umma_commit(bar_s0 + 8 * (i & 1));
+      umma_commit(bar_kempty0 + 8 * s);          // the keys are free once these MMAs have read them
       return true;
     };
     if (ok) ok = issue_scores(0);
@@ -211,8 +225,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) break;
       ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read, O is rescaled
       if (!ok) break;
-      tc_fence_after();
       const int s = i % STAGES;
+      ok = mbar_wait(bar_vfull0 + 8 * s, (i / STAGES) & 1, ab);
+      if (!ok) break;
+      tc_fence_after();
       const uint32_t v_src = kv_smem + s * kv_stage_bytes + chunks * BKV * 128;
       for (int k = 0; k < BKV / 16; ++k) {      // O_tile = P V over the 64 keys
         // V [keys, hd] is MN-major for B: 16 keys down = 2048 bytes; 64-wide chunks of hd are BKV*128 apart
@@ -220,7 +236,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_bf16(tmem_o, smem_desc(p_smem + k * 32), vd, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(bar_o);
-      umma_commit(bar_empty0 + 8 * s);
+      umma_commit(bar_vempty0 + 8 * s);
     }
   } else if (warp >= 2) {
     // ---------------------------------------------------------------- softmax rows
@@ -242,17 +258,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool need_mask = (kv0 + BKV - 1 > pos0) || (p.window > 0 && kv0 < pos0 + n_rows - p.window);
       float sc[BKV];
       tmem_ld64(tmem_s + (i & 1) * BKV + lane_addr, sc);
-      float mraw = -INFINITY;                       // of the raw scores; the scale is positive
+      // the maximum of the raw scores (the scale is positive), in four strands so that the chain is short
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BKV; ++c) {
           const int kj = kv0 + c;
-          if (kj <= q_pos && kj >= first) mraw = fmaxf(mraw, sc[c]);
+          if (kj <= q_pos && kj >= first) m4[c & 3] = fmaxf(m4[c & 3], sc[c]);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < BKV; ++c) mraw = fmaxf(mraw, sc[c]);
+        for (int c = 0; c < BKV; ++c) m4[c & 3] = fmaxf(m4[c & 3], sc[c]);
       }
+      const float mraw = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       const float mx = fmaxf(ref, mraw * p.scale_log2);
       // P V of the previous tile must be done before O is touched or P's buffer is written again
       if (i > 0) {
@@ -276,7 +294,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       // probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
-      float sum = 0.f;
+      // the row's sum is kept in float32 from the unrounded probabilities (four strands)
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_ref = -ref;
 #pragma unroll
       for (int c0 = 0; c0 < BKV; c0 += 8) {
         uint32_t packed[4];
@@ -285,22 +305,22 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           float pr[2];
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
-            pr[e] = ex2(fmaf(sc[c0 + c + e], p.scale_log2, -ref));
+            pr[e] = ex2(fmaf(sc[c0 + c + e], p.scale_log2, neg_ref));
             if (need_mask) {
               const int kj = kv0 + c0 + c + e;
               if (!(kj <= q_pos && kj >= first)) pr[e] = 0.f;
             }
           }
           const __nv_bfloat162 b = __floats2bfloat162_rn(pr[0], pr[1]);
-          // the sum uses the rounded values that the MMA will see
-          sum += __bfloat162float(b.x) + __bfloat162float(b.y);
+          s4[c & 2] += pr[0];
+          s4[(c & 2) + 1] += pr[1];
           packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
         }
         const uint32_t addr = p_smem + r * 128 + (((c0 >> 3) ^ (r & 7)) << 4);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[0]), "r"(packed[1]),
                      "r"(packed[2]), "r"(packed[3]) : "memory");
       }
-      l += sum;
+      l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
       // hand P (and the rescaled O) to the tensor core: make this row's shared-memory writes visible to
       // the async proxy, then arrive (the barrier counts all 128 rows; no thread waits on another here)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
