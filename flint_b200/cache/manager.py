@@ -8,6 +8,10 @@ declares fixed-size state gets one slab ``[max_slots, *shape]`` that is zeroed w
 request is admitted; the reference keeps such state outside its paged pool, indexed
 by sequence slot, in the same way (crates/thuban_architectures/src/qwen35/state.rs:5-55).
 Phi-MoE has one group and no state.
+
+The bookkeeping (free lists, tables, which slot is live) is done by the native runtime
+(``csrc/host/runtime.cpp``), which also keeps the host mirror of each block table up to date;
+this file owns the device memory and copies changed table rows to it.
 """
 from __future__ import annotations
 
@@ -15,6 +19,7 @@ from dataclasses import dataclass
 
 import torch
 
+from ..csrc import runtime as rt
 from ..errors import CacheError
 from .pages import NO_PAGE, GroupPages
 
@@ -38,9 +43,16 @@ class StateSpec:
 class GroupCache:
     """Device side of one group: K/V storage for each of its calls and the block table."""
 
-    def __init__(self, spec: KVSpec, calls, pages: GroupPages, dtype, device):
+    def __init__(self, spec: KVSpec, calls, n_pages: int, page_size: int, max_slots: int, max_pages_per_request: int,
+                 dtype, device):
         self.spec = spec
         self.calls = list(calls)
+        # the host mirror of the block table is written by the native bookkeeping
+        self._host_table = torch.full((max_slots, max_pages_per_request), NO_PAGE, dtype=torch.int32)
+        if torch.device(device).type == "cuda":
+            self._host_table = self._host_table.pin_memory()
+        pages = GroupPages(n_pages, page_size, spec.window, max_slots, max_pages_per_request,
+                           host_table_ptr=self._host_table.data_ptr())
         self.pages = pages
         P = pages.page_size
         n = pages.pool.n_pages
@@ -48,26 +60,13 @@ class GroupCache:
         # contiguous P x head_dim tile
         self.storage = torch.zeros((len(self.calls), 2, n, spec.num_kv_heads, P, spec.head_dim),
                                    dtype=dtype, device=device)
-        self.block_table = torch.full((len(pages.tables), pages.max_pages_per_request), NO_PAGE,
-                                      dtype=torch.int32, device=device)
-        self._host_table = torch.full((len(pages.tables), pages.max_pages_per_request), NO_PAGE,
-                                      dtype=torch.int32)
-        if torch.device(device).type == "cuda":
-            self._host_table = self._host_table.pin_memory()
+        self.block_table = torch.full((max_slots, max_pages_per_request), NO_PAGE, dtype=torch.int32, device=device)
 
     def sync_tables(self):
         """Copy the rows of changed block tables to the device."""
-        dirty = self.pages.dirty_slots
-        if not dirty:
-            return
-        for slot in dirty:
-            row = self.pages.tables[slot].pages
-            self._host_table[slot].fill_(NO_PAGE)
-            if row:
-                self._host_table[slot, :len(row)] = torch.tensor(row, dtype=torch.int32)
-        lo, hi = min(dirty), max(dirty) + 1
-        self.block_table[lo:hi].copy_(self._host_table[lo:hi], non_blocking=True)
-        dirty.clear()
+        lo, hi = self.pages.take_dirty()
+        if lo < hi:
+            self.block_table[lo:hi].copy_(self._host_table[lo:hi], non_blocking=True)
 
     def view(self, call_index: int):
         i = self.calls.index(call_index)
@@ -105,72 +104,66 @@ class CacheManager:
         by_spec: dict = {}
         for call, spec in kv_calls.items():
             by_spec.setdefault(spec, []).append(call)
+        self._lib = rt.lib()
+        self._core = self._lib.flint_rt_cache_create(self.page_size, self.max_slots, self.max_context)
         self.groups: list[GroupCache] = []
         self._group_of_call = {}
         for spec, calls in by_spec.items():
-            pages = GroupPages(n_pages, page_size, spec.window, max_slots, max_pages_per_request)
-            g = GroupCache(spec, calls, pages, dtype, device)
+            g = GroupCache(spec, calls, n_pages, page_size, max_slots, max_pages_per_request, dtype, device)
+            self._lib.flint_rt_cache_add_group(self._core, g.pages.handle)
             for c in calls:
                 self._group_of_call[c] = g
             self.groups.append(g)
         self.state = {call: torch.zeros((max_slots, *spec.shape), dtype=spec.dtype, device=device)
                       for call, spec in state_calls.items()}
-        self._free_slots = list(range(max_slots - 1, -1, -1))
-        self._live: set[int] = set()
+
+    def __del__(self):
+        if getattr(self, "_core", None):
+            self._lib.flint_rt_cache_destroy(self._core)
+            self._core = None
+
+    @property
+    def core(self):
+        """Handle of the native bookkeeping (for the native scheduler)."""
+        return self._core
 
     # ------------------------------------------------------------------ slots
     @property
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.flint_rt_cache_free_slots(self._core)
 
     def admit(self) -> int:
         """Take a slot for a new request and zero its state."""
-        if not self._free_slots:
-            raise CacheError("no free request slot")
-        slot = self._free_slots.pop()
-        self._live.add(slot)
+        slot = rt.checked(self._lib.flint_rt_cache_admit(self._core))
+        self.reset_state(slot)
+        return slot
+
+    def reset_state(self, slot: int):
         for s in self.state.values():
             s[slot].zero_()
-        return slot
 
     def release(self, slot: int):
         """Give back the slot and every page it holds."""
-        if slot not in self._live:
-            raise CacheError(f"slot {slot} released twice or never admitted")
-        for g in self.groups:
-            g.pages.release_all(slot)
-        self._live.remove(slot)
-        self._free_slots.append(slot)
+        rt.checked(self._lib.flint_rt_cache_release(self._core, int(slot)))
 
     # ------------------------------------------------------------------ pages
     def pages_needed(self, slot: int, start: int, end: int) -> int:
         """The largest number of new pages any group needs to run positions [start, end)."""
-        return max((g.pages.pages_needed(slot, start, end) for g in self.groups), default=0)
+        return self._lib.flint_rt_cache_pages_needed(self._core, slot, start, end)
 
     def free_pages(self) -> int:
-        return min((g.pages.pool.free_pages for g in self.groups), default=1 << 30)
+        return self._lib.flint_rt_cache_free_pages(self._core)
 
     def can_run(self, slot: int, start: int, end: int) -> bool:
-        if end > self.max_context:
-            return False
-        return all(g.pages.pages_needed(slot, start, end) <= g.pages.pool.free_pages for g in self.groups)
+        return bool(self._lib.flint_rt_cache_can_run(self._core, slot, start, end))
 
     def ensure(self, slot: int, start: int, end: int):
         """Make pages cover what running positions [start, end) reads and writes."""
-        if slot not in self._live:
-            raise CacheError(f"slot {slot} is not admitted")
-        if end > self.max_context:
-            raise CacheError(f"context limit {self.max_context} reached")
-        if not self.can_run(slot, start, end):
-            raise CacheError(f"page pool exhausted: slot {slot} needs {self.pages_needed(slot, start, end)} "
-                             f"pages, {self.free_pages()} free")
-        for g in self.groups:
-            g.pages.ensure(slot, start, end)
+        rt.checked(self._lib.flint_rt_cache_ensure(self._core, int(slot), int(start), int(end)))
 
     def advance(self, slot: int, next_pos: int):
         """After a step: positions below the windows of all later queries are given back."""
-        for g in self.groups:
-            g.pages.release_behind(slot, next_pos)
+        rt.checked(self._lib.flint_rt_cache_advance(self._core, int(slot), int(next_pos)))
 
     def sync(self):
         for g in self.groups:
@@ -184,8 +177,4 @@ class CacheManager:
         return self.state.get(call_index)
 
     def check(self):
-        for g in self.groups:
-            g.pages.check()
-        assert len(set(self._free_slots)) == len(self._free_slots)
-        assert not (set(self._free_slots) & self._live)
-        assert len(self._free_slots) + len(self._live) == self.max_slots
+        rt.checked(self._lib.flint_rt_cache_check(self._core))

@@ -5,83 +5,120 @@ the same structure with 32-token pages, a LIFO free list and one table per seque
 slot (crates/thuban_model/src/pool.rs:11-118); it never returns pages that a sliding
 window has passed.  Here each *group* of layers with the same needs owns a pool, and
 a group with a window gives pages back as soon as no later query can reach them.
-Nothing in this file touches a device.
+
+The bookkeeping itself lives in the native runtime (``csrc/host/runtime.cpp``); the classes
+here are its Python faces.  Nothing in this file touches a device.
 """
 from __future__ import annotations
 
+from ctypes import c_int, byref
+
+from ..csrc import runtime as rt
 from ..errors import CacheError
 
 NO_PAGE = -1
+
+
+class _Native:
+    """Owner of one native group (pool + tables)."""
+
+    def __init__(self, n_pages, page_size, window, max_slots, max_pages_per_request, host_table_ptr=None):
+        self.lib = rt.lib()
+        self.handle = self.lib.flint_rt_group_create(n_pages, page_size, window, max_slots, max_pages_per_request,
+                                                     host_table_ptr)
+        if not self.handle:
+            raise CacheError((self.lib.flint_rt_last_error() or b"cannot create a page pool").decode())
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            self.lib.flint_rt_group_destroy(self.handle)
+            self.handle = None
 
 
 class PagePool:
     """Page numbers 0..n_pages-1 with a LIFO free list (a page just freed is the next
     one handed out, which keeps reuse frequent and easy to test)."""
 
-    def __init__(self, n_pages: int):
+    def __init__(self, n_pages: int, _native: _Native | None = None):
         if n_pages <= 0:
             raise CacheError("a page pool needs at least one page")
         self.n_pages = int(n_pages)
-        self._free = list(range(self.n_pages - 1, -1, -1))
-        self._held = [False] * self.n_pages
-        self.total_allocations = 0
-        self.served = [0] * self.n_pages      # how many times each page was handed out
+        self._n = _native or _Native(self.n_pages, 1, 0, 1, 1)
+        self._lib = self._n.lib
 
     @property
     def free_pages(self) -> int:
-        return len(self._free)
+        return self._lib.flint_rt_group_free_pages(self._n.handle)
 
     @property
     def used_pages(self) -> int:
-        return self.n_pages - len(self._free)
+        return self.n_pages - self.free_pages
+
+    @property
+    def total_allocations(self) -> int:
+        return self._lib.flint_rt_group_total_allocations(self._n.handle)
+
+    @property
+    def served(self) -> list:
+        """How many times each page was handed out."""
+        out = (c_int * self.n_pages)()
+        self._lib.flint_rt_group_served(self._n.handle, out)
+        return list(out)
 
     def take(self) -> int:
-        if not self._free:
-            raise CacheError("page pool exhausted")
-        p = self._free.pop()
-        assert not self._held[p], f"page {p} handed out twice"
-        self._held[p] = True
-        self.total_allocations += 1
-        self.served[p] += 1
-        return p
+        return rt.checked(self._lib.flint_rt_group_take(self._n.handle))
 
     def give_back(self, page: int):
-        if not (0 <= page < self.n_pages) or not self._held[page]:
-            raise CacheError(f"page {page} freed twice or never allocated")
-        self._held[page] = False
-        self._free.append(page)
+        rt.checked(self._lib.flint_rt_group_give_back(self._n.handle, int(page)))
 
     def check(self):
         """Invariant: every page is either free exactly once or held."""
-        assert len(set(self._free)) == len(self._free), "a page is on the free list twice"
-        for p in range(self.n_pages):
-            assert self._held[p] != (p in set(self._free)), f"page {p} both held and free (or neither)"
+        rt.checked(self._lib.flint_rt_group_check(self._n.handle, 0))
 
 
 class PageTable:
-    """Logical page index -> physical page for one request in one group.  Entries
-    before ``first_live`` have been given back (window) and read NO_PAGE."""
+    """Logical page index -> physical page for one request in one group (a read-only view of
+    the native table).  Entries before ``first_live`` have been given back (window) and read
+    NO_PAGE."""
 
-    __slots__ = ("pages", "first_live")
+    __slots__ = ("_n", "_slot", "_cap")
 
-    def __init__(self):
-        self.pages: list[int] = []
-        self.first_live = 0
+    def __init__(self, native: _Native, slot: int, cap: int):
+        self._n, self._slot, self._cap = native, slot, cap
+
+    @property
+    def pages(self) -> list:
+        out = (c_int * self._cap)()
+        n = self._n.lib.flint_rt_group_table(self._n.handle, self._slot, out, self._cap)
+        return list(out[:n])
+
+    @property
+    def first_live(self) -> int:
+        return self._n.lib.flint_rt_group_first_live(self._n.handle, self._slot)
 
     def held(self):
         return [p for p in self.pages if p != NO_PAGE]
 
 
 class GroupPages:
-    """Pages of one layer group: a pool plus one table per request slot."""
+    """Pages of one layer group: a pool plus one table per request slot.  ``host_table_ptr``,
+    if given, is the address of an int32 [max_slots, max_pages_per_request] array that mirrors
+    the tables (the block table that is copied to the device)."""
 
-    def __init__(self, n_pages: int, page_size: int, window: int, max_slots: int, max_pages_per_request: int):
+    def __init__(self, n_pages: int, page_size: int, window: int, max_slots: int, max_pages_per_request: int,
+                 host_table_ptr=None):
         self.page_size = int(page_size)
         self.window = int(window)          # 0 = every key is kept
-        self.pool = PagePool(n_pages)
-        self.tables = [PageTable() for _ in range(max_slots)]
         self.max_pages_per_request = int(max_pages_per_request)
-        self.dirty_slots: set[int] = set()
+        self._n = _Native(int(n_pages), self.page_size, self.window, int(max_slots), self.max_pages_per_request,
+                          host_table_ptr)
+        self._lib = self._n.lib
+        self.pool = PagePool(n_pages, self._n)
+        self.tables = [PageTable(self._n, s, self.max_pages_per_request) for s in range(max_slots)]
+
+    @property
+    def handle(self):
+        return self._n.handle
 
     # the first position a query at ``pos`` can still see
     def first_visible(self, pos: int) -> int:
@@ -89,73 +126,29 @@ class GroupPages:
 
     def pages_needed(self, slot: int, start: int, end: int) -> int:
         """New pages to run positions [start, end) of this request."""
-        t = self.tables[slot]
-        want_hi = -(-end // self.page_size)
-        lo = max(len(t.pages), self.first_visible(start) // self.page_size)
-        return max(0, want_hi - lo)
+        return self._lib.flint_rt_group_pages_needed(self._n.handle, slot, start, end)
 
     def ensure(self, slot: int, start: int, end: int):
         """Make pages exist for positions [first_visible(start), end)."""
-        t = self.tables[slot]
-        want_hi = -(-end // self.page_size)
-        if want_hi > self.max_pages_per_request:
-            raise CacheError(f"context limit {self.max_pages_per_request * self.page_size} reached")
-        need = self.pages_needed(slot, start, end)
-        if need > self.pool.free_pages:
-            raise CacheError(f"page pool exhausted: {need} pages requested, {self.pool.free_pages} free")
-        first = self.first_visible(start) // self.page_size
-        while len(t.pages) < want_hi:
-            i = len(t.pages)
-            if i < first:
-                t.pages.append(NO_PAGE)       # never needed: behind the window from the start
-                t.first_live = max(t.first_live, i + 1)
-            else:
-                t.pages.append(self.pool.take())
-            self.dirty_slots.add(slot)
+        rt.checked(self._lib.flint_rt_group_ensure(self._n.handle, slot, start, end))
 
     def release_behind(self, slot: int, next_pos: int) -> int:
         """Give back pages that no query at ``next_pos`` or later can see."""
-        if not self.window:
-            return 0
-        t = self.tables[slot]
-        dead_hi = min(self.first_visible(next_pos) // self.page_size, len(t.pages))
-        n = 0
-        for i in range(t.first_live, dead_hi):
-            if t.pages[i] != NO_PAGE:
-                self.pool.give_back(t.pages[i])
-                t.pages[i] = NO_PAGE
-                n += 1
-        if dead_hi > t.first_live:
-            t.first_live = dead_hi
-            self.dirty_slots.add(slot)
-        return n
+        return rt.checked(self._lib.flint_rt_group_release_behind(self._n.handle, slot, next_pos))
 
     def release_all(self, slot: int) -> int:
-        t = self.tables[slot]
-        held = t.held()
-        for p in held:
-            self.pool.give_back(p)
-        t.pages = []
-        t.first_live = 0
-        self.dirty_slots.add(slot)
-        return len(held)
+        return rt.checked(self._lib.flint_rt_group_release_all(self._n.handle, slot))
 
     def truncate(self, slot: int, keep_tokens: int):
         """Drop pages above ``keep_tokens`` positions (crates/thuban_model/src/pool.rs:73-79)."""
-        t = self.tables[slot]
-        keep = min(-(-keep_tokens // self.page_size), len(t.pages))
-        for p in t.pages[keep:]:
-            if p != NO_PAGE:
-                self.pool.give_back(p)
-        del t.pages[keep:]
-        t.first_live = min(t.first_live, keep)
-        self.dirty_slots.add(slot)
+        rt.checked(self._lib.flint_rt_group_truncate(self._n.handle, slot, keep_tokens))
+
+    def take_dirty(self):
+        """(lo, hi): the range of slots whose tables changed since the last call; lo >= hi if none."""
+        lo, hi = c_int(), c_int()
+        self._lib.flint_rt_group_take_dirty(self._n.handle, byref(lo), byref(hi))
+        return lo.value, hi.value
 
     def check(self):
-        self.pool.check()
-        seen = set()
-        for t in self.tables:
-            for p in t.held():
-                assert p not in seen, f"page {p} held by two requests"
-                seen.add(p)
-        assert len(seen) == self.pool.used_pages, "a page is lost (held by no request, not free)"
+        """The pool's invariant, and: no page is held by two requests, none is lost."""
+        rt.checked(self._lib.flint_rt_group_check(self._n.handle, 1))

@@ -8,7 +8,10 @@ per-user folder under the system's temporary directory.  Nothing needs the netwo
 a home directory or a pre-built cache.  While a module compiles, a line is printed
 to stderr when it starts, every few seconds, and when it ends.
 
-There is no fallback: if nvcc is missing or a module fails to compile or load, a
+The host runtime (``host/runtime.cpp``: page pools, scheduler, step packing; no device
+code) is built the same way with the host C++ compiler.
+
+There is no fallback: if a compiler is missing or a module fails to compile or load, a
 ``KernelError`` says so.
 """
 from __future__ import annotations
@@ -30,12 +33,15 @@ SRC_DIR = Path(__file__).resolve().parent
 MODULES = ("elementwise", "row_fused", "gemm_simt", "gemm_tc", "attention", "attention_tc", "moe", "sampling", "noalloc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-shared", "-Xcompiler", "-fPIC"]
+HOST_MODULES = ("runtime",)
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC"]
 _LOCK = threading.Lock()
 _LOADED: dict[str, ctypes.CDLL] = {}
 
 
 def available_modules():
-    return [m for m in MODULES if (SRC_DIR / f"{m}.cu").is_file()]
+    return [m for m in MODULES if (SRC_DIR / f"{m}.cu").is_file()] + \
+           [m for m in HOST_MODULES if (SRC_DIR / "host" / f"{m}.cpp").is_file()]
 
 
 def _nvcc() -> str:
@@ -46,12 +52,25 @@ def _nvcc() -> str:
                       "the CUDA kernels cannot be built and there is no fallback")
 
 
+def _host_compiler() -> str:
+    for cand in (os.environ.get("FLINT_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"),
+                 shutil.which("clang++")):
+        if cand and (Path(cand).is_file() or shutil.which(cand)):
+            return cand
+    raise KernelError("no C++ compiler found (looked at $FLINT_CXX, $CXX, g++, c++, clang++); "
+                      "the host runtime cannot be built and there is no fallback")
+
+
 def _source_hash(name: str) -> str:
     h = hashlib.sha256()
-    for f in sorted(SRC_DIR.glob("*.cuh")) + [SRC_DIR / f"{name}.cu"]:
+    if name in HOST_MODULES:
+        files, flags = [SRC_DIR / "host" / f"{name}.cpp"], HOST_FLAGS
+    else:
+        files, flags = sorted(SRC_DIR.glob("*.cuh")) + [SRC_DIR / f"{name}.cu"], NVCC_FLAGS
+    for f in files:
         h.update(f.name.encode())
         h.update(f.read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags).encode())
     return h.hexdigest()[:16]
 
 
@@ -83,9 +102,10 @@ def library_path(name: str) -> Path | None:
 
 
 def compile_module(name: str, verbose: bool = True) -> Path:
-    src = SRC_DIR / f"{name}.cu"
+    host = name in HOST_MODULES
+    src = SRC_DIR / "host" / f"{name}.cpp" if host else SRC_DIR / f"{name}.cu"
     if not src.is_file():
-        raise KernelError(f"no CUDA source {src}")
+        raise KernelError(f"no source {src}")
     found = library_path(name)
     if found is not None:
         return found
@@ -95,9 +115,12 @@ def compile_module(name: str, verbose: bool = True) -> Path:
                           + ", ".join(str(d) for d in _build_dirs()) + ")")
     out = out_dir / f"flint_{name}_{_source_hash(name)}.so"
     tmp = out_dir / f".{out.name}.{os.getpid()}_{threading.get_ident()}.tmp"
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(SRC_DIR), "-o", str(tmp), str(src)]
+    if host:
+        cmd = [_host_compiler(), *HOST_FLAGS, "-o", str(tmp), str(src)]
+    else:
+        cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(SRC_DIR), "-o", str(tmp), str(src)]
     if verbose:
-        print(f"[flint_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+        print(f"[flint_b200] compiling {src.name}" + ("" if host else " for sm_100a") + " ...", file=sys.stderr, flush=True)
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -105,7 +128,7 @@ def compile_module(name: str, verbose: bool = True) -> Path:
     def tick():
         while not done.wait(10.0):
             if verbose:
-                print(f"[flint_b200]   {name}.cu: still compiling ({time.time() - t0:.0f} s)",
+                print(f"[flint_b200]   {src.name}: still compiling ({time.time() - t0:.0f} s)",
                       file=sys.stderr, flush=True)
     th = threading.Thread(target=tick, daemon=True)
     th.start()
@@ -116,10 +139,10 @@ def compile_module(name: str, verbose: bool = True) -> Path:
             tmp.unlink()
         except OSError:
             pass
-        raise KernelError(f"nvcc failed on {name}.cu:\n{log}")
+        raise KernelError(f"the compiler failed on {src.name}:\n{log}")
     os.replace(tmp, out)
     if verbose:
-        print(f"[flint_b200] compiled {name}.cu in {time.time() - t0:.1f} s -> {out}", file=sys.stderr, flush=True)
+        print(f"[flint_b200] compiled {src.name} in {time.time() - t0:.1f} s -> {out}", file=sys.stderr, flush=True)
     return out
 
 

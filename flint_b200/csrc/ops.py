@@ -118,7 +118,8 @@ class CudaOps:
         mods = list(modules or build.available_modules())
         build.compile_all(mods)
         for m in mods:
-            self._fn(m, f"flint_{m}_last_error")
+            if m in build.MODULES:              # the host runtime is loaded by its own face
+                self._fn(m, f"flint_{m}_last_error")
 
     # ------------------------------------------------------------------ row-wise
     def embed(self, ids, table, out, scale=1.0):

@@ -15,16 +15,18 @@ limit, or needing more pages than the pool has) fails alone, with an error.
 The reference fills a step of at most 128 tokens by walking its sessions, gives a
 prefilling session what is left of the budget, reserves all pages of a prompt at
 creation, has no waiting queue and no preemption: a failed page allocation aborts the
-step for everyone (crates/thuban_generate/src/engine.rs:103-300).  This file needs no
-device: it sees the cache manager only through ``can_run / ensure / advance / admit /
-release / free_slots``.
+step for everyone (crates/thuban_generate/src/engine.rs:103-300).
+
+The decisions are taken by the native runtime (``csrc/host/runtime.cpp``), on the cache
+manager's native bookkeeping; ``Scheduler`` here is its Python face and keeps the
+``Request`` objects that callers hold in step with it.  Nothing here needs a device.
 """
 from __future__ import annotations
 
-from collections import deque
+from ctypes import c_int, byref
 from dataclasses import dataclass, field
 
-from ..errors import CacheError
+from ..csrc import runtime as rt
 from ..sampling.params import SamplingParams, SplitMix64
 
 WAITING, RUNNING, FINISHED, FAILED = "waiting", "running", "finished", "failed"
@@ -80,6 +82,9 @@ class Portion:
 
 
 class Scheduler:
+    _STATES = (WAITING, RUNNING, FINISHED, FAILED)
+    _REASONS = (None, "stop", "length", "context", "abort", "error")
+
     def __init__(self, cache, *, max_step_tokens=8192, prefill_chunk=2048, max_context=None, total_pages=None,
                  page_size=None):
         self.cache = cache
@@ -89,160 +94,119 @@ class Scheduler:
         self.page_size = int(page_size if page_size is not None else cache.page_size)
         self.total_pages = int(total_pages if total_pages is not None else
                                min(g.pages.pool.n_pages for g in cache.groups) if cache.groups else 1 << 30)
-        self.waiting: deque = deque()
-        self.running: list = []
-        self.preemptions = 0
-        self.steps = 0
+        self._lib = rt.lib()
+        self._h = self._lib.flint_rt_sched_create(cache.core, self.max_step_tokens, self.prefill_chunk, self.max_context,
+                                                  self.page_size, self.total_pages)
+        self._reqs: dict = {}                       # native handle -> Request
+        self._out = (c_int * (4 * (self.max_step_tokens + 1)))()
+        self._fields = (c_int * 8)()
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.flint_rt_sched_destroy(self._h)
+            self._h = None
+
+    # ------------------------------------------------------------------ the requests' mirrors
+    def _pull(self, req: Request):
+        """Bring a Request in step with its native record."""
+        f = self._fields
+        self._lib.flint_rt_sched_request(self._h, req._handle, f)
+        slot_before = req.slot
+        _, req.n_cached, req.slot, state, reason, req.preemptions, req.prefill_tokens, req.decode_tokens = f
+        req.state = self._STATES[state]
+        req.finish_reason = self._REASONS[reason]
+        if req.state == FAILED and req.error is None:
+            req.error = (self._lib.flint_rt_sched_request_error(self._h, req._handle) or b"").decode()
+        if req.slot >= 0 and req.slot != slot_before and self.cache.state:
+            self.cache.reset_state(req.slot)        # a newly admitted request starts from zeroed state
+
+    def _push_stop(self, req: Request):
+        stop = tuple(int(t) for t in req.stop)
+        if stop != req._stop_pushed:
+            self._lib.flint_rt_sched_set_stop(self._h, req._handle, rt.ints(stop), len(stop))
+            req._stop_pushed = stop
+
+    def _list(self, which):
+        n = self._lib.flint_rt_sched_list(self._h, which, self._out, len(self._out))
+        return [self._reqs[h] for h in self._out[:n]]
+
+    @property
+    def waiting(self) -> list:
+        """The waiting requests in queue order."""
+        return self._list(0)
+
+    @property
+    def running(self) -> list:
+        return self._list(1)
+
+    @property
+    def preemptions(self) -> int:
+        a, b = c_int(), c_int()
+        self._lib.flint_rt_sched_counters(self._h, byref(a), byref(b))
+        return a.value
+
+    @property
+    def steps(self) -> int:
+        a, b = c_int(), c_int()
+        self._lib.flint_rt_sched_counters(self._h, byref(a), byref(b))
+        return b.value
 
     # ------------------------------------------------------------------ admission
     def add(self, req: Request):
-        if not req.prompt:
-            self._fail(req, "empty prompt")
-            return
-        if len(req.prompt) + 1 > self.max_context:
-            self._fail(req, f"prompt of {len(req.prompt)} tokens does not fit the context limit {self.max_context}")
-            return
-        req.state = WAITING
-        self.waiting.append(req)
-
-    def _fail(self, req, msg):
-        req.state, req.error, req.finish_reason = FAILED, msg, "error"
+        stop = tuple(int(t) for t in req.stop)
+        req._handle = self._lib.flint_rt_sched_add(self._h, len(req.prompt), int(req.max_tokens), int(req.arrival),
+                                                   rt.ints(stop), len(stop))
+        req._stop_pushed = stop
+        self._reqs[req._handle] = req
+        self._pull(req)
 
     def has_work(self):
-        return bool(self.waiting or self.running)
+        return bool(self._lib.flint_rt_sched_has_work(self._h))
 
     # ------------------------------------------------------------------ planning
-    def _preempt(self, victim):
-        """Give back the pages and the slot of a running request; it will be recomputed."""
-        self.running.remove(victim)
-        self.cache.release(victim.slot)
-        victim.slot, victim.n_cached, victim.state = -1, 0, WAITING
-        victim.preemptions += 1
-        self.preemptions += 1
-        self.waiting.appendleft(victim)
-
-    def _fits_portion(self, req, n):
-        """Largest m <= n such that pages exist for positions [n_cached, n_cached + m)."""
-        while n > 0 and not self.cache.can_run(req.slot, req.n_cached, req.n_cached + n):
-            n = (n - 1) // self.page_size * self.page_size if n > self.page_size else n - 1
-        return n
-
-    def _make_room(self, req, portions, planned):
-        """Pages ran out for ``req``: preempt running requests that arrived after it, the
-        last one first, until at least one token of ``req`` fits.  Returns the budget
-        given back by voided portions.  If nobody younger is left, ``req`` itself is
-        preempted (others are older and go first), or fails if it is alone."""
-        refund = 0
-        while req in self.running and not self.cache.can_run(req.slot, req.n_cached, req.n_cached + 1):
-            younger = [r for r in self.running if r.arrival > req.arrival]
-            if younger:
-                victim = max(younger, key=lambda r: r.arrival)
-            elif len(self.running) == 1:
-                self.running.remove(req)
-                self.cache.release(req.slot)
-                req.slot = -1
-                self._fail(req, f"request of {req.n_tokens} tokens needs more pages than the pool has")
-                break
-            else:
-                victim = req
-            if victim in planned:
-                for p in [p for p in portions if p.request is victim]:
-                    refund += p.n_tokens
-                    portions.remove(p)
-                planned.discard(victim)
-            self._preempt(victim)
-        return refund
-
     def plan(self):
         """Returns the list of Portions of the next step (their pages are made)."""
-        budget = self.max_step_tokens
-        portions, planned = [], set()
-        # 1. decoding requests, then 2. running requests with prompt (or recomputation) left;
-        #    each oldest first
-        for decoding in (True, False):
-            for req in sorted(self.running, key=lambda r: r.arrival):
-                if req not in self.running or req in planned or budget <= 0 or req.remaining < 1:
-                    continue
-                if decoding != (req.remaining == 1):
-                    continue
-                n = self._fits_portion(req, min(req.remaining, self.prefill_chunk, budget))
-                if n == 0:
-                    budget += self._make_room(req, portions, planned)
-                    if req not in self.running:
-                        continue
-                    n = self._fits_portion(req, min(req.remaining, self.prefill_chunk, budget))
-                    if n == 0:
-                        continue
-                self.cache.ensure(req.slot, req.n_cached, req.n_cached + n)
-                portions.append(Portion(req, req.n_cached, n, n == req.remaining))
-                planned.add(req)
-                budget -= n
-        # 3. admit waiting requests, first come first served; never preempts
-        while self.waiting and budget > 0 and self.cache.free_slots > 0:
-            req = self.waiting[0]
-            need_pages = -(-req.n_tokens // self.page_size)
-            if req.n_tokens + 1 > self.max_context or (need_pages > self.total_pages and not self._windowed()):
-                self.waiting.popleft()
-                self._fail(req, f"request of {req.n_tokens} tokens can never fit "
-                                f"({self.total_pages} pages of {self.page_size}, context limit {self.max_context})")
-                continue
-            slot = self.cache.admit()
-            req.slot = slot
-            n = self._fits_portion(req, min(req.remaining, self.prefill_chunk, budget))
-            if n == 0:
-                self.cache.release(slot)
-                req.slot = -1
-                break                            # no pages now; it keeps its place at the head
-            self.waiting.popleft()
-            req.state = RUNNING
-            self.running.append(req)
-            self.cache.ensure(slot, req.n_cached, req.n_cached + n)
-            portions.append(Portion(req, req.n_cached, n, n == req.remaining))
-            planned.add(req)
-            budget -= n
-        self.steps += 1
+        n = rt.checked(self._lib.flint_rt_sched_plan(self._h, self._out, len(self._out) // 4))
+        out = self._out
+        portions = [Portion(self._reqs[out[4 * i]], out[4 * i + 1], out[4 * i + 2], bool(out[4 * i + 3])) for i in range(n)]
+        self._pull_touched()                        # preempted or failed
+        for p in portions:                          # admitted or just planned
+            self._pull(p.request)
         return portions
 
-    def _windowed(self):
-        return any(g.pages.window for g in self.cache.groups) if getattr(self.cache, "groups", None) else False
+    def _pull_touched(self):
+        n = self._lib.flint_rt_sched_take_touched(self._h, self._out, len(self._out))
+        for h in set(self._out[:n]):
+            self._pull(self._reqs[h])
 
     # ------------------------------------------------------------------ after the step
     def commit(self, portions, sampled):
         """``sampled``: one token per portion that wanted logits, in order.  Returns the
         list of (request, token) emitted in this step."""
-        emitted = []
-        it = iter(sampled)
+        flat = []
         for p in portions:
-            req = p.request
-            if p.n_tokens == 1 and p.start >= len(req.prompt):
-                req.decode_tokens += 1
-            else:
-                req.prefill_tokens += p.n_tokens
-            req.n_cached = p.start + p.n_tokens
-            self.cache.advance(req.slot, req.n_cached)
-            if not p.wants_logits:
-                continue
-            token = int(next(it))
-            if token in req.stop:
-                self._finish(req, "stop")
-                continue
+            self._push_stop(p.request)
+            flat += (p.request._handle, p.start, p.n_tokens, 1 if p.wants_logits else 0)
+        tokens = [int(t) for t in sampled]
+        emitted = (c_int * (2 * max(len(portions), 1)))()
+        n = rt.checked(self._lib.flint_rt_sched_commit(self._h, rt.ints(flat), len(portions), rt.ints(tokens), len(tokens),
+                                                       emitted, len(portions)))
+        out = []
+        for i in range(n):
+            req, token = self._reqs[emitted[2 * i]], emitted[2 * i + 1]
             req.generated.append(token)
-            emitted.append((req, token))
-            if len(req.generated) >= req.max_tokens:
-                self._finish(req, "length")
-            elif req.n_tokens + 1 > self.max_context:
-                self._finish(req, "context")
-        return emitted
+            out.append((req, token))
+        self._pull_touched()
+        for p in portions:
+            self._pull(p.request)
+        self._forget_finished()
+        return out
 
-    def _finish(self, req, reason):
-        req.state, req.finish_reason = FINISHED, reason
-        if req in self.running:
-            self.running.remove(req)
-        if req.slot >= 0:
-            self.cache.release(req.slot)
-            req.slot = -1
+    def _forget_finished(self):
+        if len(self._reqs) > 4096:
+            self._reqs = {h: r for h, r in self._reqs.items() if r.state in (WAITING, RUNNING)}
 
     def abort(self, req):
-        if req in self.waiting:
-            self.waiting.remove(req)
-        self._finish(req, "abort")
+        rt.checked(self._lib.flint_rt_sched_abort(self._h, req._handle))
+        self._pull_touched()
+        self._pull(req)

@@ -8,16 +8,19 @@ cut anywhere.  The reference's batch is the same thing
 position kept inside the model; here the caller passes it, so that the step function
 holds no per-request state and the replay tool can drive it directly.
 
-The flattened metadata is packed into one int32 buffer and copied to the device with
-a single copy: token ids, positions, slots, and the rows whose logits are wanted (the
-reference uploads 8 words per row: crates/thuban_model/src/rows.rs:7-30).
+The flattened metadata is packed (by the native runtime, ``csrc/host/runtime.cpp``) into
+one pinned int32 buffer and copied to the device with a single copy: token ids, positions,
+slots, and the rows whose logits are wanted (the reference uploads 8 words per row:
+crates/thuban_model/src/rows.rs:7-30).
 """
 from __future__ import annotations
 
+from ctypes import c_int
 from dataclasses import dataclass, field
 
 import torch
 
+from ..csrc import runtime as rt
 from ..errors import ModelError
 
 
@@ -72,61 +75,37 @@ class StepStaging:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._in_flight = False
+        self._lib = rt.lib()
 
     def pack(self, entries, vocab_size: int, max_positions: int, padded_tokens: int | None = None) -> StepContext:
         """Flatten, validate and upload.  ``padded_tokens`` fixes the device-side row
         count (for a captured graph of a given size)."""
-        T = sum(len(e.tokens) for e in entries)
-        if T == 0:
+        n_entries = len(entries)
+        if n_entries == 0:
             raise ModelError("a step needs at least one token")
-        if T > self.max_tokens:
-            raise ModelError(f"step of {T} tokens exceeds the limit of {self.max_tokens}")
-        ids, pos, slot, want, starts, tiles, others = [], [], [], [], [], [], []
-        seen = set()
-        max_kv = 0
+        tokens, want = [], []
         for e in entries:
-            if e.slot in seen:
-                raise ModelError(f"request slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            n = len(e.tokens)
-            if n == 0:
-                raise ModelError("an entry needs at least one token")
-            if e.start_pos < 0 or e.start_pos + n > max_positions:
-                raise ModelError(f"positions {e.start_pos}..{e.start_pos + n - 1} exceed the model's "
-                                 f"{max_positions} positions")
-            base = len(ids)
-            starts.append(base)
-            for t in e.tokens:
-                if not 0 <= int(t) < vocab_size:
-                    raise ModelError(f"token id {t} is outside the vocabulary of {vocab_size}")
-            ids.extend(int(t) for t in e.tokens)
-            pos.extend(range(e.start_pos, e.start_pos + n))
-            slot.extend([e.slot] * n)
-            for w in e.want:
-                if not 0 <= w < n:
-                    raise ModelError(f"wanted place {w} is outside the entry's {n} tokens")
-                want.append(base + w)
-            if n >= TILE_MIN_ROWS:
-                for r in range(0, n, TILE_ROWS):
-                    tiles += [base + r, min(TILE_ROWS, n - r), e.slot, e.start_pos + r]
-            else:
-                others.extend(range(base, base + n))
-            max_kv = max(max_kv, e.start_pos + n)
-        R = len(want)
+            tokens.extend(e.tokens)
+            want.extend(e.want)
+        try:
+            tok_arr, want_arr = rt.ints([int(t) for t in tokens]), rt.ints([int(w) for w in want])
+        except (TypeError, ValueError, OverflowError) as err:
+            raise ModelError(f"token ids and wanted places must be integers: {err}") from None
+        starts = (c_int * n_entries)()
+        meta = (c_int * 5)()
         M = self.max_tokens
-        h = self.host
         if self._in_flight:          # the last upload must have left the pinned buffer
             self._copied.synchronize()
-        h[0:T] = torch.tensor(ids, dtype=torch.int32)
-        h[M:M + T] = torch.tensor(pos, dtype=torch.int32)
-        h[2 * M:2 * M + T] = torch.tensor(slot, dtype=torch.int32)
-        if R:
-            h[3 * M:3 * M + R] = torch.tensor(want, dtype=torch.int32)
-        if others:
-            h[4 * M:4 * M + len(others)] = torch.tensor(others, dtype=torch.int32)
-        if tiles:
-            h[5 * M:5 * M + len(tiles)] = torch.tensor(tiles, dtype=torch.int32)
-        self.dev.copy_(h, non_blocking=True)
+        # flattening, validation and the tiles of long portions are done by the native runtime,
+        # straight into the pinned buffer
+        rt.checked(self._lib.flint_rt_pack_step(
+            n_entries, rt.ints([e.slot for e in entries]), rt.ints([e.start_pos for e in entries]),
+            rt.ints([len(e.tokens) for e in entries]), rt.ints([len(e.want) for e in entries]), tok_arr, want_arr,
+            int(vocab_size), int(max_positions), M, self.max_tiles, TILE_ROWS, TILE_MIN_ROWS, 4096,
+            self.host.data_ptr(), starts, meta))
+        T, R, n_tiles, n_others, max_kv = meta
+        starts = list(starts)
+        self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
             self._copied.record()
             self._in_flight = True
@@ -134,5 +113,5 @@ class StepStaging:
         return StepContext(n_tokens=T, ids=d[0:T], pos=d[M:M + T], slot=d[2 * M:2 * M + T],
                            want_rows=d[3 * M:3 * M + R], n_want=R, max_kv_len=max_kv, status=self.status,
                            entries=list(entries), entry_start=starts,
-                           tiles=d[5 * M:5 * M + len(tiles)].view(-1, 4), n_tiles=len(tiles) // 4,
-                           other_rows=d[4 * M:4 * M + len(others)], n_other_rows=len(others))
+                           tiles=d[5 * M:5 * M + 4 * n_tiles].view(-1, 4), n_tiles=n_tiles,
+                           other_rows=d[4 * M:4 * M + n_others], n_other_rows=n_others)
