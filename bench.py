@@ -47,8 +47,10 @@ def peaks():
     return dict(FALLBACK_PEAKS)
 
 
-def mini_config(layers=None):
+def mini_config(layers=None, expert_intermediate=None):
     cfg = dict(MINI)
+    if expert_intermediate:
+        cfg["intermediate_size"] = int(expert_intermediate)
     r = random.Random(7)
     cfg["rope_scaling"] = {"type": "longrope",
                            "short_factor": [round(r.uniform(1, 4), 4) for _ in range(64)],
@@ -286,6 +288,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-tokens", type=int, default=2048)
     ap.add_argument("--ctx-size", type=int, default=4096)
+    ap.add_argument("--expert-intermediate", type=int, default=None,
+                    help="expert width (default 960, the Phi-mini-MoE sizes; 6400 gives the Phi-3.5-MoE sizes)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are named)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--one-step", choices=["decode", "prefill"], default=None,
@@ -307,7 +311,7 @@ def main():
 
     import torch
     pk = peaks()
-    cfg = mini_config(args.layers)
+    cfg = mini_config(args.layers, args.expert_intermediate)
     rng = random.Random(0)
     max_batch = max(args.batch, 1 if args.no_points else 64)
     model = build_model(cfg, max_batch, args.ctx_size)
@@ -337,9 +341,10 @@ def main():
         "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
-        "config": {"model": "Phi-mini-MoE sizes", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
+        "config": {"model": "Phi-mini-MoE sizes" if cfg["intermediate_size"] == 960 else
+                            f"Phi-MoE sizes with experts of {cfg['intermediate_size']}", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
                    "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "experts": 16, "top_k": 2,
-                   "expert_intermediate": 960, "vocab": 32064, "global_batch": args.batch,
+                   "expert_intermediate": cfg["intermediate_size"], "vocab": 32064, "global_batch": args.batch,
                    "prompt_tokens": args.prompt_tokens, "seq_len": args.ctx_size, "page_size": 64,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed every step)",
                    "peaks": pk["source"]},
