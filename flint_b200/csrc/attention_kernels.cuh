@@ -198,8 +198,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ scratch, TO* 
 #pragma unroll
         for (int u = 0; u < 8; ++u) t[u] = s0 + u < n_splits ? base[(size_t)(s0 + u) * (hd + 2) + d] : 0.f;
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (s0 + u < n_splits) o += w_s[s0 + u] * t[u];
+        for (int u = 0; u < 8; ++u)      // an empty slot (weight 0) may hold anything, even NaN: it is left out
+          if (s0 + u < n_splits && w_s[s0 + u] != 0.f) o += w_s[s0 + u] * t[u];
       }
       out[out_rh * hd + d] = from_f32<TO>(o * inv);
     }

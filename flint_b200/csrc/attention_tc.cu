@@ -564,6 +564,235 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   }
 }
 
+// The same kernel with the work cut stream fashion: the 16-key steps of all (row, kv head, chunk of query
+// heads) items, laid end to end, are divided into equal runs, one per warp of the grid, so that every warp
+// reads the same number of keys whatever the rows' lengths are (a batch of requests of different lengths, a
+// context shorter than the launch was sized for).  A warp's run may end one item and begin the next; each
+// piece of an item goes to its own slot of the scratch records, in order, and the first piece marks the
+// slots that the item does not use as empty (m = -inf, l = 0), so the merge needs no counts.
+constexpr int MAX_STREAM_ROWS = 256;
+constexpr int MIN_STREAM_STEPS = 3;      // a warp takes at least 48 keys
+
+template <int HD>
+__global__ void __launch_bounds__(128)
+attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                           const DecodeParams p) {
+  using flint_attn::ldsm4;
+  using flint_attn::ldsm4t;
+  using flint_attn::mma16816;
+  constexpr int MG = 8;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
+  // units (steps of 16 keys x items of a row) before each row, and each row's steps: every warp works them
+  // out for itself (a scan by shuffles), so that no warp waits for another before its first copy
+  __shared__ int prefix_all[4][MAX_STREAM_ROWS + 1];
+  __shared__ int steps_all[4][MAX_STREAM_ROWS];
+  pdl_launch();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int* prefix = prefix_all[warp];
+  int* steps_of = steps_all[warp];
+  const int hd = p.hd, nq = p.nq;
+  const int G = nq / p.nkv;
+  const int ipr = p.nkv * p.g_chunks;               // items (kv head x chunk of query heads) per row
+  int max_steps = 1, carried = 0;
+  for (int base = 0; base < p.n_rows; base += 32) {
+    const int ti = base + lane;
+    int st = 0;
+    if (ti < p.n_rows) {
+      // steps of the row: its visible keys, from the 16-key boundary at or below the first one
+      const int t = p.row_list ? p.row_list[ti] : ti;
+      const int pq = p.pos[t];
+      const int lo_row = p.window > 0 ? max(0, pq + 1 - p.window) : 0;
+      st = (pq + 1 - (lo_row & ~(DK - 1)) + DK - 1) / DK;
+      steps_of[ti] = st;
+    }
+    max_steps = max(max_steps, st);
+    int incl = st * ipr;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (ti < p.n_rows) prefix[ti] = carried + incl - st * ipr;
+    carried += __shfl_sync(0xffffffffu, incl, 31);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) max_steps = max(max_steps, __shfl_xor_sync(0xffffffffu, max_steps, o));
+  if (lane == 0) prefix[p.n_rows] = carried;
+  __syncwarp();
+  const int total_units = carried;
+  // equal runs of units, one per warp of the grid; long enough that an item has at most n_splits pieces
+  const int n_warps = gridDim.x * 4;
+  const int run_min = p.n_splits > 1 ? (max_steps - 1 + p.n_splits - 2) / (p.n_splits - 1) : max_steps;
+  int run = max(max((total_units + n_warps - 1) / n_warps, run_min), MIN_STREAM_STEPS);
+  if (p.n_splits == 1) run = ((run + max_steps - 1) / max_steps) * max_steps;
+  const int w = blockIdx.x * 4 + warp;
+  const long long u_begin = (long long)w * run;
+  if (u_begin >= total_units) return;
+  const int u_end = (int)min((long long)total_units, u_begin + run);
+  const int gid = lane >> 2, tid4 = lane & 3;
+  constexpr int KB = HD / 16, DB = HD / 8;
+  const int kb_n = hd / 16, db_n = hd / 8, chunks = (hd + 63) / 64;
+
+  const uint32_t ring = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * (DSTAGES * DSTAGE_BYTES);
+  const uint32_t bar0 = smem_u32(&bars[warp * DSTAGES]);
+  if (lane == 0) {
+    for (int s = 0; s < DSTAGES; ++s) mbar_init(bar0 + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  int kc = 0;                       // stages issued so far by this warp: the rings run on across segments
+  int failed = 0;
+  int ti = 0;
+  for (int u = (int)u_begin; u < u_end && !failed;) {
+    // the segment that starts at unit u: row, item of the row, first step
+    while (prefix[ti + 1] <= u) ++ti;
+    const int steps_row = steps_of[ti];
+    const int rem = u - prefix[ti];
+    const int j = rem / steps_row, s_begin = rem % steps_row;
+    const int s_end = min(steps_row, s_begin + (u_end - u));
+    const int kvh = j % p.nkv, gchunk = j / p.nkv;
+    const int t = p.row_list ? p.row_list[ti] : ti;
+    const int g0 = gchunk * MG;
+    const int ng = min(MG, G - g0);
+    const int h0 = kvh * G + g0;
+    const int pq = p.pos[t];
+    const int lo_row = p.window > 0 ? max(0, pq + 1 - p.window) : 0;
+    const int first = lo_row & ~(DK - 1);
+    const int lo = max(lo_row, first + s_begin * DK);
+    const int hi = min(pq + 1, first + s_end * DK);
+    const int* bt = p.block_table + (size_t)p.slot[t] * p.max_pages;
+    // which piece of its item this segment is, and how many pieces the item has
+    const int item_u0 = prefix[ti] + j * steps_row;
+    const int first_w = item_u0 / run;
+    const int piece = w - first_w;
+    const int pieces = (item_u0 + steps_row - 1) / run - first_w + 1;
+    uint32_t qa[KB][2];
+  #pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+      qa[kb][0] = qa[kb][1] = 0u;
+      if (gid < ng && kb < kb_n) {
+        const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
+        qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
+        qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+    }
+    float o[DB][4];
+  #pragma unroll
+    for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    // stages cover absolute key positions [first + step*16, +16): tiles never straddle a page
+    const int n_steps = s_end - s_begin;
+    auto issue = [&](int step, int stage) {      // lane 0 only
+      const int j0 = first + (s_begin + step) * DK;
+      const int lp = j0 / p.page_size;
+      int page = lp < p.max_pages ? bt[lp] : -1;
+      if (page < 0) page = 0;                    // never visible (masked): any finite page will do
+      const int row = (page * p.nkv + kvh) * p.page_size + j0 % p.page_size;
+      const uint32_t dst = ring + stage * DSTAGE_BYTES, bar = bar0 + 8 * stage;
+      mbar_expect_tx(bar, 2 * chunks * DK * 128);
+      for (int c = 0; c < chunks; ++c) {
+        tma_load_2d(dst + c * DK * 128, &map_k, c * 64, row, bar);
+        tma_load_2d(dst + 2 * DK * 128 + c * DK * 128, &map_v, c * 64, row, bar);
+      }
+    };
+    __syncwarp();          // the previous segment's last reads of the ring are done
+    if (lane == 0)
+      for (int s0 = 0; s0 < DSTAGES - 1 && s0 < n_steps; ++s0) issue(s0, (kc + s0) % DSTAGES);
+
+  #pragma unroll 1
+    for (int step = 0; step < n_steps; ++step) {
+      const int stage = (kc + step) % DSTAGES;
+      __syncwarp();        // every lane is done reading the stage that is refilled next
+      if (lane == 0 && step + DSTAGES - 1 < n_steps) issue(step + DSTAGES - 1, (kc + step + DSTAGES - 1) % DSTAGES);
+      {   // bounded wait for this stage's tile
+        const uint32_t bar = bar0 + 8 * stage, parity = ((kc + step) / DSTAGES) & 1;
+        if (!mbar_try_wait(bar, parity)) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(bar, parity))
+            if (clock64() - t0 > WAIT_CYCLES) { failed = 1; break; }
+        }
+      }
+      failed = __any_sync(0xffffffffu, failed) ? 1 : 0;
+      if (failed) break;
+      const uint32_t ks = ring + stage * DSTAGE_BYTES, vs = ks + 2 * DK * 128;
+      const int j0 = first + (s_begin + step) * DK;
+      float sacc[2][4];
+  #pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+        sacc[nb][0] = sacc[nb][1] = sacc[nb][2] = sacc[nb][3] = 0.f;
+  #pragma unroll
+        for (int kb = 0; kb < KB; kb += 2) {
+          if (kb < kb_n) {
+            // matrices: this block's 8 keys x dims [kb*16, +8), [+8, +16), [(kb+1)*16, +8), [+8, +16)
+            const int r = nb * 8 + (lane & 7);
+            const int unit = kb * 2 + (lane >> 3);              // 16-byte unit along the head dimension
+            uint32_t b0, b1, b2, b3;
+            ldsm4(ks + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+            mma16816(sacc[nb], qa[kb][0], 0u, qa[kb][1], 0u, b0, b1);
+            if (kb + 1 < kb_n) mma16816(sacc[nb], qa[kb + 1][0], 0u, qa[kb + 1][1], 0u, b2, b3);
+          }
+        }
+      }
+      float sv[4];
+      float mx = m;
+  #pragma unroll
+      for (int nb = 0; nb < 2; ++nb)
+  #pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = j0 + nb * 8 + tid4 * 2 + e;
+          sv[nb * 2 + e] = (j >= lo && j < hi) ? sacc[nb][e] * p.scale : -INFINITY;
+          mx = fmaxf(mx, sv[nb * 2 + e]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float alpha = mx > -INFINITY ? expf(m - mx) : 1.f;
+      m = mx;
+      float pv[4];
+  #pragma unroll
+      for (int i = 0; i < 4; ++i) pv[i] = sv[i] > -INFINITY ? expf(sv[i] - mx) : 0.f;
+      const __nv_bfloat162 p01 = __floats2bfloat162_rn(pv[0], pv[1]), p23 = __floats2bfloat162_rn(pv[2], pv[3]);
+      l = l * alpha + ((__bfloat162float(p01.x) + __bfloat162float(p01.y)) + (__bfloat162float(p23.x) + __bfloat162float(p23.y)));
+      const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p01), pa2 = *reinterpret_cast<const uint32_t*>(&p23);
+  #pragma unroll
+      for (int db = 0; db < DB; db += 2) {
+        if (db < db_n) {
+          o[db][0] *= alpha; o[db][1] *= alpha; o[db + 1][0] *= alpha; o[db + 1][1] *= alpha;
+          const int r = (lane & 7) + ((lane >> 3) & 1) * 8;      // key row
+          const int unit = db + (lane >> 4);                      // 16-byte unit = 8 dims
+          uint32_t b0, b1, b2, b3;
+          ldsm4t(vs + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+          mma16816(o[db], pa0, 0u, pa2, 0u, b0, b1);
+          mma16816(o[db + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+      }
+    }
+    if (failed) break;
+    kc += n_steps;
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (gid < ng) {
+      float* dst = p.scratch + (((size_t)ti * nq + h0 + gid) * p.n_splits + piece) * (hd + 2);
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+        if (db < db_n) { dst[db * 8 + tid4 * 2] = o[db][0]; dst[db * 8 + tid4 * 2 + 1] = o[db][1]; }
+      if (tid4 == 0) { dst[hd] = m; dst[hd + 1] = l; }
+      // the first piece marks the slots that the item has no piece for as empty
+      if (piece == 0 && tid4 == 0)
+        for (int z = pieces; z < p.n_splits; ++z) {
+          float* e = p.scratch + (((size_t)ti * nq + h0 + gid) * p.n_splits + z) * (hd + 2);
+          e[hd] = -INFINITY;
+          e[hd + 1] = 0.f;
+        }
+    }
+    u += n_steps;
+  }
+  if (failed && lane == 0) atomicExch(p.error_flag, 1);
+}
+
 }  // namespace
 
 // q, out [T, nq*hd] bf16; k_cache, v_cache pages [n_pages, nkv, page_size, hd] bf16;
@@ -647,6 +876,58 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   if (rc || n_splits == 1) return rc;
   launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
              dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
+  return check_launch("attention_combine");
+}
+
+// The same contract with the work cut into equal runs of keys on the device (see the stream kernel): any mix of
+// row lengths keeps every warp equally busy, and nothing about the launch depends on the lengths, so one
+// captured launch serves every context length.  n_slices (2..64): the most pieces an item may be cut into;
+// scratch: T * nq * n_slices * (hd + 2) floats.  Up to 256 rows.
+extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache, const void* v_cache, int n_pages,
+                                             const int* block_table, int max_pages, int page_size, const int* pos,
+                                             const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
+                                             float scale, int n_slices, float* scratch, const int* row_list,
+                                             int* error_flag, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (T > MAX_STREAM_ROWS) return fail("attention_decode_stream: %d rows (up to %d)", T, MAX_STREAM_ROWS);
+  if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_stream: head size %d (multiples of 16 up to 128)", hd);
+  if (nkv <= 0 || nq % nkv) return fail("attention_decode_stream: %d query heads do not divide into %d kv heads", nq, nkv);
+  if (page_size <= 0 || page_size % DK) return fail("attention_decode_stream: page size %d must be a multiple of %d", page_size, DK);
+  if (n_slices < 2 || n_slices > 64) return fail("attention_decode_stream: %d slices (2..64)", n_slices);
+  if (!scratch || !error_flag) return fail("attention_decode_stream: needs scratch memory and an error flag");
+  CUtensorMap mk, mv;
+  const long long kv_rows = (long long)n_pages * nkv * page_size;
+  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, DK);
+  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, DK);
+  if (rc) return fail("attention_decode_stream: cuTensorMapEncodeTiled failed (%d)", rc);
+  DecodeParams p;
+  p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot; p.row_list = row_list;
+  p.out = (__nv_bfloat16*)out; p.scratch = scratch; p.error_flag = error_flag;
+  p.n_rows = T; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd;
+  p.window = window; p.split_keys = 0; p.n_splits = n_slices;
+  p.g_chunks = (nq / nkv + 7) / 8;
+  p.scale = scale;
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const size_t smem = 4 * DSTAGES * DSTAGE_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attention_decode_stream_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(attention_decode_stream_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    configured = true;
+  }
+  const unsigned blocks = 2u * (unsigned)sm_count;           // two blocks of four warps stay resident per SM
+  if (hd <= 64) launch_pdl(attention_decode_stream_kernel<64>, dim3(blocks), dim3(128), smem, stream, mk, mv, p);
+  else launch_pdl(attention_decode_stream_kernel<128>, dim3(blocks), dim3(128), smem, stream, mk, mv, p);
+  rc = check_launch("attention_decode_stream");
+  if (rc) return rc;
+  launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
+             dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_slices, nq, row_list);
   return check_launch("attention_combine");
 }
 

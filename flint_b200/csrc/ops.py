@@ -435,7 +435,7 @@ class CudaOps:
                   c_int(plan.max_tiles if plan else 0), c_int(plan.tile_rows if plan else 0), c_int(M), c_int(N), c_int(K))
 
     # ------------------------------------------------------------------ attention
-    def attention_plan(self, T, nq, nkv, span, hd=128, bf16=True):
+    def attention_plan(self, T, nq, nkv, span, hd=128, bf16=True, ragged=True):
         """Which kernel and how to split the key range so that the device is filled:
         (kernel, keys per split, splits).  Few rows (decode), bfloat16, head sizes up to 128: the
         TMA-fed tensor-core kernel, one warp per (row, kv head, split); few rows otherwise: one block
@@ -447,6 +447,12 @@ class CudaOps:
             # tensor-core decode kernel fed by TMA: 8 query heads per warp, at most one wave of 8 warps
             # per SM (a second, nearly empty wave would cost as much as a full one), at least 64 keys per warp
             base8 = T * nkv * -(-(nq // nkv) // 8)
+            if span > 64 and (ragged or base8 >= 256):
+                # rows of different lengths, or many rows: the kernel cuts the keys of all rows into equal runs
+                # itself; the count is the most pieces one (row, kv head) may be cut into: enough for one wave
+                # of 8 warps per SM.  (Few rows of about the same length are a little faster with the key
+                # range of each row cut into the same number of pieces, below.)
+                return "stream", span, self._stream_slices(base8)
             n = max(1, min(span // 64, 1184 // base8))
             keys = -(-(-(-span // n)) // 16) * 16
             return "tma", keys, -(-span // keys)
@@ -460,6 +466,12 @@ class CudaOps:
         keys = -(-(-(-span // n)) // 32) * 32
         return "warp", keys, -(-span // keys)
 
+    @staticmethod
+    def _stream_slices(items):
+        """The most pieces the stream kernel may cut one (row, kv head) item into: enough for one wave of
+        8 warps per SM over all items."""
+        return max(2, min(64, -(-1184 // items) + 1))
+
     def attention(self, q, cache, step, out, nq, nkv, hd, window, scale):
         """Attention of all rows of a step: long portions on the tensor cores (bfloat16, head
         sizes up to 128), decoded tokens and short portions row by row."""
@@ -468,7 +480,8 @@ class CudaOps:
               and (64 % P == 0 or P % 64 == 0) and step.attention_splits is None)
         if not tc:
             return self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale,
-                                        step.max_kv_len, splits=step.attention_splits)
+                                        step.max_kv_len, splits=step.attention_splits,
+                                        ragged=not step.even_lengths)
         self.attention_prefill_tc(q, cache, step.tiles, step.n_tiles, out, nq, nkv, hd, window, scale)
         if step.n_other_rows:
             self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len,
@@ -489,8 +502,9 @@ class CudaOps:
                   c_int(hd), c_int(window), c_float(scale), _ptr(self.tc_error))
 
     def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,
-                        kernel=None, rows=None):
-        """rows: int32 list of the batch rows to compute (default: all)."""
+                        kernel=None, rows=None, ragged=True):
+        """rows: int32 list of the batch rows to compute (default: all).  ragged: the rows' key ranges may
+        differ much in length (False: a decode batch whose requests are about equally long)."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
@@ -503,15 +517,26 @@ class CudaOps:
             raise KernelError("paged_attention: cache pages do not match the head counts")
         span = min(max_kv_len, window) if window else max_kv_len
         auto_kernel, split_keys, n_splits = self.attention_plan(
-            T, nq, nkv, span, hd, q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16)
+            T, nq, nkv, span, hd, q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16, ragged)
         kernel = kernel or auto_kernel
         if splits is not None:
             split_keys, n_splits = splits
+            if kernel == "stream":          # a given split is kept: the kernel with fixed key ranges
+                kernel = "tma"
         if split_keys * n_splits < span:
             raise KernelError(f"paged_attention: {n_splits} splits of {split_keys} keys do not cover {span} keys")
         scratch = None
         if n_splits > 1:
             scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+        if kernel == "stream":
+            if auto_kernel != "stream":
+                n_splits = self._stream_slices(T * nkv * -(-(nq // nkv) // 8))
+                scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+            return self._run("attention_tc", "flint_attention_decode_stream", _ptr(q), _ptr(cache.k), _ptr(cache.v),
+                             c_int(cache.k.shape[0]), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
+                             c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
+                             c_int(hd), c_int(window), c_float(scale), c_int(n_splits), _ptr(scratch), _ptr(rows),
+                             _ptr(self.tc_error))
         if kernel == "tma":
             if rows is not None and rows.numel() != T:
                 raise KernelError("paged_attention: bad row list")

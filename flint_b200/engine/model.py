@@ -204,9 +204,13 @@ class Model:
 
     def _graphed_decode(self, step):
         bucket, _ = self._decode_splits(step)
-        key = (step.n_tokens, bucket)
-        entry = self._graphs.get(key)
         step.max_kv_len = bucket          # splits are chosen for the bucket, not the exact length
+        # requests of about the same length share one way of cutting their keys; a ragged batch lets the
+        # attention kernel cut the keys of all rows into equal runs itself
+        lens = [e.start_pos + 1 for e in step.entries]
+        step.even_lengths = min(lens) * 4 >= max(lens) * 3
+        key = (step.n_tokens, bucket, step.even_lengths)
+        entry = self._graphs.get(key)
         if entry is None:
             self.forward(step)            # loads modules and warms the allocator outside the capture
             torch.cuda.synchronize(self.device)

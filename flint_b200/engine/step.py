@@ -57,6 +57,7 @@ class StepContext:
     other_rows: torch.Tensor = None
     n_other_rows: int = 0
     attention_splits: tuple | None = None
+    even_lengths: bool = False  # a decode batch whose requests are about equally long (set by the caller)
     record: dict | None = None  # filled by parts when a test asks for internals
 
 

@@ -477,6 +477,49 @@ def test_attention_prefill_on_tensor_cores(ops, ref, nq, nkv, hd, P, window, len
     close(out, exp, 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,P,window,lens", [
+    (8, 8, 128, 64, 0, (77,)),                                # one short row: items of 5 steps cut into runs of 3
+    (32, 8, 128, 64, 0, (700, 128, 77, 1, 16, 17)),           # ragged: a run ends one item and begins the next
+    (4, 2, 64, 16, 0, (300,)),
+    (6, 2, 48, 32, 40, (500, 90, 41, 300)),                   # a window: the first step starts below the first visible key
+    (16, 4, 128, 64, 0, tuple(300 + 7 * i for i in range(64))),   # many rows
+])
+def test_attention_decode_stream_cuts_keys_into_equal_runs(ops, ref, nq, nkv, hd, P, window, lens):
+    """The decode kernel that divides the 16-key steps of all rows among its warps by itself, on rows of
+    very different lengths, through a row list, with scattered pages."""
+    g = torch.Generator().manual_seed(len(lens) * 31 + hd)
+    need = [-(-n // P) for n in lens]
+    n_pages = sum(need) + 2
+    k = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    bt = torch.full((len(lens), max(need) + 1), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    o = 0
+    for s_, n in enumerate(need):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    T = len(lens)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slot = torch.arange(T, dtype=torch.int32)
+    q = torch.randn(T, nq * hd, generator=g).to(torch.bfloat16)
+    spec = KVSpec(nkv, hd, window)
+    dv = CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec)
+    scale = 1 / math.sqrt(hd)
+    exp = torch.zeros(T, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, window, scale, max(lens))
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens), kernel="stream")
+    assert int(ops.tc_error.item()) == 0
+    close(out, exp, 2e-2, 2e-2)
+    if T > 2:       # every other row through a row list: the rest stays untouched
+        rows = torch.arange(0, T, 2, dtype=torch.int32)
+        out2 = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out2, nq, nkv, hd, window, scale, max(lens),
+                            kernel="stream", rows=rows.to(DEV))
+        assert torch.isnan(out2[1::2]).all()
+        close(out2[0::2], exp[0::2], 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("ramp", [0.02, 0.3])
 def test_attention_prefill_growing_scores(ops, ref, ramp):
     """Keys aligned with the queries and growing with their position: a row's maximum keeps rising, slowly
