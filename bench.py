@@ -221,6 +221,31 @@ def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
     return {"tok_s": n_tok / dt, "h2d": h2d, "d2h": batch * 4, "ms": dt * 1000 / steps}
 
 
+def run_mixed(model, cfg, n_requests, lo, hi, decode_tokens, rng):
+    """Continuous batching through the engine: requests with prompts of lo..hi random tokens, all submitted
+    at once, each decoding ``decode_tokens`` tokens greedily; wall time from the first step to the last."""
+    import torch
+    from flint_b200.engine.engine import Engine
+    from flint_b200.sampling.params import SamplingParams
+    eng = Engine(model, SamplingParams.greedy(), seed=1, prefill_chunk=2048, max_step_tokens=2048 + n_requests)
+    V = cfg["vocab_size"]
+    lens = [rng.randint(lo, hi) for _ in range(n_requests)]
+    ids = [eng.create([rng.randrange(V) for _ in range(n)], decode_tokens) for n in lens]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps = 0
+    while eng.has_work():
+        eng.step()
+        steps += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    stats = [eng.stats(i) for i in ids]
+    for i in ids:
+        eng.close(i)
+    return {"seconds": dt, "steps": steps, "prompt_tokens": sum(lens), "decoded": sum(s.decode_tokens + 1 for s in stats),
+            "preemptions": sum(s.preemptions for s in stats)}
+
+
 def profile(model, cfg, args, rng):
     """Per-kernel device time (CUDA events around every launch, graphs off): one prefill of 2,048
     tokens and one decode step of the batch.  Launches are serialised by the events, so compare shares."""
@@ -288,6 +313,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-tokens", type=int, default=2048)
     ap.add_argument("--ctx-size", type=int, default=4096)
+    ap.add_argument("--mixed", type=int, nargs=4, metavar=("REQUESTS", "MIN_PROMPT", "MAX_PROMPT", "DECODE"), default=None,
+                    help="instead of the default run: continuous batching of this many requests through the engine")
     ap.add_argument("--expert-intermediate", type=int, default=None,
                     help="expert width (default 960, the Phi-mini-MoE sizes; 6400 gives the Phi-3.5-MoE sizes)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (both are named)")
@@ -313,13 +340,21 @@ def main():
     pk = peaks()
     cfg = mini_config(args.layers, args.expert_intermediate)
     rng = random.Random(0)
-    max_batch = max(args.batch, 1 if args.no_points else 64)
+    max_batch = max(args.batch, 1 if args.no_points else 64, args.mixed[0] if args.mixed else 1)
     model = build_model(cfg, max_batch, args.ctx_size)
 
     if args.profile:
         return profile(model, cfg, args, rng)
     if args.one_step:
         return one_step(model, cfg, args, rng)
+    if args.mixed:
+        n, lo, hi, dec = args.mixed
+        for _ in range(2):          # the first pass compiles kernels and captures graphs
+            r = run_mixed(model, cfg, n, lo, hi, dec, rng)
+        print(json.dumps({"metric": f"mixed serving: {n} requests, prompts of {lo}..{hi} tokens, {dec} decoded each",
+                          "value": round((r["prompt_tokens"] + r["decoded"]) / r["seconds"], 1), "unit": "tokens/s (prompt + decoded)",
+                          "decode_tok_s": round(r["decoded"] / r["seconds"], 1), **r}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()
