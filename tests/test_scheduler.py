@@ -143,3 +143,53 @@ def test_context_limit_ends_a_request():
     r = req(0, 20, max_tokens=100)
     run(s, [r])
     assert r.finish_reason == "context" and len(r.tokens) == 32
+
+
+def test_random_workloads_keep_every_promise():
+    """Random pools, budgets, windows and arrivals (requests join while others run, some are aborted): every
+    step keeps the budget and the one-portion-per-request rule, the cache's invariants hold after every
+    commit, every request ends (finished, failed alone, or aborted), a finished request produced exactly what
+    it produces alone, and in the end every page and slot is free."""
+    import random
+    for seed in range(12):
+        rnd = random.Random(seed)
+        page = 16
+        n_pages = rnd.randint(3, 24)
+        slots = rnd.randint(1, 5)
+        window = rnd.choice([0, 0, 32, 48])
+        budget = rnd.randint(4, 48)
+        chunk = rnd.randint(2, 32)
+        cache, s = setup(n_pages=n_pages, page=page, slots=slots, ctx=256, budget=budget, chunk=chunk, window=window)
+        todo = [req(i, rnd.randint(1, 90), max_tokens=rnd.randint(1, 40)) for i in range(rnd.randint(3, 10))]
+        everyone = list(todo)
+        aborted = set()
+        steps = 0
+        while (todo or s.has_work()) and steps < 5000:
+            while todo and (rnd.random() < 0.4 or not s.has_work()):
+                s.add(todo.pop(0))
+            if rnd.random() < 0.03:
+                live = [r for r in everyone if r.state in (WAITING, RUNNING) and r not in todo]
+                if live:
+                    victim = rnd.choice(live)
+                    s.abort(victim)
+                    aborted.add(victim.id)
+            portions = s.plan()
+            assert sum(p.n_tokens for p in portions) <= budget
+            assert len({p.request.id for p in portions}) == len(portions)
+            for p in portions:
+                assert p.n_tokens <= chunk and p.request.state == RUNNING and p.request.slot >= 0
+                assert p.start == p.request.n_cached and p.wants_logits == (p.start + p.n_tokens == p.request.n_tokens)
+            s.commit(portions, [next_token(p.request) for p in portions if p.wants_logits])
+            cache.check()
+            steps += 1
+        assert steps < 5000, f"seed {seed}: no end"
+        for r in everyone:
+            assert r.state in (FINISHED, FAILED), (seed, r.id, r.state)
+            if r.state == FINISHED and r.id not in aborted:
+                solo = req(r.id, len(r.prompt), max_tokens=r.max_tokens)
+                _, s2 = setup(n_pages=64, page=page, slots=1, ctx=256, budget=64, chunk=64, window=window)
+                run(s2, [solo])
+                assert solo.generated == r.generated, (seed, r.id)
+            if r.state == FAILED:
+                assert r.error
+        assert cache.free_pages() == n_pages and cache.free_slots == slots, seed
