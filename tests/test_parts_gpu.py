@@ -1,7 +1,8 @@
 """Each part alone on the GPU beside its plain function, and the generality of the composition:
 a toy mixer with state of its own, a dense feed-forward, an RMS norm, a parallel block, a layer
-that runs twice and a layer that reads another layer's cache -- all registered and built from the
-test, without a change to the package."""
+that runs twice and a layer that reads another layer's cache; and a second toy model with a feed-forward
+that routes by itself and a position encoding of its own -- all registered and built from the test,
+without a change to the package."""
 import math
 
 import pytest
@@ -12,7 +13,7 @@ from flint_b200.cache.manager import CacheManager, KVSpec, StateSpec
 from flint_b200.config.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from flint_b200.engine.model import Model
 from flint_b200.engine.step import StepEntry, StepStaging
-from flint_b200.parts.base import BuildContext, Mixer, mat
+from flint_b200.parts.base import BuildContext, FeedForward, Mixer, PositionEncoding, mat
 from flint_b200.registry import ARCHITECTURES, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
 from flint_b200.weights.sources import RandomSource
 
@@ -272,3 +273,132 @@ def test_toy_architecture_with_a_stateful_mixer_is_built_and_stepped():
     finally:
         MIXERS.unregister("test_running_sum")
         ARCHITECTURES.unregister("ToyStateLM")
+
+
+# ------------------------------------------------------------------------------------------------
+# a second toy architecture: a feed-forward with routing of its own and another position encoding
+
+class SwitchFeedForward(FeedForward):
+    """Top-1 routing over small ReLU experts: y = p_e * W2_e relu(W1_e x), e = argmax of the router logits,
+    p = softmax(logits)[e].  Written with ordinary tensor operations: a part may compute however it likes."""
+
+    graph_safe = True
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.inner, self.experts = params["width"], params["inner"], params["experts"]
+
+    def weights(self):
+        return {"router.weight": mat(self.experts, self.width), "w1.weight": mat(self.experts * self.inner, self.width),
+                "w2.weight": mat(self.experts * self.width, self.inner)}
+
+    def load(self, t):
+        self.wr = t["router.weight"].float()
+        self.w1 = t["w1.weight"].float().view(self.experts, self.inner, self.width)
+        self.w2 = t["w2.weight"].float().view(self.experts, self.width, self.inner)
+
+    def input_dtypes(self):
+        return (torch.float32,)
+
+    def forward(self, x, residual, step):
+        x32 = x[torch.float32]
+        prob = torch.softmax(x32 @ self.wr.T, -1)
+        e = prob.argmax(-1)
+        hid = torch.relu(torch.einsum("tw,tiw->ti", x32, self.w1[e]))
+        residual += torch.einsum("ti,twi->tw", hid, self.w2[e]) * prob.gather(1, e[:, None])
+
+
+class InterpolatedRotary(PositionEncoding):
+    """Rotary angles of position / factor (position interpolation) over the first ``rotary_dim`` dims of a head."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.rotary_dim = int(params["rotary_dim"])
+
+    def tables(self):
+        half = self.rotary_dim // 2
+        inv = float(self.params["theta"]) ** (-2.0 * torch.arange(half, dtype=torch.float64) / self.rotary_dim)
+        ang = (torch.arange(int(self.params["max_positions"]), dtype=torch.float64) / float(self.params["factor"]))[:, None] * inv
+        return torch.cos(ang).float().to(self.ctx.device), torch.sin(ang).float().to(self.ctx.device)
+
+
+def routed_spec(H=40, V=61):
+    pos = PartSpec("test_interpolated_rotary", {"rotary_dim": 8, "theta": 100.0, "factor": 3.5, "max_positions": 128})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "window": 24,
+                                  "qkv_bias": True, "out_bias": False, "position": pos})
+    ln = PartSpec("layernorm", {"width": H, "eps": 1e-5, "bias": True})
+    switch = PartSpec("test_switch_ffn", {"width": H, "inner": 24, "experts": 5})
+    names = {"norm1": "n1.", "mixer": "mix.", "norm2": "n2.", "ffn": "ff."}
+    layers = tuple(LayerSpec("prenorm", {"norm1": ln, "mixer": attn, "norm2": ln, "ffn": switch}, f"layers.{i}.", names)
+                   for i in range(2))
+    return ModelSpec(architecture="ToyRoutedLM", vocab_size=V, hidden_size=H, max_positions=128, layers=layers,
+                     order=(LayerCall(0), LayerCall(1)), final_norm=ln, head_bias=False, tie_word_embeddings=True)
+
+
+def routed_plain(w, tokens):
+    T = len(tokens)
+    h = P.embed(tokens, w["embed_tokens.weight"])
+    half = 4
+    inv = 100.0 ** (-2.0 * torch.arange(half, dtype=torch.float64) / 8)
+    ang = (torch.arange(T, dtype=torch.float64) / 3.5)[:, None] * inv
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    for i in range(2):
+        p = f"layers.{i}."
+        x = P.layer_norm(h, w[p + "n1.weight"], w[p + "n1.bias"], 1e-5)
+        q = P.rope_rotate((x @ w[p + "mix.q_proj.weight"].T + w[p + "mix.q_proj.bias"]).view(T, 4, 16), cos, sin)
+        k = P.rope_rotate((x @ w[p + "mix.k_proj.weight"].T + w[p + "mix.k_proj.bias"]).view(T, 2, 16), cos, sin)
+        v = (x @ w[p + "mix.v_proj.weight"].T + w[p + "mix.v_proj.bias"]).view(T, 2, 16)
+        h = h + P.attention(q, k, v, 24).reshape(T, 64) @ w[p + "mix.o_proj.weight"].T
+        x = P.layer_norm(h, w[p + "n2.weight"], w[p + "n2.bias"], 1e-5)
+        prob = torch.softmax(x @ w[p + "ff.router.weight"].T, -1)
+        e = prob.argmax(-1)
+        w1, w2 = w[p + "ff.w1.weight"].view(5, 24, 40), w[p + "ff.w2.weight"].view(5, 40, 24)
+        for t in range(T):
+            h[t] = h[t] + (w2[e[t]] @ torch.relu(w1[e[t]] @ x[t])) * prob[t, e[t]]
+    return P.layer_norm(h, w["norm.weight"], w["norm.bias"], 1e-5) @ w["embed_tokens.weight"].T
+
+
+def test_toy_architecture_with_its_own_routing_and_position_encoding():
+    """A feed-forward with routing and a position encoding that the package does not have, registered from here,
+    built by the generic model and stepped in portions and token by token (one-token batches go through the
+    graph path, which the toy feed-forward declares itself safe for)."""
+    FEED_FORWARDS.register("test_switch_ffn", SwitchFeedForward, replace=True)
+    POSITION_ENCODINGS.register("test_interpolated_rotary", InterpolatedRotary, replace=True)
+
+    class RoutedArch:
+        @staticmethod
+        def parse_config(d):
+            return d
+
+        @staticmethod
+        def model_spec(cfg):
+            return routed_spec()
+    ARCHITECTURES.register("ToyRoutedLM", RoutedArch, replace=True)
+    try:
+        from flint_b200.engine.model import Layer, architecture_of, expected_tensors
+        spec = architecture_of({"architectures": ["ToyRoutedLM"]}).model_spec({})
+        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers])
+        for n, ws in NORMS.get("layernorm")(spec.final_norm.params, ctx_for("float32")).weights().items():
+            expected["norm." + n] = ws
+        src = RandomSource(expected, 5, dtype=torch.float32)
+        model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=8, max_slots=2)
+        w = {n: src.read(n).double() for n in expected}
+        tokens = [(i * 13 + 5) % 61 for i in range(70)]          # longer than the window of 24 and than 4 pages hold
+        want = routed_plain(w, tokens)
+        slot = model.cache.admit()
+        got, done = [], 0
+        for n in [9, 2, 17, 1, 1, 1, 30, 1, 1, 1, 1, 1, 1, 1, 1]:
+            n = min(n, len(tokens) - done)
+            if n <= 0:
+                break
+            model.cache.ensure(slot, done, done + n)
+            got.append(model.step([StepEntry(slot, done, tokens[done:done + n], list(range(n)))]).cpu())
+            done += n
+            model.cache.advance(slot, done)
+        err = (torch.cat(got).double() - want[:done]).abs().max().item()
+        assert err < 1e-4, f"{err:.2e}"
+        assert model.cache.groups[0].pages.pool.used_pages <= 3      # the window of 24 lets earlier pages go
+    finally:
+        FEED_FORWARDS.unregister("test_switch_ffn")
+        POSITION_ENCODINGS.unregister("test_interpolated_rotary")
+        ARCHITECTURES.unregister("ToyRoutedLM")
