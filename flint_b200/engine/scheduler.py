@@ -177,7 +177,9 @@ class Scheduler:
     def _pull_touched(self):
         n = self._lib.flint_rt_sched_take_touched(self._h, self._out, len(self._out))
         for h in set(self._out[:n]):
-            self._pull(self._reqs[h])
+            req = self._reqs.get(h)            # a request that ended long ago may have been forgotten
+            if req is not None:
+                self._pull(req)
 
     # ------------------------------------------------------------------ after the step
     def commit(self, portions, sampled):
