@@ -415,7 +415,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     if (sm_count <= 0) sm_count = 148;
   }
   constexpr int acc_cols = 2 * BN;
-  const int per_sm = (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
+  const int per_sm = (smem <= 74 * 1024 && acc_cols <= 128) ? 3 : (smem <= 110 * 1024 && acc_cols <= 256) ? 2 : 1;
   // stream-K: the work is cut into as many runs as blocks stay resident (at least one K block each)
   const long long items = p.stream_k ? (long long)grid.x * grid.y * ((p.K + BK - 1) / BK)
                                      : (long long)grid.x * grid.y * grid.z;
@@ -494,6 +494,9 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   p.kb_per_split = kbps; p.splits = splits; p.defer = defer; p.stream_k = stream_k;
   p.w_expert_rows = w_expert_rows;
   p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
+  // few rows: the product streams its weights and is bound by how many bytes an SM keeps in flight and by how
+  // evenly the tiles spread; four stages of 18 KB let three blocks share an SM (444 resident blocks)
+  if (bn < 64 && g_stage_override == 0 && p.stages > 4) p.stages = 4;
   if (p.stages > total_kb && total_kb >= 2) p.stages = total_kb;
   dim3 grid(w_up ? (N + GATED_FEATURES - 1) / GATED_FEATURES : (N + BM - 1) / BM, tiles_n, splits);
   int rc;

@@ -346,9 +346,9 @@ class CudaOps:
         kb = -(-K // 64)
         if tiles >= 148 or kb < 8:
             return 1
-        # as many pieces as still fit one wave of two blocks per SM (a second, partial wave would
-        # cost as much as a full one)
-        return max(1, min(296 // tiles, kb // 4, 16))
+        # as many pieces as still fit one wave of resident blocks (three per SM with the narrow token tiles,
+        # else two; a second, partial wave would cost as much as a full one)
+        return max(1, min((444 if bn < 64 else 296) // tiles, kb // 4, 16))
 
     def _gemm(self, x, w, gated, out, bias, accumulate, act, plan):
         _check(x, "x", dims=2, contiguous=False)
