@@ -181,6 +181,11 @@ class Model:
         step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
         step.record = record
         step.attention_splits = attention_splits
+        if step.n_tokens == len(entries):
+            # a batch of decoded tokens: requests of about the same length share one way of cutting their keys;
+            # a ragged batch lets the attention kernel cut the keys of all rows into equal runs itself
+            lens = [e.start_pos + 1 for e in entries]
+            step.even_lengths = min(lens) * 4 >= max(lens) * 3
         if (self.use_graphs and attention_splits is None
                 and step.n_tokens == len(entries) <= self.graph_max_batch and step.n_want == step.n_tokens):
             return self._graphed_decode(step)
@@ -205,10 +210,6 @@ class Model:
     def _graphed_decode(self, step):
         bucket, _ = self._decode_splits(step)
         step.max_kv_len = bucket          # splits are chosen for the bucket, not the exact length
-        # requests of about the same length share one way of cutting their keys; a ragged batch lets the
-        # attention kernel cut the keys of all rows into equal runs itself
-        lens = [e.start_pos + 1 for e in step.entries]
-        step.even_lengths = min(lens) * 4 >= max(lens) * 3
         key = (step.n_tokens, bucket, step.even_lengths)
         entry = self._graphs.get(key)
         if entry is None:
