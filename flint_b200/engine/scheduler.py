@@ -128,6 +128,9 @@ class Scheduler:
 
     def _list(self, which):
         n = self._lib.flint_rt_sched_list(self._h, which, self._out, len(self._out))
+        if n > len(self._out):                      # a queue longer than the buffer: take a larger one
+            self._out = (c_int * (2 * n))()
+            n = self._lib.flint_rt_sched_list(self._h, which, self._out, len(self._out))
         return [self._reqs[h] for h in self._out[:n]]
 
     @property
@@ -175,7 +178,7 @@ class Scheduler:
         return portions
 
     def _pull_touched(self):
-        n = self._lib.flint_rt_sched_take_touched(self._h, self._out, len(self._out))
+        n = min(self._lib.flint_rt_sched_take_touched(self._h, self._out, len(self._out)), len(self._out))
         for h in set(self._out[:n]):
             req = self._reqs.get(h)            # a request that ended long ago may have been forgotten
             if req is not None:
