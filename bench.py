@@ -47,14 +47,19 @@ def peaks():
     return dict(FALLBACK_PEAKS)
 
 
-def mini_config(layers=None, expert_intermediate=None):
+def mini_config(layers=None, expert_intermediate=None, sizes=None):
+    """The Phi-mini-MoE sizes, with any of them replaced (``sizes``: config.json key -> value)."""
     cfg = dict(MINI)
     if expert_intermediate:
         cfg["intermediate_size"] = int(expert_intermediate)
+    for key, value in (sizes or {}).items():
+        if value:
+            cfg[key] = int(value)
     r = random.Random(7)
+    half = cfg["head_dim"] // 2
     cfg["rope_scaling"] = {"type": "longrope",
-                           "short_factor": [round(r.uniform(1, 4), 4) for _ in range(64)],
-                           "long_factor": [round(r.uniform(1, 4), 4) for _ in range(64)]}
+                           "short_factor": [round(r.uniform(1, 4), 4) for _ in range(half)],
+                           "long_factor": [round(r.uniform(1, 4), 4) for _ in range(half)]}
     if layers:
         cfg["num_hidden_layers"] = layers
     return cfg
@@ -313,6 +318,10 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-tokens", type=int, default=2048)
     ap.add_argument("--ctx-size", type=int, default=4096)
+    # the reference bench's own names for the sizes and the workload (crates/thuban_bench/src/main.rs:12-63)
+    for flag in ("--hidden", "--intermediate", "--q-heads", "--kv-heads", "--head-dim", "--vocab", "--prefill-tokens",
+                 "--decode-tokens", "--max-seq"):
+        ap.add_argument(flag, type=int, default=None)
     ap.add_argument("--mixed", type=int, nargs=4, metavar=("REQUESTS", "MIN_PROMPT", "MAX_PROMPT", "DECODE"), default=None,
                     help="instead of the default run: continuous batching of this many requests through the engine")
     ap.add_argument("--expert-intermediate", type=int, default=None,
@@ -338,7 +347,15 @@ def main():
 
     import torch
     pk = peaks()
-    cfg = mini_config(args.layers, args.expert_intermediate)
+    cfg = mini_config(args.layers, args.expert_intermediate or args.intermediate,
+                      {"hidden_size": args.hidden, "num_attention_heads": args.q_heads, "num_key_value_heads": args.kv_heads,
+                       "head_dim": args.head_dim, "vocab_size": args.vocab})
+    if args.max_seq:
+        args.ctx_size = args.max_seq
+    if args.prefill_tokens:
+        args.prompt_tokens = args.prefill_tokens
+    if args.decode_tokens:
+        args.steps = args.decode_tokens
     rng = random.Random(0)
     max_batch = max(args.batch, 1 if args.no_points else 64, args.mixed[0] if args.mixed else 1)
     model = build_model(cfg, max_batch, args.ctx_size)
@@ -371,15 +388,19 @@ def main():
     pre_flops = step_flops(cfg, 2048, range(1, 2049))
     bytes_step = decode_bytes(cfg, model, dec["kv_lens"], dec["distinct"])
     achieved = bytes_step / (dec["ms"] * 1e-3) / 1e9
+    mini = all(cfg[k] == MINI[k] for k in MINI if k != "num_hidden_layers")
     out = {
-        "metric": "decode tok/s at batch 8 (Phi-mini-MoE layer sizes, 2,048-token prompts, context 4,096)",
+        "metric": f"decode tok/s at batch {args.batch} ({'Phi-mini-MoE layer sizes' if mini else 'other layer sizes, see config'}, "
+                  f"{args.prompt_tokens:,}-token prompts, context {args.ctx_size:,})",
         "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
-        "config": {"model": "Phi-mini-MoE sizes" if cfg["intermediate_size"] == 960 else
-                            f"Phi-MoE sizes with experts of {cfg['intermediate_size']}", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
-                   "hidden": 4096, "q_heads": 32, "kv_heads": 8, "head_dim": 128, "experts": 16, "top_k": 2,
-                   "expert_intermediate": cfg["intermediate_size"], "vocab": 32064, "global_batch": args.batch,
+        "config": {"model": "Phi-mini-MoE sizes" if mini else
+                            f"Phi-MoE sizes: hidden {cfg['hidden_size']}, experts of {cfg['intermediate_size']}", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"],
+                   "top_k": 2, "expert_intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "global_batch": args.batch,
                    "prompt_tokens": args.prompt_tokens, "seq_len": args.ctx_size, "page_size": 64,
                    "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed every step)",
                    "peaks": pk["source"]},
