@@ -223,7 +223,7 @@ def run_e2e(model, cfg, batch, prompt_len, steps, warmup, rng):
     h2d = model.staging.host.numel() * 4
     for i in ids:
         eng.close(i)
-    return {"tok_s": n_tok / dt, "h2d": h2d, "d2h": batch * 4, "ms": dt * 1000 / steps}
+    return {"tok_s": n_tok / dt, "h2d": h2d, "d2h": (batch + 2) * 4, "ms": dt * 1000 / steps}
 
 
 def run_mixed(model, cfg, n_requests, lo, hi, decode_tokens, rng):

@@ -71,8 +71,14 @@ class CudaOps:
         self._libs = {}
         self.launches = 0
         self._profile = None
-        self.tc_error = torch.zeros(1, dtype=torch.int32, device=self.device)   # set by a tensor-core
-        # kernel whose bounded wait ran out
+        # One buffer for what the host reads back after a step, so that one copy brings all of it: a flag set by
+        # a tensor-core kernel whose bounded wait ran out, a flag set by a kernel that met a position without a
+        # page, and the sampled tokens.
+        self.MAX_TOKEN_ROWS = 4096
+        self.readback = torch.zeros(2 + self.MAX_TOKEN_ROWS, dtype=torch.int32, device=self.device)
+        self.tc_error = self.readback[0:1]
+        self.page_error = self.readback[1:2]
+        self.token_out = self.readback[2:]
 
     # ------------------------------------------------------------------ plumbing
     def _fn(self, module, name):

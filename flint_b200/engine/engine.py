@@ -128,6 +128,8 @@ class Engine:
         logits = self.model.step(entries)
         rows = [(p.request.sampling, p.request.rng, p.request.generated) for p in portions if p.wants_logits]
         tokens = self.sampler.sample(logits, rows)
+        if any(self.sampler.last_flags):        # a kernel gave up or met a missing page: do not go on with garbage
+            self.model.check_status(self.sampler.last_flags)
         now = time.perf_counter()
         for req, tok in self.scheduler.commit(portions, tokens):
             s = self.sessions[req.id]

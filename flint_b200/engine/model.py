@@ -133,7 +133,7 @@ class Model:
         cache_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
         self.cache = CacheManager(kv_calls, state_calls, page_size=page_size, n_pages=n_pages, max_slots=max_slots,
                                   max_context=self.max_context, dtype=cache_dtype, device=self.device)
-        self.staging = StepStaging(max_step_tokens, self.device)
+        self.staging = StepStaging(max_step_tokens, self.device, status=getattr(ops, "page_error", None))
         self.max_step_tokens = max_step_tokens
         # decode steps (one token per entry) are captured once per batch size and key-range
         # split, and replayed: their hundreds of small launches would otherwise be bound by
@@ -249,13 +249,17 @@ class Model:
             ops.gemm(x[wdt], self.head_weight, logits, bias=self.head_bias)
         return logits
 
-    def check_status(self):
-        """Raise if a kernel met a position without a page (synchronises)."""
-        if int(self.staging.status.item()) != 0:
+    def check_status(self, flags=None):
+        """Raise if a kernel met a position without a page or gave up a bounded wait.  ``flags``: the two
+        flags (tensor-core error, page error) if the caller has read them already; else they are read here
+        (which synchronises)."""
+        tc = getattr(self.ops, "tc_error", None)
+        if flags is None:
+            flags = (int(tc.item()) if tc is not None else 0, int(self.staging.status.item()))
+        if flags[1]:
             self.staging.status.zero_()
             raise ModelError("a kernel met a position whose page was not allocated")
-        tc = getattr(self.ops, "tc_error", None)
-        if tc is not None and int(tc.item()) != 0:
+        if flags[0]:
             tc.zero_()
             raise ModelError("a tensor-core kernel gave up waiting for its operands")
 

@@ -64,7 +64,7 @@ class StepContext:
 class StepStaging:
     """Pinned host memory and device memory for the packed metadata of a step."""
 
-    def __init__(self, max_tokens: int, device):
+    def __init__(self, max_tokens: int, device, status=None):
         self.max_tokens = int(max_tokens)
         self.device = torch.device(device)
         self.max_tiles = self.max_tokens // 8 + 16
@@ -73,7 +73,8 @@ class StepStaging:
         if self.device.type == "cuda":
             self.host = self.host.pin_memory()
         self.dev = torch.zeros(n, dtype=torch.int32, device=self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # set non-zero by a kernel that met a position without a page (the caller may pass a flag of its own)
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copied = torch.cuda.Event() if self.device.type == "cuda" else None
         self._in_flight = False
         self._lib = rt.lib()

@@ -26,8 +26,17 @@ class BatchSampler:
         self._ctx_host = torch.full((max_rows, max_context), -1, dtype=torch.int32, pin_memory=pin)
         self._params = torch.zeros((max_rows, 8), dtype=torch.float32, device=self.device)
         self._ctx = torch.full((max_rows, max_context), -1, dtype=torch.int32, device=self.device)
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        # the tokens land beside the kernels' error flags when the kernel set keeps such a buffer: one copy
+        # to the host then brings both
+        self._readback = getattr(ops, "readback", None)
+        if self._readback is not None and max_rows <= ops.MAX_TOKEN_ROWS:
+            self._out = ops.token_out[:max_rows]
+            self._host = torch.zeros(2 + max_rows, dtype=torch.int32, pin_memory=pin)
+        else:
+            self._readback = None
+            self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+            self._host = torch.zeros(2 + max_rows, dtype=torch.int32, pin_memory=pin)
+        self.last_flags = (0, 0)          # (tensor-core error, page error) as of the last read
         self._work = None
 
     def sample(self, logits: torch.Tensor, rows):
@@ -58,5 +67,11 @@ class BatchSampler:
                 self._work = torch.empty((max(R, min(self.max_rows, 64)), logits.shape[1]), dtype=torch.float32,
                                          device=self.device)
             self.ops.sample(logits, self._params[:R], self._ctx[:R], self._work[:R], out)
-        self._out_host[:R].copy_(out)      # device -> host read of the step's result (synchronises)
-        return self._out_host[:R].tolist()
+        # device -> host read of the step's result (synchronises)
+        if self._readback is not None:
+            self._host[:2 + R].copy_(self._readback[:2 + R])
+            got = self._host[:2 + R].tolist()
+            self.last_flags = (got[0], got[1])
+            return got[2:]
+        self._host[2:2 + R].copy_(out)
+        return self._host[2:2 + R].tolist()

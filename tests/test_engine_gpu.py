@@ -229,6 +229,30 @@ def test_greedy_generation_through_the_entry_point(setup):
     assert eng.scheduler.preemptions > 0
 
 
+def test_a_kernel_error_flag_stops_the_engine(setup):
+    """The flags that kernels raise (a bounded wait that ran out, a position without a page) come back with the
+    sampled tokens of every step; the engine raises instead of going on with garbage.  The flag is set by hand
+    here: nothing on the device is made to fail."""
+    from flint_b200.errors import ModelError
+    which, dtype, folder, reqs, plain = setup
+    m = load_model(folder, dtype=dtype, page_size=16, n_pages=16, max_slots=2, max_step_tokens=24)
+    eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16)
+    sid = eng.create(list(reqs["r0"])[:5], 4)
+    m.ops.tc_error.fill_(1)
+    with pytest.raises(ModelError, match="gave up waiting"):
+        while not eng.finished(sid):
+            eng.step()
+    assert int(m.ops.tc_error.item()) == 0            # cleared when it was reported
+    eng.close(sid)
+    sid = eng.create(list(reqs["r0"])[:5], 4)
+    m.ops.page_error.fill_(1)
+    with pytest.raises(ModelError, match="page was not allocated"):
+        while not eng.finished(sid):
+            eng.step()
+    eng.close(sid)
+    assert eng.generate([list(reqs["r0"])[:5]], 3)[0]     # and the engine works again afterwards
+
+
 def test_temperature_sampling_is_reproducible_and_follows_the_host_sampler(setup):
     which, dtype, folder, reqs, plain = setup
     m = load_model(folder, dtype=dtype, page_size=16, n_pages=32, max_slots=4)
