@@ -11,26 +11,32 @@
 using namespace flint;
 
 // --------------------------------------------------------------------------- embed
+// fed_rows (may be null): for each row -1, or the place in `fed_from` (the sampler's last output, still on the
+// device) that holds the row's token: a decoded token can be fed to the next step before the host has read it.
 template <typename TT>
-__global__ void embed_kernel(const int* __restrict__ ids, const TT* __restrict__ table,
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ fed_rows,
+                             const int* __restrict__ fed_from, const TT* __restrict__ table,
                              float* __restrict__ out, int T, int H, int V, float scale) {
   pdl_launch();
   pdl_wait();
   const int r = blockIdx.x;
-  int id = ids[r];
+  const int fed = fed_rows ? fed_rows[r] : -1;
+  int id = fed >= 0 ? fed_from[fed] : ids[r];
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);  // ids are validated on the host; never read outside
   const TT* src = table + (size_t)id * H;
   float* dst = out + (size_t)r * H;
   for (int d = threadIdx.x; d < H; d += blockDim.x) dst[d] = to_f32(src[d]) * scale;
 }
 
-extern "C" int flint_embed(const int* ids, const void* table, int table_dtype, float* out,
-                           int T, int H, int V, float scale, cudaStream_t stream) {
+extern "C" int flint_embed(const int* ids, const int* fed_rows, const int* fed_from, const void* table, int table_dtype,
+                           float* out, int T, int H, int V, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
+  if ((fed_rows == nullptr) != (fed_from == nullptr)) return fail("embed: fed rows and their source come together");
   const int threads = H >= 1024 ? 256 : (H >= 256 ? 128 : 64);
   FLINT_DISPATCH_DTYPE(table_dtype, TT,
-      launch_pdl(embed_kernel<TT>, dim3(T), dim3(threads), 0, stream, ids, (const TT*)table, out, T, H, V, scale));
+      launch_pdl(embed_kernel<TT>, dim3(T), dim3(threads), 0, stream, ids, fed_rows, fed_from, (const TT*)table, out, T,
+                 H, V, scale));
   return check_launch("embed");
 }
 

@@ -280,12 +280,14 @@ struct Cache {
 // back, recomputed later from the head of the queue); an older request never loses to a younger one, and a
 // request that cannot fit alone fails alone.
 enum State { WAITING = 0, RUNNING = 1, FINISHED = 2, FAILED = 3 };
+constexpr int UNREAD = -1;          // a sampled token whose value the host has not read yet
 enum Reason { R_NONE = 0, R_STOP = 1, R_LENGTH = 2, R_CONTEXT = 3, R_ABORT = 4, R_ERROR = 5 };
 
 struct Request {
   int n_prompt = 0, n_generated = 0, max_tokens = 0, arrival = 0;
   int n_cached = 0, slot = -1, state = WAITING, reason = R_NONE;
   int preemptions = 0, prefill_tokens = 0, decode_tokens = 0;
+  int n_unread = 0;       // the last n_unread generated tokens were committed before their values were read
   std::vector<int> stop;
   std::string error;
   int n_tokens() const { return n_prompt + n_generated; }
@@ -335,6 +337,7 @@ struct Scheduler {
   }
   // give back the pages and the slot of a running request; it will be recomputed
   int preempt(int victim) {
+    if (reqs[victim].n_unread) return fail(E_CHECK, "a request with unread tokens cannot be recomputed");
     drop_running(victim);
     if (int rc = cache->release(reqs[victim].slot)) return rc;
     Request& v = reqs[victim];
@@ -473,7 +476,11 @@ struct Scheduler {
       if (!p.wants_logits) continue;
       if (next >= n_sampled) return fail(E_MODEL, "fewer sampled tokens than portions that wanted logits");
       const int token = sampled[next++];
-      if (std::find(q.stop.begin(), q.stop.end(), token) != q.stop.end()) {
+      if (token == UNREAD) {
+        ++q.n_unread;                   // its value, and whether it stops the request, come with resolve()
+      } else if (q.n_unread) {
+        return fail(E_MODEL, "a token was committed while earlier ones of its request are unread");
+      } else if (std::find(q.stop.begin(), q.stop.end(), token) != q.stop.end()) {
         if (int rc = finish(p.req, R_STOP)) return rc;
         continue;
       }
@@ -488,8 +495,38 @@ struct Scheduler {
     }
     return 0;
   }
+  // The value of the oldest unread token of r.  0: it is the request's next token; 1: it is a stop token, the
+  // request ends before it and what was run after it is void; 2: nothing of r is unread any more (the request
+  // ended at an earlier token or was aborted), the value is dropped.
+  int resolve(int r, int token) {
+    Request& q = reqs[r];
+    if (q.n_unread == 0) return 2;
+    if (std::find(q.stop.begin(), q.stop.end(), token) == q.stop.end()) {
+      --q.n_unread;
+      return 0;
+    }
+    q.n_generated -= q.n_unread;
+    q.n_unread = 0;
+    if (q.state == RUNNING) {
+      if (int rc = finish(r, R_STOP)) return rc;
+    } else {
+      q.reason = R_STOP;              // it had reached its length with this very token
+      touched.push_back(r);
+    }
+    return 1;
+  }
+  // nothing waits, every running request has exactly its next token left to run, and pages for one more token
+  // of each are free: the next step can be planned before the last one's tokens are read
+  bool steady() const {
+    if (!waiting.empty() || running.empty()) return false;
+    for (int r : running)
+      if (reqs[r].remaining() != 1) return false;
+    return cache->free_pages() >= (int)running.size();
+  }
   int abort(int r) {
     waiting.erase(std::remove(waiting.begin(), waiting.end(), r), waiting.end());
+    reqs[r].n_generated -= reqs[r].n_unread;
+    reqs[r].n_unread = 0;
     return finish(r, R_ABORT);
   }
 };
@@ -610,6 +647,8 @@ int flint_rt_sched_commit(void* s, const int* portions, int n_portions, const in
   return (int)out.size() / 2;
 }
 int flint_rt_sched_abort(void* s, int r) { return ((Scheduler*)s)->abort(r); }
+int flint_rt_sched_resolve(void* s, int r, int token) { return ((Scheduler*)s)->resolve(r, token); }
+int flint_rt_sched_steady(void* s) { return ((Scheduler*)s)->steady() ? 1 : 0; }
 int flint_rt_sched_has_work(void* s) {
   const Scheduler* p = (Scheduler*)s;
   return !p->waiting.empty() || !p->running.empty();
@@ -653,13 +692,17 @@ void flint_rt_sched_counters(void* s, int* preemptions, int* steps) {
 
 // ---- packing of a step
 // Entries: slot, start position, number of tokens, number of wanted places of each; their tokens and wanted
-// places laid end to end.  Fills the host buffer (six regions of `m` ints, the last of 4 * max_tiles: token
-// ids, positions, slots, wanted rows, rows outside any tile, tiles of four ints) and
-// meta = {tokens, wanted rows, tiles, other rows, largest position + 1}; entry_start gets the first row of
-// each entry.  Portions of at least tile_min rows are cut into tiles of up to tile_rows consecutive rows.
+// places laid end to end.  Fills the host buffer (regions of `m` ints, but the tiles' of 4 * max_tiles: token
+// ids, positions, slots, wanted rows, rows outside any tile, tiles of four ints, and for each row the place
+// in the sampler's last output that holds its token, or -1) and
+// meta = {tokens, wanted rows, tiles, other rows, largest position + 1, rows fed from the sampler's output};
+// entry_start gets the first row of each entry.  Portions of at least tile_min rows are cut into tiles of up
+// to tile_rows consecutive rows.  feed (may be null): for each entry -1, or the place in the sampler's last
+// output whose token is the entry's first one (the host does not know its value yet).
 int flint_rt_pack_step(int n_entries, const int* slots, const int* start_pos, const int* n_tokens, const int* n_want,
-                       const int* tokens, const int* want, int vocab_size, int max_positions, int m, int max_tiles,
-                       int tile_rows, int tile_min, int max_slots_seen, int* host, int* entry_start, int* meta) {
+                       const int* tokens, const int* want, const int* feed, int vocab_size, int max_positions, int m,
+                       int max_tiles, int tile_rows, int tile_min, int max_slots_seen, int* host, int* entry_start,
+                       int* meta) {
   long long total = 0;
   for (int e = 0; e < n_entries; ++e) total += n_tokens[e];
   if (total == 0) return fail(E_MODEL, "a step needs at least one token");
@@ -671,7 +714,8 @@ int flint_rt_pack_step(int n_entries, const int* slots, const int* start_pos, co
   int* want_rows = host + 3 * (size_t)m;
   int* others = host + 4 * (size_t)m;
   int* tiles = host + 5 * (size_t)m;
-  int T = 0, R = 0, n_tiles = 0, n_others = 0, max_kv = 0, tok_off = 0, want_off = 0;
+  int* fed = tiles + 4 * (size_t)max_tiles;
+  int T = 0, R = 0, n_tiles = 0, n_others = 0, max_kv = 0, tok_off = 0, want_off = 0, n_fed = 0;
   for (int e = 0; e < n_entries; ++e) {
     const int s = slots[e], n = n_tokens[e], p0 = start_pos[e];
     if (s >= 0 && s < (int)seen.size()) {
@@ -686,8 +730,16 @@ int flint_rt_pack_step(int n_entries, const int* slots, const int* start_pos, co
       return fail(E_MODEL, "positions %d..%d exceed the model's %d positions", p0, p0 + n - 1, max_positions);
     const int base = T;
     entry_start[e] = base;
+    const int from = feed ? feed[e] : -1;
+    if (from >= m) return fail(E_MODEL, "an entry's token is fed from place %d of at most %d", from, m);
     for (int i = 0; i < n; ++i) {
-      const int t = tokens[tok_off + i];
+      int t = tokens[tok_off + i];
+      fed[T] = -1;
+      if (i == 0 && from >= 0) {
+        fed[T] = from;
+        ++n_fed;
+        t = 0;                          // replaced on the device before the step runs
+      }
       if (t < 0 || t >= vocab_size) return fail(E_MODEL, "token id %d is outside the vocabulary of %d", t, vocab_size);
       ids[T] = t;
       pos[T] = p0 + i;
@@ -720,6 +772,7 @@ int flint_rt_pack_step(int n_entries, const int* slots, const int* start_pos, co
   meta[2] = n_tiles;
   meta[3] = n_others;
   meta[4] = max_kv;
+  meta[5] = n_fed;
   return 0;
 }
 

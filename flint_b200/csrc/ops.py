@@ -128,15 +128,25 @@ class CudaOps:
                 self._fn(m, f"flint_{m}_last_error")
 
     # ------------------------------------------------------------------ row-wise
-    def embed(self, ids, table, out, scale=1.0):
+    def embed(self, ids, table, out, scale=1.0, fed_rows=None, fed_from=None):
+        """Rows of the table by token id.  ``fed_rows`` [T] with ``fed_from``: where a row's entry is not
+        negative, its token is read from that place of ``fed_from`` (tokens sampled on the device that the
+        host has not read yet) instead of ``ids``."""
         _check(ids, "ids", torch.int32, 1)
         _check(table, "table", dims=2)
         _check(out, "out", torch.float32, 2)
         T, (V, H) = ids.numel(), table.shape
         if tuple(out.shape) != (T, H):
             raise KernelError(f"embed: out must be [{T}, {H}]")
-        self._run("elementwise", "flint_embed", _ptr(ids), _ptr(table), c_int(_code(table.dtype)), _ptr(out),
-                  c_int(T), c_int(H), c_int(V), c_float(scale))
+        if (fed_rows is None) != (fed_from is None):
+            raise KernelError("embed: fed rows and their source come together")
+        if fed_rows is not None:
+            _check(fed_rows, "fed_rows", torch.int32, 1)
+            _check(fed_from, "fed_from", torch.int32, 1)
+            if fed_rows.numel() != T:
+                raise KernelError(f"embed: fed_rows must have {T} entries")
+        self._run("elementwise", "flint_embed", _ptr(ids), _ptr(fed_rows), _ptr(fed_from), _ptr(table),
+                  c_int(_code(table.dtype)), _ptr(out), c_int(T), c_int(H), c_int(V), c_float(scale))
 
     def norm(self, x, gamma, beta, eps, mode, out_f32=None, out_bf16=None, row_index=None):
         """mode 'layer' or 'rms'; writes float32 and/or bfloat16 copies of the result."""

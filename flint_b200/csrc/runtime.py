@@ -54,14 +54,16 @@ _SIGNATURES = {
     "flint_rt_sched_plan": (c_int, [c_void_p, _INT_P, c_int]),
     "flint_rt_sched_commit": (c_int, [c_void_p, _INT_P, c_int, _INT_P, c_int, _INT_P, c_int]),
     "flint_rt_sched_abort": (c_int, [c_void_p, c_int]),
+    "flint_rt_sched_resolve": (c_int, [c_void_p, c_int, c_int]),
+    "flint_rt_sched_steady": (c_int, [c_void_p]),
     "flint_rt_sched_has_work": (c_int, [c_void_p]),
     "flint_rt_sched_request": (None, [c_void_p, c_int, _INT_P]),
     "flint_rt_sched_request_error": (c_char_p, [c_void_p, c_int]),
     "flint_rt_sched_list": (c_int, [c_void_p, c_int, _INT_P, c_int]),
     "flint_rt_sched_take_touched": (c_int, [c_void_p, _INT_P, c_int]),
     "flint_rt_sched_counters": (None, [c_void_p, _INT_P, _INT_P]),
-    "flint_rt_pack_step": (c_int, [c_int, _INT_P, _INT_P, _INT_P, _INT_P, _INT_P, _INT_P, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_int, c_void_p, _INT_P, _INT_P]),
+    "flint_rt_pack_step": (c_int, [c_int, _INT_P, _INT_P, _INT_P, _INT_P, _INT_P, _INT_P, _INT_P, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_int, c_void_p, _INT_P, _INT_P]),
 }
 
 E_CACHE, E_MODEL, E_CHECK = -1, -2, -3

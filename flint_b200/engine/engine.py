@@ -2,7 +2,10 @@
 
 ``Engine`` has the reference engine's interface: ``create`` a session from a prompt,
 ``step`` the batch, ``poll`` new pieces, ask whether a session is ``finished``, read its
-``stats`` and ``close`` it (crates/thuban_generate/src/engine.rs:77-339).  The stop set is
+``stats`` and ``close`` it (crates/thuban_generate/src/engine.rs:77-339).  Unlike the reference,
+which waits for every step's tokens before it builds the next batch, steady decoding runs one
+step ahead: the next step is enqueued with its tokens taken on the device from the sampler's
+output, and the host reads a step's tokens while the following step runs.  The stop set is
 the model's end-of-sequence ids plus the engine's and the request's extras
 (:130-135); the seed of a session is the engine's seed incremented per ``create``
 (:129,142).  ``generate`` is the one-call form: token ids (or text, if the model folder
@@ -20,7 +23,7 @@ from ..errors import ModelError
 from ..sampling.params import SamplingParams, SplitMix64
 from ..sampling.sampler import BatchSampler
 from .model import Model, load_model
-from .scheduler import FAILED, FINISHED, Request, Scheduler
+from .scheduler import FAILED, FINISHED, UNREAD, Request, Scheduler
 from .step import StepEntry
 
 
@@ -46,6 +49,16 @@ class _Session:
     created: float = 0.0
     first_token_at: float | None = None
     finished_at: float | None = None
+
+
+@dataclass
+class _Flight:
+    """A step that has been enqueued and committed, whose tokens the host has not read yet."""
+    portions: list
+    ticket: int                # the sampler's
+    rows: list                 # the request of each sampled row, in order
+    n_tokens: int
+    plain: bool                # no row's sampling needs earlier token values on the host (a repeat penalty does)
 
 
 def load_tokenizer(model_dir):
@@ -79,7 +92,8 @@ def render_chat(system: str, user: str, history=()) -> str:
 
 class Engine:
     def __init__(self, model: Model, sampling: SamplingParams | None = None, seed: int = 42, stop=(),
-                 tokenizer=None, prefill_chunk: int = 2048, max_step_tokens: int | None = None):
+                 tokenizer=None, prefill_chunk: int = 2048, max_step_tokens: int | None = None,
+                 run_ahead: bool | None = None):
         self.model = model
         self.sampling = sampling or SamplingParams()
         self.seed = int(seed)
@@ -92,6 +106,14 @@ class Engine:
         self.sessions: dict[int, _Session] = {}
         self._next_id = 0
         self.steps = 0
+        # steady decoding enqueues the next step before it reads the last one's tokens, if the sampler leaves
+        # them where the model can take them
+        can = self.sampler.feeds_next_step and model.fed_from is not None
+        if run_ahead and not can:
+            raise ModelError("running ahead needs a kernel set that keeps the sampled tokens on the device")
+        self.run_ahead = can if run_ahead is None else bool(run_ahead)
+        self._flight: _Flight | None = None
+        self.steps_ahead = 0        # steps that were enqueued before the tokens of the step before were read
 
     # ------------------------------------------------------------------ sessions
     def create(self, prompt, max_tokens: int, sampling: SamplingParams | None = None, stop_extra=()) -> int:
@@ -119,30 +141,81 @@ class Engine:
         return sid
 
     def step(self):
-        """One batch through the model; returns the number of tokens it ran."""
+        """One batch through the model; returns the number of tokens it ran.  While every running request is
+        decoding (and none waits, pages are plentiful, no repeat penalty is set) the step's tokens are read
+        during the next call, after that call's batch has been enqueued: they reach ``poll`` one call later.
+        A call that finds nothing left to run only brings in the tokens that are still on their way."""
+        flight = self._flight
+        if flight is not None and not self._may_run_ahead(flight):
+            self._land(flight)
+            flight = None
         portions = self.scheduler.plan()
         if not portions:
-            return 0
-        entries = [StepEntry(p.request.slot, p.start, p.request.span(p.start, p.n_tokens),
-                             [p.n_tokens - 1] if p.wants_logits else []) for p in portions]
+            return self._land(flight) if flight is not None else 0
+        place = {id(req): i for i, req in enumerate(flight.rows)} if flight is not None else {}
+        entries = []
+        for p in portions:
+            req, feed = p.request, -1
+            if req.n_unread:
+                # the request's last token is still on the device: the step takes it from the sampler's output
+                if req.n_unread != 1 or p.n_tokens != 1 or p.start != req.n_tokens - 1 or id(req) not in place:
+                    raise ModelError("a portion needs token values that the host has not read")
+                tokens, feed = [0], place[id(req)]
+            else:
+                tokens = req.span(p.start, p.n_tokens)
+            entries.append(StepEntry(req.slot, p.start, tokens, [p.n_tokens - 1] if p.wants_logits else [], feed))
         logits = self.model.step(entries)
-        rows = [(p.request.sampling, p.request.rng, p.request.generated) for p in portions if p.wants_logits]
-        tokens = self.sampler.sample(logits, rows)
+        sampled = [p.request for p in portions if p.wants_logits]
+        ticket = self.sampler.launch(logits, [(r.sampling, r.rng, r.generated) for r in sampled])
+        plain = all(r.sampling.repeat_penalty == 1.0 or r.sampling.repeat_last_n <= 0 for r in sampled)
+        launched = _Flight(portions, ticket, sampled, sum(p.n_tokens for p in portions), plain)
+        # everything but the stop set is decided without the tokens' values
+        self.scheduler.commit(portions, [UNREAD] * len(sampled))
+        self._flight = launched
+        self.steps += 1
+        if flight is not None:
+            self.steps_ahead += 1
+            self._land(flight)
+        if self._flight is launched and not self._may_run_ahead(launched):
+            self._land(launched)
+        return launched.n_tokens
+
+    def _may_run_ahead(self, flight) -> bool:
+        return self.run_ahead and flight.plain and self.scheduler.steady()
+
+    def _land(self, flight) -> int:
+        """Read a flight's tokens (waiting for them) and hand them to their sessions."""
+        self.model.wait_uploads()       # the tables of a later step are on the device: they may change now
+        tokens = self.sampler.read(flight.ticket)
         if any(self.sampler.last_flags):        # a kernel gave up or met a missing page: do not go on with garbage
+            self._void_flights(flight)
             self.model.check_status(self.sampler.last_flags)
         now = time.perf_counter()
-        for req, tok in self.scheduler.commit(portions, tokens):
-            s = self.sessions[req.id]
+        for req, tok in zip(flight.rows, tokens):
+            if not self.scheduler.resolve(req, tok):
+                continue
+            s = self.sessions.get(req.id)
+            if s is None:
+                continue
             if s.first_token_at is None:
                 s.first_token_at = now
             text = self.tokenizer.decode([tok]) if self.tokenizer is not None else ""
             s.queue.append(Piece(tok, text))
-        for p in portions:
-            s = self.sessions[p.request.id]
-            if p.request.state in (FINISHED, FAILED) and s.finished_at is None:
+        for p in flight.portions:
+            s = self.sessions.get(p.request.id)
+            if s is not None and p.request.state in (FINISHED, FAILED) and s.finished_at is None:
                 s.finished_at = now
-        self.steps += 1
-        return sum(p.n_tokens for p in portions)
+        if self._flight is flight:
+            self._flight = None
+        return flight.n_tokens
+
+    def _void_flights(self, flight):
+        """After a kernel error: what is in flight is garbage; the requests that wait for it end."""
+        for f in (flight, self._flight):
+            for req in (f.rows if f is not None else ()):
+                if req.n_unread:
+                    self.scheduler.abort(req)
+        self._flight = None
 
     def poll(self, sid: int):
         s = self.sessions.get(sid)
@@ -153,7 +226,7 @@ class Engine:
 
     def finished(self, sid: int) -> bool:
         s = self.sessions.get(sid)
-        return s is None or (s.request.state in (FINISHED, FAILED) and not s.queue)
+        return s is None or (s.request.state in (FINISHED, FAILED) and not s.queue and not s.request.n_unread)
 
     def error(self, sid: int):
         s = self.sessions.get(sid)
@@ -174,7 +247,7 @@ class Engine:
             self.scheduler.abort(s.request)
 
     def has_work(self):
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._flight is not None
 
     # ------------------------------------------------------------------ one call
     def generate(self, prompts, max_tokens: int = 64, sampling: SamplingParams | None = None, stop_extra=()):

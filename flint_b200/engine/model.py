@@ -135,6 +135,9 @@ class Model:
                                   max_context=self.max_context, dtype=cache_dtype, device=self.device)
         self.staging = StepStaging(max_step_tokens, self.device, status=getattr(ops, "page_error", None))
         self.max_step_tokens = max_step_tokens
+        # where the sampler leaves its tokens on the device, if the kernel set has such a place: an entry may
+        # take its token from there (StepEntry.feed) instead of from the host
+        self.fed_from = getattr(ops, "token_out", None)
         # decode steps (one token per entry) are captured once per batch size and key-range
         # split, and replayed: their hundreds of small launches would otherwise be bound by
         # the host
@@ -179,6 +182,8 @@ class Model:
                                      f"{e.start_pos + len(e.tokens) - 1}")
         self.cache.sync()
         step = self.staging.pack(entries, self.spec.vocab_size, self.spec.max_positions)
+        if step.n_fed and self.fed_from is None:
+            raise ModelError("an entry's token is fed from the sampler's output, but this kernel set keeps none")
         step.record = record
         step.attention_splits = attention_splits
         if step.n_tokens == len(entries):
@@ -234,7 +239,10 @@ class Model:
         ops, spec = self.ops, self.spec
         T = step.n_tokens
         h = torch.empty((T, spec.hidden_size), dtype=torch.float32, device=self.device)
-        ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
+        if self.fed_from is not None:
+            ops.embed(step.ids, self.embed_table, h, spec.embed_scale, fed_rows=step.fed_rows, fed_from=self.fed_from)
+        else:
+            ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
         carry = None     # an addition to h that a layer left for the next norm to apply
         for i, call in enumerate(self.order):
             layer = self.layers[call.layer]
@@ -248,6 +256,11 @@ class Model:
             x, _ = run_norm(self.final_norm, h, (wdt,), carry, row_index=step.want_rows)
             ops.gemm(x[wdt], self.head_weight, logits, bias=self.head_bias)
         return logits
+
+    def wait_uploads(self):
+        """Block until the last step's block tables and batch have been copied to the device (and everything
+        enqueued before them has run): after this the host may change the tables for the next step."""
+        self.staging.wait_uploaded()
 
     def check_status(self, flags=None):
         """Raise if a kernel met a position without a page or gave up a bounded wait.  ``flags``: the two

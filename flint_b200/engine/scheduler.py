@@ -30,6 +30,7 @@ from ..csrc import runtime as rt
 from ..sampling.params import SamplingParams, SplitMix64
 
 WAITING, RUNNING, FINISHED, FAILED = "waiting", "running", "finished", "failed"
+UNREAD = -1        # a sampled token that was committed before the host has read its value
 
 
 @dataclass(eq=False)
@@ -50,6 +51,7 @@ class Request:
     preemptions: int = 0
     prefill_tokens: int = 0
     decode_tokens: int = 0
+    n_unread: int = 0          # the last n_unread entries of ``generated`` are placeholders (UNREAD)
 
     @property
     def tokens(self):
@@ -186,8 +188,9 @@ class Scheduler:
 
     # ------------------------------------------------------------------ after the step
     def commit(self, portions, sampled):
-        """``sampled``: one token per portion that wanted logits, in order.  Returns the
-        list of (request, token) emitted in this step."""
+        """``sampled``: one token per portion that wanted logits, in order; ``UNREAD`` for a token whose
+        value is still on the device (everything but the stop set is decided without it; ``resolve``
+        brings the value later).  Returns the list of (request, token) emitted in this step."""
         flat = []
         for p in portions:
             self._push_stop(p.request)
@@ -200,6 +203,8 @@ class Scheduler:
         for i in range(n):
             req, token = self._reqs[emitted[2 * i]], emitted[2 * i + 1]
             req.generated.append(token)
+            if token == UNREAD:
+                req.n_unread += 1
             out.append((req, token))
         self._pull_touched()
         for p in portions:
@@ -211,7 +216,32 @@ class Scheduler:
         if len(self._reqs) > 4096:
             self._reqs = {h: r for h, r in self._reqs.items() if r.state in (WAITING, RUNNING)}
 
+    def resolve(self, req, token) -> bool:
+        """The value of the request's oldest unread token.  True: it is the request's next token.  False: it
+        is a stop token (the request ends before it; what ran after it is void), or the request has ended
+        at an earlier token or was aborted and the value is dropped."""
+        self._push_stop(req)
+        rc = rt.checked(self._lib.flint_rt_sched_resolve(self._h, req._handle, int(token)))
+        if rc == 0:
+            req.generated[len(req.generated) - req.n_unread] = int(token)
+            req.n_unread -= 1
+            return True
+        if rc == 1:
+            del req.generated[len(req.generated) - req.n_unread:]
+            req.n_unread = 0
+            self._pull_touched()
+            self._pull(req)
+        return False
+
+    def steady(self) -> bool:
+        """Nothing waits, every running request has exactly its next token left to run, and pages for one
+        more token of each are free: the next step can be planned before the last one's tokens are read."""
+        return bool(self._lib.flint_rt_sched_steady(self._h))
+
     def abort(self, req):
+        if req.n_unread:
+            del req.generated[len(req.generated) - req.n_unread:]
+            req.n_unread = 0
         rt.checked(self._lib.flint_rt_sched_abort(self._h, req._handle))
         self._pull_touched()
         self._pull(req)

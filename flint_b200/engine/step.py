@@ -34,6 +34,7 @@ class StepEntry:
     start_pos: int         # position of tokens[0] in the request
     tokens: list           # token ids this step brings
     want: list = field(default_factory=list)   # indices into tokens whose logits are wanted
+    feed: int = -1         # >= 0: tokens[0] is not known on the host yet; it is this place of the sampler's last output
 
 
 @dataclass
@@ -57,6 +58,8 @@ class StepContext:
     other_rows: torch.Tensor = None
     n_other_rows: int = 0
     attention_splits: tuple | None = None
+    fed_rows: torch.Tensor = None  # [T] int32: the place in the sampler's last output that holds a row's token, or -1
+    n_fed: int = 0
     even_lengths: bool = False  # a decode batch whose requests are about equally long (set by the caller)
     record: dict | None = None  # filled by parts when a test asks for internals
 
@@ -68,7 +71,7 @@ class StepStaging:
         self.max_tokens = int(max_tokens)
         self.device = torch.device(device)
         self.max_tiles = self.max_tokens // 8 + 16
-        n = 5 * self.max_tokens + 4 * self.max_tiles
+        n = 6 * self.max_tokens + 4 * self.max_tiles
         self.host = torch.zeros(n, dtype=torch.int32)
         if self.device.type == "cuda":
             self.host = self.host.pin_memory()
@@ -79,9 +82,13 @@ class StepStaging:
         self._in_flight = False
         self._lib = rt.lib()
 
-    def pack(self, entries, vocab_size: int, max_positions: int, padded_tokens: int | None = None) -> StepContext:
-        """Flatten, validate and upload.  ``padded_tokens`` fixes the device-side row
-        count (for a captured graph of a given size)."""
+    def wait_uploaded(self):
+        """Block until the last upload (and everything enqueued before it) has run."""
+        if self._in_flight:
+            self._copied.synchronize()
+
+    def pack(self, entries, vocab_size: int, max_positions: int) -> StepContext:
+        """Flatten, validate and upload."""
         n_entries = len(entries)
         if n_entries == 0:
             raise ModelError("a step needs at least one token")
@@ -94,7 +101,7 @@ class StepStaging:
         except (TypeError, ValueError, OverflowError) as err:
             raise ModelError(f"token ids and wanted places must be integers: {err}") from None
         starts = (c_int * n_entries)()
-        meta = (c_int * 5)()
+        meta = (c_int * 6)()
         M = self.max_tokens
         if self._in_flight:          # the last upload must have left the pinned buffer
             self._copied.synchronize()
@@ -103,9 +110,9 @@ class StepStaging:
         rt.checked(self._lib.flint_rt_pack_step(
             n_entries, rt.ints([e.slot for e in entries]), rt.ints([e.start_pos for e in entries]),
             rt.ints([len(e.tokens) for e in entries]), rt.ints([len(e.want) for e in entries]), tok_arr, want_arr,
-            int(vocab_size), int(max_positions), M, self.max_tiles, TILE_ROWS, TILE_MIN_ROWS, 4096,
-            self.host.data_ptr(), starts, meta))
-        T, R, n_tiles, n_others, max_kv = meta
+            rt.ints([e.feed for e in entries]), int(vocab_size), int(max_positions), M, self.max_tiles, TILE_ROWS,
+            TILE_MIN_ROWS, 4096, self.host.data_ptr(), starts, meta))
+        T, R, n_tiles, n_others, max_kv, n_fed = meta
         starts = list(starts)
         self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
@@ -116,4 +123,5 @@ class StepStaging:
                            want_rows=d[3 * M:3 * M + R], n_want=R, max_kv_len=max_kv, status=self.status,
                            entries=list(entries), entry_start=starts,
                            tiles=d[5 * M:5 * M + 4 * n_tiles].view(-1, 4), n_tiles=n_tiles,
-                           other_rows=d[4 * M:4 * M + n_others], n_other_rows=n_others)
+                           other_rows=d[4 * M:4 * M + n_others], n_other_rows=n_others,
+                           fed_rows=d[5 * M + 4 * self.max_tiles:5 * M + 4 * self.max_tiles + T], n_fed=n_fed)

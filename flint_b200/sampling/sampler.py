@@ -16,42 +16,56 @@ MAX_CONTEXT = 64
 
 
 class BatchSampler:
+    """``launch`` enqueues the sampling of a step and the copy of its tokens to the host and returns a
+    ticket; ``read`` waits for that copy and returns the tokens.  Two steps may be in flight (the host
+    buffers alternate), so a caller can enqueue the next step before it reads this one's tokens.
+    ``sample`` is the two in one."""
+
     def __init__(self, ops, device, max_rows: int, max_context: int = MAX_CONTEXT):
         self.ops = ops
         self.device = torch.device(device)
         self.max_rows = max_rows
         self.max_context = max_context
-        pin = self.device.type == "cuda"
-        self._params_host = torch.zeros((max_rows, 8), dtype=torch.float32, pin_memory=pin)
-        self._ctx_host = torch.full((max_rows, max_context), -1, dtype=torch.int32, pin_memory=pin)
+        cuda = self.device.type == "cuda"
+        self._params_host = [torch.zeros((max_rows, 8), dtype=torch.float32, pin_memory=cuda) for _ in range(2)]
+        self._ctx_host = [torch.full((max_rows, max_context), -1, dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
         self._params = torch.zeros((max_rows, 8), dtype=torch.float32, device=self.device)
         self._ctx = torch.full((max_rows, max_context), -1, dtype=torch.int32, device=self.device)
         # the tokens land beside the kernels' error flags when the kernel set keeps such a buffer: one copy
-        # to the host then brings both
+        # to the host then brings both, and the next step can take its tokens from there on the device
         self._readback = getattr(ops, "readback", None)
         if self._readback is not None and max_rows <= ops.MAX_TOKEN_ROWS:
             self._out = ops.token_out[:max_rows]
-            self._host = torch.zeros(2 + max_rows, dtype=torch.int32, pin_memory=pin)
         else:
             self._readback = None
             self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-            self._host = torch.zeros(2 + max_rows, dtype=torch.int32, pin_memory=pin)
+        self._host = [torch.zeros(2 + max_rows, dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
+        self._done = [torch.cuda.Event() if cuda else None for _ in range(2)]
+        self._rows = [0, 0]
+        self._next = 0
         self.last_flags = (0, 0)          # (tensor-core error, page error) as of the last read
         self._work = None
 
-    def sample(self, logits: torch.Tensor, rows):
-        """``rows``: one (SamplingParams, generator, generated_tokens) per logits row.
-        Returns a list of token ids (host)."""
+    @property
+    def feeds_next_step(self) -> bool:
+        """The tokens stay on the device where the model's embedding can take them (StepEntry.feed)."""
+        return self._readback is not None
+
+    def launch(self, logits: torch.Tensor, rows) -> int:
+        """``rows``: one (SamplingParams, generator, generated_tokens) per logits row.  Returns a ticket."""
         R = logits.shape[0]
-        if R == 0:
-            return []
         assert R == len(rows) <= self.max_rows
+        ticket = self._next
+        self._next ^= 1
+        self._rows[ticket] = R
+        if R == 0:
+            return ticket
         all_greedy = all(p.temperature <= 0 and p.repeat_penalty == 1.0 for p, _, _ in rows)
         out = self._out[:R]
         if all_greedy:
             self.ops.argmax(logits, out)
         else:
-            ph, ch = self._params_host, self._ctx_host
+            ph, ch = self._params_host[ticket], self._ctx_host[ticket]
             for i, (p, rng, generated) in enumerate(rows):
                 n_ctx = 0
                 if p.repeat_penalty != 1.0 and p.repeat_last_n > 0 and generated:
@@ -67,11 +81,28 @@ class BatchSampler:
                 self._work = torch.empty((max(R, min(self.max_rows, 64)), logits.shape[1]), dtype=torch.float32,
                                          device=self.device)
             self.ops.sample(logits, self._params[:R], self._ctx[:R], self._work[:R], out)
-        # device -> host read of the step's result (synchronises)
+        # device -> host copy of the step's result, read (and waited for) by read()
+        host = self._host[ticket]
         if self._readback is not None:
-            self._host[:2 + R].copy_(self._readback[:2 + R])
-            got = self._host[:2 + R].tolist()
+            host[:2 + R].copy_(self._readback[:2 + R], non_blocking=True)
+        else:
+            host[2:2 + R].copy_(out, non_blocking=True)
+        if self._done[ticket] is not None:
+            self._done[ticket].record()
+        return ticket
+
+    def read(self, ticket: int):
+        """The tokens of a launched step (host list).  Blocks until they have arrived."""
+        R = self._rows[ticket]
+        if R == 0:
+            return []
+        if self._done[ticket] is not None:
+            self._done[ticket].synchronize()
+        got = self._host[ticket][:2 + R].tolist()
+        if self._readback is not None:
             self.last_flags = (got[0], got[1])
-            return got[2:]
-        self._host[2:2 + R].copy_(out)
-        return self._host[2:2 + R].tolist()
+        return got[2:]
+
+    def sample(self, logits: torch.Tensor, rows):
+        """Returns a list of token ids (host)."""
+        return self.read(self.launch(logits, rows))

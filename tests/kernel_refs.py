@@ -26,10 +26,18 @@ class RefOps:
     def __init__(self, compute_dtype=torch.float32):
         self.cd = compute_dtype     # float64 gives an oracle for kernel tests
         self.launches = 0
+        # the sampled tokens beside the two error flags, as the device kernels keep them
+        self.MAX_TOKEN_ROWS = 256
+        self.readback = torch.zeros(2 + self.MAX_TOKEN_ROWS, dtype=torch.int32)
+        self.tc_error, self.page_error, self.token_out = self.readback[0:1], self.readback[1:2], self.readback[2:]
 
     # ------------------------------------------------------------------ row-wise
-    def embed(self, ids, table, out, scale=1.0):
-        out.copy_((table[ids.long()].to(self.cd) * scale).to(out.dtype))
+    def embed(self, ids, table, out, scale=1.0, fed_rows=None, fed_from=None):
+        ids = ids.long()
+        if fed_rows is not None:
+            fed = fed_rows.long()
+            ids = torch.where(fed >= 0, fed_from.to(fed.device).long()[fed.clamp(min=0)], ids)
+        out.copy_((table[ids].to(self.cd) * scale).to(out.dtype))
 
     def norm(self, x, gamma, beta, eps, mode, out_f32=None, out_bf16=None, row_index=None):
         xs = x[row_index.long()] if row_index is not None else x

@@ -123,3 +123,51 @@ def test_session_interface(setup):
         eng.create([], 4)
     with pytest.raises(ModelError, match="tokenizer"):
         eng.create("hello", 4)
+
+
+def test_running_one_step_ahead_changes_nothing_but_the_order_of_work(setup):
+    """In steady decoding the engine enqueues a step before it has read the tokens of the step before.  The
+    tokens, the stop decisions (a stop token is found one step late: what ran after it is void) and the
+    pages are the same as when every step waits for its tokens."""
+    which, folder, reqs, plain = setup
+    prompts = [t[:n] for t, n in zip(reqs.values(), (7, 13, 32))]
+
+    def engine(run_ahead, **kw):
+        m = load_model(folder, dtype="float32", device="cpu", ops=RefOps(), page_size=16, n_pages=16, max_slots=4,
+                       max_step_tokens=24)
+        return m, Engine(m, SamplingParams.greedy(), prefill_chunk=16, run_ahead=run_ahead, **kw)
+
+    m, eng = engine(False)
+    base = eng.generate(prompts, 12)
+    assert eng.steps_ahead == 0
+    m, eng = engine(True)
+    assert eng.generate(prompts, 12) == base and eng.steps_ahead >= 8
+    assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
+    # a stop token in the middle of one request's text: found while the next step is already on its way
+    longest = max(base, key=len)
+    assert len(longest) >= 6
+    stop = longest[4]
+    cut = [o[:o.index(stop)] if stop in o else o for o in base]
+    for run_ahead in (False, True):
+        m, eng = engine(run_ahead, stop=(stop,))
+        assert eng.generate(prompts, 12) == cut
+        assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
+        m.cache.check()
+    # sessions: pieces arrive one call late at most, none is lost, a session closed in flight leaves nothing behind
+    m, eng = engine(True)
+    a = eng.create(prompts[0], 6)
+    b = eng.create(prompts[1], 9)
+    got = {a: [], b: []}
+    calls = 0
+    while not (eng.finished(a) and eng.finished(b)):
+        eng.step()
+        calls += 1
+        for sid in (a, b):
+            got[sid] += [p.token for p in eng.poll(sid)]
+        if calls == 4:
+            eng.close(b)            # b is decoding, its last token unread
+    assert got[a] == base[0][:6] and got[b] == base[1][:len(got[b])] and len(got[b]) < 9
+    while eng.has_work():
+        eng.step()
+    eng.close(a)
+    assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4

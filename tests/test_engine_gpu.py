@@ -273,6 +273,31 @@ def test_temperature_sampling_is_reproducible_and_follows_the_host_sampler(setup
             toks.append(tok)
 
 
+def test_running_one_step_ahead_gives_the_same_tokens(setup):
+    """Steady decoding enqueues a step before the host has read the tokens of the step before (the device
+    feeds them to the embedding).  Tokens, stop decisions and pages are those of waiting for every step,
+    with greedy and with temperature sampling; a repeat penalty needs the values on the host and waits."""
+    which, dtype, folder, reqs, plain = setup
+    m = load_model(folder, dtype=dtype, page_size=16, n_pages=32, max_slots=4, max_step_tokens=48)
+    prompts = [list(reqs["r1"])[:9], list(reqs["r3"])[:30], list(reqs["r0"])[:5]]
+    for params in (SamplingParams.greedy(), SamplingParams(temperature=0.8, top_k=20, top_p=0.8)):
+        wait = Engine(m, params, seed=5, prefill_chunk=16, run_ahead=False)
+        base = wait.generate(prompts, 40)
+        assert wait.steps_ahead == 0
+        ahead = Engine(m, params, seed=5, prefill_chunk=16)
+        assert ahead.run_ahead and ahead.generate(prompts, 40) == base and ahead.steps_ahead >= 20
+        longest = max(base, key=len)
+        stop = longest[len(longest) // 2]
+        cut = [o[:o.index(stop)] if stop in o else o for o in base]
+        assert Engine(m, params, seed=5, prefill_chunk=16, stop=(stop,)).generate(prompts, 40) == cut
+        assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
+        m.cache.check()
+    pen = SamplingParams(temperature=0.0, repeat_penalty=1.3)
+    eng = Engine(m, pen, prefill_chunk=16)
+    out = eng.generate(prompts[:2], 12)
+    assert eng.steps_ahead == 0 and out == Engine(m, pen, prefill_chunk=16, run_ahead=False).generate(prompts[:2], 12)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_as_a_program(tmp_path, dtype):
     """bin/trace_run in a process of its own, fed a mixed trace over standard input."""

@@ -193,3 +193,68 @@ def test_random_workloads_keep_every_promise():
             if r.state == FAILED:
                 assert r.error
         assert cache.free_pages() == n_pages and cache.free_slots == slots, seed
+
+
+def test_tokens_committed_unread_are_resolved_later():
+    """A step's tokens may be committed before the host knows their values (everything but the stop set is
+    decided without them); the values come one step later.  A stop token found then ends the request before
+    it and voids what ran after it; the outcome is the one of committing the values at once."""
+    from flint_b200.engine.scheduler import UNREAD
+
+    def next_scripted(n_tokens):
+        """Scripted model: the token sampled after a request's first n_tokens tokens; 555 is a stop token."""
+        return 555 if n_tokens == 9 else 100 + n_tokens
+
+    def drive(ahead):
+        cache, s = setup()
+        r = req(0, 6, max_tokens=8, stop=(555,))
+        q = req(1, 5, max_tokens=2)             # ends by length while its last token is unread
+        s.add(r)
+        s.add(q)
+        pending = None                          # (requests, tokens) of the step whose values are not read yet
+        for _ in range(40):
+            if not s.has_work():
+                break
+            if pending and not (ahead and s.steady()):
+                for x, t in zip(*pending):
+                    s.resolve(x, t)
+                pending = None
+            portions = s.plan()
+            if portions:
+                sampled = [p.request for p in portions if p.wants_logits]
+                # what the device samples; the host learns it one step later
+                values = [next_scripted(x.n_tokens) for x in sampled]
+                s.commit(portions, [UNREAD] * len(sampled))
+            cache.check()
+            if pending:
+                for x, t in zip(*pending):
+                    s.resolve(x, t)
+                pending = None
+            if portions:
+                pending = (sampled, values)
+        if pending:
+            for x, t in zip(*pending):
+                s.resolve(x, t)
+        cache.check()
+        assert not s.has_work() and cache.free_slots == 4 and cache.free_pages() == 16
+        return r, q
+
+    for ahead in (False, True):
+        r, q = drive(ahead)
+        assert r.generated == [106, 107, 108] and r.finish_reason == "stop" and r.n_unread == 0, (ahead, r.generated)
+        assert q.generated == [105, 106] and q.finish_reason == "length" and q.n_unread == 0
+    # a stop token as the last allowed token: the request had ended by length, the reason becomes "stop"
+    cache, s = setup()
+    r = req(0, 4, max_tokens=1, stop=(7,))
+    s.add(r)
+    s.commit(s.plan(), [UNREAD])
+    assert r.state == FINISHED and r.finish_reason == "length" and r.generated == [UNREAD]
+    assert s.resolve(r, 7) is False
+    assert r.generated == [] and r.finish_reason == "stop"
+    assert s.resolve(r, 9) is False              # nothing unread any more: dropped
+    # an aborted request forgets its unread tokens
+    r = req(1, 4, max_tokens=5)
+    s.add(r)
+    s.commit(s.plan(), [UNREAD])
+    s.abort(r)
+    assert r.generated == [] and s.resolve(r, 3) is False and cache.free_pages() == 16
