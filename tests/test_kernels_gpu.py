@@ -66,15 +66,18 @@ def test_norm(ops, ref, mode, bias, T, H):
 
 @pytest.mark.parametrize("T,H,E,wd", [(1, 4096, 16, torch.bfloat16), (9, 96, 6, torch.float32), (33, 64, 4, torch.bfloat16),
                                       (5, 1000, 7, torch.float32), (3, 8192, 16, torch.bfloat16), (2, 2052, 3, torch.float32),
-                                      (301, 4096, 16, torch.bfloat16), (258, 96, 6, torch.float32)])
+                                      (301, 4096, 16, torch.bfloat16), (258, 96, 6, torch.float32),
+                                      (4, 16384, 40, torch.bfloat16), (8, 4096, 64, torch.float32),
+                                      (16, 1536, 16, torch.bfloat16)])
 @pytest.mark.parametrize("mode", ["layer", "rms"])
 def test_row_norm_with_pending_additions_and_router(ops, ref, T, H, E, wd, mode):
     """The fused row kernel beside the separate references: split-K partial sums + bias, the gated sum
-    of two expert rows, the norm, and the routing of the normalised row."""
+    of two expert rows, the norm, and the routing of the normalised row.  Up to 16 rows of at least 512
+    values are shared by a cluster of blocks each; more rows, or narrower ones, get a block each."""
     from flint_b200.parts.base import Pending, RouterRequest
     x0 = rnd(T, H, scale=2.0) + 0.5
     gamma, beta = 1 + rnd(H, seed=1) * 0.1, (rnd(H, seed=2) * 0.1 if mode == "layer" else None)
-    partials, bias = rnd(3, T, H, seed=3), rnd(H, seed=4)
+    partials, bias = rnd(13 if H == 4096 else 3, T, H, seed=3), rnd(H, seed=4)
     y = rnd(2 * T, H, seed=5)
     row_of = torch.randperm(2 * T, generator=torch.Generator().manual_seed(6)).to(torch.int32).view(T, 2)
     gts = torch.rand(T, 2)
