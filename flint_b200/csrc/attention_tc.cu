@@ -388,9 +388,58 @@ struct DecodeParams {
   __nv_bfloat16* out;
   float* scratch;
   int* error_flag;
+  int* arrivals;     // one counter per (row, kv head, chunk of query heads), zero between launches; null: the
+                     // pieces of an item are merged by a kernel of its own
   int n_rows, max_pages, page_size, nq, nkv, hd, window, split_keys, n_splits, g_chunks;
   float scale;
 };
+
+// Merge records [0, n_rec) of the ng query heads of one item, by a whole block of 128 threads:
+// out = sum_s e^{m_s-M} o_s / sum_s e^{m_s-M} l_s, the records in order.  A thread takes pairs of output
+// dims and fetches eight records at a time, all loads in flight together.  The records were written by other
+// blocks: they are read past the first-level cache.
+__device__ __forceinline__ void merge_records(const DecodeParams& p, int ti, int t, int h0, int ng, int n_rec) {
+  const int hd = p.hd, rec = hd + 2, cols = hd >> 1;
+  for (int pair = threadIdx.x; pair < ng * cols; pair += 128) {
+    const int g = pair / cols, d = (pair % cols) * 2;
+    const float* base = p.scratch + ((size_t)ti * p.nq + h0 + g) * p.n_splits * rec;
+    float M = -INFINITY, L = 0.f;
+    float2 acc = make_float2(0.f, 0.f);
+    for (int s0 = 0; s0 < n_rec; s0 += 8) {
+      float ms[8], ls[8];
+      float2 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const bool in = s0 + u < n_rec;
+        const float* r = base + (size_t)(in ? s0 + u : 0) * rec;
+        ms[u] = in ? __ldcg(r + hd) : -INFINITY;
+        ls[u] = in ? __ldcg(r + hd + 1) : 0.f;
+        v[u] = in ? __ldcg(reinterpret_cast<const float2*>(r + d)) : make_float2(0.f, 0.f);
+      }
+      float Mn = M;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) Mn = fmaxf(Mn, ms[u]);
+      if (Mn > -INFINITY) {
+        const float keep = M > -INFINITY ? expf(M - Mn) : 0.f;      // what was merged so far, on the new scale
+        L *= keep;
+        acc.x *= keep;
+        acc.y *= keep;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (ms[u] > -INFINITY) {                                   // an empty record is left out
+            const float w = expf(ms[u] - Mn);
+            L += w * ls[u];
+            acc.x += w * v[u].x;
+            acc.y += w * v[u].y;
+          }
+        M = Mn;
+      }
+    }
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    *reinterpret_cast<__nv_bfloat162*>(p.out + ((size_t)t * p.nq + h0 + g) * hd + d) =
+        __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+  }
+}
 
 template <int HD>
 __global__ void __launch_bounds__(128)
@@ -542,26 +591,110 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       }
     }
   }
-  if (failed) {
-    if (lane == 0) atomicExch(p.error_flag, 1);
-    return;
-  }
+  if (failed && lane == 0) atomicExch(p.error_flag, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 2);
-  if (gid >= ng) return;
   if (p.n_splits == 1) {
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
-    __nv_bfloat16* dst = p.out + ((size_t)t * nq + h0 + gid) * hd + tid4 * 2;
+    if (gid < ng && !failed) {
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)t * nq + h0 + gid) * hd + tid4 * 2;
 #pragma unroll
-    for (int db = 0; db < DB; ++db)
-      if (db < db_n) *reinterpret_cast<__nv_bfloat162*>(dst + db * 8) = __floats2bfloat162_rn(o[db][0] * inv, o[db][1] * inv);
-  } else {
-    float* dst = p.scratch + (((size_t)ti * nq + h0 + gid) * p.n_splits + split) * (hd + 2);
+      for (int db = 0; db < DB; ++db)
+        if (db < db_n) *reinterpret_cast<__nv_bfloat162*>(dst + db * 8) = __floats2bfloat162_rn(o[db][0] * inv, o[db][1] * inv);
+    }
+    return;
+  }
+  if (failed) {            // an empty record: the merge leaves it out
+    m = -INFINITY;
+    l = 0.f;
+  }
+  const int rec = hd + 2;
+  const int group = (int)(item / p.n_splits);
+  if (!p.arrivals) {
+    // one record per warp; a kernel of its own merges them
+    if (gid < ng) {
+      float* dst = p.scratch + (((size_t)ti * nq + h0 + gid) * p.n_splits + split) * rec;
+#pragma unroll
+      for (int db = 0; db < DB; ++db)
+        if (db < db_n) { dst[db * 8 + tid4 * 2] = o[db][0]; dst[db * 8 + tid4 * 2 + 1] = o[db][1]; }
+      if (tid4 == 0) { dst[hd] = m; dst[hd + 1] = l; }
+    }
+    return;
+  }
+  // The splits of an item come in fours, and the four warps of this block hold four consecutive splits of one
+  // item: they merge through shared memory first, each warp taking two of the eight query heads, so that a
+  // block leaves one record (or, with four splits in all, the result).
+  __shared__ int s_failed[4];
+  __shared__ int s_last;
+  float* mine = reinterpret_cast<float*>(smem_raw + (ring - smem_u32(smem_raw)));    // this warp's ring, now free
+  if (lane == 0) s_failed[warp] = failed;
+  if (gid < ng && !failed) {
+    float* dst = mine + gid * rec;
 #pragma unroll
     for (int db = 0; db < DB; ++db)
       if (db < db_n) { dst[db * 8 + tid4 * 2] = o[db][0]; dst[db * 8 + tid4 * 2 + 1] = o[db][1]; }
     if (tid4 == 0) { dst[hd] = m; dst[hd + 1] = l; }
   }
+  __syncthreads();
+  const int n_rec = p.n_splits >> 2, rec_index = split >> 2;
+  for (int g = warp * 2; g < min(warp * 2 + 2, ng); ++g) {
+    const float* r4[4];
+    float ms[4], M = -INFINITY;
+#pragma unroll
+    for (int w2 = 0; w2 < 4; ++w2) {
+      r4[w2] = reinterpret_cast<const float*>(smem_raw + (ring - smem_u32(smem_raw)) + (w2 - warp) * (DSTAGES * DSTAGE_BYTES)) + g * rec;
+      ms[w2] = s_failed[w2] ? -INFINITY : r4[w2][hd];
+      M = fmaxf(M, ms[w2]);
+    }
+    float L = 0.f;
+    float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int w2 = 0; w2 < 4; ++w2) {
+      if (ms[w2] > -INFINITY) {
+        const float wgt = expf(ms[w2] - M);
+        L += wgt * r4[w2][hd + 1];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int d = lane * 2 + 64 * i;
+          if (d < hd) {
+            const float2 v = *reinterpret_cast<const float2*>(r4[w2] + d);
+            acc[i].x += wgt * v.x;
+            acc[i].y += wgt * v.y;
+          }
+        }
+      }
+    }
+    if (n_rec == 1) {
+      const float inv = L > 0.f ? 1.0f / L : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)t * nq + h0 + g) * hd;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int d = lane * 2 + 64 * i;
+        if (d < hd) *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(acc[i].x * inv, acc[i].y * inv);
+      }
+    } else {
+      float* dst = p.scratch + (((size_t)ti * nq + h0 + g) * p.n_splits + rec_index) * rec;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int d = lane * 2 + 64 * i;
+        if (d < hd) *reinterpret_cast<float2*>(dst + d) = acc[i];
+      }
+      if (lane == 0) { dst[hd] = M; dst[hd + 1] = L; }
+    }
+  }
+  if (n_rec == 1) return;
+  // the block that arrives last of the item's blocks merges their records
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int prev = atomicAdd(p.arrivals + group, 1);
+    s_last = prev == n_rec - 1;
+    if (s_last) p.arrivals[group] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  merge_records(p, ti, t, h0, ng, n_rec);
 }
 
 // The same kernel with the work cut stream fashion: the 16-key steps of all (row, kv head, chunk of query
@@ -836,11 +969,14 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
 
 // Decode rows (or any rows, one at a time) over the paged bfloat16 cache: the contract of
 // flint_paged_attention with bfloat16 q/out, page sizes that are multiples of 16, head sizes up to 128.
+// arrivals (may be null): n_arrivals counters, zero before the first launch and left zero by every launch;
+// given enough of them and splits in fours, the splits of a row are merged inside this kernel.
 extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                          const int* block_table, int max_pages, int page_size, const int* pos,
                                          const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
                                          float scale, int split_keys, int n_splits, float* scratch,
-                                         const int* row_list, int* error_flag, cudaStream_t stream) {
+                                         const int* row_list, int* error_flag, int* arrivals, int n_arrivals,
+                                         cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_tc: head size %d (multiples of 16 up to 128)", hd);
   if (nkv <= 0 || nq % nkv) return fail("attention_decode_tc: %d query heads do not divide into %d kv heads", nq, nkv);
@@ -860,6 +996,9 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   p.window = window; p.split_keys = split_keys; p.n_splits = n_splits;
   p.g_chunks = (nq / nkv + 7) / 8;
   p.scale = scale;
+  // with splits in fours and a counter for every (row, kv head, chunk of query heads) the pieces are merged by
+  // the block that finishes last; else by a kernel of its own
+  p.arrivals = (arrivals && n_splits % 4 == 0 && (long long)T * nkv * p.g_chunks <= n_arrivals) ? arrivals : nullptr;
   const long long items = (long long)T * nkv * p.g_chunks * n_splits;
   const long long blocks = (items + 3) / 4;
   if (blocks > 0x7fffffffLL) return fail("attention_decode_tc: too many work items");
@@ -873,7 +1012,7 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
   else launch_pdl(attention_decode_tc_kernel<128>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
   rc = check_launch("attention_decode_tc");
-  if (rc || n_splits == 1) return rc;
+  if (rc || n_splits == 1 || p.arrivals) return rc;
   launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
              dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
   return check_launch("attention_combine");
@@ -907,6 +1046,7 @@ extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache,
   p.window = window; p.split_keys = 0; p.n_splits = n_slices;
   p.g_chunks = (nq / nkv + 7) / 8;
   p.scale = scale;
+  p.arrivals = nullptr;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;

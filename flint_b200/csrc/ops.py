@@ -79,6 +79,9 @@ class CudaOps:
         self.tc_error = self.readback[0:1]
         self.page_error = self.readback[1:2]
         self.token_out = self.readback[2:]
+        # arrival counters of the decode attention kernels (one per row, kv head and chunk of query heads): zero
+        # between launches; a launch that gave up a wait may leave some set, so they are cleared with its flag
+        self.attention_arrivals = torch.zeros(1 << 15, dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ plumbing
     def _fn(self, module, name):
@@ -471,7 +474,13 @@ class CudaOps:
                 return "stream", span, self._stream_slices(base8)
             n = max(1, min(span // 64, 1184 // base8))
             keys = -(-(-(-span // n)) // 16) * 16
-            return "tma", keys, -(-span // keys)
+            n = -(-span // keys)
+            if n > 4 and n % 4:
+                # splits in fours: the four warps of a block then hold one row's splits and merge them themselves
+                # (the kernel divides a row's keys evenly over the splits; the last one may stay empty)
+                n = n // 4 * 4
+                keys = -(-(-(-span // n)) // 16) * 16
+            return "tma", keys, n
         if T <= 256:
             n = max(1, min(-(-span // 128), -(-1184 // base)))
             keys = -(-(-(-span // n)) // 128) * 128
@@ -518,9 +527,11 @@ class CudaOps:
                   c_int(hd), c_int(window), c_float(scale), _ptr(self.tc_error))
 
     def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,
-                        kernel=None, rows=None, ragged=True):
+                        kernel=None, rows=None, ragged=True, merge_in_kernel=True):
         """rows: int32 list of the batch rows to compute (default: all).  ragged: the rows' key ranges may
-        differ much in length (False: a decode batch whose requests are about equally long)."""
+        differ much in length (False: a decode batch whose requests are about equally long).
+        merge_in_kernel (the tensor-core decode kernel with splits in fours): the pieces of a row's key range
+        are merged by the block that finishes last; False: by a kernel of its own."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
@@ -544,6 +555,7 @@ class CudaOps:
         scratch = None
         if n_splits > 1:
             scratch = torch.empty(T * nq * n_splits * (hd + 2), dtype=torch.float32, device=q.device)
+        arrivals = self.attention_arrivals if merge_in_kernel else None
         if kernel == "stream":
             if auto_kernel != "stream":
                 n_splits = self._stream_slices(T * nkv * -(-(nq // nkv) // 8))
@@ -560,7 +572,8 @@ class CudaOps:
                              c_int(cache.k.shape[0]), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
                              c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
                              c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
-                             _ptr(scratch), _ptr(rows), _ptr(self.tc_error))
+                             _ptr(scratch), _ptr(rows), _ptr(self.tc_error), _ptr(arrivals),
+                             c_int(arrivals.numel() if arrivals is not None else 0))
         fn = {"warp": "flint_paged_attention", "block": "flint_paged_attention_block"}[kernel]
         self._run("attention", fn, _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),

@@ -274,6 +274,9 @@ class Model:
             raise ModelError("a kernel met a position whose page was not allocated")
         if flags[0]:
             tc.zero_()
+            counters = getattr(self.ops, "attention_arrivals", None)
+            if counters is not None:
+                counters.zero_()          # a kernel that gave up may have left an arrival uncounted
             raise ModelError("a tensor-core kernel gave up waiting for its operands")
 
 

@@ -523,6 +523,52 @@ def test_attention_decode_stream_cuts_keys_into_equal_runs(ops, ref, nq, nkv, hd
         close(out2[0::2], exp[0::2], 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("nq,nkv,hd,P,window,lens,splits", [
+    (32, 8, 128, 64, 0, (2048, 2040, 1990, 2047), (128, 16)),     # four warps of a block merge, then the blocks of an item
+    (32, 8, 128, 64, 0, (500, 512), (128, 4)),                    # four splits: the block writes the result itself
+    (8, 1, 64, 16, 0, (300, 20), (64, 5)),                        # splits not in fours: merged by a kernel of its own
+    (32, 8, 128, 64, 0, (4000,), (64, 64)),                       # sixteen records an item: merged eight at a time
+    (6, 2, 80, 16, 0, (333,), (48, 8)),                           # three query heads per kv head, a head size between
+    (5, 5, 128, 32, 100, (400, 90), (32, 4)),                     # one query head per kv head, a window
+    (48, 2, 96, 64, 0, (700, 640, 1), (64, 12)),                  # 24 query heads per kv head: three chunks of eight
+])
+def test_attention_decode_splits_are_merged_by_the_last_to_arrive(ops, ref, nq, nkv, hd, P, window, lens, splits):
+    """The decode kernel with a fixed cut of every row's key range: the pieces of a (row, kv head) are merged
+    inside the kernel when they come in fours (the four warps of a block through shared memory, then the
+    blocks of the item by the one that finishes last), or by a kernel of its own; both give the reference's
+    result, and the arrival counters are zero again after every launch."""
+    g = torch.Generator().manual_seed(len(lens) * 17 + hd + nq)
+    need = [-(-n // P) for n in lens]
+    n_pages = sum(need) + 2
+    k = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    bt = torch.full((len(lens), max(need) + 1), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    o = 0
+    for s_, n in enumerate(need):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    T = len(lens)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slot = torch.arange(T, dtype=torch.int32)
+    q = torch.randn(T, nq * hd, generator=g).to(torch.bfloat16)
+    spec = KVSpec(nkv, hd, window)
+    dv = CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec)
+    scale = 1 / math.sqrt(hd)
+    exp = torch.zeros(T, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, window, scale, max(lens))
+    outs = []
+    for merge_in_kernel in (True, True, False):
+        out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens),
+                            kernel="tma", splits=splits, merge_in_kernel=merge_in_kernel)
+        assert int(ops.tc_error.item()) == 0 and int(ops.attention_arrivals.abs().sum().item()) == 0
+        close(out, exp, 2e-2, 2e-2)
+        outs.append(out.float().cpu())
+    assert torch.equal(outs[0], outs[1])
+    close(outs[0], outs[2].double(), 1e-2, 1e-2)
+
+
 @pytest.mark.parametrize("ramp", [0.02, 0.3])
 def test_attention_prefill_growing_scores(ops, ref, ramp):
     """Keys aligned with the queries and growing with their position: a row's maximum keeps rising, slowly
