@@ -68,7 +68,8 @@ def test_norm(ops, ref, mode, bias, T, H):
                                       (5, 1000, 7, torch.float32), (3, 8192, 16, torch.bfloat16), (2, 2052, 3, torch.float32),
                                       (301, 4096, 16, torch.bfloat16), (258, 96, 6, torch.float32),
                                       (4, 16384, 40, torch.bfloat16), (8, 4096, 64, torch.float32),
-                                      (16, 1536, 16, torch.bfloat16)])
+                                      (16, 1536, 16, torch.bfloat16), (300, 1000, 7, torch.bfloat16),
+                                      (260, 2048, 40, torch.bfloat16), (1030, 4096, 16, torch.bfloat16)])
 @pytest.mark.parametrize("mode", ["layer", "rms"])
 def test_row_norm_with_pending_additions_and_router(ops, ref, T, H, E, wd, mode):
     """The fused row kernel beside the separate references: split-K partial sums + bias, the gated sum
