@@ -379,11 +379,14 @@ def main():
     dec = run_decode(model, cfg, args.batch, args.prompt_tokens, args.steps, warmup, rng)
     clock = clocks.stop()
     e2e = run_e2e(model, cfg, args.batch, args.prompt_tokens, args.steps, warmup, rng)
-    points = {}
+    points, points_frac = {}, {}
     if not args.no_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = round(run_decode(model, cfg, b, args.prompt_tokens, max(8, args.steps // 2), warmup,
-                                                      rng, count_experts=False)["tok_s"], 1)
+            r = run_decode(model, cfg, b, args.prompt_tokens, max(8, args.steps // 2), warmup, rng)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            # the same roofline as the headline's: bytes the step must read over its time, of the copy peak
+            points_frac[f"decode_b{b}"] = round(decode_bytes(cfg, model, r["kv_lens"], r["distinct"]) / (r["ms"] * 1e-3) / 1e9
+                                                / pk["hbm_gbs"], 4)
 
     pre_flops = step_flops(cfg, 2048, range(1, 2049))
     bytes_step = decode_bytes(cfg, model, dec["kv_lens"], dec["distinct"])
@@ -413,6 +416,7 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": bytes_step,
                      "distinct_experts_per_layer": round(sum(dec["distinct"]) / len(dec["distinct"]), 2)},
         "points": points,
+        "points_roofline_frac": points_frac,
         "clocks": clock,
     }
     print(json.dumps(out))

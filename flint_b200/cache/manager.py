@@ -61,12 +61,33 @@ class GroupCache:
         self.storage = torch.zeros((len(self.calls), 2, n, spec.num_kv_heads, P, spec.head_dim),
                                    dtype=dtype, device=device)
         self.block_table = torch.full((max_slots, max_pages_per_request), NO_PAGE, dtype=torch.int32, device=device)
+        # The copy to the device is asynchronous and may run long after it was asked for (behind a whole step
+        # that is still running), while the bookkeeping goes on changing the host mirror for the next step:
+        # the changed rows are therefore copied from a snapshot, two of which alternate.
+        self._cuda = torch.device(device).type == "cuda"
+        if self._cuda:
+            self._snapshots = [torch.empty_like(self._host_table).pin_memory() for _ in range(2)]
+            self._snapshot_sent = [torch.cuda.Event(), torch.cuda.Event()]
+            self._snapshot_used = [False, False]
+            self._next_snapshot = 0
 
     def sync_tables(self):
         """Copy the rows of changed block tables to the device."""
         lo, hi = self.pages.take_dirty()
-        if lo < hi:
-            self.block_table[lo:hi].copy_(self._host_table[lo:hi], non_blocking=True)
+        if lo >= hi:
+            return
+        if not self._cuda:
+            self.block_table[lo:hi].copy_(self._host_table[lo:hi])
+            return
+        i = self._next_snapshot
+        self._next_snapshot ^= 1
+        if self._snapshot_used[i]:
+            self._snapshot_sent[i].synchronize()      # its last copy has left it (two syncs ago: long done)
+        snap = self._snapshots[i]
+        snap[lo:hi].copy_(self._host_table[lo:hi])
+        self.block_table[lo:hi].copy_(snap[lo:hi], non_blocking=True)
+        self._snapshot_sent[i].record()
+        self._snapshot_used[i] = True
 
     def view(self, call_index: int):
         i = self.calls.index(call_index)

@@ -185,7 +185,6 @@ class Engine:
 
     def _land(self, flight) -> int:
         """Read a flight's tokens (waiting for them) and hand them to their sessions."""
-        self.model.wait_uploads()       # the tables of a later step are on the device: they may change now
         tokens = self.sampler.read(flight.ticket)
         if any(self.sampler.last_flags):        # a kernel gave up or met a missing page: do not go on with garbage
             self._void_flights(flight)

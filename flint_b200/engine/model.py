@@ -257,11 +257,6 @@ class Model:
             ops.gemm(x[wdt], self.head_weight, logits, bias=self.head_bias)
         return logits
 
-    def wait_uploads(self):
-        """Block until the last step's block tables and batch have been copied to the device (and everything
-        enqueued before them has run): after this the host may change the tables for the next step."""
-        self.staging.wait_uploaded()
-
     def check_status(self, flags=None):
         """Raise if a kernel met a position without a page or gave up a bounded wait.  ``flags``: the two
         flags (tensor-core error, page error) if the caller has read them already; else they are read here

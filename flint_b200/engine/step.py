@@ -82,11 +82,6 @@ class StepStaging:
         self._in_flight = False
         self._lib = rt.lib()
 
-    def wait_uploaded(self):
-        """Block until the last upload (and everything enqueued before it) has run."""
-        if self._in_flight:
-            self._copied.synchronize()
-
     def pack(self, entries, vocab_size: int, max_positions: int) -> StepContext:
         """Flatten, validate and upload."""
         n_entries = len(entries)

@@ -292,6 +292,32 @@ def test_running_one_step_ahead_gives_the_same_tokens(setup):
         assert Engine(m, params, seed=5, prefill_chunk=16, stop=(stop,)).generate(prompts, 40) == cut
         assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
         m.cache.check()
+    # The copies of a step's batch and block tables run when the device gets to them, which may be a whole step
+    # after they were asked for, while the host already books the next step (pages given back by requests that
+    # end or by the window).  A delay on the device before every step makes that lag certain.
+    plain_step = m.step
+
+    def late_step(entries, **kw):
+        torch.cuda._sleep(3_000_000)
+        return plain_step(entries, **kw)
+    # each request's last step takes a new page (its input token is the first of a page: prompt + n - 2 is a
+    # multiple of the page size), so its table row is on its way to the device when the request ends
+    lengths = [16 - len(prompts[0]) + 2, 48 - len(prompts[1]) + 2, 32 - len(prompts[2]) + 2]
+    base = [Engine(m, SamplingParams.greedy(), prefill_chunk=16, run_ahead=False).generate([p], n)[0]
+            for p, n in zip(prompts, lengths)]
+    m.step = late_step
+    try:
+        eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16)
+        ids = [eng.create(p, n) for p, n in zip(prompts, lengths)]
+        got = {i: [] for i in ids}
+        while eng.has_work():
+            eng.step()
+            for i in ids:
+                got[i] += [piece.token for piece in eng.poll(i)]
+        assert [got[i] for i in ids] == base and eng.steps_ahead >= 10
+    finally:
+        m.step = plain_step
+    assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups)
     pen = SamplingParams(temperature=0.0, repeat_penalty=1.3)
     eng = Engine(m, pen, prefill_chunk=16)
     out = eng.generate(prompts[:2], 12)
