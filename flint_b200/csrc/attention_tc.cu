@@ -391,6 +391,7 @@ struct DecodeParams {
   int* arrivals;     // one counter per (row, kv head, chunk of query heads), zero between launches; null: the
                      // pieces of an item are merged by a kernel of its own
   int n_rows, max_pages, page_size, nq, nkv, hd, window, split_keys, n_splits, g_chunks;
+  int fresh_keys;    // at most this many of a row's newest keys (its own included) are written by the kernel before
   float scale;
 };
 
@@ -452,7 +453,9 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
   pdl_launch();
-  pdl_wait();
+  // Nothing below reads what the kernels before this one write, until pdl_wait(): positions, slots and block
+  // tables come from the host, and of the cache only a row's newest p.fresh_keys keys and values are written
+  // in this step.
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * 4 + warp;
   const long long n_items = (long long)p.n_rows * p.nkv * p.g_chunks * p.n_splits;
@@ -490,16 +493,6 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   }
   __syncwarp();
 
-  uint32_t qa[KB][2];
-#pragma unroll
-  for (int kb = 0; kb < KB; ++kb) {
-    qa[kb][0] = qa[kb][1] = 0u;
-    if (gid < ng && kb < kb_n) {
-      const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
-      qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
-      qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
-    }
-  }
   float o[DB][4];
 #pragma unroll
   for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
@@ -521,8 +514,25 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       tma_load_2d(dst + 2 * DK * 128 + c * DK * 128, &map_v, c * 64, row, bar);
     }
   };
+  // the first tiles are asked for while the kernel before this one (which writes the newest keys and values, and
+  // the queries) may still run; a tile that holds a key written in this step waits for it
+  int issued = 0;
   if (lane == 0)
-    for (int s0 = 0; s0 < DSTAGES - 1 && s0 < n_steps; ++s0) issue(s0, s0);
+    for (; issued < DSTAGES - 1 && issued < n_steps && first + (issued + 1) * DK <= pq + 1 - p.fresh_keys; ++issued)
+      issue(issued, issued);
+  pdl_wait();
+  if (lane == 0)
+    for (; issued < DSTAGES - 1 && issued < n_steps; ++issued) issue(issued, issued);
+  uint32_t qa[KB][2];
+#pragma unroll
+  for (int kb = 0; kb < KB; ++kb) {
+    qa[kb][0] = qa[kb][1] = 0u;
+    if (gid < ng && kb < kb_n) {
+      const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
+      qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
+      qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
 
   int failed = 0;
 #pragma unroll 1
@@ -721,7 +731,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
   __shared__ int prefix_all[4][MAX_STREAM_ROWS + 1];
   __shared__ int steps_all[4][MAX_STREAM_ROWS];
   pdl_launch();
-  pdl_wait();
+  // nothing below reads what the kernels before this one write, until pdl_wait() (see the kernel above)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* prefix = prefix_all[warp];
   int* steps_of = steps_all[warp];
@@ -778,6 +788,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
 
   int kc = 0;                       // stages issued so far by this warp: the rings run on across segments
   int failed = 0;
+  bool waited = false;              // for the kernel before this one
   int ti = 0;
   for (int u = (int)u_begin; u < u_end && !failed;) {
     // the segment that starts at unit u: row, item of the row, first step
@@ -802,16 +813,6 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     const int first_w = item_u0 / run;
     const int piece = w - first_w;
     const int pieces = (item_u0 + steps_row - 1) / run - first_w + 1;
-    uint32_t qa[KB][2];
-  #pragma unroll
-    for (int kb = 0; kb < KB; ++kb) {
-      qa[kb][0] = qa[kb][1] = 0u;
-      if (gid < ng && kb < kb_n) {
-        const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
-        qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
-        qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
-      }
-    }
     float o[DB][4];
   #pragma unroll
     for (int db = 0; db < DB; ++db) o[db][0] = o[db][1] = o[db][2] = o[db][3] = 0.f;
@@ -833,8 +834,29 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       }
     };
     __syncwarp();          // the previous segment's last reads of the ring are done
+    // the warp's first tiles are asked for while the kernel before this one may still run, unless they hold a
+    // key that it writes
+    int issued = 0;
     if (lane == 0)
-      for (int s0 = 0; s0 < DSTAGES - 1 && s0 < n_steps; ++s0) issue(s0, (kc + s0) % DSTAGES);
+      for (; issued < DSTAGES - 1 && issued < n_steps &&
+             (waited || first + (s_begin + issued + 1) * DK <= pq + 1 - p.fresh_keys); ++issued)
+        issue(issued, (kc + issued) % DSTAGES);
+    if (!waited) {
+      pdl_wait();
+      waited = true;
+      if (lane == 0)
+        for (; issued < DSTAGES - 1 && issued < n_steps; ++issued) issue(issued, (kc + issued) % DSTAGES);
+    }
+    uint32_t qa[KB][2];
+  #pragma unroll
+    for (int kb = 0; kb < KB; ++kb) {
+      qa[kb][0] = qa[kb][1] = 0u;
+      if (gid < ng && kb < kb_n) {
+        const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
+        qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
+        qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+    }
 
   #pragma unroll 1
     for (int step = 0; step < n_steps; ++step) {
@@ -971,12 +993,15 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
 // flint_paged_attention with bfloat16 q/out, page sizes that are multiples of 16, head sizes up to 128.
 // arrivals (may be null): n_arrivals counters, zero before the first launch and left zero by every launch;
 // given enough of them and splits in fours, the splits of a row are merged inside this kernel.
+// fresh_keys: how many of a row's newest keys (its own included) the kernel before this one in the stream may
+// have written (1 for decoded tokens; the length of the longest portion otherwise): tiles below them are
+// fetched before that kernel has finished.
 extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                          const int* block_table, int max_pages, int page_size, const int* pos,
                                          const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
                                          float scale, int split_keys, int n_splits, float* scratch,
                                          const int* row_list, int* error_flag, int* arrivals, int n_arrivals,
-                                         cudaStream_t stream) {
+                                         int fresh_keys, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_tc: head size %d (multiples of 16 up to 128)", hd);
   if (nkv <= 0 || nq % nkv) return fail("attention_decode_tc: %d query heads do not divide into %d kv heads", nq, nkv);
@@ -999,6 +1024,7 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   // with splits in fours and a counter for every (row, kv head, chunk of query heads) the pieces are merged by
   // the block that finishes last; else by a kernel of its own
   p.arrivals = (arrivals && n_splits % 4 == 0 && (long long)T * nkv * p.g_chunks <= n_arrivals) ? arrivals : nullptr;
+  p.fresh_keys = fresh_keys < 1 ? 1 : fresh_keys;
   const long long items = (long long)T * nkv * p.g_chunks * n_splits;
   const long long blocks = (items + 3) / 4;
   if (blocks > 0x7fffffffLL) return fail("attention_decode_tc: too many work items");
@@ -1021,12 +1047,12 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
 // The same contract with the work cut into equal runs of keys on the device (see the stream kernel): any mix of
 // row lengths keeps every warp equally busy, and nothing about the launch depends on the lengths, so one
 // captured launch serves every context length.  n_slices (2..64): the most pieces an item may be cut into;
-// scratch: T * nq * n_slices * (hd + 2) floats.  Up to 256 rows.
+// scratch: T * nq * n_slices * (hd + 2) floats.  Up to 256 rows.  fresh_keys: as for flint_attention_decode_tc.
 extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                              const int* block_table, int max_pages, int page_size, const int* pos,
                                              const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
                                              float scale, int n_slices, float* scratch, const int* row_list,
-                                             int* error_flag, cudaStream_t stream) {
+                                             int* error_flag, int fresh_keys, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (T > MAX_STREAM_ROWS) return fail("attention_decode_stream: %d rows (up to %d)", T, MAX_STREAM_ROWS);
   if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_stream: head size %d (multiples of 16 up to 128)", hd);
@@ -1047,6 +1073,7 @@ extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache,
   p.g_chunks = (nq / nkv + 7) / 8;
   p.scale = scale;
   p.arrivals = nullptr;
+  p.fresh_keys = fresh_keys < 1 ? 1 : fresh_keys;
   static int sm_count = 0;
   if (!sm_count) {
     int dev = 0;

@@ -506,11 +506,11 @@ class CudaOps:
         if not tc:
             return self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale,
                                         step.max_kv_len, splits=step.attention_splits,
-                                        ragged=not step.even_lengths)
+                                        ragged=not step.even_lengths, fresh_keys=step.longest_entry)
         self.attention_prefill_tc(q, cache, step.tiles, step.n_tiles, out, nq, nkv, hd, window, scale)
         if step.n_other_rows:
             self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len,
-                                 rows=step.other_rows)
+                                 rows=step.other_rows, fresh_keys=step.longest_entry)
 
     def attention_prefill_tc(self, q, cache, tiles, n_tiles, out, nq, nkv, hd, window, scale):
         _check(q, "q", torch.bfloat16, 2)
@@ -527,11 +527,13 @@ class CudaOps:
                   c_int(hd), c_int(window), c_float(scale), _ptr(self.tc_error))
 
     def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,
-                        kernel=None, rows=None, ragged=True, merge_in_kernel=True):
+                        kernel=None, rows=None, ragged=True, merge_in_kernel=True, fresh_keys=1 << 30):
         """rows: int32 list of the batch rows to compute (default: all).  ragged: the rows' key ranges may
         differ much in length (False: a decode batch whose requests are about equally long).
         merge_in_kernel (the tensor-core decode kernel with splits in fours): the pieces of a row's key range
-        are merged by the block that finishes last; False: by a kernel of its own."""
+        are merged by the block that finishes last; False: by a kernel of its own.
+        fresh_keys: how many of a row's newest keys the kernel before this one in the stream may have written
+        (1 for a batch of decoded tokens); the default assumes all of them."""
         _check(q, "q", dims=2)
         _check(out, "out", q.dtype, 2)
         T = q.shape[0]
@@ -564,7 +566,7 @@ class CudaOps:
                              c_int(cache.k.shape[0]), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),
                              c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
                              c_int(hd), c_int(window), c_float(scale), c_int(n_splits), _ptr(scratch), _ptr(rows),
-                             _ptr(self.tc_error))
+                             _ptr(self.tc_error), c_int(max(1, int(fresh_keys))))
         if kernel == "tma":
             if rows is not None and rows.numel() != T:
                 raise KernelError("paged_attention: bad row list")
@@ -573,7 +575,7 @@ class CudaOps:
                              c_int(cache.page_size), _ptr(pos), _ptr(slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv),
                              c_int(hd), c_int(window), c_float(scale), c_int(split_keys), c_int(n_splits),
                              _ptr(scratch), _ptr(rows), _ptr(self.tc_error), _ptr(arrivals),
-                             c_int(arrivals.numel() if arrivals is not None else 0))
+                             c_int(arrivals.numel() if arrivals is not None else 0), c_int(max(1, int(fresh_keys))))
         fn = {"warp": "flint_paged_attention", "block": "flint_paged_attention_block"}[kernel]
         self._run("attention", fn, _ptr(q), c_int(_code(q.dtype)), _ptr(cache.k), _ptr(cache.v),
                   c_int(_code(cache.k.dtype)), _ptr(cache.block_table), c_int(cache.block_table.shape[1]),

@@ -47,6 +47,7 @@ class StepContext:
     want_rows: torch.Tensor    # [R] int32 rows of the flattened batch
     n_want: int
     max_kv_len: int            # largest (position + 1) in the step, host value
+    longest_entry: int         # most tokens any one request brings in this step, host value
     status: torch.Tensor       # [1] int32, set non-zero by a kernel that met a missing page
     entries: list              # the host-side StepEntry list
     entry_start: list          # first flattened row of each entry (host)
@@ -115,7 +116,8 @@ class StepStaging:
             self._in_flight = True
         d = self.dev
         return StepContext(n_tokens=T, ids=d[0:T], pos=d[M:M + T], slot=d[2 * M:2 * M + T],
-                           want_rows=d[3 * M:3 * M + R], n_want=R, max_kv_len=max_kv, status=self.status,
+                           want_rows=d[3 * M:3 * M + R], n_want=R, max_kv_len=max_kv,
+                           longest_entry=max(len(e.tokens) for e in entries), status=self.status,
                            entries=list(entries), entry_start=starts,
                            tiles=d[5 * M:5 * M + 4 * n_tiles].view(-1, 4), n_tiles=n_tiles,
                            other_rows=d[4 * M:4 * M + n_others], n_other_rows=n_others,

@@ -512,9 +512,12 @@ def test_attention_decode_stream_cuts_keys_into_equal_runs(ops, ref, nq, nkv, hd
     exp = torch.zeros(T, nq * hd, dtype=torch.float64)
     ref.paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, window, scale, max(lens))
     out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens), kernel="stream")
-    assert int(ops.tc_error.item()) == 0
-    close(out, exp, 2e-2, 2e-2)
+    for fresh_keys in (1 << 30, 1):      # 1: a decode step, the first tiles are fetched before the wait for the kernel before
+        out.fill_(float("nan"))
+        ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens),
+                            kernel="stream", fresh_keys=fresh_keys)
+        assert int(ops.tc_error.item()) == 0
+        close(out, exp, 2e-2, 2e-2)
     if T > 2:       # every other row through a row list: the rest stays untouched
         rows = torch.arange(0, T, 2, dtype=torch.int32)
         out2 = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
@@ -561,8 +564,11 @@ def test_attention_decode_splits_are_merged_by_the_last_to_arrive(ops, ref, nq, 
     outs = []
     for merge_in_kernel in (True, True, False):
         out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        # fresh_keys=1: only a row's own key may be written by the kernel before (a decode step), so the first
+        # tiles are fetched before the wait for that kernel
         ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, max(lens),
-                            kernel="tma", splits=splits, merge_in_kernel=merge_in_kernel)
+                            kernel="tma", splits=splits, merge_in_kernel=merge_in_kernel,
+                            fresh_keys=1 if merge_in_kernel else 1 << 30)
         assert int(ops.tc_error.item()) == 0 and int(ops.attention_arrivals.abs().sum().item()) == 0
         close(out, exp, 2e-2, 2e-2)
         outs.append(out.float().cpu())
