@@ -113,10 +113,11 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                                int nq, int nkv, int hd, int write_kv, int* __restrict__ status,
                                int n_partials, long long partial_stride, const float* __restrict__ bias) {
   pdl_launch();
-  pdl_wait();
   // One block per token.  A work item is a pair of dims (d, d + rot/2) of one head (or two
   // neighbouring dims beyond the rotary part, or of a value head), so that every input element
   // is read exactly once; consecutive threads take consecutive pairs.
+  // Positions, slots, block tables, the cos/sin tables and the bias are not written by any kernel: they are read
+  // before the wait for the kernel before this one, whose output (qkv) is read only after it.
   const int t = blockIdx.x;
   const int p = pos[t];
   const int half = rot >> 1;
@@ -124,29 +125,12 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
   const int heads = nq + (write_kv ? 2 * nkv : 0);
   const size_t row_off = (size_t)t * (nq + 2 * nkv) * hd;
   long long cache_tok = -1;                  // row of this token in [page, kv_head, P] units, head 0
+  bool missing = false;
   if (write_kv) {
     const int page = block_table[(size_t)slot[t] * max_pages + p / page_size];
-    if (page < 0) {                          // the host must have allocated the page; record and skip
-      if (threadIdx.x == 0) atomicExch(status, 1);
-    } else {
-      cache_tok = (long long)page * nkv * page_size + (p % page_size);
-    }
+    if (page < 0) missing = true;            // the host must have allocated the page; record and skip
+    else cache_tok = (long long)page * nkv * page_size + (p % page_size);
   }
-  // the projection may arrive as partial sums over pieces of its K range, and without its bias:
-  // they are added here in a fixed order
-  auto rd = [&](size_t off, int col) {
-    const float* src = qkv + row_off + off;
-    if (n_partials == 1) return bias ? src[0] + bias[col] : src[0];
-    float v = 0.f;
-    for (int z0 = 0; z0 < n_partials; z0 += 8) {      // eight loads in flight, added in order
-      float t[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) t[u] = z0 + u < n_partials ? src[(size_t)(z0 + u) * partial_stride] : 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) v += t[u];
-    }
-    return bias ? v + bias[col] : v;
-  };
   // with few tokens several blocks share a token (gridDim.y), each a contiguous range of items
   const int n_items = heads * pairs;
   const int per_block = (n_items + gridDim.y - 1) / gridDim.y;
@@ -158,6 +142,8 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                            reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
                            reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
   if (n_partials == 1 && (half & 3) == 0 && (hd & 7) == 0 && gridDim.y == 1 && aligned16) {
+    pdl_wait();
+    if (missing && threadIdx.x == 0) atomicExch(status, 1);
     const int quads = pairs >> 2;
     for (int item = threadIdx.x; item < heads * quads; item += blockDim.x) {
       const int head = item / quads, i = (item % quads) * 4;      // first pair of the four
@@ -199,33 +185,67 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
     }
     return;
   }
-  for (int item = blockIdx.y * per_block + threadIdx.x; item < item_end; item += blockDim.x) {
-    const int head = item / pairs, i = item % pairs;
-    const bool is_q = head < nq, is_v = head >= nq + nkv;
+  // what an item needs that no kernel writes: its dims, its cos and sin, its bias
+  struct Item { int head, d0, d1; bool rotate; float c, s, b0, b1; };
+  auto prepare = [&](int item) {
+    Item it;
+    it.head = item / pairs;
+    const int i = item % pairs;
+    const bool is_v = it.head >= nq + nkv;
     // dims of this item: inside the rotary part (d, d + half); beyond it (rot + 2j, rot + 2j + 1)
-    int d0, d1;
-    bool rotate = false;
-    if (!is_v && i < half) { d0 = i; d1 = i + half; rotate = true; }
-    else if (is_v) { d0 = 2 * i; d1 = 2 * i + 1; }
-    else { d0 = rot + 2 * (i - half); d1 = d0 + 1; }
-    const size_t base = (size_t)head * hd;
-    float x0 = rd(base + d0, head * hd + d0), x1 = rd(base + d1, head * hd + d1);
-    if (rotate) {
-      const float c = cos_t[(size_t)p * half + i], s = sin_t[(size_t)p * half + i];
-      const float y0 = x0 * c - x1 * s, y1 = x1 * c + x0 * s;
+    it.rotate = false;
+    if (!is_v && i < half) { it.d0 = i; it.d1 = i + half; it.rotate = true; }
+    else if (is_v) { it.d0 = 2 * i; it.d1 = 2 * i + 1; }
+    else { it.d0 = rot + 2 * (i - half); it.d1 = it.d0 + 1; }
+    it.c = it.rotate ? cos_t[(size_t)p * half + i] : 1.f;
+    it.s = it.rotate ? sin_t[(size_t)p * half + i] : 0.f;
+    it.b0 = bias ? bias[it.head * hd + it.d0] : 0.f;
+    it.b1 = bias ? bias[it.head * hd + it.d1] : 0.f;
+    return it;
+  };
+  int item = blockIdx.y * per_block + threadIdx.x;
+  Item it;
+  if (item < item_end) it = prepare(item);
+  pdl_wait();
+  if (missing && threadIdx.x == 0) atomicExch(status, 1);
+  while (item < item_end) {
+    // the projection may arrive as partial sums over pieces of its K range, and without its bias: they are
+    // added here in a fixed order (up to sixteen loads of each of the two values in flight)
+    const float* s0 = qkv + row_off + (size_t)it.head * hd + it.d0;
+    const float* s1 = qkv + row_off + (size_t)it.head * hd + it.d1;
+    float x0 = 0.f, x1 = 0.f;
+    for (int z0 = 0; z0 < n_partials; z0 += 16) {
+      float t0[16], t1[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const bool in = z0 + u < n_partials;
+        t0[u] = in ? s0[(size_t)(z0 + u) * partial_stride] : 0.f;
+        t1[u] = in ? s1[(size_t)(z0 + u) * partial_stride] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { x0 += t0[u]; x1 += t1[u]; }
+    }
+    x0 += it.b0;
+    x1 += it.b1;
+    if (it.rotate) {
+      const float y0 = x0 * it.c - x1 * it.s, y1 = x1 * it.c + x0 * it.s;
       x0 = y0;
       x1 = y1;
     }
+    const int head = it.head;
+    const bool is_q = head < nq, is_v = head >= nq + nkv;
     if (is_q) {
       TQ* dst = q_out + ((size_t)t * nq + head) * hd;
-      dst[d0] = from_f32<TQ>(x0);
-      dst[d1] = from_f32<TQ>(x1);
+      dst[it.d0] = from_f32<TQ>(x0);
+      dst[it.d1] = from_f32<TQ>(x1);
     } else if (cache_tok >= 0) {
       const int kvh = is_v ? head - nq - nkv : head - nq;
       TC* dst = (is_v ? v_cache : k_cache) + (cache_tok + (long long)kvh * page_size) * hd;
-      dst[d0] = from_f32<TC>(x0);
-      dst[d1] = from_f32<TC>(x1);
+      dst[it.d0] = from_f32<TC>(x0);
+      dst[it.d1] = from_f32<TC>(x1);
     }
+    item += blockDim.x;
+    if (item < item_end) it = prepare(item);
   }
 }
 
