@@ -93,30 +93,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   pdl_launch();
   if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
   const bool grouped = p.tile_expert != nullptr;
-  if (grouped) pdl_wait();                    // the tile map comes from the routing plan of an earlier kernel
   constexpr int FM = GATED ? GATED_FEATURES : BM;      // output features per tile
   const int tiles_m = (p.N + FM - 1) / FM;
-  const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
   const int total_kb = (p.K + BK - 1) / BK;
-  const int n_items = tiles_m * tiles_n * p.splits;
-  // Stream-K (few rows, partial sums deferred to the consumer): the K blocks of all tiles are laid end to end
-  // and cut into runs of `run` blocks, one run per block of the grid, so that every block streams the same
-  // number of weight bytes however many tiles there are (with experts, the number of tiles is only known
-  // here).  A tile is then covered by up to p.splits pieces (run is kept long enough for that); piece i
-  // of a tile goes to partial slice i, and the first piece also clears the slices the tile does not use.
-  int run = 0, unit0 = 0, unit1 = 0;
-  if (p.stream_k) {
-    const long long units = (long long)tiles_m * tiles_n * total_kb;
-    const int run_min = p.splits > 1 ? (total_kb - 1 + p.splits - 2) / (p.splits - 1) : total_kb;
-    run = max(max((int)((units + gridDim.x - 1) / gridDim.x), run_min), 1);
-    if (p.splits == 1) run = ((run + total_kb - 1) / total_kb) * total_kb;     // whole tiles only
-    const long long u0 = (long long)blockIdx.x * run;
-    if (u0 >= units) return;
-    unit0 = (int)u0;
-    unit1 = (int)min(units, u0 + run);
-  } else if ((int)blockIdx.x >= n_items) {
-    return;
-  }
 
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -146,6 +125,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
   volatile int* ab = &abort_flag;
+
+  // The barriers and the tensor memory above need nothing from earlier kernels.  With experts, the tile map
+  // comes from the routing plan of an earlier kernel: from here on the block has to wait for it.
+  if (grouped) pdl_wait();
+  const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
+  const int n_items = tiles_m * tiles_n * p.splits;
+  // Stream-K (few rows, partial sums deferred to the consumer): the K blocks of all tiles are laid end to end
+  // and cut into runs of `run` blocks, one run per block of the grid, so that every block streams the same
+  // number of weight bytes however many tiles there are (with experts, the number of tiles is only known
+  // here).  A tile is then covered by up to p.splits pieces (run is kept long enough for that); piece i
+  // of a tile goes to partial slice i, and the first piece also clears the slices the tile does not use.
+  // A block without work (unit0 == unit1, or no item of its own) goes straight to the teardown.
+  int run = 1, unit0 = 0, unit1 = 0;
+  if (p.stream_k) {
+    const long long units = (long long)tiles_m * tiles_n * total_kb;
+    const int run_min = p.splits > 1 ? (total_kb - 1 + p.splits - 2) / (p.splits - 1) : total_kb;
+    run = max(max((int)((units + gridDim.x - 1) / gridDim.x), run_min), 1);
+    if (p.splits == 1) run = ((run + total_kb - 1) / total_kb) * total_kb;     // whole tiles only
+    const long long u0 = (long long)blockIdx.x * run;
+    if (u0 < units) {
+      unit0 = (int)u0;
+      unit1 = (int)min(units, u0 + run);
+    }
+  }
 
   // item -> (piece of K, feature tile, row tile): pieces of one tile and neighbouring feature tiles go
   // to neighbouring blocks, which then share the activation tile in L2
