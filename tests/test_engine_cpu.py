@@ -171,3 +171,48 @@ def test_running_one_step_ahead_changes_nothing_but_the_order_of_work(setup):
         eng.step()
     eng.close(a)
     assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 4
+
+
+def test_random_arrivals_with_and_without_running_ahead(setup):
+    """Requests of random lengths arrive at random calls, some carry a stop token, pages are scarce (requests
+    are preempted and recomputed), a session is closed half-way: with and without running a step ahead every
+    request gets the same tokens, and every page and slot comes back."""
+    import random
+    which, folder, reqs, plain = setup
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    V = cfg["vocab_size"]
+    preempted = 0
+    for seed in (1, 2, 3):
+        rnd = random.Random(seed)
+        plan = []           # (call at which it arrives, prompt, max_tokens, stop)
+        for i in range(7):
+            prompt = [rnd.randrange(V) for _ in range(rnd.choice([1, 3, 9, 17, 30]))]
+            plan.append((rnd.randrange(0, 12), prompt, rnd.choice([1, 2, 5, 9, 14]), (rnd.randrange(V),) if i % 3 == 0 else ()))
+        closed_at = rnd.randrange(3, 10)
+        results = []
+        for run_ahead in (False, True):
+            m = load_model(folder, dtype="float32", device="cpu", ops=RefOps(), page_size=16, n_pages=5, max_slots=3,
+                           max_step_tokens=24)
+            eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16, run_ahead=run_ahead)
+            sids, got, call = {}, {}, 0
+            while call < 12 or eng.has_work():
+                for i, (at, prompt, n, stop) in enumerate(plan):
+                    if at == call:
+                        sids[i] = eng.create(prompt, n, stop_extra=stop)
+                        got[i] = []
+                eng.step()
+                for i, sid in sids.items():
+                    got[i] += [p.token for p in eng.poll(sid)]
+                if call == closed_at and 0 in sids:
+                    eng.close(sids[0])
+                m.cache.check()
+                call += 1
+                assert call < 400
+            assert all(eng.finished(s) for s in sids.values())
+            assert all(g.pages.pool.used_pages == 0 for g in m.cache.groups) and m.cache.free_slots == 3
+            got.pop(0, None)            # the closed session may have been cut at different tokens
+            results.append(got)
+            preempted += eng.scheduler.preemptions
+        assert results[0] == results[1], seed
+        assert eng.steps_ahead > 0
+    assert preempted > 0
