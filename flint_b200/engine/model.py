@@ -144,6 +144,7 @@ class Model:
         self.use_graphs = (use_graphs and self.device.type == "cuda" and self.final_norm.graph_safe
                            and all(p.graph_safe for layer in self.layers for p in layer.parts.values()))
         self._graphs = {}
+        self._graph_pool = None         # one memory pool for all captured steps: only one of them runs at a time
         self.graph_max_batch = 256
 
     # ------------------------------------------------------------------ facts
@@ -221,9 +222,11 @@ class Model:
             self.forward(step)            # loads modules and warms the allocator outside the capture
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
+            if self._graph_pool is None:
+                self._graph_pool = torch.cuda.graph_pool_handle()
             before = self.ops.launches
             wanted, step.record = step.record, {}     # internals are recorded as references to the
-            with torch.cuda.graph(graph):             # graph's own tensors, refreshed by every replay
+            with torch.cuda.graph(graph, pool=self._graph_pool):   # graph's own tensors, refreshed by every replay
                 logits = self.forward(step)
             entry = (graph, logits, self.ops.launches - before, step.record)
             step.record = wanted

@@ -19,3 +19,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def same_random_inputs_every_run():
+    """Inputs drawn from the global generators are the same in every run, whatever ran before: a comparison that
+    could flip on a near-tie (an expert chosen, a mask threshold) then passes or fails the same way every time."""
+    import random
+    import torch
+    random.seed(1234)
+    torch.manual_seed(1234)
+    yield
