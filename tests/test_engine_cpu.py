@@ -216,3 +216,37 @@ def test_random_arrivals_with_and_without_running_ahead(setup):
         assert results[0] == results[1], seed
         assert eng.steps_ahead > 0
     assert preempted > 0
+
+
+def test_packing_a_step_with_tokens_fed_on_the_device():
+    """An entry whose first token the host has not read carries the place of that token in the sampler's
+    output; the packed batch says so row by row, and the token id that travels is a placeholder."""
+    from flint_b200.engine.step import StepEntry, StepStaging
+    st = StepStaging(32, "cpu")
+    entries = [StepEntry(0, 10, [7], [0], feed=3), StepEntry(2, 0, [5, 6, 9], [2]), StepEntry(1, 4, [8], [0], feed=0)]
+    ctx = st.pack(entries, vocab_size=50, max_positions=64)
+    assert (ctx.n_tokens, ctx.n_want, ctx.n_fed, ctx.longest_entry, ctx.max_kv_len) == (5, 3, 2, 3, 11)
+    assert ctx.ids.tolist() == [0, 5, 6, 9, 0]
+    assert ctx.fed_rows.tolist() == [3, -1, -1, -1, 0]
+    assert ctx.pos.tolist() == [10, 0, 1, 2, 4] and ctx.slot.tolist() == [0, 2, 2, 2, 1]
+    assert ctx.want_rows.tolist() == [0, 3, 4]
+    with pytest.raises(ModelError, match="fed from place"):
+        st.pack([StepEntry(0, 0, [1], [0], feed=32)], 50, 64)
+
+
+def test_decode_attention_is_cut_into_splits_that_cover_the_keys():
+    """The plan of the decode attention: the splits cover every key, and with more than four of them they come
+    in fours (the four warps of a block then hold one row's splits and merge them themselves)."""
+    from flint_b200.csrc.ops import CudaOps
+
+    class Sizes:                      # the plan is arithmetic on sizes: no device is needed
+        _stream_slices = staticmethod(CudaOps._stream_slices)
+    for T in (1, 2, 3, 8, 16, 31):
+        for nq, nkv in ((32, 8), (8, 8), (6, 2), (48, 2)):
+            for span in (1, 63, 64, 65, 300, 2049, 2100, 4096, 16384, 40000):
+                kernel, keys, n = CudaOps.attention_plan(Sizes, T, nq, nkv, span, 128, True, False)
+                assert keys * n >= span and keys >= 1 and n >= 1, (T, nq, nkv, span, kernel, keys, n)
+                if kernel == "tma":
+                    assert keys % 16 == 0 and (n <= 4 or n % 4 == 0), (T, nq, nkv, span, keys, n)
+                ragged = CudaOps.attention_plan(Sizes, T, nq, nkv, span, 128, True, True)
+                assert ragged[0] in ("stream", "tma") and 2 <= ragged[2] <= 64 or ragged[0] == "tma"
