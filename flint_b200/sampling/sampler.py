@@ -66,17 +66,20 @@ class BatchSampler:
             self.ops.argmax(logits, out)
         else:
             ph, ch = self._params_host[ticket], self._ctx_host[ticket]
+            flat, any_ctx = [], False
             for i, (p, rng, generated) in enumerate(rows):
                 n_ctx = 0
                 if p.repeat_penalty != 1.0 and p.repeat_last_n > 0 and generated:
                     recent = generated[-min(p.repeat_last_n, self.max_context):]
                     n_ctx = len(recent)
                     ch[i, :n_ctx] = torch.tensor(recent, dtype=torch.int32)
+                    any_ctx = True
                 u = rng.next_f32() if p.temperature > 0 else 0.0
-                ph[i] = torch.tensor([p.temperature, float(p.top_k), p.top_p, p.min_p, p.repeat_penalty, u,
-                                      float(n_ctx), 0.0])
+                flat += (p.temperature, float(p.top_k), p.top_p, p.min_p, p.repeat_penalty, u, float(n_ctx), 0.0)
+            ph[:R] = torch.tensor(flat, dtype=torch.float32).view(R, 8)       # one write for all rows
             self._params[:R].copy_(ph[:R], non_blocking=True)
-            self._ctx[:R].copy_(ch[:R], non_blocking=True)
+            if any_ctx:                     # rows without a penalty never read their context
+                self._ctx[:R].copy_(ch[:R], non_blocking=True)
             if self._work is None or self._work.shape[0] < R or self._work.shape[1] != logits.shape[1]:
                 self._work = torch.empty((max(R, min(self.max_rows, 64)), logits.shape[1]), dtype=torch.float32,
                                          device=self.device)
