@@ -442,7 +442,9 @@ __device__ __forceinline__ void merge_records(const DecodeParams& p, int ti, int
   }
 }
 
-template <int HD>
+// DKT: keys per stage of the ring, 16 or 32 (a stage of 32 keys is worked through as two halves of 16; it takes
+// half as many copies and waits per key, and pages must be multiples of 32 keys)
+template <int HD, int DKT>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const DecodeParams p) {
@@ -450,6 +452,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   using flint_attn::ldsm4t;
   using flint_attn::mma16816;
   constexpr int MG = 8;
+  constexpr int SB = 2 * 2 * DKT * 128;        // bytes of a stage: K and V, two chunks of 64 dims
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
   pdl_launch();
@@ -476,8 +479,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   const int lo_row = p.window > 0 ? max(0, pq + 1 - p.window) : 0;
   // the row's keys are divided evenly over the splits (in steps of 16), so that a row shorter than the
   // launch was sized for still keeps every split busy; split_keys is the upper bound
-  const int even = ((pq + 1 - lo_row + p.n_splits - 1) / p.n_splits + DK - 1) & ~(DK - 1);
-  const int sk = min(p.split_keys, max(even, DK));
+  const int even = ((pq + 1 - lo_row + p.n_splits - 1) / p.n_splits + DKT - 1) & ~(DKT - 1);
+  const int sk = min(p.split_keys, max(even, DKT));
   const int lo = lo_row + split * sk;
   const int hi = min(pq + 1, lo + sk);
   const int* bt = p.block_table + (size_t)p.slot[t] * p.max_pages;
@@ -485,7 +488,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   constexpr int KB = HD / 16, DB = HD / 8;
   const int kb_n = hd / 16, db_n = hd / 8, chunks = (hd + 63) / 64;
 
-  const uint32_t ring = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * (DSTAGES * DSTAGE_BYTES);
+  const uint32_t ring = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * (DSTAGES * SB);
   const uint32_t bar0 = smem_u32(&bars[warp * DSTAGES]);
   if (lane == 0) {
     for (int s = 0; s < DSTAGES; ++s) mbar_init(bar0 + 8 * s, 1);
@@ -499,26 +502,26 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   float m = -INFINITY, l = 0.f;
 
   // stages cover absolute key positions [first + step*16, +16): tiles never straddle a page
-  const int first = lo & ~(DK - 1);
-  const int n_steps = hi > lo ? (hi - first + DK - 1) / DK : 0;
+  const int first = lo & ~(DKT - 1);
+  const int n_steps = hi > lo ? (hi - first + DKT - 1) / DKT : 0;
   auto issue = [&](int step, int stage) {      // lane 0 only
-    const int j0 = first + step * DK;
+    const int j0 = first + step * DKT;
     const int lp = j0 / p.page_size;
     int page = lp < p.max_pages ? bt[lp] : -1;
     if (page < 0) page = 0;                    // never visible (masked): any finite page will do
     const int row = (page * p.nkv + kvh) * p.page_size + j0 % p.page_size;
-    const uint32_t dst = ring + stage * DSTAGE_BYTES, bar = bar0 + 8 * stage;
-    mbar_expect_tx(bar, 2 * chunks * DK * 128);
+    const uint32_t dst = ring + stage * SB, bar = bar0 + 8 * stage;
+    mbar_expect_tx(bar, 2 * chunks * DKT * 128);
     for (int c = 0; c < chunks; ++c) {
-      tma_load_2d(dst + c * DK * 128, &map_k, c * 64, row, bar);
-      tma_load_2d(dst + 2 * DK * 128 + c * DK * 128, &map_v, c * 64, row, bar);
+      tma_load_2d(dst + c * DKT * 128, &map_k, c * 64, row, bar);
+      tma_load_2d(dst + 2 * DKT * 128 + c * DKT * 128, &map_v, c * 64, row, bar);
     }
   };
   // the first tiles are asked for while the kernel before this one (which writes the newest keys and values, and
   // the queries) may still run; a tile that holds a key written in this step waits for it
   int issued = 0;
   if (lane == 0)
-    for (; issued < DSTAGES - 1 && issued < n_steps && first + (issued + 1) * DK <= pq + 1 - p.fresh_keys; ++issued)
+    for (; issued < DSTAGES - 1 && issued < n_steps && first + (issued + 1) * DKT <= pq + 1 - p.fresh_keys; ++issued)
       issue(issued, issued);
   pdl_wait();
   if (lane == 0)
@@ -549,8 +552,10 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       }
     }
     if (__any_sync(0xffffffffu, failed)) break;
-    const uint32_t ks = ring + stage * DSTAGE_BYTES, vs = ks + 2 * DK * 128;
-    const int j0 = first + step * DK;
+#pragma unroll
+    for (int sub = 0; sub < DKT / 16; ++sub) {
+    const uint32_t ks = ring + stage * SB + sub * 16 * 128, vs = ks + 2 * DKT * 128;
+    const int j0 = first + step * DKT + sub * 16;
     float sacc[2][4];
 #pragma unroll
     for (int nb = 0; nb < 2; ++nb) {
@@ -562,7 +567,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
           const int r = nb * 8 + (lane & 7);
           const int unit = kb * 2 + (lane >> 3);              // 16-byte unit along the head dimension
           uint32_t b0, b1, b2, b3;
-          ldsm4(ks + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+          ldsm4(ks + (unit >> 3) * DKT * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
           mma16816(sacc[nb], qa[kb][0], 0u, qa[kb][1], 0u, b0, b1);
           if (kb + 1 < kb_n) mma16816(sacc[nb], qa[kb + 1][0], 0u, qa[kb + 1][1], 0u, b2, b3);
         }
@@ -595,11 +600,12 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
         const int r = (lane & 7) + ((lane >> 3) & 1) * 8;      // key row
         const int unit = db + (lane >> 4);                      // 16-byte unit = 8 dims
         uint32_t b0, b1, b2, b3;
-        ldsm4t(vs + (unit >> 3) * DK * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
+        ldsm4t(vs + (unit >> 3) * DKT * 128 + r * 128 + (((unit & 7) ^ (r & 7)) << 4), b0, b1, b2, b3);
         mma16816(o[db], pa0, 0u, pa2, 0u, b0, b1);
         mma16816(o[db + 1], pa0, 0u, pa2, 0u, b2, b3);
       }
     }
+    }   // halves of a stage
   }
   if (failed && lane == 0) atomicExch(p.error_flag, 1);
   l += __shfl_xor_sync(0xffffffffu, l, 1);
@@ -652,7 +658,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
     float ms[4], M = -INFINITY;
 #pragma unroll
     for (int w2 = 0; w2 < 4; ++w2) {
-      r4[w2] = reinterpret_cast<const float*>(smem_raw + (ring - smem_u32(smem_raw)) + (w2 - warp) * (DSTAGES * DSTAGE_BYTES)) + g * rec;
+      r4[w2] = reinterpret_cast<const float*>(smem_raw + (ring - smem_u32(smem_raw)) + (w2 - warp) * (DSTAGES * SB)) + g * rec;
       ms[w2] = s_failed[w2] ? -INFINITY : r4[w2][hd];
       M = fmaxf(M, ms[w2]);
     }
@@ -1005,14 +1011,18 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   if (T <= 0) return 0;
   if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_tc: head size %d (multiples of 16 up to 128)", hd);
   if (nkv <= 0 || nq % nkv) return fail("attention_decode_tc: %d query heads do not divide into %d kv heads", nq, nkv);
+  // Keys per stage: 32 for a row or two (one block of four warps per SM is then enough, and a stage of 32 keys
+  // takes half as many copies and waits per key: -2.5 % of a decode step at batch 1), else 16, with which two
+  // blocks share an SM (at batch 8 stages of 32 keys cost 8 % of the step)
+  const int dk = (page_size % 32 == 0 && (long long)T * nkv * ((nq / nkv + 7) / 8) <= 8) ? 32 : DK;
   if (page_size <= 0 || page_size % DK) return fail("attention_decode_tc: page size %d must be a multiple of %d", page_size, DK);
   if (n_splits < 1 || split_keys < 1) return fail("attention_decode_tc: bad split (%d keys, %d splits)", split_keys, n_splits);
   if (n_splits > 1 && !scratch) return fail("attention_decode_tc: splits need scratch memory");
   if (!error_flag) return fail("attention_decode_tc: needs an error flag");
   CUtensorMap mk, mv;
   const long long kv_rows = (long long)n_pages * nkv * page_size;
-  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, DK);
-  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, DK);
+  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, dk);
+  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, dk);
   if (rc) return fail("attention_decode_tc: cuTensorMapEncodeTiled failed (%d)", rc);
   DecodeParams p;
   p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot; p.row_list = row_list;
@@ -1028,15 +1038,23 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   const long long items = (long long)T * nkv * p.g_chunks * n_splits;
   const long long blocks = (items + 3) / 4;
   if (blocks > 0x7fffffffLL) return fail("attention_decode_tc: too many work items");
-  const size_t smem = 4 * DSTAGES * DSTAGE_BYTES + 1024;
+  const size_t smem = (size_t)4 * DSTAGES * (2 * 2 * dk * 128) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaFuncSetAttribute(attention_decode_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    cudaFuncSetAttribute(attention_decode_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int big = 4 * DSTAGES * (2 * 2 * 32 * 128) + 1024;
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
     configured = true;
   }
-  if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
-  else launch_pdl(attention_decode_tc_kernel<128>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+  if (dk == 32) {
+    if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64, 32>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+    else launch_pdl(attention_decode_tc_kernel<128, 32>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+  } else {
+    if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64, 16>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+    else launch_pdl(attention_decode_tc_kernel<128, 16>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
+  }
   rc = check_launch("attention_decode_tc");
   if (rc || n_splits == 1 || p.arrivals) return rc;
   launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
