@@ -258,3 +258,27 @@ def test_tokens_committed_unread_are_resolved_later():
     s.commit(s.plan(), [UNREAD])
     s.abort(r)
     assert r.generated == [] and s.resolve(r, 3) is False and cache.free_pages() == 16
+
+
+def test_steady_says_when_the_next_step_needs_no_token_values():
+    """Running a step ahead is allowed only while nothing waits, every running request has exactly its next
+    token to run, and a page for each of them is free (so that no request can be preempted unread)."""
+    from flint_b200.engine.scheduler import UNREAD
+    cache, s = setup(n_pages=4, page=16, slots=2, budget=32, chunk=16)
+    a, b = req(0, 20, max_tokens=40), req(1, 5, max_tokens=40)
+    s.add(a)
+    assert not s.steady()                      # a waits
+    s.commit(s.plan(), [])                     # first portion of a's prompt: no logits yet
+    assert not s.steady()                      # a has prompt left
+    s.commit(s.plan(), [UNREAD])
+    assert s.steady()                          # a decodes, its token unread, two pages free
+    s.add(b)
+    assert not s.steady()                      # b waits
+    s.resolve(a, 7)
+    s.commit(s.plan(), [UNREAD, UNREAD])       # a decodes, b's prompt is run: both now decode with a token unread
+    assert a.n_unread == 1 and b.n_unread == 1
+    assert cache.free_pages() == 1 and not s.steady()      # two requests, one free page: one of them could be preempted
+    s.resolve(a, 8)
+    s.resolve(b, 9)
+    s.abort(b)
+    assert cache.free_pages() == 2 and s.steady()
