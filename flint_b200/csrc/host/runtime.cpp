@@ -306,6 +306,7 @@ struct Scheduler {
   std::vector<int> running;
   int preemptions = 0, steps = 0;
   std::vector<int> touched;        // requests whose state changed outside a portion (for the caller's mirrors)
+  std::vector<int> free_handles;   // records of ended requests that the caller has let go of
 
   void fail_request(int r, const std::string& msg) {
     touched.push_back(r);
@@ -322,8 +323,15 @@ struct Scheduler {
     q.max_tokens = max_tokens;
     q.arrival = arrival;
     q.stop.assign(stop, stop + n_stop);
-    reqs.push_back(q);
-    const int r = (int)reqs.size() - 1;
+    int r;
+    if (!free_handles.empty()) {          // the record of a request that the caller has forgotten is used again
+      r = free_handles.back();
+      free_handles.pop_back();
+      reqs[r] = q;
+    } else {
+      reqs.push_back(q);
+      r = (int)reqs.size() - 1;
+    }
     char buf[160];
     if (n_prompt <= 0) {
       fail_request(r, "empty prompt");
@@ -523,6 +531,14 @@ struct Scheduler {
       if (reqs[r].remaining() != 1) return false;
     return cache->free_pages() >= (int)running.size();
   }
+  // the caller keeps no reference to an ended request any more: its record may serve a new one
+  int forget(int r) {
+    if (r < 0 || r >= (int)reqs.size()) return fail(E_MODEL, "no such request %d", r);
+    if (reqs[r].state != FINISHED && reqs[r].state != FAILED) return fail(E_MODEL, "request %d has not ended", r);
+    touched.erase(std::remove(touched.begin(), touched.end(), r), touched.end());
+    free_handles.push_back(r);
+    return 0;
+  }
   int abort(int r) {
     waiting.erase(std::remove(waiting.begin(), waiting.end(), r), waiting.end());
     reqs[r].n_generated -= reqs[r].n_unread;
@@ -647,6 +663,9 @@ int flint_rt_sched_commit(void* s, const int* portions, int n_portions, const in
   return (int)out.size() / 2;
 }
 int flint_rt_sched_abort(void* s, int r) { return ((Scheduler*)s)->abort(r); }
+int flint_rt_sched_forget(void* s, int r) { return ((Scheduler*)s)->forget(r); }
+// how many request records exist (in use or waiting to be used again)
+int flint_rt_sched_records(void* s) { return (int)((Scheduler*)s)->reqs.size(); }
 int flint_rt_sched_resolve(void* s, int r, int token) { return ((Scheduler*)s)->resolve(r, token); }
 int flint_rt_sched_steady(void* s) { return ((Scheduler*)s)->steady() ? 1 : 0; }
 int flint_rt_sched_has_work(void* s) {

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "flint_rt_sched_plan": (c_int, [c_void_p, _INT_P, c_int]),
     "flint_rt_sched_commit": (c_int, [c_void_p, _INT_P, c_int, _INT_P, c_int, _INT_P, c_int]),
     "flint_rt_sched_abort": (c_int, [c_void_p, c_int]),
+    "flint_rt_sched_forget": (c_int, [c_void_p, c_int]),
+    "flint_rt_sched_records": (c_int, [c_void_p]),
     "flint_rt_sched_resolve": (c_int, [c_void_p, c_int, c_int]),
     "flint_rt_sched_steady": (c_int, [c_void_p]),
     "flint_rt_sched_has_work": (c_int, [c_void_p]),

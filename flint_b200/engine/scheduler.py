@@ -100,6 +100,7 @@ class Scheduler:
         self._h = self._lib.flint_rt_sched_create(cache.core, self.max_step_tokens, self.prefill_chunk, self.max_context,
                                                   self.page_size, self.total_pages)
         self._reqs: dict = {}                       # native handle -> Request
+        self.keep_ended = 4096                      # ended requests are forgotten when more than this many are known
         self._out = (c_int * (4 * (self.max_step_tokens + 1)))()
         self._fields = (c_int * 8)()
 
@@ -213,13 +214,20 @@ class Scheduler:
         return out
 
     def _forget_finished(self):
-        if len(self._reqs) > 4096:
-            self._reqs = {h: r for h, r in self._reqs.items() if r.state in (WAITING, RUNNING)}
+        """Let go of requests that ended long ago (their native records are then used again).  A request with
+        unread tokens is kept: its values are still to come."""
+        if len(self._reqs) > self.keep_ended:
+            for h, r in list(self._reqs.items()):
+                if r.state in (FINISHED, FAILED) and not r.n_unread:
+                    del self._reqs[h]
+                    rt.checked(self._lib.flint_rt_sched_forget(self._h, h))
 
     def resolve(self, req, token) -> bool:
         """The value of the request's oldest unread token.  True: it is the request's next token.  False: it
         is a stop token (the request ends before it; what ran after it is void), or the request has ended
         at an earlier token or was aborted and the value is dropped."""
+        if not self._known(req):
+            return False
         self._push_stop(req)
         rc = rt.checked(self._lib.flint_rt_sched_resolve(self._h, req._handle, int(token)))
         if rc == 0:
@@ -238,7 +246,18 @@ class Scheduler:
         more token of each are free: the next step can be planned before the last one's tokens are read."""
         return bool(self._lib.flint_rt_sched_steady(self._h))
 
+    def _known(self, req) -> bool:
+        """False for a request that ended and was forgotten: its native record may belong to another by now."""
+        return self._reqs.get(getattr(req, "_handle", None)) is req
+
+    @property
+    def records(self) -> int:
+        """Native request records in existence (those of forgotten requests are used again)."""
+        return self._lib.flint_rt_sched_records(self._h)
+
     def abort(self, req):
+        if not self._known(req):
+            return
         if req.n_unread:
             del req.generated[len(req.generated) - req.n_unread:]
             req.n_unread = 0

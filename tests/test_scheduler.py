@@ -282,3 +282,24 @@ def test_steady_says_when_the_next_step_needs_no_token_values():
     s.resolve(b, 9)
     s.abort(b)
     assert cache.free_pages() == 2 and s.steady()
+
+
+def test_ended_requests_are_forgotten_and_their_records_used_again():
+    """A long-running scheduler does not grow with the number of requests it has served."""
+    cache, s = setup(n_pages=16, slots=4, budget=32, chunk=16)
+    s.keep_ended = 4
+    done = []
+    for i in range(60):
+        r = req(i, 3 + i % 5, max_tokens=2)
+        run(s, [r])
+        assert r.state == FINISHED and len(r.generated) == 2
+        done.append(r)
+    assert s.records <= 8
+    s.abort(done[0])                       # a forgotten request: nothing happens, least of all to its record's new owner
+    assert s.resolve(done[0], 5) is False
+    live = req(100, 4, max_tokens=3)
+    s.add(live)
+    s.abort(done[1])
+    run(s, [])
+    assert live.state == FINISHED and len(live.generated) == 3
+    assert cache.free_slots == 4 and cache.free_pages() == 16
