@@ -108,6 +108,15 @@ def build_model(cfg, max_slots, ctx, device="cuda:0"):
                  max_slots=max_slots, max_context=ctx, max_step_tokens=2048 + max_slots)
 
 
+def checked(model, logits, what):
+    """A timed region counts only if no kernel raised a flag in it (a bounded wait that ran out, a position
+    without a page) and its last logits are finite numbers."""
+    import torch
+    model.check_status()
+    if logits is not None and not bool(torch.isfinite(logits).all()):
+        raise SystemExit(f"bench.py: {what} produced logits that are not finite; no number is reported")
+
+
 def step_flops(cfg, n_tokens, kv_lens):
     """Multiply-add flops x2 of one step: projections, attention over the cache, router, two experts."""
     H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
@@ -165,9 +174,10 @@ def run_decode(model, cfg, batch, prompt_len, steps, warmup, rng, count_experts=
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        one()
+        last = one()
     e1.record()
     torch.cuda.synchronize()
+    checked(model, last, f"decoding at batch {batch}")
     ms = e0.elapsed_time(e1) / steps
     launches = model.ops.launches - l0
     kv_lens = [pos] * batch
@@ -188,9 +198,10 @@ def run_prefill(model, cfg, n_tokens, reps, warmup, rng):
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        model.step([StepEntry(s, 0, toks, [n_tokens - 1])])
+        last = model.step([StepEntry(s, 0, toks, [n_tokens - 1])])
         e1.record()
         torch.cuda.synchronize()
+        checked(model, last, f"the prefill of {n_tokens} tokens")
         if i >= warmup:
             times.append(e0.elapsed_time(e1))
         model.cache.release(s)

@@ -217,13 +217,18 @@ def expert_mlp(x, w1, w3, w2, act="silu"):
 def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None, forced=None):
     """x [T,H] -> sum over the two selected experts of gate * expert(x).
 
+    The routing is decided token by token; each expert then runs once on all the rows that chose it
+    (the same arithmetic per row as one call per token, and fast enough for real layer sizes).
+
     ``forced`` (tests of reduced-precision engines): per token an engine's decision
     (i1, i2, g1, g2).  Where it differs from this function's own decision, the engine's
     is used and the record notes the difference with this row's fragility, so that a test
     can require every difference to be a near-tie."""
-    out = torch.zeros_like(x)
+    T = x.shape[0]
     logits = x @ router_w.T
-    for t in range(x.shape[0]):
+    chosen = torch.zeros((T, 2), dtype=torch.long)
+    gates = torch.zeros((T, 2), dtype=x.dtype)
+    for t in range(T):
         i1, g1, i2, g2 = sparsemixer_top2(logits[t], jitter_eps)
         differs = False
         if forced is not None:
@@ -233,10 +238,15 @@ def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None, 
                 i1, i2, g1, g2 = f1, f2, fg1, fg2
         if record is not None:
             record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps), differs))
-        y1 = expert_mlp(x[t:t + 1], *experts[i1], act=act)[0]
-        y2 = expert_mlp(x[t:t + 1], *experts[i2], act=act)[0]
-        out[t] = g1 * y1 + g2 * y2
-    return out
+        chosen[t, 0], chosen[t, 1] = i1, i2
+        gates[t, 0], gates[t, 1] = g1, g2
+    y = torch.zeros((2,) + tuple(x.shape), dtype=x.dtype)          # y[c, t] = expert chosen[t, c] applied to x[t]
+    for e, (w1, w3, w2) in enumerate(experts):
+        for c in range(2):
+            rows = torch.nonzero(chosen[:, c] == e).flatten()
+            if rows.numel():
+                y[c, rows] = expert_mlp(x[rows], w1, w3, w2, act=act)
+    return gates[:, 0:1] * y[0] + gates[:, 1:2] * y[1]
 
 
 # ----------------------------------------------------------------------------- model
@@ -248,9 +258,10 @@ def norm_eps_of(cfg):
     return 1e-5
 
 
-def forward(cfg, w, token_ids, record_experts=None, forced_routing=None):
+def forward(cfg, w, token_ids, record_experts=None, forced_routing=None, logit_rows=None):
     """Logits [T, V] of one whole sequence (order of operations as
-    crates/thuban_architectures/src/transformer/forward.rs:88-468)."""
+    crates/thuban_architectures/src/transformer/forward.rs:88-468).  ``logit_rows``: only these
+    positions go through the final norm and the output head ([len(logit_rows), V])."""
     H = cfg["hidden_size"]
     nq = cfg["num_attention_heads"]
     nkv = cfg["num_key_value_heads"]
@@ -285,6 +296,8 @@ def forward(cfg, w, token_ids, record_experts=None, forced_routing=None):
                                  forced_routing[l] if forced_routing is not None else None)
         if record_experts is not None:
             record_experts.append(rec)
+    if logit_rows is not None:
+        h = h[torch.as_tensor(list(logit_rows), dtype=torch.long)]
     x = layer_norm(h, w["norm.weight"], w.get("norm.bias"), eps)
     head = w["embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return linear(x, head, w.get("lm_head.bias"))

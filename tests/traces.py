@@ -13,27 +13,35 @@ def _step(i, entries, end=()):
     return {"step": i, "entries": entries, "end": list(end)}
 
 
-def whole(reqs):
-    """Each request alone and whole, logits at every place."""
-    return [_step(i, [{"id": rid, "tokens": t, "want": list(range(len(t)))}], [rid])
+def _wanted(rid, start, places, keep):
+    """``places`` (indices into a portion that starts at position ``start``) restricted to the
+    positions that ``keep`` (request id -> set of positions, or None for all) names."""
+    if keep is None:
+        return list(places)
+    return [w for w in places if start + w in keep[rid]]
+
+
+def whole(reqs, keep=None):
+    """Each request alone and whole, logits at every place (or at the kept positions)."""
+    return [_step(i, [{"id": rid, "tokens": t, "want": _wanted(rid, 0, range(len(t)), keep)}], [rid])
             for i, (rid, t) in enumerate(reqs.items())]
 
 
-def tail_decoded(reqs, tail=32):
+def tail_decoded(reqs, tail=32, keep=None):
     """All but the last ``tail`` tokens in one step, then the rest one token per step."""
     steps = []
     for rid, t in reqs.items():
         head = max(len(t) - tail, 1)
-        steps.append(_step(len(steps), [{"id": rid, "tokens": t[:head], "want": [head - 1]}]))
+        steps.append(_step(len(steps), [{"id": rid, "tokens": t[:head], "want": _wanted(rid, 0, [head - 1], keep)}]))
         for j in range(head, len(t)):
-            steps.append(_step(len(steps), [{"id": rid, "tokens": [t[j]], "want": [0]}],
+            steps.append(_step(len(steps), [{"id": rid, "tokens": [t[j]], "want": _wanted(rid, j, [0], keep)}],
                                [rid] if j == len(t) - 1 else []))
         if head == len(t):
             steps[-1]["end"] = [rid]
     return steps
 
 
-def portions(reqs, sizes=(7, 2, 13, 3, 5, 2, 16, 1, 2, 31, 2, 64)):
+def portions(reqs, sizes=(7, 2, 13, 3, 5, 2, 16, 1, 2, 31, 2, 64), keep=None):
     """Portions of changing size, down to two tokens, logits everywhere."""
     steps = []
     for rid, t in reqs.items():
@@ -41,13 +49,13 @@ def portions(reqs, sizes=(7, 2, 13, 3, 5, 2, 16, 1, 2, 31, 2, 64)):
         while i < len(t):
             n = min(sizes[k % len(sizes)], len(t) - i)
             k += 1
-            steps.append(_step(len(steps), [{"id": rid, "tokens": t[i:i + n], "want": list(range(n))}],
+            steps.append(_step(len(steps), [{"id": rid, "tokens": t[i:i + n], "want": _wanted(rid, i, range(n), keep)}],
                                [rid] if i + n == len(t) else []))
             i += n
     return steps
 
 
-def mixed(reqs, seed=0, max_live=4, decode_tail=12):
+def mixed(reqs, seed=0, max_live=4, decode_tail=12, sizes=(2, 2, 3, 5, 8, 16, 33), keep=None):
     """Up to ``max_live`` live requests; each step takes portions of some beside single tokens of
     others; some requests sit a step out; finished requests leave and new ones come in."""
     rnd = random.Random(seed)
@@ -67,9 +75,9 @@ def mixed(reqs, seed=0, max_live=4, decode_tail=12):
             if left <= decode_tail:
                 n = 1
             else:
-                n = min(rnd.choice([2, 2, 3, 5, 8, 16, 33]), left - decode_tail)
+                n = min(rnd.choice(list(sizes)), left - decode_tail)
             want = sorted(set(rnd.sample(range(n), k=min(n, rnd.choice([0, 1, 2, n])))) | ({n - 1} if n == 1 else set()))
-            entries.append({"id": rid, "tokens": t[done:done + n], "want": want})
+            entries.append({"id": rid, "tokens": t[done:done + n], "want": _wanted(rid, done, want, keep)})
             live[rid] = done + n
             if live[rid] == len(t):
                 end.append(rid)
