@@ -184,7 +184,8 @@ class CudaOps:
                 tmp = torch.empty((T, H), dtype=torch.float32, device=x.device)
             self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
             if router is not None:
-                self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates)
+                self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates,
+                                        getattr(router, "logits", None))
             return
         rows = row_index.numel() if row_index is not None else T
         for o, dt in ((out_f32, torch.float32), (out_bf16, torch.bfloat16)):
@@ -208,17 +209,23 @@ class CudaOps:
                 _check(y, "pending expert rows", torch.float32, 2)
                 if y.shape[1] != H or row_of.numel() != 2 * T or gts.numel() != 2 * T:
                     raise KernelError("row_norm: pending expert rows do not match the residual")
-        wr = wcode = None
+        wr = logits = None
         E, jit, ids, gates = 0, 0.0, None, None
         if router is not None:
             wr, E, jit, ids, gates = router.weight, router.weight.shape[0], router.jitter_eps, router.expert_ids, router.gates
+            logits = getattr(router, "logits", None)
+            if logits is not None:
+                _check(logits, "router logits", torch.float32, 2)
+                if tuple(logits.shape) != (T, E):
+                    raise KernelError(f"row_norm: router logits must be [{T}, {E}]")
             _check(wr, "router weight", dims=2)
             if wr.shape[1] != H or ids.numel() != 2 * T or gates.numel() != 2 * T:
                 raise KernelError("row_norm: router shapes do not match")
         self._run("row_fused", "flint_row_norm", _ptr(x), _ptr(row_index), c_int(rows), c_int(H), _ptr(partials),
                   c_int(S), c_longlong(stride), _ptr(bias), _ptr(y), _ptr(row_of), _ptr(gts), _ptr(gamma), _ptr(beta),
                   c_float(eps), c_int({"layer": 0, "rms": 1}[mode]), _ptr(out_f32), _ptr(out_bf16), _ptr(wr),
-                  c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates))
+                  c_int(_code(wr.dtype) if wr is not None else 0), c_int(E), c_float(jit), _ptr(ids), _ptr(gates),
+                  _ptr(logits))
 
     def apply_pending(self, x, pending):
         """x += what a part left pending (for a norm that cannot take it along)."""

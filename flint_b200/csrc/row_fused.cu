@@ -30,6 +30,7 @@ struct RowArgs {
   const float* gamma; const float* beta; float eps; int mode;
   float* out_f32; __nv_bfloat16* out_bf16;
   const void* wr; int E; float jitter_eps; int* expert_ids; float* gates;
+  float* router_logits;        // optional [rows, E]: the logits the selection was made from (for tests)
   int H;
 };
 
@@ -270,6 +271,7 @@ row_norm_kernel(const RowArgs a) {
     if (lane < E) {
       sv = 0.f;
       for (int i = 0; i < k; ++i) sv += part[lane * k + i];    // fixed order
+      if (a.router_logits) a.router_logits[(size_t)r * E + lane] = sv;
     }
     select_two_by_lanes(sv, lane, E, a.jitter_eps, a.expert_ids + 2 * r, a.gates + 2 * r);
     return;
@@ -280,6 +282,7 @@ row_norm_kernel(const RowArgs a) {
     float t = 0.f;
     for (int i = 0; i < k; ++i) t += part[e * k + i];    // fixed order
     s[e] = t;
+    if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
   }
   select_two_serial(s, E, a.jitter_eps, a.expert_ids + 2 * r, a.gates + 2 * r);
 }
@@ -499,6 +502,7 @@ row_norm_cluster_kernel(const RowArgs a, const int vec_per_block) {
     if (lane < E) {
       sv = 0.f;
       for (uint32_t q = 0; q < CL; ++q) sv += logit_slots[q * E + lane];    // fixed order
+      if (a.router_logits) a.router_logits[(size_t)r * E + lane] = sv;
     }
     select_two_by_lanes(sv, lane, E, a.jitter_eps, a.expert_ids + 2 * r, a.gates + 2 * r);
     return;
@@ -508,6 +512,7 @@ row_norm_cluster_kernel(const RowArgs a, const int vec_per_block) {
     float t = 0.f;
     for (uint32_t q = 0; q < CL; ++q) t += logit_slots[q * E + e];
     s[e] = t;
+    if (a.router_logits) a.router_logits[(size_t)r * E + e] = t;
   }
   select_two_serial(s, E, a.jitter_eps, a.expert_ids + 2 * r, a.gates + 2 * r);
 }
@@ -561,13 +566,14 @@ extern "C" int flint_row_norm_set_cluster_rows(int rows) {
 // pending: partials [n_partials][T][H] (stride partial_stride floats) + add_bias [H]; and/or
 //          comb_y [2T, H] with comb_row_of [T, 2] and comb_gates [T, 2].
 // gamma NULL: only apply the pending additions.  wr != NULL (router weights [E, H], bf16 or f32):
-// also fill expert_ids [rows, 2] and gates [rows, 2]; then row_index must be NULL.
+// also fill expert_ids [rows, 2] and gates [rows, 2] (and router_logits [rows, E] if given); then row_index
+// must be NULL.
 extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, const float* partials,
                               int n_partials, long long partial_stride, const float* add_bias,
                               const float* comb_y, const int* comb_row_of, const float* comb_gates,
                               const float* gamma, const float* beta, float eps, int mode, float* out_f32,
                               void* out_bf16, const void* wr, int w_dtype, int E, float jitter_eps,
-                              int* expert_ids, float* gates, cudaStream_t stream) {
+                              int* expert_ids, float* gates, float* router_logits, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (H <= 0 || (H & 3) || H > 4 * 1024 * MAX_VPT) return fail("row_norm: width %d (multiples of 4 up to %d)", H, 4096 * MAX_VPT);
   if (gamma && !out_f32 && !out_bf16 && !wr) return fail("row_norm: no output given");
@@ -582,6 +588,7 @@ extern "C" int flint_row_norm(float* x, const int* row_index, int rows, int H, c
   a.gamma = gamma; a.beta = beta; a.eps = eps; a.mode = mode;
   a.out_f32 = out_f32; a.out_bf16 = (__nv_bfloat16*)out_bf16;
   a.wr = wr; a.E = E; a.jitter_eps = jitter_eps; a.expert_ids = expert_ids; a.gates = gates;
+  a.router_logits = wr ? router_logits : nullptr;
   a.H = H;
   const int n4 = H / 4;
   // a handful of rows: a cluster of blocks per row

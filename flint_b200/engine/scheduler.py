@@ -114,14 +114,11 @@ class Scheduler:
         """Bring a Request in step with its native record."""
         f = self._fields
         self._lib.flint_rt_sched_request(self._h, req._handle, f)
-        slot_before = req.slot
         _, req.n_cached, req.slot, state, reason, req.preemptions, req.prefill_tokens, req.decode_tokens = f
         req.state = self._STATES[state]
         req.finish_reason = self._REASONS[reason]
         if req.state == FAILED and req.error is None:
             req.error = (self._lib.flint_rt_sched_request_error(self._h, req._handle) or b"").decode()
-        if req.slot >= 0 and req.slot != slot_before and self.cache.state:
-            self.cache.reset_state(req.slot)        # a newly admitted request starts from zeroed state
 
     def _push_stop(self, req: Request):
         stop = tuple(int(t) for t in req.stop)
@@ -178,6 +175,11 @@ class Scheduler:
         self._pull_touched()                        # preempted or failed
         for p in portions:                          # admitted or just planned
             self._pull(p.request)
+            # A portion that starts at position 0 belongs to a request that was admitted in this plan, for the
+            # first time or again after a preemption (possibly in this same plan, and possibly into the slot it
+            # had before): its fixed-size state starts from zero.  The slot alone cannot tell.
+            if p.start == 0 and self.cache.state:
+                self.cache.reset_state(p.request.slot)
         return portions
 
     def _pull_touched(self):

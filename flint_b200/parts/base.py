@@ -51,11 +51,13 @@ class Pending:
 class RouterRequest:
     """What a feed-forward asks a norm to compute while the normalised row is at hand: router
     logits over ``weight`` [E, H], sparsemixer top-2 with ``jitter_eps``, into ``expert_ids`` and
-    ``gates`` ([T, 2] each)."""
+    ``gates`` ([T, 2] each).  ``logits`` ([T, E] float32, optional): the logits the choice was made from
+    are written there too (tests compare them)."""
     weight: torch.Tensor
     jitter_eps: float
     expert_ids: torch.Tensor
     gates: torch.Tensor
+    logits: torch.Tensor | None = None
 
 
 @dataclass

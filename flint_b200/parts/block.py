@@ -7,6 +7,8 @@ An arrangement only orders parts; it does not know what they are.
 """
 from __future__ import annotations
 
+import torch
+
 from ..registry import BLOCKS
 
 
@@ -56,6 +58,9 @@ class PreNormBlock(Block):
         x, _ = run_norm(p["norm1"], residual, mixer.input_dtypes(), carry)
         pend = mixer.forward(x, residual, step, cache, state, writes_cache)
         request = ffn.router_request(residual.shape[0]) if hasattr(ffn, "router_request") else None
+        if request is not None and step.record is not None and getattr(request, "logits", 0) is None:
+            # a test asked for this step's internals: the logits behind the routing come along
+            request.logits = request.weight.new_empty((residual.shape[0], request.weight.shape[0]), dtype=torch.float32)
         want = ffn.input_dtypes_when_routed() if request is not None and p["norm2"].supports_router \
             else ffn.input_dtypes()
         x, routed = run_norm(p["norm2"], residual, want, pend, request)

@@ -96,11 +96,12 @@ class SparseMixerMoE(FeedForward):
         T = xa.shape[0]
         dev = xa.device
         if routed is not None:
-            ids, gates = routed.expert_ids, routed.gates
+            ids, gates, logits = routed.expert_ids, routed.gates, routed.logits
         else:
             ids = torch.empty((T, 2), dtype=torch.int32, device=dev)
             gates = torch.empty((T, 2), dtype=torch.float32, device=dev)
-            ops.router_sparsemixer(x[torch.float32], self.w_router, self.eps, ids, gates)
+            logits = torch.empty((T, self.E), dtype=torch.float32, device=dev) if step.record is not None else None
+            ops.router_sparsemixer(x[torch.float32], self.w_router, self.eps, ids, gates, logits)
         plan, xs = ops.moe_dispatch(ids, self.E, ops.moe_tile_rows(T, self.E, self.w13.dtype), xa)
         a = torch.empty((2 * T, self.inter), dtype=self.w13.dtype, device=dev)
         ops.gated_gemm(xs, self.w13, a, self.act, plan)
@@ -109,5 +110,7 @@ class SparseMixerMoE(FeedForward):
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
             step.record.setdefault("gates", []).append(gates)
+            if logits is not None:
+                step.record.setdefault("router_logits", []).append(logits)
         # the gated sum of the two experts' rows is added by the next norm's kernel
         return Pending(y=y, row_of=plan.row_of, gates=gates)

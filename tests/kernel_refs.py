@@ -66,7 +66,8 @@ class RefOps:
             tmp = torch.empty((x.shape[0], x.shape[1]), dtype=torch.float32)
         self.norm(x, gamma, beta, eps, mode, out_f32=tmp, out_bf16=out_bf16, row_index=row_index)
         if router is not None:
-            self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates)
+            self.router_sparsemixer(tmp, router.weight, router.jitter_eps, router.expert_ids, router.gates,
+                                    getattr(router, "logits", None))
 
     def apply_pending(self, x, pending):
         if pending.partials is not None:

@@ -223,7 +223,8 @@ def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None, 
     ``forced`` (tests of reduced-precision engines): per token an engine's decision
     (i1, i2, g1, g2).  Where it differs from this function's own decision, the engine's
     is used and the record notes the difference with this row's fragility, so that a test
-    can require every difference to be a near-tie."""
+    can require every difference to be a near-tie.  A record entry is (i1, i2, g1, g2, fragility,
+    differs, this row's router logits)."""
     T = x.shape[0]
     logits = x @ router_w.T
     chosen = torch.zeros((T, 2), dtype=torch.long)
@@ -237,7 +238,7 @@ def moe_feed_forward(x, router_w, experts, jitter_eps, act="silu", record=None, 
             if differs:
                 i1, i2, g1, g2 = f1, f2, fg1, fg2
         if record is not None:
-            record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps), differs))
+            record.append((i1, i2, float(g1), float(g2), routing_fragility(logits[t], jitter_eps), differs, logits[t]))
         chosen[t, 0], chosen[t, 1] = i1, i2
         gates[t, 0], gates[t, 1] = g1, g2
     y = torch.zeros((2,) + tuple(x.shape), dtype=x.dtype)          # y[c, t] = expert chosen[t, c] applied to x[t]

@@ -43,7 +43,7 @@ def test_replay_matches_plain_under_every_cut(setup, cut, page_size):
     steps = {"whole": traces.whole, "tail": traces.tail_decoded, "portions": traces.portions,
              "mixed": lambda r: traces.mixed(r, seed=3)}[cut](reqs)
     out, rp = replay(folder, dtype, steps, page_size)
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, router_logits=rp.router_logits)
     if cut == "mixed":
         assert max(max(g.pages.pool.served) for g in rp.model.cache.groups) >= 2, "no page was used again"
 
@@ -94,7 +94,7 @@ def test_long_decoding_and_first_tokens(setup):
     assert all(len(e["tokens"]) == 1 for s in steps for e in s["entries"])
     out, rp = replay(folder, dtype, steps, 16)
     assert len(rp.model._graphs) >= 1, "decode steps did not go through the captured graph"
-    compare(out, steps, plain, dtype, rp.routing, one, folder)
+    compare(out, steps, plain, dtype, rp.routing, one, folder, router_logits=rp.router_logits)
 
 
 def test_greedy_generation_through_the_entry_point(setup):
@@ -244,6 +244,6 @@ def test_trace_run_as_a_program(tmp_path, dtype):
         if n:
             out[s["step"]] = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(n, 384))
     inproc, rp = replay(folder, dtype, steps, 64)        # the same trace in this process, for its routing
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, router_logits=rp.router_logits)
     for k in out:
         assert (out[k] - inproc[k]).abs().max().item() <= 1e-2 * float(plain["r3"].abs().max())

@@ -78,7 +78,7 @@ def test_real_sizes_match_plain_under_every_cut(big, cut, dtype):
                    and min(len(e["tokens"]) for e in s["entries"]) == 1 for s in steps), \
             "the trace has no 2,048-token portion beside a decoded token"
     out, rp = replay(folder, dtype, steps, 64)
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -94,4 +94,4 @@ def test_real_sizes_eight_requests_decoded_together(big, dtype):
                       "entries": [{"id": rid, "tokens": [t[len(t) - tail + j]], "want": [0]} for rid, t in reqs.items()]})
     out, rp = replay(folder, dtype, steps, 64, max_requests=8)
     assert any(k[0] == 8 for k in rp.model._graphs), "the batch of eight did not go through the captured graph"
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits)

@@ -303,3 +303,33 @@ def test_ended_requests_are_forgotten_and_their_records_used_again():
     run(s, [])
     assert live.state == FINISHED and len(live.generated) == 3
     assert cache.free_slots == 4 and cache.free_pages() == 16
+
+
+def test_a_request_preempted_and_admitted_again_in_one_plan_starts_from_zeroed_state():
+    """With two pages, the older request's next page costs the younger one its place; the same plan then
+    admits the younger one again, into the slot it just gave back.  Its fixed-size state must start from
+    zero all the same (a scripted mixer marks the state of every request that ran)."""
+    from flint_b200.cache.manager import StateSpec
+    cache = CacheManager({0: KVSpec(1, 16, 0)}, {0: StateSpec((4,))}, page_size=16, n_pages=2, max_slots=2,
+                         max_context=256, dtype=torch.float32, device="cpu")
+    s = Scheduler(cache, max_step_tokens=24, prefill_chunk=8)
+    a, b = req(0, 10, 12), req(1, 16, 6)
+    s.add(a)
+    s.add(b)
+    same_slot_again = 0
+    for _ in range(300):
+        if not s.has_work():
+            break
+        before = {r.id: (r.slot, r.preemptions) for r in (a, b)}
+        portions = s.plan()
+        for p in portions:
+            r = p.request
+            if p.start == 0:
+                assert float(cache.state[0][r.slot].abs().sum()) == 0.0, "a request starts on another run's state"
+                if r.preemptions > before[r.id][1] and r.slot == before[r.id][0]:
+                    same_slot_again += 1
+            cache.state[0][r.slot] += 1.0                  # the scripted mixer's running state
+        s.commit(portions, [next_token(p.request) for p in portions if p.wants_logits])
+        cache.check()
+    assert same_slot_again > 0, "the scenario did not come about"
+    assert a.state == FINISHED and b.state == FINISHED
