@@ -38,6 +38,14 @@ LENGTHS = (300, 700, 2100, 4200)                 # the last one crosses the orig
 SHORT = (40, 75, 130, 61, 222, 97, 160, 33)      # eight more, decoded together
 
 
+# With random weights of these sizes a router logit carries about 0.6 % of bfloat16 noise (the attention's
+# probabilities, keys and values are all rounded), and the gaps between the sixteen logits of a row are dense
+# enough near zero that several per cent of the decisions sit inside that noise.  Every differing decision
+# still has to be proven a near-tie from the engine's own router logits (engine_checks.plain_following); this
+# only bounds how many there may be.
+DIFFERING = {"float32": 0.0005, "bfloat16": 0.10}
+
+
 def kept_positions(n):
     """The positions of a request of n tokens whose logits are compared: the first ones, every 61st, the
     ones around the original context's end, and the last 36 (all of the decoded tail)."""
@@ -78,7 +86,7 @@ def test_real_sizes_match_plain_under_every_cut(big, cut, dtype):
                    and min(len(e["tokens"]) for e in s["entries"]) == 1 for s in steps), \
             "the trace has no 2,048-token portion beside a decoded token"
     out, rp = replay(folder, dtype, steps, 64)
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits, DIFFERING[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -94,4 +102,4 @@ def test_real_sizes_eight_requests_decoded_together(big, dtype):
                       "entries": [{"id": rid, "tokens": [t[len(t) - tail + j]], "want": [0]} for rid, t in reqs.items()]})
     out, rp = replay(folder, dtype, steps, 64, max_requests=8)
     assert any(k[0] == 8 for k in rp.model._graphs), "the batch of eight did not go through the captured graph"
-    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits, DIFFERING[dtype])
