@@ -52,6 +52,7 @@ struct Params {
   int* error_flag;
   int max_pages, page_size, nq, nkv, hd, window;
   float scale_log2;          // scale * log2(e)
+  long long wait_cycles;     // limit of every wait on an mbarrier
 };
 
 __device__ __forceinline__ uint32_t idesc_f16(int n, int b_mn_major) {
@@ -175,7 +176,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // one operand (keys or values) of tile i into its half of stage i % STAGES
     auto load_tile = [&](int i, bool values) -> bool {
       const int s = i % STAGES;
-      if (!mbar_wait((values ? bar_vempty0 : bar_kempty0) + 8 * s, ((i / STAGES) & 1) ^ 1, ab)) return false;
+      if (!mbar_wait((values ? bar_vempty0 : bar_kempty0) + 8 * s, ((i / STAGES) & 1) ^ 1, ab, p.wait_cycles)) return false;
       const uint32_t bar = (values ? bar_vfull0 : bar_kfull0) + 8 * s;
       mbar_expect_tx(bar, kv_stage_bytes / 2);
       const uint32_t dst = kv_smem + s * kv_stage_bytes + (values ? chunks * BKV * 128 : 0);
@@ -202,11 +203,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   } else if (warp == 1 && lane == 0) {
     // ---------------------------------------------------------------- MMA issue
     const uint32_t idesc_s = idesc_f16(BKV, 0), idesc_o = idesc_f16(hd, 1);
-    bool ok = mbar_wait(bar_q, 0, ab);
+    bool ok = mbar_wait(bar_q, 0, ab, p.wait_cycles);
     // S_i = Q K_i^T into score buffer i & 1, as soon as the keys of tile i have landed
     auto issue_scores = [&](int i) -> bool {
       const int s = i % STAGES;
-      if (!mbar_wait(bar_kfull0 + 8 * s, (i / STAGES) & 1, ab)) return false;
+      if (!mbar_wait(bar_kfull0 + 8 * s, (i / STAGES) & 1, ab, p.wait_cycles)) return false;
       tc_fence_after();
       const uint32_t k_src = kv_smem + s * kv_stage_bytes;
       for (int k = 0; k < hd / 16; ++k) {
@@ -223,10 +224,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // the next tile's scores first: their buffer was last read for tile i-1, whose P has been handed over
       if (i + 1 < n_kv_tiles) ok = issue_scores(i + 1);
       if (!ok) break;
-      ok = mbar_wait(bar_p, i & 1, ab);         // P is in shared memory, S has been read, O is rescaled
+      ok = mbar_wait(bar_p, i & 1, ab, p.wait_cycles);         // P is in shared memory, S has been read, O is rescaled
       if (!ok) break;
       const int s = i % STAGES;
-      ok = mbar_wait(bar_vfull0 + 8 * s, (i / STAGES) & 1, ab);
+      ok = mbar_wait(bar_vfull0 + 8 * s, (i / STAGES) & 1, ab, p.wait_cycles);
       if (!ok) break;
       tc_fence_after();
       const uint32_t v_src = kv_smem + s * kv_stage_bytes + chunks * BKV * 128;
@@ -250,7 +251,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float ref = -1e30f, l = 0.f;                    // reference of the exponentials, sum of P
     bool ok = true;
     for (int i = 0; i < n_kv_tiles && ok; ++i) {
-      ok = mbar_wait(bar_s0 + 8 * (i & 1), (i >> 1) & 1, ab);
+      ok = mbar_wait(bar_s0 + 8 * (i & 1), (i >> 1) & 1, ab, p.wait_cycles);
       if (!ok) break;
       tc_fence_after();
       const int kv0 = (tile_lo + i) * BKV;
@@ -274,7 +275,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const float mx = fmaxf(ref, mraw * p.scale_log2);
       // P V of the previous tile must be done before O is touched or P's buffer is written again
       if (i > 0) {
-        ok = mbar_wait(bar_o, (i - 1) & 1, ab);
+        ok = mbar_wait(bar_o, (i - 1) & 1, ab, p.wait_cycles);
         if (!ok) break;
         tc_fence_after();
       }
@@ -327,7 +328,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       mbar_arrive(bar_p);
     }
-    if (ok) ok = mbar_wait(bar_o, (n_kv_tiles - 1) & 1, ab);
+    if (ok) ok = mbar_wait(bar_o, (n_kv_tiles - 1) & 1, ab, p.wait_cycles);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -393,6 +394,7 @@ struct DecodeParams {
   int n_rows, max_pages, page_size, nq, nkv, hd, window, split_keys, n_splits, g_chunks;
   int fresh_keys;    // at most this many of a row's newest keys (its own included) are written by the kernel before
   float scale;
+  long long wait_cycles;     // limit of every wait on an mbarrier
 };
 
 // Merge records [0, n_rec) of the ng query heads of one item, by a whole block of 128 threads:
@@ -548,7 +550,7 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       if (!mbar_try_wait(bar, parity)) {
         const long long t0 = clock64();
         while (!mbar_try_wait(bar, parity))
-          if (clock64() - t0 > WAIT_CYCLES) { failed = 1; break; }
+          if (clock64() - t0 > p.wait_cycles) { failed = 1; break; }
       }
     }
     if (__any_sync(0xffffffffu, failed)) break;
@@ -874,7 +876,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         if (!mbar_try_wait(bar, parity)) {
           const long long t0 = clock64();
           while (!mbar_try_wait(bar, parity))
-            if (clock64() - t0 > WAIT_CYCLES) { failed = 1; break; }
+            if (clock64() - t0 > p.wait_cycles) { failed = 1; break; }
         }
       }
       failed = __any_sync(0xffffffffu, failed) ? 1 : 0;
@@ -983,6 +985,7 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   p.tiles = tiles; p.block_table = block_table; p.out = (__nv_bfloat16*)out; p.error_flag = error_flag;
   p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.wait_cycles = wait_limit();
   const int chunks = (hd + 63) / 64;
   const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128;
   dim3 grid(n_tiles, nq);
@@ -1031,6 +1034,7 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
   p.window = window; p.split_keys = split_keys; p.n_splits = n_splits;
   p.g_chunks = (nq / nkv + 7) / 8;
   p.scale = scale;
+  p.wait_cycles = wait_limit();
   // with splits in fours and a counter for every (row, kv head, chunk of query heads) the pieces are merged by
   // the block that finishes last; else by a kernel of its own
   p.arrivals = (arrivals && n_splits % 4 == 0 && (long long)T * nkv * p.g_chunks <= n_arrivals) ? arrivals : nullptr;
@@ -1090,6 +1094,7 @@ extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache,
   p.window = window; p.split_keys = 0; p.n_splits = n_slices;
   p.g_chunks = (nq / nkv + 7) / 8;
   p.scale = scale;
+  p.wait_cycles = wait_limit();
   p.arrivals = nullptr;
   p.fresh_keys = fresh_keys < 1 ? 1 : fresh_keys;
   static int sm_count = 0;
@@ -1115,5 +1120,8 @@ extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache,
              dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_slices, nq, row_list);
   return check_launch("attention_combine");
 }
+
+// The limit (clock cycles) that later launches of this module give their waits; 0 restores the default.
+extern "C" void flint_attention_tc_set_wait_cycles(long long cycles) { wait_limit() = cycles > 0 ? cycles : WAIT_CYCLES; }
 
 extern "C" const char* flint_attention_tc_last_error() { return g_error; }

@@ -67,6 +67,7 @@ struct Params {
   int defer;                   // write raw partial tiles even for a single split; the consumer sums them
   int stream_k;                // cut the K blocks of all tiles, laid end to end, into equal runs, one per block
   int w_expert_rows;           // rows between two experts in the stacked weight tensor
+  long long wait_cycles;       // limit of every wait on an mbarrier
 };
 
 // Instruction descriptor, kind::f16: fp32 accumulator, bf16 A and B, both K-major, M = 128, N = bn.
@@ -220,7 +221,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       for (; i < w.nkb; ++i, ++kc) {
         const int s = kc % stages;
-        if (!mbar_wait(empty0 + 8 * s, ((kc / stages) & 1) ^ 1, ab)) { ok = false; break; }
+        if (!mbar_wait(empty0 + 8 * s, ((kc / stages) & 1) ^ 1, ab, p.wait_cycles)) { ok = false; break; }
         const uint32_t a = tiles + s * STAGE_BYTES, bar = full0 + 8 * s;
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (w.kb0 + i) * BK;
@@ -236,14 +237,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const Item w = item_at(j);
       if (!w.valid) break;
       const int buf = j & 1;
-      ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, ab);     // the epilogue has drained this set
+      ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, ab, p.wait_cycles);     // the epilogue has drained this set
       if (!ok) break;
       tc_fence_after();
       const uint32_t acc_addr = tmem + buf * ACC_COLS;
       const uint32_t idesc = instr_desc(w.mma_n);
       for (int i = 0; i < w.nkb; ++i, ++kc) {
         const int s = kc % stages;
-        ok = mbar_wait(full0 + 8 * s, (kc / stages) & 1, ab);
+        ok = mbar_wait(full0 + 8 * s, (kc / stages) & 1, ab, p.wait_cycles);
         if (!ok) break;
         tc_fence_after();
         const uint32_t a = tiles + s * STAGE_BYTES;
@@ -265,7 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       const Item w = item_at(j);
       if (!w.valid) break;
       const int buf = j & 1;
-      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, ab)) break;
+      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, ab, p.wait_cycles)) break;
       tc_fence_after();
       if (!waited) { pdl_wait(); waited = true; }   // before reading or writing what earlier kernels touch
       // output feature of this thread: its lane of the accumulator, or, gated, one of the warp's 16
@@ -496,6 +497,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   p.rows = rows; p.N = N; p.K = K;
   p.kb_per_split = kbps; p.splits = splits; p.defer = defer; p.stream_k = stream_k;
   p.w_expert_rows = w_expert_rows;
+  p.wait_cycles = wait_limit();
   p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
   // few rows: the product streams its weights and is bound by how many bytes an SM keeps in flight and by how
   // evenly the tiles spread; four stages of 18 KB let three blocks share an SM (444 resident blocks)
@@ -518,5 +520,31 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
                                                                         out_dtype, ldo, accumulate);
   return check_launch("gemm_tc split reduce");
 }
+
+// ------------------------------------------------------------------ the bounded wait by itself
+// One thread waits, with the given limit, on an mbarrier at which nobody ever arrives: the wait runs out, the
+// thread raises the error flag exactly as the product kernels do when a wait of theirs runs out, and the kernel
+// returns.  Nothing faults and nothing hangs; tests use it to see the whole path from a wait that gave up to
+// the host's error and back to a working engine.
+__global__ void wait_probe_kernel(long long limit, int* error_flag) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait(smem_u32(&bar), 0, &abort_flag, limit)) atomicExch(error_flag, 1);
+  }
+}
+
+extern "C" int flint_gemm_tc_wait_probe(long long limit_cycles, int* error_flag, cudaStream_t stream) {
+  if (limit_cycles < 1 || limit_cycles > WAIT_CYCLES) return fail("wait probe: the limit must be 1..%lld cycles", WAIT_CYCLES);
+  if (!error_flag) return fail("wait probe: needs an error flag");
+  wait_probe_kernel<<<1, 32, 0, stream>>>(limit_cycles, error_flag);
+  return check_launch("wait probe");
+}
+
+// The limit (clock cycles) that later launches of this module give their waits; 0 restores the default.
+extern "C" void flint_gemm_tc_set_wait_cycles(long long cycles) { wait_limit() = cycles > 0 ? cycles : WAIT_CYCLES; }
 
 extern "C" const char* flint_gemm_tc_last_error() { return g_error; }

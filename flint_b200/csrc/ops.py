@@ -122,6 +122,20 @@ class CudaOps:
         self._profile = None
         return out
 
+    def wait_probe(self, limit_cycles=1_000_000):
+        """Launch a kernel whose one wait, on a barrier nobody arrives at, runs out after ``limit_cycles`` clock
+        cycles: it raises the same flag as a product kernel whose wait ran out, and returns.  Nothing faults or
+        hangs.  For tests of the path from a kernel that gave up to the host's error."""
+        self._run("gemm_tc", "flint_gemm_tc_wait_probe", c_longlong(int(limit_cycles)), _ptr(self.tc_error))
+
+    def set_wait_cycles(self, cycles=0):
+        """The limit (clock cycles) of every bounded wait in later launches of the tensor-core kernels;
+        0 restores the default of about two seconds."""
+        for module in ("gemm_tc", "attention_tc"):
+            fn = self._fn(module, f"flint_{module}_set_wait_cycles")
+            fn.restype = None
+            fn(c_longlong(int(cycles)))
+
     def preload(self, modules=None):
         """Compile and load modules ahead of their first use."""
         mods = list(modules or build.available_modules())

@@ -7,7 +7,13 @@
 
 namespace flint_tc {
 
-constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds
+constexpr long long WAIT_CYCLES = 4000000000LL;   // about two seconds: the default limit of every wait
+
+// The limit (in clock cycles) that launches of a module give their kernels' waits; a test may shorten it.
+inline long long& wait_limit() {
+  static long long cycles = WAIT_CYCLES;
+  return cycles;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -28,14 +34,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 // Bounded wait.  Returns false (and raises *abort) when the limit passes or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit = WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 255) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > WAIT_CYCLES) {
+      if (clock64() - t0 > limit) {
         *abort_flag = 1;
         return false;
       }

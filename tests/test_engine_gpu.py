@@ -151,6 +151,32 @@ def test_a_kernel_error_flag_stops_the_engine(setup):
     assert eng.generate([list(reqs["r0"])[:5]], 3)[0]     # and the engine works again afterwards
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_engine_goes_on(setup):
+    """A kernel's bounded wait really runs out (a barrier at which nobody arrives, a limit of a million cycles):
+    the kernel raises the flag and returns, the engine's next step reports it as an error, the flag is cleared,
+    and generation works again.  Nothing on the device faults or hangs."""
+    from flint_b200.errors import ModelError
+    which, dtype, folder, reqs, plain = setup
+    m = load_model(folder, dtype=dtype, page_size=16, n_pages=16, max_slots=2, max_step_tokens=24)
+    eng = Engine(m, SamplingParams.greedy(), prefill_chunk=16)
+    want = eng.generate([list(reqs["r0"])[:5]], 3)
+    assert int(m.ops.tc_error.item()) == 0
+    m.ops.wait_probe(1_000_000)
+    torch.cuda.synchronize()
+    assert int(m.ops.tc_error.item()) == 1            # the wait gave up and the kernel came back
+    sid = eng.create(list(reqs["r0"])[:5], 3)
+    with pytest.raises(ModelError, match="gave up waiting"):
+        while not eng.finished(sid):
+            eng.step()
+    eng.close(sid)
+    assert int(m.ops.tc_error.item()) == 0
+    m.ops.set_wait_cycles(50_000_000)                 # product kernels take their limit per launch
+    try:
+        assert eng.generate([list(reqs["r0"])[:5]], 3) == want
+    finally:
+        m.ops.set_wait_cycles(0)
+
+
 def test_temperature_sampling_is_reproducible_and_follows_the_host_sampler(setup):
     which, dtype, folder, reqs, plain = setup
     m = load_model(folder, dtype=dtype, page_size=16, n_pages=32, max_slots=4)

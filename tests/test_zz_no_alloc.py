@@ -4,8 +4,8 @@ Some users of this library cannot allocate device memory when they call it (thei
 all GPU memory to a pool of its own, or an allocation's device-wide synchronisation is not
 acceptable where they stand).  ``flint_paged_attention_noalloc`` serves them: the partial results
 of a split key range live in a 32 MiB array inside the library.  This test checks, on two calls
-in a row that share that array, that it returns what the ordinary entry point returns, and that
-it refuses a shape whose scratch would not fit.  The file is named so that pytest collects it
+in a row that share that array, that it returns what the ordinary entry point returns and what a plain float64 attention over the same
+cache gives, and that it refuses a shape whose scratch would not fit.  The file is named so that pytest collects it
 last.
 """
 import ctypes
@@ -33,6 +33,7 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
     from flint_b200.cache.manager import CacheView, KVSpec
     from flint_b200.csrc import build
     from flint_b200.csrc.ops import get_ops
+    from kernel_refs import RefOps
     ops = get_ops(DEV)
     lib = build.load_module("noalloc")
     lib.flint_noalloc_last_error.restype = ctypes.c_char_p
@@ -69,6 +70,13 @@ def test_noalloc_matches_the_ordinary_entry_point_twice_in_a_row(dtype):
         torch.cuda.synchronize()
         err = (got.double() - expected.double()).abs().max().item()
         assert err <= tol, f"call {call}: differs from the ordinary entry point by {err:.3e}"
+        # and against arithmetic that shares nothing with either entry point
+        plain = torch.zeros(q.shape, dtype=torch.float64)
+        RefOps(torch.float64).paged_attention(q.cpu(), CacheView(k.cpu(), v.cpu(), bt.cpu(), P, KVSpec(nkv, hd, window)),
+                                              pos.cpu(), slot.cpu(), plain, nq, nkv, hd, window, 1.0 / math.sqrt(hd),
+                                              max(lens))
+        err = (got.double().cpu() - plain).abs().max().item()
+        assert err <= tol, f"call {call}: differs from the plain attention by {err:.3e}"
     # a shape beyond the built-in array is refused with a clear error, and nothing runs
     big_T, big_splits = 4096, 64
     assert lib.flint_paged_attention_noalloc_floats(big_T, nq, hd, big_splits) * 4 > 32 * 1024 * 1024
