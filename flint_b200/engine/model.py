@@ -27,9 +27,6 @@ from ..weights.loader import load_tensors
 from ..weights.sources import SafetensorsSource, WeightSpec
 from .step import StepEntry, StepStaging
 
-_ROLE_REGISTRY = {"norm1": NORMS, "norm2": NORMS, "mixer": MIXERS, "ffn": FEED_FORWARDS}
-
-
 def registry_for_role(role: str):
     if role.startswith("norm"):
         return NORMS
@@ -56,18 +53,40 @@ class Layer:
                 out[self.spec.prefix + self.spec.names[role] + name] = ws
         return out
 
+    def fused(self):
+        out = {}
+        for role, part in self.parts.items():
+            pre = self.spec.prefix + self.spec.names[role]
+            for name, pieces in part.fused().items():
+                out[pre + name] = [pre + p for p in pieces]
+        return out
+
     def load(self, tensors):
         for role, part in self.parts.items():
             pre = self.spec.prefix + self.spec.names[role]
             part.load({name: tensors[pre + name] for name in part.weights() if pre + name in tensors})
 
 
-def expected_tensors(spec: ModelSpec, layers) -> dict:
+def expected_tensors(spec: ModelSpec, layers, final_norm) -> dict:
     """Every tensor name the model reads, with its shape and role."""
     exp = {spec.embed_name + "weight": WeightSpec((spec.vocab_size, spec.hidden_size))}
     for layer in layers:
         exp.update(layer.weights())
+    for name, ws in final_norm.weights().items():
+        exp[spec.final_norm_name + name] = ws
+    if not spec.tie_word_embeddings:
+        exp[spec.head_name + "weight"] = WeightSpec((spec.vocab_size, spec.hidden_size))
+    if spec.head_bias:
+        exp[spec.head_name + "bias"] = WeightSpec((spec.vocab_size,), role="vector")
     return exp
+
+
+def fused_tensors(layers) -> dict:
+    """Fused tensor name -> the expected tensors a checkpoint may store stacked in it."""
+    out = {}
+    for layer in layers:
+        out.update(layer.fused())
+    return out
 
 
 class Model:
@@ -89,15 +108,9 @@ class Model:
         self.layers = [Layer(ls, self.ctx) for ls in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, self.ctx)
 
-        expected = expected_tensors(spec, self.layers)
-        for name, ws in self.final_norm.weights().items():
-            expected[spec.final_norm_name + name] = ws
-        if not spec.tie_word_embeddings:
-            expected[spec.head_name + "weight"] = WeightSpec((spec.vocab_size, spec.hidden_size))
-        if spec.head_bias:
-            expected[spec.head_name + "bias"] = WeightSpec((spec.vocab_size,), role="vector")
+        expected = expected_tensors(spec, self.layers, self.final_norm)
         self.expected = expected
-        tensors = load_tensors(source, expected, dtype, self.device)
+        tensors = load_tensors(source, expected, dtype, self.device, fused_tensors(self.layers))
         self.embed_table = tensors[spec.embed_name + "weight"]
         self.head_weight = self.embed_table if spec.tie_word_embeddings else tensors[spec.head_name + "weight"]
         self.head_bias = tensors.get(spec.head_name + "bias")

@@ -62,6 +62,12 @@ class Attention(Mixer):
             w["o_proj.bias"] = vec(H)
         return w
 
+    def fused(self):
+        f = {"qkv_proj.weight": ["q_proj.weight", "k_proj.weight", "v_proj.weight"]}
+        if self.qkv_bias:
+            f["qkv_proj.bias"] = ["q_proj.bias", "k_proj.bias", "v_proj.bias"]
+        return f
+
     def load(self, t):
         dt = matmul_dtype(t["q_proj.weight"], t["k_proj.weight"], t["v_proj.weight"])
         self.w_qkv = torch.cat([t["q_proj.weight"].to(dt), t["k_proj.weight"].to(dt), t["v_proj.weight"].to(dt)], 0)

@@ -90,6 +90,11 @@ class Part:
         """name (under this part's prefix) -> WeightSpec"""
         return {}
 
+    def fused(self) -> dict:
+        """Fused tensors a checkpoint may store instead of some of ``weights()``: fused name -> the names it
+        stands for, stacked by rows in that order (all under this part's prefix)."""
+        return {}
+
     def load(self, tensors: dict):
         """Receives the tensors named by ``weights()`` (already on the device and typed
         by the loader's policy)."""

@@ -30,6 +30,9 @@ class GatedMLP(FeedForward):
         return {"gate_proj.weight": mat(self.inter, self.hidden), "up_proj.weight": mat(self.inter, self.hidden),
                 "down_proj.weight": mat(self.hidden, self.inter)}
 
+    def fused(self):
+        return {"gate_up_proj.weight": ["gate_proj.weight", "up_proj.weight"]}
+
     def load(self, t):
         dt = matmul_dtype(*t.values())
         # gate and up rows in the layout the kernels want: one product gives both

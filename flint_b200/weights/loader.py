@@ -13,7 +13,7 @@ import torch
 
 from ..errors import WeightError
 from .safetensors_io import save_safetensors
-from .sources import RandomSource, WeightSpec
+from .sources import FusedView, RandomSource, WeightSpec
 
 
 def check_names_and_shapes(source, expected: dict):
@@ -30,6 +30,7 @@ def check_names_and_shapes(source, expected: dict):
             dt = source.dtype(n)
             if s.role == "table" and dt.is_floating_point or s.role != "table" and not dt.is_floating_point:
                 wrong.append(f"{n}: expected {'an integer' if s.role == 'table' else 'a floating'} type, found {dt}")
+    wrong += list(getattr(source, "problems", ()))
     if missing or unexpected or wrong:
         lines = ["checkpoint does not match the model:"]
         if missing:
@@ -54,8 +55,11 @@ def place(t: torch.Tensor, spec: WeightSpec, compute: str, device) -> torch.Tens
     return t.to(device=device, dtype=torch.bfloat16).contiguous()
 
 
-def load_tensors(source, expected: dict, compute: str, device) -> dict:
-    """All expected tensors, checked, converted by ``place`` and moved to ``device``."""
+def load_tensors(source, expected: dict, compute: str, device, fused: dict | None = None) -> dict:
+    """All expected tensors, checked, converted by ``place`` and moved to ``device``.  ``fused``: fused tensor
+    name -> the expected tensors it may stand for, stacked by rows (see ``FusedView``)."""
+    if fused:
+        source = FusedView(source, fused, expected)
     check_names_and_shapes(source, expected)
     out = {}
     have = set(source.names())

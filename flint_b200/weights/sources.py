@@ -119,3 +119,58 @@ class RandomSource:
         else:
             t = t.mul_(spec.std)
         return t.to(self.store_dtype).to(device)
+
+
+class FusedView:
+    """A source seen through the fused tensors it may hold: where a checkpoint stores several of a part's
+    matrices stacked by rows in one tensor (q|k|v as ``qkv_proj``, gate|up as ``gate_up_proj``), the pieces
+    appear under their own names, each a run of the fused tensor's rows.  The reference splits the same way at
+    load (crates/thuban_architectures/src/phi.rs:109-160).
+
+    ``fused``: fused name -> list of piece names, in row order; the row counts come from ``expected``.
+    A fused tensor whose shape is not the pieces' rows stacked is reported in ``problems`` (and its pieces stay
+    missing), for the loader's one error message."""
+
+    def __init__(self, source, fused: dict, expected: dict):
+        self.source = source
+        self.problems = []
+        self._piece = {}                     # piece name -> (fused name, first row, rows)
+        self._hidden = set()                 # fused names that are served as pieces
+        have = set(source.names())
+        for fname, pieces in fused.items():
+            if fname not in have or any(p in have for p in pieces) or any(p not in expected for p in pieces):
+                continue                     # absent, or stored both ways (then the fused one is unexpected)
+            rows = [int(expected[p].shape[0]) for p in pieces]
+            rest = tuple(expected[pieces[0]].shape[1:])
+            want = (sum(rows), *rest)
+            found = tuple(source.shape(fname))
+            self._hidden.add(fname)
+            if found != want or any(tuple(expected[p].shape[1:]) != rest for p in pieces):
+                self.problems.append(f"{fname}: expected {want} (rows of {' | '.join(pieces)} = "
+                                     f"{' + '.join(map(str, rows))}), found {found}")
+                continue
+            r0 = 0
+            for p, n in zip(pieces, rows):
+                self._piece[p] = (fname, r0, n)
+                r0 += n
+        self._cache = (None, None)
+
+    def names(self):
+        return [n for n in self.source.names() if n not in self._hidden] + list(self._piece)
+
+    def shape(self, name):
+        if name in self._piece:
+            fname, _, n = self._piece[name]
+            return (n, *tuple(self.source.shape(fname))[1:])
+        return self.source.shape(name)
+
+    def dtype(self, name):
+        return self.source.dtype(self._piece[name][0] if name in self._piece else name)
+
+    def read(self, name, spec=None, device="cpu"):
+        if name not in self._piece:
+            return self.source.read(name, spec, device)
+        fname, r0, n = self._piece[name]
+        if self._cache[0] != fname:          # the pieces of one fused tensor are read one after the other
+            self._cache = (fname, self.source.read(fname, None, device))
+        return self._cache[1][r0:r0 + n].contiguous()

@@ -273,3 +273,36 @@ def test_trace_run_as_a_program(tmp_path, dtype):
     compare(out, steps, plain, dtype, rp.routing, reqs, folder, router_logits=rp.router_logits)
     for k in out:
         assert (out[k] - inproc[k]).abs().max().item() <= 1e-2 * float(plain["r3"].abs().max())
+
+
+@pytest.mark.parametrize("source", ["folder", "random-config"])
+def test_chat_program_prints_the_plain_arg_max_tokens(tmp_path, source):
+    """bin/flint_chat in a process of its own, token ids in and out, greedy: from a model folder, and with
+    ``--random-config FILE --seed N`` (nothing written), which must give the tokens of the folder that the
+    random-weights mode writes for the same configuration and seed."""
+    seed = 9
+    folder = tiny.write_tiny(tmp_path / "model", "A", seed=seed, dtype=torch.float32)
+    prompt = tiny.random_tokens(11, tiny.TINY_A["vocab_size"], 77)
+    if source == "folder":
+        where = ["--model", str(folder)]
+    else:
+        cfg_file = tmp_path / "only_config.json"
+        cfg_file.write_text(json.dumps(tiny.TINY_A))
+        where = ["--random-config", str(cfg_file)]
+    proc = subprocess.run([sys.executable, os.path.join(REPO, "bin", "flint_chat"), *where, "--prompt",
+                           " ".join(map(str, prompt)), "--max-tokens", "8", "--temperature", "0", "--seed", str(seed),
+                           "--dtype", "float32", "--ctx-size", "128"],
+                          capture_output=True, text=True, timeout=600, env={**os.environ, "VERIFY_IDS": "1"})
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [int(x) for x in proc.stdout.split()]
+    assert "prefill: 11 tok" in proc.stderr and "decode:" in proc.stderr
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    eos = cfg["eos_token_id"] if isinstance(cfg["eos_token_id"], list) else [cfg["eos_token_id"]]
+    toks, want = list(prompt), []
+    for _ in range(8):
+        t = int(torch.argmax(plain_phimoe.forward(cfg, w, toks)[-1]))
+        if t in eos:
+            break
+        want.append(t)
+        toks.append(t)
+    assert got == want and len(got) >= 1

@@ -96,3 +96,51 @@ def test_random_source_is_order_independent():
     b1 = s1.read("b")
     a1 = s1.read("a")
     assert torch.equal(s2.read("a"), a1) and torch.equal(s2.read("b"), b1)
+
+
+def test_fused_checkpoint_tensors_are_split_by_rows(tmp_path):
+    """A folder that stores q|k|v stacked as ``qkv_proj`` (weights and biases) loads to the same tensors as one
+    that stores them apart; a fused tensor of the wrong shape is named in the one error."""
+    d = write_random_model(tmp_path / "m", TINY_A, seed=2, dtype=torch.float32)
+    _, expected, fused = expected_from_config(TINY_A, with_fused=True)
+    apart = load_tensors(SafetensorsSource(d), expected, "float32", "cpu", fused)
+    tensors = read_safetensors(d / "model.safetensors")
+    for l in range(TINY_A["num_hidden_layers"]):
+        pre = f"model.layers.{l}.self_attn."
+        for kind in ("weight", "bias"):
+            tensors[pre + "qkv_proj." + kind] = torch.cat([tensors.pop(pre + f"{x}_proj.{kind}") for x in "qkv"], 0)
+    save_safetensors(d / "model.safetensors", tensors)
+    src = SafetensorsSource(d)
+    assert "layers.0.self_attn.q_proj.weight" not in src.names()
+    together = load_tensors(src, expected, "float32", "cpu", fused)
+    assert set(together) == set(apart) and all(torch.equal(together[k], apart[k]) for k in apart)
+    # without the rule the same folder is refused, and the message names what is missing and what is unexpected
+    with pytest.raises(WeightError, match="qkv_proj"):
+        load_tensors(src, expected, "float32", "cpu")
+    # a fused tensor with the wrong number of rows
+    tensors["model.layers.1.self_attn.qkv_proj.weight"] = torch.zeros(100, 64)
+    save_safetensors(d / "model.safetensors", tensors)
+    with pytest.raises(WeightError) as e:
+        load_tensors(SafetensorsSource(d), expected, "float32", "cpu", fused)
+    msg = str(e.value)
+    assert "layers.1.self_attn.qkv_proj.weight: expected (128, 64)" in msg and "64 + 32 + 32" in msg and "found (100, 64)" in msg
+    assert "layers.1.self_attn.q_proj.weight" in msg           # its pieces are reported missing
+
+
+def test_fused_gate_up_of_the_dense_feed_forward():
+    """The dense gated MLP takes ``gate_up_proj`` (gate rows, then up rows), as the reference's Phi loader does."""
+    from flint_b200.parts.base import BuildContext
+    from flint_b200.parts.ffn import GatedMLP
+    from flint_b200.weights.sources import FusedView
+    part = GatedMLP({"hidden_size": 8, "intermediate_size": 6}, BuildContext(None, torch.device("cpu"), "float32"))
+    expected = part.weights()
+
+    class Src:
+        t = {"gate_up_proj.weight": torch.arange(96.0).view(12, 8), "down_proj.weight": torch.zeros(8, 6)}
+        def names(self): return list(self.t)
+        def shape(self, n): return tuple(self.t[n].shape)
+        def dtype(self, n): return self.t[n].dtype
+        def read(self, n, spec=None, device="cpu"): return self.t[n]
+    got = load_tensors(Src(), expected, "float32", "cpu", part.fused())
+    assert torch.equal(got["gate_proj.weight"], Src.t["gate_up_proj.weight"][:6])
+    assert torch.equal(got["up_proj.weight"], Src.t["gate_up_proj.weight"][6:])
