@@ -159,6 +159,9 @@ class Model:
         self._graphs = {}
         self._graph_pool = None         # one memory pool for all captured steps: only one of them runs at a time
         self.graph_max_batch = 256
+        # Captured graphs are kept by (batch size, context bucket, even lengths); a long-running engine with
+        # varying batches would collect thousands, so only the most recently used ones are kept.
+        self.graph_max_kept = 64
 
     # ------------------------------------------------------------------ facts
     @property
@@ -210,29 +213,25 @@ class Model:
             return self._graphed_decode(step)
         return self.forward(step)
 
-    def _decode_splits(self, step):
-        """Key-range split for a decode batch, from a bucketed context length so that
-        few graphs are needed as requests grow."""
-        # four buckets per doubling of the context, at least 256 apart: a graph serves a range of
-        # lengths, and the key-range split it was captured with is never much longer than needed
+    @staticmethod
+    def _context_bucket(step):
+        """A decode batch's context length rounded up to a bucket, so that few graphs are needed as requests
+        grow: four buckets per doubling of the context, at least 256 apart.  A graph serves a range of lengths,
+        and the key-range split it was captured with is never much longer than needed."""
         kv = max(step.max_kv_len, 1)
         gran = max(256, 1 << max(kv.bit_length() - 3, 0))
-        bucket = -(-kv // gran) * gran
-        spans = [bucket]
-        for i, call in enumerate(self.order):
-            mixer = self.layers[call.layer].parts.get("mixer")
-            ks = mixer.cache_spec() if mixer is not None else None
-            if ks is not None and ks.window:
-                spans.append(min(bucket, ks.window))
-        return bucket, spans
+        return -(-kv // gran) * gran
 
     def _graphed_decode(self, step):
-        bucket, _ = self._decode_splits(step)
+        bucket = self._context_bucket(step)
         step.max_kv_len = bucket          # splits are chosen for the bucket, not the exact length
         key = (step.n_tokens, bucket, step.even_lengths)
-        entry = self._graphs.get(key)
+        entry = self._graphs.pop(key, None)
         if entry is None:
-            self.forward(step)            # loads modules and warms the allocator outside the capture
+            # The first step of its kind runs eagerly (which also loads modules and warms the allocator) and its
+            # result is the step's result; the capture that follows executes nothing, so a part with state of
+            # its own advances once.
+            logits = self.forward(step)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             if self._graph_pool is None:
@@ -240,10 +239,13 @@ class Model:
             before = self.ops.launches
             wanted, step.record = step.record, {}     # internals are recorded as references to the
             with torch.cuda.graph(graph, pool=self._graph_pool):   # graph's own tensors, refreshed by every replay
-                logits = self.forward(step)
-            entry = (graph, logits, self.ops.launches - before, step.record)
+                graph_logits = self.forward(step)
+            self._graphs[key] = (graph, graph_logits, self.ops.launches - before, step.record)
             step.record = wanted
-            self._graphs[key] = entry
+            while len(self._graphs) > self.graph_max_kept:       # the least recently used goes
+                self._graphs.pop(next(iter(self._graphs)))
+            return logits
+        self._graphs[key] = entry         # most recently used last
         graph, logits, n, internals = entry
         graph.replay()
         self.ops.launches += n

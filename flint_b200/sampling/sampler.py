@@ -12,7 +12,7 @@ import torch
 
 from .params import SamplingParams
 
-MAX_CONTEXT = 64
+MAX_CONTEXT = 64        # width the context buffers start with; they grow to the largest repeat_last_n in use
 
 
 class BatchSampler:
@@ -28,9 +28,8 @@ class BatchSampler:
         self.max_context = max_context
         cuda = self.device.type == "cuda"
         self._params_host = [torch.zeros((max_rows, 8), dtype=torch.float32, pin_memory=cuda) for _ in range(2)]
-        self._ctx_host = [torch.full((max_rows, max_context), -1, dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
         self._params = torch.zeros((max_rows, 8), dtype=torch.float32, device=self.device)
-        self._ctx = torch.full((max_rows, max_context), -1, dtype=torch.int32, device=self.device)
+        self._size_context(max_context)
         # the tokens land beside the kernels' error flags when the kernel set keeps such a buffer: one copy
         # to the host then brings both, and the next step can take its tokens from there on the device
         self._readback = getattr(ops, "readback", None)
@@ -45,6 +44,16 @@ class BatchSampler:
         self._next = 0
         self.last_flags = (0, 0)          # (tensor-core error, page error) as of the last read
         self._work = None
+
+    def _size_context(self, width: int):
+        """Buffers for the last ``width`` generated tokens of every row (the repeat penalty's context).  The
+        reference honours any ``repeat_last_n`` (crates/thuban_generate/src/sampler.rs:145-160); so the buffers
+        grow when a request asks for more than they hold."""
+        cuda = self.device.type == "cuda"
+        self.max_context = int(width)
+        self._ctx_host = [torch.full((self.max_rows, self.max_context), -1, dtype=torch.int32, pin_memory=cuda)
+                          for _ in range(2)]
+        self._ctx = torch.full((self.max_rows, self.max_context), -1, dtype=torch.int32, device=self.device)
 
     @property
     def feeds_next_step(self) -> bool:
@@ -65,6 +74,9 @@ class BatchSampler:
         if all_greedy:
             self.ops.argmax(logits, out)
         else:
+            need = max((min(p.repeat_last_n, len(g)) for p, _, g in rows if p.repeat_penalty != 1.0 and g), default=0)
+            if need > self.max_context:
+                self._size_context(1 << (need - 1).bit_length())
             ph, ch = self._params_host[ticket], self._ctx_host[ticket]
             flat, any_ctx = [], False
             for i, (p, rng, generated) in enumerate(rows):

@@ -78,3 +78,24 @@ def test_uniform_logits_and_extremes():
     rows = [dict(t=1.0, k=0, p=0.25, min_p=0.0, pen=1.0, u=u) for u in (0.01, 0.5, 0.99, 0.999999)]
     got, _ = run_kernel(ops, logits, rows, [[]] * 4)
     assert got == [0, 12, 24, 24]                      # the smallest prefix reaching 0.25 is 25 tokens
+
+
+def test_repeat_penalty_over_more_than_64_tokens():
+    """``repeat_last_n`` beyond the width the sampler's buffers start with: the penalty reaches back as far as
+    the request says (the buffers grow), as the reference's does for any ``last_n``."""
+    from flint_b200.csrc.ops import get_ops
+    from flint_b200.sampling.params import SamplingParams, SplitMix64
+    from flint_b200.sampling.sampler import BatchSampler
+    ops = get_ops(DEV)
+    V = 300
+    sampler = BatchSampler(ops, DEV, max_rows=2)
+    logits = torch.zeros(2, V)
+    logits[:, 7] = 5.0            # the favourite, generated 150 tokens ago
+    logits[:, 9] = 4.0
+    generated = [7] + [11 + (i % 50) for i in range(149)]
+    far = SamplingParams(temperature=0.0, repeat_penalty=2.0, repeat_last_n=200)     # sees token 7: 5 / 2 < 4
+    near = SamplingParams(temperature=0.0, repeat_penalty=2.0, repeat_last_n=64)     # does not
+    got = sampler.sample(logits.to(DEV), [(far, SplitMix64(1), generated), (near, SplitMix64(2), generated)])
+    assert got == [9, 7] and sampler.max_context >= 150
+    want = [PlainSampler(0.0, 0, 1.0, 0.0, 2.0, repeat_last_n=n).sample(logits[0].numpy(), generated) for n in (200, 64)]
+    assert got == want
