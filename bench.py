@@ -33,7 +33,7 @@ MINI = {
     "attention_bias": True, "lm_head_bias": True, "tie_word_embeddings": False,
     "num_local_experts": 16, "num_experts_per_tok": 2, "router_jitter_noise": 0.01,
 }
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def peaks():
@@ -41,7 +41,8 @@ def peaks():
     if os.path.isfile(path):
         try:
             d = json.load(open(path))
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
         except (ValueError, KeyError, TypeError):
             pass
     return dict(FALLBACK_PEAKS)
@@ -97,14 +98,14 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-def build_model(cfg, max_slots, ctx, device="cuda:0"):
+def build_model(cfg, max_slots, ctx, device="cuda:0", n_pages=None):
     import torch
     from flint_b200.engine.loading import expected_from_config
     from flint_b200.engine.model import Model
     from flint_b200.weights.sources import RandomSource
     spec, expected = expected_from_config(cfg)
     src = RandomSource(expected, seed=0, dtype=torch.bfloat16, on_device=True)
-    return Model(spec, src, dtype="bfloat16", device=device, page_size=64, n_pages=max_slots * (ctx // 64),
+    return Model(spec, src, dtype="bfloat16", device=device, page_size=64, n_pages=n_pages or max_slots * (ctx // 64),
                  max_slots=max_slots, max_context=ctx, max_step_tokens=2048 + max_slots)
 
 
@@ -262,32 +263,250 @@ def run_mixed(model, cfg, n_requests, lo, hi, decode_tokens, rng):
             "preemptions": sum(s.preemptions for s in stats)}
 
 
-def profile(model, cfg, args, rng):
-    """Per-kernel device time (CUDA events around every launch, graphs off): one prefill of 2,048
-    tokens and one decode step of the batch.  Launches are serialised by the events, so compare shares."""
+def run_long(cfg, pk, rng, lengths, decode_tokens, chunk=2048):
+    """Long contexts (the last configuration of BASELINE.json): prompts of ``lengths`` tokens run in portions of
+    ``chunk`` through the step function, each portion timed with its depth; then ``decode_tokens`` steps of all
+    requests together; then the same workload through ``Engine`` (continuous batching: a request decodes while
+    the next one's prompt runs), wall clock."""
+    import torch
+    from flint_b200.engine.engine import Engine
+    from flint_b200.engine.step import StepEntry
+    from flint_b200.sampling.params import SamplingParams
+    V = cfg["vocab_size"]
+    ctx = max(lengths) + decode_tokens
+    n_pages = sum(-(-(n + decode_tokens) // 64) for n in lengths) + 8
+    model = build_model(cfg, len(lengths), ctx, n_pages=n_pages)
+    by_depth = {}
+    slots = []
+    t_prefill = 0.0
+    for n in lengths:
+        s = model.cache.admit()
+        slots.append(s)
+        model.cache.ensure(s, 0, n)
+        for p0 in range(0, n, chunk):
+            m = min(chunk, n - p0)
+            toks = [rng.randrange(V) for _ in range(m)]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            last = model.step([StepEntry(s, p0, toks, [m - 1] if p0 + m == n else [])])
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            t_prefill += ms
+            if m == chunk:
+                by_depth.setdefault(p0, []).append(ms)
+        checked(model, last, f"the prefill of {n} tokens")
+    depth_points = {}
+    for d in (0, 4096, 16384, 32768 - chunk, 65536, max(lengths) // chunk * chunk - chunk):
+        if d in by_depth:
+            depth_points[f"prefill_tok_s_at_depth_{d}"] = round(chunk * 1000.0 / statistics.median(by_depth[d]), 1)
+    pos = list(lengths)
+
+    def one(record=None):
+        for i, s in enumerate(slots):
+            model.cache.ensure(s, pos[i], pos[i] + 1)
+        out = model.step([StepEntry(s, pos[i], [rng.randrange(V)], [0]) for i, s in enumerate(slots)], record=record)
+        for i in range(len(pos)):
+            pos[i] += 1
+        return out
+    rec = {}
+    one(rec)
+    distinct = [int(torch.unique(ids).numel()) for ids in rec["experts"]]
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    n_timed = decode_tokens - 4
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_timed):
+        last = one()
+    e1.record()
+    torch.cuda.synchronize()
+    checked(model, last, "decoding at long contexts")
+    ms = e0.elapsed_time(e1) / n_timed
+    bytes_step = decode_bytes(cfg, model, pos, distinct)
+    for s in slots:
+        model.cache.release(s)
+    # as served: all requests submitted at once
+    eng = Engine(model, SamplingParams.greedy(), seed=1, prefill_chunk=chunk, max_step_tokens=chunk + len(lengths))
+    ids = [eng.create([rng.randrange(V) for _ in range(n)], decode_tokens) for n in lengths]
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while eng.has_work():
+        eng.step()
+    torch.cuda.synchronize()
+    served = time.perf_counter() - t0
+    stats = [eng.stats(i) for i in ids]
+    errors = [eng.error(i) for i in ids if eng.error(i)]
+    for i in ids:
+        eng.close(i)
+    if errors:
+        raise SystemExit(f"bench.py: the served run failed: {errors[0]}")
+    return {"metric": f"long contexts: prompts of {', '.join(f'{n:,}' for n in lengths)} tokens in portions of {chunk:,}, "
+                      f"then {decode_tokens} decoded tokens each",
+            "value": round(sum(lengths) * 1000.0 / t_prefill, 1), "unit": "prompt tokens/s (all portions, device time)",
+            **depth_points,
+            "decode_ms_per_step": round(ms, 3), "decode_tok_s": round(len(lengths) * 1000.0 / ms, 1),
+            "decode_roofline_frac": round(bytes_step / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+            "decode_bytes_per_step": bytes_step, "cache_tokens": sum(pos),
+            "served_seconds": round(served, 2), "served_tok_s": round((sum(lengths) + sum(s.decode_tokens + 1 for s in stats)) / served, 1),
+            "config": config_of(cfg, len(lengths), max(lengths), ctx, pk)}
+
+
+def run_tiny(which, reps=5):
+    """The tiny workloads of the two test configurations, in 32-bit: through ``Engine`` on the GPU (wall clock,
+    host tokens in and out) and on the timed CPU baseline, the plain C++ implementation of the test-suite
+    (tests/plain_phimoe.cpp: float32, whole-sequence forward pass for every token, one thread)."""
+    import tempfile
+    import torch
+    sys.path.insert(0, os.path.join(REPO, "tests"))
+    import plain_cpp
+    import tiny
+    from flint_b200.engine.engine import Engine
+    from flint_b200.engine.model import load_model
+    from flint_b200.sampling.params import SamplingParams
+    cfg = tiny.CONFIGS[which]
+    if which == "A":
+        lens, n_tokens, params, chunk = (7, 13, 32), 16, SamplingParams.greedy(), 2048
+    else:
+        lens, n_tokens, params, chunk = (5, 40, 70, 100), 24, SamplingParams(temperature=0.8, top_k=20, top_p=0.8), 16
+    prompts = [tiny.random_tokens(n, cfg["vocab_size"], 100 + n) for n in lens]
+    with tempfile.TemporaryDirectory() as d:
+        folder = tiny.write_tiny(os.path.join(d, "tiny"), which, seed=0, dtype=torch.float32)
+        base_tokens, base_secs = plain_cpp.generate(folder, prompts, n_tokens, params.temperature, params.top_k,
+                                                    params.top_p, seed=42)
+        model = load_model(folder, dtype="float32", page_size=16, n_pages=64, max_slots=len(prompts), max_step_tokens=256)
+        times = []
+        for i in range(reps + 2):
+            eng = Engine(model, params, seed=42, prefill_chunk=chunk, stop=())
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            got = eng.generate(prompts, n_tokens)
+            torch.cuda.synchronize()
+            if i >= 2:
+                times.append(time.perf_counter() - t0)
+        model.check_status()
+    n_out = sum(len(g) for g in got)
+    ours = n_out / statistics.median(times)
+    base = sum(len(g) for g in base_tokens) / base_secs
+    return {"metric": f"generated tokens/s, Tiny {which} workload ({len(prompts)} requests, prompts of "
+                      f"{'/'.join(map(str, lens))} tokens, {n_tokens} tokens each, "
+                      f"{'greedy' if params.temperature <= 0 else 'temperature 0.8, seed 42'})",
+            "value": round(ours, 1), "unit": "tokens/s", "n_gpus": 1, "dtype": "fp32", "higher_is_better": True,
+            "vs_baseline": round(ours / base, 2),
+            "baseline": {"impl": "tests/plain_phimoe.cpp: plain float32 C++, whole-sequence forward pass per token, one CPU thread",
+                         "value": round(base, 1), "seconds": round(base_secs, 4)},
+            "tokens_match_baseline": got == base_tokens, "seconds": round(statistics.median(times), 5),
+            "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours"}
+
+
+def config_of(cfg, batch, prompt_tokens, ctx, pk):
+    """Every size of a run, flat."""
+    mini = all(cfg[k] == MINI[k] for k in MINI if k != "num_hidden_layers")
+    return {"model": "Phi-mini-MoE sizes" if mini else
+                     f"Phi-MoE sizes: hidden {cfg['hidden_size']}, experts of {cfg['intermediate_size']}",
+            "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
+            "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"],
+            "top_k": 2, "expert_intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": batch, "prompt_tokens": prompt_tokens, "seq_len": ctx, "page_size": 64,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed every step)",
+            "peaks": pk["source"]}
+
+
+def profile_tables(model, cfg, batch, prompt_len, rng):
+    """Per-kernel device time (CUDA events around every launch, graphs off, so launches are serialised): one
+    prefill of ``prompt_len`` tokens and one decode step of the batch at that context.  Returns
+    (prefill table, decode table, distinct experts per layer of the decode step), tables as
+    {launcher name and product shape: (launches, ms)}."""
     import torch
     from flint_b200.engine.step import StepEntry
     V = cfg["vocab_size"]
-    model.use_graphs = False
-    slots = [model.cache.admit() for _ in range(args.batch)]
+    graphs, model.use_graphs = model.use_graphs, False
+    slots = [model.cache.admit() for _ in range(batch)]
     for i, s in enumerate(slots):
-        model.cache.ensure(s, 0, args.prompt_tokens + 2)
+        model.cache.ensure(s, 0, prompt_len + 2)
         if i == len(slots) - 1:
             model.ops.start_profile()
-        model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(args.prompt_tokens)], [args.prompt_tokens - 1])])
-    table = model.ops.stop_profile()
+        model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(prompt_len)], [prompt_len - 1])])
+    prefill = model.ops.stop_profile()
+    dec = lambda p, rec=None: model.step([StepEntry(s, p, [rng.randrange(V)], [0]) for s in slots], record=rec)
+    dec(prompt_len)
+    rec = {}
+    model.ops.start_profile()
+    dec(prompt_len + 1, rec)
+    decode = model.ops.stop_profile()
+    distinct = [int(torch.unique(ids).numel()) for ids in rec.get("experts", [])]
+    for s in slots:
+        model.cache.release(s)
+    model.use_graphs = graphs
+    return prefill, decode, distinct
+
+
+def kernel_class(name, cfg):
+    """The dominant kernels by what they compute; everything else is the small row-wise work."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    if "attention_prefill" in name:
+        return "attention_prefill"
+    if "attention" in name:
+        return "attention_decode"
+    if "gemm" in name and " " in name:
+        shape = name.split(" ")[1]
+        n, k = (int(x) for x in shape.split("x"))
+        if "experts" in name:
+            return "expert_gate_up" if k == H else "expert_down"
+        if n == (nq + 2 * nkv) * hd and k == H:
+            return "qkv"
+        if n == V:
+            return "head"
+        if n == H and k == nq * hd:
+            return "o_proj"
+    return "other"
+
+
+def kernel_fractions(table, cfg, pk, kind, n_tokens, kv_lens, distinct):
+    """Flat {class.us, class.frac}: device time of each dominant kernel over a whole step and its fraction of the
+    measured peak: bytes it must read over the copy bandwidth for a decode step, flops over the sustained library
+    product rate for a prefill.  ``other`` (norms with routing, rotary write, plan, activation, embedding) has a
+    time only."""
+    H, I, L, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    us = {}
+    for name, (_, ms) in table.items():
+        c = kernel_class(name, cfg)
+        us[c] = us.get(c, 0.0) + ms * 1000.0
+    keys = sum(kv_lens)
+    if kind == "decode":
+        work = {"qkv": L * (nq + 2 * nkv) * hd * H * 2, "o_proj": L * H * nq * hd * 2,
+                "expert_gate_up": sum(distinct) * 2 * I * H * 2, "expert_down": sum(distinct) * H * I * 2,
+                "attention_decode": keys * nkv * hd * 2 * 2 * L, "head": V * H * 2}
+        peak = pk["hbm_gbs"] * 1e9
+    else:
+        T = n_tokens
+        work = {"qkv": 2 * T * (nq + 2 * nkv) * hd * H * L, "o_proj": 2 * T * H * nq * hd * L,
+                "expert_gate_up": 2 * (2 * T) * (2 * I) * H * L, "expert_down": 2 * (2 * T) * H * I * L,
+                "attention_prefill": 4 * nq * hd * keys * L}
+        peak = pk["bf16_tflops_sustained"] * 1e12
+    out = {}
+    for c, t in sorted(us.items(), key=lambda kv: -kv[1]):
+        out[f"{kind}.{c}.us"] = round(t, 1)
+        if c in work and t > 0:
+            out[f"{kind}.{c}.frac"] = round(work[c] / (t * 1e-6) / peak, 3)
+    return out
+
+
+def profile(model, cfg, args, rng):
+    """``--profile``: the tables to stderr."""
+    prefill, decode, _ = profile_tables(model, cfg, args.batch, args.prompt_tokens, rng)
 
     def show(title, table):
         total = sum(ms for _, ms in table.values())
         print(f"--- {title}: {total:.3f} ms in {sum(n for n, _ in table.values())} launches", file=sys.stderr)
         for name, (n, ms) in sorted(table.items(), key=lambda kv: -kv[1][1]):
-            print(f"{name:32s} {n:6d} launches {ms:10.3f} ms {100 * ms / total:6.1f} %", file=sys.stderr)
-    show(f"prefill of {args.prompt_tokens} tokens", table)
-    dec = lambda p: model.step([StepEntry(s, p, [rng.randrange(V)], [0]) for s in slots])
-    dec(args.prompt_tokens)
-    model.ops.start_profile()
-    dec(args.prompt_tokens + 1)
-    show(f"decode step, batch {args.batch}, context {args.prompt_tokens}", model.ops.stop_profile())
+            print(f"{name:48s} {n:6d} launches {ms:10.3f} ms {100 * ms / total:6.1f} %", file=sys.stderr)
+    show(f"prefill of {args.prompt_tokens} tokens", prefill)
+    show(f"decode step, batch {args.batch}, context {args.prompt_tokens}", decode)
     return 0
 
 
@@ -342,6 +561,15 @@ def main():
     ap.add_argument("--one-step", choices=["decode", "prefill"], default=None,
                     help="run the set-up, then one warm and one measured eager step of this kind, and exit "
                          "(for a launch list under ncu: the launch counts to skip and capture go to stderr)")
+    ap.add_argument("--tiny", choices=["A", "B"], default=None,
+                    help="instead of the default run: the tiny workload of that test configuration, in 32-bit, against "
+                         "the timed CPU baseline (the plain C++ implementation)")
+    ap.add_argument("--long", action="store_true",
+                    help="instead of the default run: prompts of 4 x 32,768 and one of 130,944 tokens (with its 128 decoded "
+                         "tokens the model's 131,072 positions) in portions of 2,048, then 128 decoded tokens each; "
+                         "use with --expert-intermediate 6400 for the Phi-3.5-MoE sizes")
+    ap.add_argument("--long-prompts", type=int, nargs="+", default=None, help="other prompt lengths for --long")
+    ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
     args = ap.parse_args()
@@ -368,6 +596,12 @@ def main():
     if args.decode_tokens:
         args.steps = args.decode_tokens
     rng = random.Random(0)
+    if args.tiny:
+        print(json.dumps(run_tiny(args.tiny)))
+        return 0
+    if args.long:
+        print(json.dumps(run_long(cfg, pk, rng, args.long_prompts or [32768] * 4 + [131072 - 128], 128)))
+        return 0
     max_batch = max(args.batch, 1 if args.no_points else 64, args.mixed[0] if args.mixed else 1)
     model = build_model(cfg, max_batch, args.ctx_size)
 
@@ -399,6 +633,11 @@ def main():
             points_frac[f"decode_b{b}"] = round(decode_bytes(cfg, model, r["kv_lens"], r["distinct"]) / (r["ms"] * 1e-3) / 1e9
                                                 / pk["hbm_gbs"], 4)
 
+    kernels = {}
+    if not args.no_kernels:
+        pre_t, dec_t, distinct = profile_tables(model, cfg, args.batch, args.prompt_tokens, rng)
+        kernels.update(kernel_fractions(dec_t, cfg, pk, "decode", args.batch, [args.prompt_tokens + 2] * args.batch, distinct))
+        kernels.update(kernel_fractions(pre_t, cfg, pk, "prefill", args.prompt_tokens, range(1, args.prompt_tokens + 1), None))
     pre_flops = step_flops(cfg, 2048, range(1, 2049))
     bytes_step = decode_bytes(cfg, model, dec["kv_lens"], dec["distinct"])
     achieved = bytes_step / (dec["ms"] * 1e-3) / 1e9
@@ -409,25 +648,23 @@ def main():
         "value": round(dec["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(dec["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform-random token ids", "impl": "ours",
-        "config": {"model": "Phi-mini-MoE sizes" if mini else
-                            f"Phi-MoE sizes: hidden {cfg['hidden_size']}, experts of {cfg['intermediate_size']}", "layers": cfg["num_hidden_layers"], "layers_of_config": 32,
-                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
-                   "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "experts": cfg["num_local_experts"],
-                   "top_k": 2, "expert_intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-                   "global_batch": args.batch,
-                   "prompt_tokens": args.prompt_tokens, "seq_len": args.ctx_size, "page_size": 64,
-                   "parallelism": "single GPU", "l2": "inputs larger than L2 (weights streamed every step)",
-                   "peaks": pk["source"]},
+        "config": config_of(cfg, args.batch, args.prompt_tokens, args.ctx_size, pk),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s", "ms_per_step": round(e2e["ms"], 4),
                 "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": dec["launches"],
         "prefill": {"value": round(2048 * 1000.0 / pre_ms, 1), "tokens": 2048, "ms": round(pre_ms, 3),
-                    "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)},
+                    "frac": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                    "frac_of_sustained": round(pre_flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": bytes_step,
                      "distinct_experts_per_layer": round(sum(dec["distinct"]) / len(dec["distinct"]), 2)},
         "points": points,
         "points_roofline_frac": points_frac,
+        "kernels": kernels,
+        "kernels_how": "device time per step by CUDA events around every launch of one eager step (no graph, launches "
+                       "serialised: a little longer than inside the captured step); decode fractions: bytes the kernel "
+                       "must read over the measured copy bandwidth; prefill fractions: flops over the measured sustained "
+                       "library product rate",
         "clocks": clock,
     }
     print(json.dumps(out))

@@ -71,6 +71,7 @@ class CudaOps:
         self._libs = {}
         self.launches = 0
         self._profile = None
+        self._label = None          # what the next launch works on (profiles list products by their shape)
         # One buffer for what the host reads back after a step, so that one copy brings all of it: a flag set by
         # a tensor-core kernel whose bounded wait ran out, a flag set by a kernel that met a position without a
         # page, and the sampled tokens.
@@ -99,9 +100,10 @@ class CudaOps:
             e0.record()
             rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
             e1.record()
-            self._profile.append((name, e0, e1))
+            self._profile.append((name + (" " + self._label if self._label else ""), e0, e1))
         else:
             rc = fn(*args, c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        self._label = None
         self.launches += 1
         if rc != 0:
             msg = getattr(self._libs[module], f"flint_{module}_last_error")()
@@ -371,6 +373,7 @@ class CudaOps:
             kbps = -(-kb // splits)
             splits = -(-kb // kbps)
         out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        self._label = self._product_label(N, K, plan, False)
         self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(0), _ptr(None),
                   _ptr(out), c_int(F32), c_int(N), c_int(0), c_int(0), _ptr(plan.tile_expert if plan else None),
                   _ptr(plan.tile_row0 if plan else None), _ptr(plan.n_tiles if plan else None),
@@ -457,6 +460,7 @@ class CudaOps:
         partial = None
         if splits > 1:
             partial = torch.empty(splits * M * N, dtype=torch.float32, device=x.device)
+        self._label = self._product_label(N, K, plan, gated)
         self._run("gemm_tc", "flint_gemm_tc", _ptr(x), c_int(x.stride(0)), _ptr(w), c_int(1 if gated else 0), _ptr(bias),
                   _ptr(out), c_int(_code(out.dtype)), c_int(out.stride(0)), c_int(1 if accumulate else 0),
                   c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
@@ -464,9 +468,15 @@ class CudaOps:
                   c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
                   c_int(splits), _ptr(partial), c_int(0), c_int(0), _ptr(self.tc_error))
 
+    @staticmethod
+    def _product_label(N, K, plan, gated):
+        """How a profile lists a product: its weight shape, and whether it is gated or over experts."""
+        return f"{N}x{K}" + (" gated" if gated else "") + (" experts" if plan is not None else "")
+
     def _gemm_simt(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
         if plan is not None and plan.tile_rows > 64:
             raise KernelError("gemm_simt: the plan's row tiles must not exceed 64 rows")
+        self._label = self._product_label(N, K, plan, gated)
         self._run("gemm_simt", "flint_gemm_simt", _ptr(x), c_int(_code(x.dtype)), c_int(x.stride(0)), _ptr(w),
                   c_int(1 if gated else 0), c_int(_code(w.dtype)), _ptr(bias), _ptr(out), c_int(_code(out.dtype)),
                   c_int(out.stride(0)), c_int(1 if accumulate else 0), c_int(act_code),

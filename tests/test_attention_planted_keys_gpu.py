@@ -167,3 +167,23 @@ def test_prefill_on_tensor_cores_finds_planted_keys_and_keeps_the_window_edge(op
         # a row may see a key planted for another row as well; what is checked is the row the key was planted for,
         # and its neighbour with the same query one position later
         assert is_planted == seen, f"row {r} (position {start + r}), key {far}, window {window}"
+
+
+@pytest.mark.parametrize("kernel", ["stream", "tma"])
+@pytest.mark.parametrize("window,far", [(0, 5), (0, 70000), (100000, 131072 - 100000), (100000, 131072 - 100001)])
+def test_decode_over_131072_keys(ops, kernel, window, far):
+    """One row at the end of the longest context the model allows, over scattered pages: against float64, and
+    with a planted key far back that must be found (or, one position outside a window of 100,000, must not)."""
+    nq, nkv, hd, L = 8, 2, 128, 131072
+    q, k, v, bt, pos, slot, planted = build_rows([(L, far)], nq, nkv, hd, seed=far % 97)
+    spec = KVSpec(nkv, hd, window)
+    dv = CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec)
+    scale = 1 / math.sqrt(hd)
+    out = torch.full((1, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.to(DEV), dv, pos.to(DEV), slot.to(DEV), out, nq, nkv, hd, window, scale, L, kernel=kernel)
+    assert int(ops.tc_error.item()) == 0
+    exp = torch.zeros(1, nq * hd, dtype=torch.float64)
+    RefOps(torch.float64).paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, window, scale, L)
+    close(out, exp, 2e-2)
+    seen = window == 0 or far >= L - window
+    assert torch.allclose(out[0, :hd].float().cpu(), planted[0].float(), atol=2e-2, rtol=1e-2) == seen

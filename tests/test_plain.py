@@ -3,8 +3,10 @@ the same way: crates/thuban_backend/tests/kernels.rs:1310-1481), and the host sa
 import math
 
 import numpy as np
+import pytest
 import torch
 
+import plain_phimoe
 import plain_phimoe as P
 
 D = torch.float64
@@ -146,3 +148,39 @@ def test_package_generator_matches_the_plain_one():
     from flint_b200.sampling.params import SplitMix64
     a, b = SplitMix64(43), P.PlainSampler(seed=43)
     assert [a.next_f32() for _ in range(8)] == [float(b.next_f32()) for _ in range(8)]
+
+
+@pytest.mark.parametrize("which", ["A", "B"])
+def test_the_two_plain_implementations_agree(tmp_path, which):
+    """The C++ float32 implementation (tests/plain_phimoe.cpp) and the torch float64 one were written
+    independently from the same formulas: same logits to float32 accuracy, the same experts everywhere
+    (except at a tie within float32 rounding), the same greedy and sampled tokens."""
+    import plain_cpp
+    import tiny
+    folder = tiny.write_tiny(tmp_path / "m", which, seed=13, dtype=torch.float32)
+    cfg, w = plain_phimoe.load_model_dir(folder)
+    V, L = cfg["vocab_size"], cfg["num_hidden_layers"]
+    reqs = [tiny.random_tokens(n, V, 40 + n) for n in ((7, 13, 32) if which == "A" else (5, 40, 70, 100))]
+    got = plain_cpp.logits(folder, reqs, L, V)
+    for toks, (lg, ex) in zip(reqs, got):
+        rec = []
+        want = plain_phimoe.forward(cfg, w, toks, rec)
+        mine = torch.tensor(lg, dtype=torch.float64).view(len(toks), V)
+        err = float((mine - want).abs().max() / want.abs().max())
+        assert err < 1e-5, err
+        ex = torch.tensor(ex).view(L, len(toks), 2)
+        for l in range(L):
+            for t in range(len(toks)):
+                assert tuple(ex[l, t].tolist()) == rec[l][t][:2] or rec[l][t][4] < 1e-5, (l, t, ex[l, t], rec[l][t])
+    # generation: greedy, and temperature 0.8 with the reference's default filters and a fixed seed
+    for temperature, k, p in ((0.0, 0, 1.0), (0.8, 20, 0.8)):
+        out, _ = plain_cpp.generate(folder, reqs[:2], 6, temperature, k, p, seed=5)
+        for i, (prompt, toks) in enumerate(zip(reqs[:2], out)):
+            s = plain_phimoe.PlainSampler(temperature, k, p, seed=5 + i + 1)
+            seq = list(prompt)
+            eos = cfg["eos_token_id"] if isinstance(cfg["eos_token_id"], list) else [cfg["eos_token_id"]]
+            for tok in toks:
+                want = s.sample(plain_phimoe.forward(cfg, w, seq)[-1].float().numpy())
+                assert tok == want
+                seq.append(tok)
+            assert len(toks) == 6 or s.sample(plain_phimoe.forward(cfg, w, seq)[-1].float().numpy()) in eos
