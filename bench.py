@@ -443,6 +443,73 @@ def profile_tables(model, cfg, batch, prompt_len, rng):
     return prefill, decode, distinct
 
 
+def graph_step_table(model, cfg, batch, prompt_len, rng):
+    """The kernels of one captured decode step with the time each adds to the step: inside the graph, kernels
+    start early under programmatic dependent launch and wait for the one before, so a kernel's share is the time
+    from the end of the kernel before it to its own end (device timestamps of one replay, read through
+    torch.profiler).  Kernels are named by pairing them, in order, with the launches of one eager step of the
+    same shape.  Returns ({label: (launches, ms)}, distinct experts per layer) or None if the profiler is not
+    available or the two sequences do not pair up."""
+    import torch
+    from flint_b200.engine.step import StepEntry
+    try:
+        from torch.profiler import ProfilerActivity, profile as torch_profile
+    except ImportError:
+        return None
+    V = cfg["vocab_size"]
+    slots = [model.cache.admit() for _ in range(batch)]
+    for s in slots:
+        model.cache.ensure(s, 0, prompt_len + 8)
+        model.step([StepEntry(s, 0, [rng.randrange(V) for _ in range(prompt_len)], [])])
+    pos = prompt_len
+
+    def dec(rec=None):
+        nonlocal pos
+        out = model.step([StepEntry(s, pos, [rng.randrange(V)], [0]) for s in slots], record=rec)
+        pos += 1
+        return out
+    graphs, model.use_graphs = model.use_graphs, False
+    dec()
+    rec = {}
+    model.ops.start_profile()
+    dec(rec)
+    labels = [name for name, _ in model.ops.stop_profile(ordered=True)]
+    distinct = [int(torch.unique(ids).numel()) for ids in rec.get("experts", [])]
+    model.use_graphs = graphs
+    table = None
+    if graphs:
+        for _ in range(3):
+            dec()
+        torch.cuda.synchronize()
+        try:
+            with torch_profile(activities=[ProfilerActivity.CUDA]) as prof:
+                dec()
+                torch.cuda.synchronize()
+            ev = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                         if e.device_type == torch.autograd.DeviceType.CUDA and "Memcpy" not in e.name and "Memset" not in e.name))
+        except Exception:            # no CUPTI here: the caller falls back to the eager table
+            ev = []
+        followers = ("splitk_reduce", "attention_combine")      # second kernels of a launcher call
+        paired, i = [], 0
+        for start, end, name in ev:
+            if any(f in name for f in followers) and paired:
+                paired.append((paired[-1][0], end))
+            elif i < len(labels):
+                paired.append((labels[i], end))
+                i += 1
+            else:
+                i += 1
+        if ev and i == len(labels):
+            table, prev = {}, ev[0][0]
+            for label, end in paired:
+                n, ms = table.get(label, (0, 0.0))
+                table[label] = (n + 1, ms + max(0.0, end - prev) / 1000.0)
+                prev = max(prev, end)
+    for s in slots:
+        model.cache.release(s)
+    return (table, distinct) if table else None
+
+
 def kernel_class(name, cfg):
     """The dominant kernels by what they compute; everything else is the small row-wise work."""
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -634,8 +701,14 @@ def main():
                                                 / pk["hbm_gbs"], 4)
 
     kernels = {}
+    kernels_decode_how = "CUDA events around every launch of one eager step (launches serialised, host gaps included)"
     if not args.no_kernels:
         pre_t, dec_t, distinct = profile_tables(model, cfg, args.batch, args.prompt_tokens, rng)
+        in_graph = graph_step_table(model, cfg, args.batch, args.prompt_tokens, rng)
+        if in_graph is not None:
+            dec_t, distinct = in_graph
+            kernels_decode_how = ("device timestamps of one replay of the captured step: a kernel's time runs from the end "
+                                  "of the kernel before it to its own end (kernels overlap under programmatic dependent launch)")
         kernels.update(kernel_fractions(dec_t, cfg, pk, "decode", args.batch, [args.prompt_tokens + 2] * args.batch, distinct))
         kernels.update(kernel_fractions(pre_t, cfg, pk, "prefill", args.prompt_tokens, range(1, args.prompt_tokens + 1), None))
     pre_flops = step_flops(cfg, 2048, range(1, 2049))
@@ -661,10 +734,10 @@ def main():
         "points": points,
         "points_roofline_frac": points_frac,
         "kernels": kernels,
-        "kernels_how": "device time per step by CUDA events around every launch of one eager step (no graph, launches "
-                       "serialised: a little longer than inside the captured step); decode fractions: bytes the kernel "
-                       "must read over the measured copy bandwidth; prefill fractions: flops over the measured sustained "
-                       "library product rate",
+        "kernels_how": "microseconds per step and fraction of the measured peak.  decode: " + kernels_decode_how +
+                       "; fractions: bytes the kernel must read over the measured copy bandwidth.  prefill: CUDA events "
+                       "around every launch of one eager step; fractions: flops over the measured sustained library "
+                       "product rate",
         "clocks": clock,
     }
     print(json.dumps(out))

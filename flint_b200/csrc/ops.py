@@ -114,9 +114,14 @@ class CudaOps:
     def start_profile(self):
         self._profile = []
 
-    def stop_profile(self):
-        """Returns {kernel name: (launches, total ms)} and stops profiling."""
+    def stop_profile(self, ordered=False):
+        """Returns {kernel name: (launches, total ms)} and stops profiling; ``ordered``: the launches in order
+        instead, [(kernel name, ms)]."""
         torch.cuda.synchronize(self.device)
+        if ordered:
+            out = [(name, e0.elapsed_time(e1)) for name, e0, e1 in self._profile or []]
+            self._profile = None
+            return out
         out = {}
         for name, e0, e1 in self._profile or []:
             n, ms = out.get(name, (0, 0.0))
