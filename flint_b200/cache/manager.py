@@ -26,11 +26,17 @@ from .pages import NO_PAGE, GroupPages
 
 @dataclass(frozen=True)
 class KVSpec:
-    """What a mixer needs cached per token: keys and values of this shape.  ``window``
-    0 means every key stays reachable; otherwise only the last ``window`` positions."""
+    """What a mixer needs cached per token: ``num_kv_heads`` keys of ``head_dim`` numbers and as many values of
+    ``value_dim`` numbers (default: as wide as the keys; 0: keys only).  ``window`` 0 means every key stays
+    reachable; otherwise only the last ``window`` positions."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int | None = None
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else int(self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -56,10 +62,10 @@ class GroupCache:
         self.pages = pages
         P = pages.page_size
         n = pages.pool.n_pages
-        # [call, k|v, page, kv_head, position in page, head_dim]: one page of one head is a
-        # contiguous P x head_dim tile
-        self.storage = torch.zeros((len(self.calls), 2, n, spec.num_kv_heads, P, spec.head_dim),
-                                   dtype=dtype, device=device)
+        # keys [call, page, kv_head, position in page, head_dim] and values [..., value width]: one page of one
+        # head is a contiguous P x width tile; keys and values may differ in width
+        self.keys = torch.zeros((len(self.calls), n, spec.num_kv_heads, P, spec.head_dim), dtype=dtype, device=device)
+        self.values = torch.zeros((len(self.calls), n, spec.num_kv_heads, P, spec.value_width), dtype=dtype, device=device)
         self.block_table = torch.full((max_slots, max_pages_per_request), NO_PAGE, dtype=torch.int32, device=device)
         # The copy to the device is asynchronous and may run long after it was asked for (behind a whole step
         # that is still running), while the bookkeeping goes on changing the host mirror for the next step:
@@ -91,14 +97,13 @@ class GroupCache:
 
     def view(self, call_index: int):
         i = self.calls.index(call_index)
-        return CacheView(self.storage[i, 0], self.storage[i, 1], self.block_table, self.pages.page_size,
-                         self.spec)
+        return CacheView(self.keys[i], self.values[i], self.block_table, self.pages.page_size, self.spec)
 
 
 @dataclass
 class CacheView:
-    """What a mixer call sees of the cache: its K and V pages [page, kv_head, P, head_dim]
-    and its group's block table [slot, logical page]."""
+    """What a mixer call sees of the cache: its K pages [page, kv_head, P, head_dim], its V pages
+    [page, kv_head, P, value width] and its group's block table [slot, logical page]."""
     k: torch.Tensor
     v: torch.Tensor
     block_table: torch.Tensor

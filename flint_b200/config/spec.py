@@ -56,3 +56,8 @@ class ModelSpec:
     tie_word_embeddings: bool = False
     embed_scale: float = 1.0
     eos_token_ids: tuple = ()
+    # A position encoding that acts on the embedded rows instead of inside a mixer (learned absolute positions
+    # and the like): a PartSpec of the position-encoding registry whose part has ``after_embedding(h, step)``;
+    # its tensors live under ``embed_position_name``.
+    embed_position: PartSpec | None = None
+    embed_position_name: str = "embed_positions."

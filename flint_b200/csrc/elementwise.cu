@@ -100,14 +100,14 @@ __device__ __forceinline__ void store4(__nv_bfloat16* dst, float4 v) {
 // --------------------------------------------------------------------------- rope + kv write
 // qkv [n_partials][T, (nq+2*nkv)*hd] float32: q heads, then k heads, then v heads; the partials
 // (pieces of a split K range, partial_stride floats apart) and the bias are added on the way in.
-// q and k are rotated (NeoX half-split over the first `rot` dims of each head) by the row of
-// the cos/sin tables that belongs to the token's position; q goes to q_out, k and v go to
+// q and k are rotated over the first `rot` dims of each head by the row of the cos/sin tables that belongs to
+// the token's position: dims i and i + rot/2 together (NeoX half-split), or, interleaved, dims 2i and 2i + 1; q goes to q_out, k and v go to
 // the token's place in the paged cache: page = block_table[slot, pos / P], row pos % P.
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(256)
 rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                                const int* __restrict__ slot, const float* __restrict__ cos_t,
-                               const float* __restrict__ sin_t, int rot, TQ* __restrict__ q_out,
+                               const float* __restrict__ sin_t, int rot, int interleaved, TQ* __restrict__ q_out,
                                TC* __restrict__ k_cache, TC* __restrict__ v_cache,
                                const int* __restrict__ block_table, int max_pages, int page_size,
                                int nq, int nkv, int hd, int write_kv, int* __restrict__ status,
@@ -141,7 +141,7 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
                            reinterpret_cast<uintptr_t>(sin_t) | reinterpret_cast<uintptr_t>(bias) |
                            reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
                            reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
-  if (n_partials == 1 && (half & 3) == 0 && (hd & 7) == 0 && gridDim.y == 1 && aligned16) {
+  if (n_partials == 1 && (half & 3) == 0 && (hd & 7) == 0 && gridDim.y == 1 && aligned16 && !interleaved) {
     pdl_wait();
     if (missing && threadIdx.x == 0) atomicExch(status, 1);
     const int quads = pairs >> 2;
@@ -194,7 +194,11 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
     const bool is_v = it.head >= nq + nkv;
     // dims of this item: inside the rotary part (d, d + half); beyond it (rot + 2j, rot + 2j + 1)
     it.rotate = false;
-    if (!is_v && i < half) { it.d0 = i; it.d1 = i + half; it.rotate = true; }
+    if (!is_v && i < half) {
+      it.d0 = interleaved ? 2 * i : i;
+      it.d1 = interleaved ? 2 * i + 1 : i + half;
+      it.rotate = true;
+    }
     else if (is_v) { it.d0 = 2 * i; it.d1 = 2 * i + 1; }
     else { it.d0 = rot + 2 * (i - half); it.d1 = it.d0 + 1; }
     it.c = it.rotate ? cos_t[(size_t)p * half + i] : 1.f;
@@ -250,7 +254,7 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
 }
 
 extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* slot,
-                                   const float* cos_t, const float* sin_t, int rot, void* q_out,
+                                   const float* cos_t, const float* sin_t, int rot, int interleaved, void* q_out,
                                    int q_dtype, void* k_cache, void* v_cache, int cache_dtype,
                                    const int* block_table, int max_pages, int page_size, int T,
                                    int nq, int nkv, int hd, int write_kv, int* status,
@@ -269,7 +273,7 @@ extern "C" int flint_rope_kv_write(const float* qkv, const int* pos, const int* 
   const int threads = share >= 256 ? 256 : ((share + 31) / 32) * 32;
   FLINT_DISPATCH_DTYPE(q_dtype, TQ, FLINT_DISPATCH_DTYPE(cache_dtype, TC,
       (launch_pdl(rope_kv_kernel<TQ, TC>, grid, dim3(threads), 0, stream,
-          qkv, pos, slot, cos_t, sin_t, rot, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,
+          qkv, pos, slot, cos_t, sin_t, rot, interleaved, (TQ*)q_out, (TC*)k_cache, (TC*)v_cache, block_table,
           max_pages, page_size, nq, nkv, hd, write_kv, status, n_partials, partial_stride, bias))));
   return check_launch("rope_kv_write");
 }

@@ -68,6 +68,8 @@ class CudaOps:
         if not torch.cuda.is_available():
             raise KernelError("no CUDA device: flint_b200 runs on the GPU only and has no CPU fallback")
         self.device = torch.device(device)
+        # launch plans are sized for the device: so many blocks or warps per multiprocessor
+        self.sm_count = int(torch.cuda.get_device_properties(self.device).multi_processor_count)
         self._libs = {}
         self.launches = 0
         self._profile = None
@@ -261,8 +263,12 @@ class CudaOps:
         if pending.y is not None:
             self.moe_combine(x, pending.y, pending.row_of, pending.gates)
 
-    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None):
-        """qkv [T, W] or [S, T, W] float32 (S partial sums that are added here, with the bias)."""
+    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None,
+                      style="half"):
+        """qkv [T, W] or [S, T, W] float32 (S partial sums that are added here, with the bias).  ``style``: which
+        dims of a head rotate together: "half" (i and i + rot/2) or "interleaved" (2i and 2i + 1)."""
+        if style not in ("half", "interleaved"):
+            raise KernelError(f"rope_kv_write: unknown rotation style {style!r}")
         if qkv.dim() == 2:
             qkv = qkv.unsqueeze(0)
         _check(qkv, "qkv", torch.float32, 3)
@@ -279,8 +285,9 @@ class CudaOps:
         if cache is not None:
             k, v, bt, P = cache.k, cache.v, cache.block_table, cache.page_size
             cdt = _code(k.dtype)
-            if tuple(k.shape[1:]) != (nkv, P, hd):
-                raise KernelError(f"rope_kv_write: cache pages are {tuple(k.shape[1:])}, expected {(nkv, P, hd)}")
+            if tuple(k.shape[1:]) != (nkv, P, hd) or tuple(v.shape[1:]) != (nkv, P, hd):
+                raise KernelError(f"rope_kv_write: cache pages are {tuple(k.shape[1:])} and {tuple(v.shape[1:])}, "
+                                  f"expected {(nkv, P, hd)} for both")
             max_pages = bt.shape[1]
         else:
             if write_kv:
@@ -288,7 +295,8 @@ class CudaOps:
             k = v = bt = None
             cdt, P, max_pages = F32, 16, 0
         self._run("elementwise", "flint_rope_kv_write", _ptr(qkv), _ptr(pos), _ptr(slot), _ptr(cos), _ptr(sin),
-                  c_int(rot), _ptr(q_out), c_int(_code(q_out.dtype)), _ptr(k), _ptr(v), c_int(cdt), _ptr(bt),
+                  c_int(rot), c_int(1 if style == "interleaved" else 0), _ptr(q_out), c_int(_code(q_out.dtype)), _ptr(k),
+                  _ptr(v), c_int(cdt), _ptr(bt),
                   c_int(max_pages), c_int(P), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write_kv else 0),
                   _ptr(status), c_int(S), c_longlong(qkv.stride(0)), _ptr(bias))
 
@@ -387,16 +395,15 @@ class CudaOps:
                   _ptr(self.tc_error))
         return out
 
-    @staticmethod
-    def _k_splits(M, N, K, bn):
+    def _k_splits(self, M, N, K, bn):
         """Pieces of the K range so that a product with few tiles still fills the device."""
         tiles = -(-N // 128) * -(-M // bn)
         kb = -(-K // 64)
-        if tiles >= 148 or kb < 8:
+        if tiles >= self.sm_count or kb < 8:
             return 1
         # as many pieces as still fit one wave of resident blocks (three per SM with the narrow token tiles,
         # else two; a second, partial wave would cost as much as a full one)
-        return max(1, min((444 if bn < 64 else 296) // tiles, kb // 4, 16))
+        return max(1, min(((3 if bn < 64 else 2) * self.sm_count) // tiles, kb // 4, 16))
 
     def _gemm(self, x, w, gated, out, bias, accumulate, act, plan):
         _check(x, "x", dims=2, contiguous=False)
@@ -508,7 +515,7 @@ class CudaOps:
                 # of 8 warps per SM.  (Few rows of about the same length are a little faster with the key
                 # range of each row cut into the same number of pieces, below.)
                 return "stream", span, self._stream_slices(base8)
-            n = max(1, min(span // 64, 1184 // base8))
+            n = max(1, min(span // 64, 8 * self.sm_count // base8))
             keys = -(-(-(-span // n)) // 16) * 16
             n = -(-span // keys)
             if n > 4 and n % 4:
@@ -518,7 +525,7 @@ class CudaOps:
                 keys = -(-(-(-span // n)) // 16) * 16
             return "tma", keys, n
         if T <= 256:
-            n = max(1, min(-(-span // 128), -(-1184 // base)))
+            n = max(1, min(-(-span // 128), -(-8 * self.sm_count // base)))
             keys = -(-(-(-span // n)) // 128) * 128
             return "block", keys, -(-span // keys)
         if base >= 2048 or span <= 64:
@@ -527,26 +534,26 @@ class CudaOps:
         keys = -(-(-(-span // n)) // 32) * 32
         return "warp", keys, -(-span // keys)
 
-    @staticmethod
-    def _stream_slices(items):
+    def _stream_slices(self, items):
         """The most pieces the stream kernel may cut one (row, kv head) item into: enough for one wave of
         8 warps per SM over all items."""
-        return max(2, min(64, -(-1184 // items) + 1))
+        return max(2, min(64, -(-8 * self.sm_count // items) + 1))
 
-    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale):
+    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale, tiling=None):
         """Attention of all rows of a step: long portions on the tensor cores (bfloat16, head
-        sizes up to 128), decoded tokens and short portions row by row."""
+        sizes up to 128), decoded tokens and short portions row by row.  ``tiling``: the step's rows cut into
+        tiles of up to 128 rows (``engine.step.Tiling``); without one every row goes row by row."""
         P = cache.page_size
-        tc = (step.n_tiles > 0 and q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16 and hd <= 128
-              and (64 % P == 0 or P % 64 == 0) and step.attention_splits is None)
+        tc = (tiling is not None and tiling.n_tiles > 0 and q.dtype == torch.bfloat16 and cache.k.dtype == torch.bfloat16
+              and hd <= 128 and (64 % P == 0 or P % 64 == 0) and step.attention_splits is None)
         if not tc:
             return self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale,
                                         step.max_kv_len, splits=step.attention_splits,
                                         ragged=not step.even_lengths, fresh_keys=step.longest_entry)
-        self.attention_prefill_tc(q, cache, step.tiles, step.n_tiles, out, nq, nkv, hd, window, scale)
-        if step.n_other_rows:
+        self.attention_prefill_tc(q, cache, tiling.tiles, tiling.n_tiles, out, nq, nkv, hd, window, scale)
+        if tiling.n_other_rows:
             self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len,
-                                 rows=step.other_rows, fresh_keys=step.longest_entry)
+                                 rows=tiling.other_rows, fresh_keys=step.longest_entry)
 
     def attention_prefill_tc(self, q, cache, tiles, n_tiles, out, nq, nkv, hd, window, scale):
         _check(q, "q", torch.bfloat16, 2)

@@ -18,7 +18,10 @@ def expected_from_config(config: dict, with_fused=False):
     spec = arch.model_spec(arch.parse_config(config))
     ctx = BuildContext(ops=None, device=torch.device("cpu"), compute="float32")
     layers = [Layer(ls, ctx) for ls in spec.layers]
-    expected = expected_tensors(spec, layers, NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx))
+    from ..registry import POSITION_ENCODINGS
+    embed_position = (POSITION_ENCODINGS.get(spec.embed_position.kind)(spec.embed_position.params, ctx)
+                      if spec.embed_position is not None else None)
+    expected = expected_tensors(spec, layers, NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx), embed_position)
     return (spec, expected, fused_tensors(layers)) if with_fused else (spec, expected)
 
 

@@ -22,7 +22,7 @@ from ..config.spec import ModelSpec
 from ..errors import ConfigError, ModelError
 from ..parts.base import BuildContext, matmul_dtype
 from ..parts.block import run_norm
-from ..registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS
+from ..registry import ARCHITECTURES, BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS
 from ..weights.loader import load_tensors
 from ..weights.sources import SafetensorsSource, WeightSpec
 from .step import StepEntry, StepStaging
@@ -67,9 +67,12 @@ class Layer:
             part.load({name: tensors[pre + name] for name in part.weights() if pre + name in tensors})
 
 
-def expected_tensors(spec: ModelSpec, layers, final_norm) -> dict:
+def expected_tensors(spec: ModelSpec, layers, final_norm, embed_position=None) -> dict:
     """Every tensor name the model reads, with its shape and role."""
     exp = {spec.embed_name + "weight": WeightSpec((spec.vocab_size, spec.hidden_size))}
+    if embed_position is not None:
+        for name, ws in embed_position.weights().items():
+            exp[spec.embed_position_name + name] = ws
     for layer in layers:
         exp.update(layer.weights())
     for name, ws in final_norm.weights().items():
@@ -107,14 +110,22 @@ class Model:
         self.ctx = BuildContext(ops=ops, device=self.device, compute=dtype)
         self.layers = [Layer(ls, self.ctx) for ls in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, self.ctx)
+        self.embed_position = None
+        if spec.embed_position is not None:
+            self.embed_position = POSITION_ENCODINGS.get(spec.embed_position.kind)(spec.embed_position.params, self.ctx)
+            if not hasattr(self.embed_position, "after_embedding"):
+                raise ConfigError(f"position encoding {spec.embed_position.kind!r} cannot act on the embedded rows "
+                                  f"(it has no after_embedding)")
 
-        expected = expected_tensors(spec, self.layers, self.final_norm)
+        expected = expected_tensors(spec, self.layers, self.final_norm, self.embed_position)
         self.expected = expected
         tensors = load_tensors(source, expected, dtype, self.device, fused_tensors(self.layers))
         self.embed_table = tensors[spec.embed_name + "weight"]
         self.head_weight = self.embed_table if spec.tie_word_embeddings else tensors[spec.head_name + "weight"]
         self.head_bias = tensors.get(spec.head_name + "bias")
         self.final_norm.load({n: tensors[spec.final_norm_name + n] for n in self.final_norm.weights()})
+        if self.embed_position is not None:
+            self.embed_position.load({n: tensors[spec.embed_position_name + n] for n in self.embed_position.weights()})
         for layer in self.layers:
             layer.load(tensors)
         del tensors
@@ -146,20 +157,25 @@ class Model:
         cache_dtype = torch.bfloat16 if dtype == "bfloat16" else torch.float32
         self.cache = CacheManager(kv_calls, state_calls, page_size=page_size, n_pages=n_pages, max_slots=max_slots,
                                   max_context=self.max_context, dtype=cache_dtype, device=self.device)
-        self.staging = StepStaging(max_step_tokens, self.device, status=getattr(ops, "page_error", None))
+        # one mixer of each kind plans the step, and the step carries a tiling for every distinct declaration
+        self.planners = list({type(m): m for m in (layer.parts.get("mixer") for layer in self.layers)
+                              if m is not None}.values())
+        needs = [n for n in (m.step_needs() for layer in self.layers for m in [layer.parts.get("mixer")] if m is not None)
+                 if n is not None]
+        self.staging = StepStaging(max_step_tokens, self.device, status=getattr(ops, "page_error", None), needs=needs)
         self.max_step_tokens = max_step_tokens
         # where the sampler leaves its tokens on the device, if the kernel set has such a place: an entry may
         # take its token from there (StepEntry.feed) instead of from the host
         self.fed_from = getattr(ops, "token_out", None)
-        # decode steps (one token per entry) are captured once per batch size and key-range
-        # split, and replayed: their hundreds of small launches would otherwise be bound by
-        # the host
+        # decode steps (one token per entry) are captured once per batch size and mixers' plan (the attention's
+        # key-range split), and replayed: their hundreds of small launches would otherwise be bound by the host
         self.use_graphs = (use_graphs and self.device.type == "cuda" and self.final_norm.graph_safe
+                           and (self.embed_position is None or self.embed_position.graph_safe)
                            and all(p.graph_safe for layer in self.layers for p in layer.parts.values()))
         self._graphs = {}
         self._graph_pool = None         # one memory pool for all captured steps: only one of them runs at a time
         self.graph_max_batch = 256
-        # Captured graphs are kept by (batch size, context bucket, even lengths); a long-running engine with
+        # Captured graphs are kept by (batch size, the mixers' plans); a long-running engine with
         # varying batches would collect thousands, so only the most recently used ones are kept.
         self.graph_max_kept = 64
 
@@ -203,29 +219,15 @@ class Model:
             raise ModelError("an entry's token is fed from the sampler's output, but this kernel set keeps none")
         step.record = record
         step.attention_splits = attention_splits
-        if step.n_tokens == len(entries):
-            # a batch of decoded tokens: requests of about the same length share one way of cutting their keys;
-            # a ragged batch lets the attention kernel cut the keys of all rows into equal runs itself
-            lens = [e.start_pos + 1 for e in entries]
-            step.even_lengths = min(lens) * 4 >= max(lens) * 3
-        if (self.use_graphs and attention_splits is None
-                and step.n_tokens == len(entries) <= self.graph_max_batch and step.n_want == step.n_tokens):
-            return self._graphed_decode(step)
+        captured = (self.use_graphs and attention_splits is None
+                    and step.n_tokens == len(entries) <= self.graph_max_batch and step.n_want == step.n_tokens)
+        plans = tuple(m.plan_step(step, captured) for m in self.planners)
+        if captured:
+            return self._graphed_decode(step, plans)
         return self.forward(step)
 
-    @staticmethod
-    def _context_bucket(step):
-        """A decode batch's context length rounded up to a bucket, so that few graphs are needed as requests
-        grow: four buckets per doubling of the context, at least 256 apart.  A graph serves a range of lengths,
-        and the key-range split it was captured with is never much longer than needed."""
-        kv = max(step.max_kv_len, 1)
-        gran = max(256, 1 << max(kv.bit_length() - 3, 0))
-        return -(-kv // gran) * gran
-
-    def _graphed_decode(self, step):
-        bucket = self._context_bucket(step)
-        step.max_kv_len = bucket          # splits are chosen for the bucket, not the exact length
-        key = (step.n_tokens, bucket, step.even_lengths)
+    def _graphed_decode(self, step, plans):
+        key = (step.n_tokens, plans)      # the batch size and what the mixers' plans say shapes their launches
         entry = self._graphs.pop(key, None)
         if entry is None:
             # The first step of its kind runs eagerly (which also loads modules and warms the allocator) and its
@@ -261,6 +263,8 @@ class Model:
             ops.embed(step.ids, self.embed_table, h, spec.embed_scale, fed_rows=step.fed_rows, fed_from=self.fed_from)
         else:
             ops.embed(step.ids, self.embed_table, h, spec.embed_scale)
+        if self.embed_position is not None:
+            self.embed_position.after_embedding(h, step)
         carry = None     # an addition to h that a layer left for the next norm to apply
         for i, call in enumerate(self.order):
             layer = self.layers[call.layer]

@@ -14,6 +14,7 @@ import math
 import torch
 
 from ..cache.manager import KVSpec
+from ..engine.step import StepNeeds
 from ..errors import ConfigError, ModelError
 from ..registry import MIXERS, POSITION_ENCODINGS
 from .base import Mixer, Pending, mat, matmul_dtype, vec
@@ -33,6 +34,8 @@ class Attention(Mixer):
     qkv_bias, out_bias, scale (optional), position (PartSpec or None)."""
 
     graph_safe = True
+    # portions of at least 16 rows go to the tensor-core attention in tiles of 128 query rows, the rest row by row
+    NEEDS = StepNeeds(tile_rows=128, tile_min_rows=16)
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -49,6 +52,7 @@ class Attention(Mixer):
         self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.hd)
         self.position = shared_position_encoding(p["position"], ctx) if p.get("position") is not None else None
         self.rot = self.position.rotary_dim if self.position is not None else 0
+        self.rot_style = self.position.style if self.position is not None else "half"
         if self.rot > self.hd:
             raise ConfigError("rotary_dim exceeds head_dim")
 
@@ -86,6 +90,25 @@ class Attention(Mixer):
     def cache_spec(self):
         return KVSpec(self.nkv, self.hd, self.window)
 
+    def step_needs(self):
+        return self.NEEDS
+
+    def plan_step(self, step, captured):
+        """How the key ranges of a batch of decoded tokens are cut.  Requests of about the same length share one
+        way of cutting their keys; a ragged batch lets the kernel cut the keys of all rows into equal runs
+        itself.  In a captured step the splits are chosen for a bucketed context length, so that few graphs are
+        needed as requests grow: four buckets per doubling of the context, at least 256 apart."""
+        if step.n_tokens != len(step.entries):
+            return None
+        lens = [e.start_pos + 1 for e in step.entries]
+        step.even_lengths = min(lens) * 4 >= max(lens) * 3
+        if not captured:
+            return (step.even_lengths,)
+        kv = max(step.max_kv_len, 1)
+        gran = max(256, 1 << max(kv.bit_length() - 3, 0))
+        step.max_kv_len = -(-kv // gran) * gran
+        return (step.max_kv_len, step.even_lengths)
+
     def forward(self, x, residual, step, cache, state, writes_cache=True):
         if cache is None:
             raise ModelError("attention needs a cache")
@@ -98,14 +121,14 @@ class Attention(Mixer):
             # the projection is left as partial sums over pieces of K; the rotary kernel adds them and the bias
             qkv = ops.gemm_partials(xin, self.w_qkv)
             ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
-                              True, step.status, bias=self.b_qkv)
+                              True, step.status, bias=self.b_qkv, style=self.rot_style)
         else:   # reads another call's cache: only the queries are needed
             width, nqd = (nq + 2 * nkv) * hd, nq * hd
             qkv = torch.empty((1, T, width), dtype=torch.float32, device=xin.device)
             ops.gemm(xin, self.w_qkv[:nqd], qkv[0, :, :nqd], bias=self.b_qkv[:nqd] if self.b_qkv is not None else None)
             ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
-                              False, step.status)
+                              False, step.status, style=self.rot_style)
         attn = torch.empty_like(q)
-        ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale)
+        ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale, tiling=step.tiling(self.NEEDS))
         # the output projection is handed to the next norm as partial sums (and its bias)
         return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)

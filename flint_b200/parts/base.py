@@ -13,14 +13,17 @@ Norm          ``forward(x, want, row_index=None, pending=None, router=None) -> {
               types the next part asked for.  A norm with ``supports_pending`` applies a
               ``Pending`` addition to x first; one with ``supports_router`` can fill a
               ``RouterRequest``.  Both are optional abilities; the block works without them.
-Mixer         ``input_dtypes()``, ``cache_spec()``, ``state_spec()``,
+Mixer         ``input_dtypes()``, ``cache_spec()``, ``state_spec()``, optionally ``step_needs()`` (rows cut into
+              tiles) and ``plan_step(step, captured)`` (how this step's work is cut),
               ``forward(x, residual, step, cache, state, writes_cache=True)``:
               adds its output into ``residual`` (float32 [T, H]) in place and returns None,
               or returns a ``Pending`` that the block hands to the next norm.
 FeedForward   ``input_dtypes()``, ``forward(x, residual, step)``: adds into ``residual`` or
               returns a ``Pending``.  A feed-forward with ``router_request(n_rows)`` gets the
               filled request back as ``forward(..., routed=request)``.
-PositionEncoding  ``rotary_dim``, ``tables() -> (cos, sin)`` float32 [positions, rotary_dim/2].
+PositionEncoding  ``rotary_dim``, ``style`` ("half": dims i and i + rotary_dim/2 rotate together, "interleaved":
+              dims 2i and 2i + 1), ``tables() -> (cos, sin)`` float32 [positions, rotary_dim/2]; one named by
+              ``ModelSpec.embed_position`` instead has ``after_embedding(h, step)`` and adds to the embedded rows.
 Block         ``forward(residual, step, cache, state, writes_cache)``: the arrangement of
               the parts of one layer.
 """
@@ -110,6 +113,18 @@ class Mixer(Part):
     def state_spec(self):
         return None
 
+    def step_needs(self):
+        """A ``StepNeeds`` if the mixer wants the step's rows cut into tiles (see ``engine/step.py``), else None."""
+        return None
+
+    def plan_step(self, step, captured: bool):
+        """Called once per step (on one mixer of each kind) before the layers run, with the host-side view of
+        the batch: the mixer may work out how it will cut its work (into ``step.plans[kind]`` or the fields it
+        reads later) and returns a hashable value naming everything about the plan that shapes its launches,
+        or None.  A decode step that is captured as a CUDA graph (``captured``) is keyed by these values, so a
+        graph is only replayed on steps that would launch the same work."""
+        return None
+
     def forward(self, x, residual, step, cache, state, writes_cache=True):
         raise NotImplementedError
 
@@ -129,6 +144,7 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     rotary_dim = 0
+    style = "half"          # which dims of a head rotate together: "half" (i, i + rotary_dim/2) or "interleaved" (2i, 2i + 1)
 
     def tables(self):
         raise NotImplementedError

@@ -86,7 +86,8 @@ class RefOps:
             self.grouped_gemm(x, w, out[0], plan)
         return out
 
-    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None):
+    def rope_kv_write(self, qkv, pos, slot, cos, sin, rot, q_out, cache, nq, nkv, hd, write_kv, status, bias=None,
+                      style="half"):
         if qkv.dim() == 3:
             qkv = qkv.to(self.cd).sum(0)
         if bias is not None:
@@ -101,6 +102,10 @@ class RefOps:
                 return h
             c = cos[p].to(self.cd)[:, None, :]
             s = sin[p].to(self.cd)[:, None, :]
+            if style == "interleaved":          # dims 2i and 2i + 1 rotate together
+                a, b, rest = h[..., 0:rot:2], h[..., 1:rot:2], h[..., rot:]
+                both = torch.stack([a * c - b * s, b * c + a * s], -1).reshape(*h.shape[:-1], rot)
+                return torch.cat([both, rest], -1)
             a, b, rest = h[..., :half], h[..., half:rot], h[..., rot:]
             return torch.cat([a * c - b * s, b * c + a * s, rest], -1)
         q_out.copy_(rotate(x[:, :nq]).reshape(T, nq * hd).to(q_out.dtype))
@@ -162,7 +167,7 @@ class RefOps:
             out[lo:hi] = (xs[lo:hi] @ w[e].to(self.cd).T).to(out.dtype)
 
     # ------------------------------------------------------------------ attention
-    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale):
+    def attention(self, q, cache, step, out, nq, nkv, hd, window, scale, tiling=None):
         self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len)
 
     def paged_attention(self, q, cache, pos, slot, out, nq, nkv, hd, window, scale, max_kv_len, splits=None,

@@ -240,7 +240,9 @@ def test_decode_attention_is_cut_into_splits_that_cover_the_keys():
     from flint_b200.csrc.ops import CudaOps
 
     class Sizes:                      # the plan is arithmetic on sizes: no device is needed
-        _stream_slices = staticmethod(CudaOps._stream_slices)
+        sm_count = 148
+        _stream_slices = CudaOps._stream_slices
+    Sizes = Sizes()
     for T in (1, 2, 3, 8, 16, 31):
         for nq, nkv in ((32, 8), (8, 8), (6, 2), (48, 2)):
             for span in (1, 63, 64, 65, 300, 2049, 2100, 4096, 16384, 40000):

@@ -403,6 +403,38 @@ def test_rope_write_and_attention(ops, ref, qd, cd, nq, nkv, hd, P, window):
         close(out_d, out_r, *((2e-5, 2e-5) if qd == torch.float32 else (2e-2, 2e-2)))
 
 
+@pytest.mark.parametrize("rot", [8, 32])
+def test_rope_write_with_neighbouring_dims_rotating_together(ops, ref, rot):
+    """The other rotation style (dims 2i and 2i + 1), with split partial sums, a bias and the cache write."""
+    T, nq, nkv, hd, P = 7, 4, 2, 32, 16
+    W = (nq + 2 * nkv) * hd
+    parts = rnd(3, T, W)
+    bias = rnd(W, seed=5)
+    k, v, bt = make_cache(4, nkv, P, hd, torch.float32, 2, 4)
+    bt[0, :2] = torch.tensor([3, 1], dtype=torch.int32)
+    bt[1, :1] = torch.tensor([0], dtype=torch.int32)
+    dv, cv = views(k, v, bt, P, nkv, hd, 0)
+    pos = torch.tensor([10, 11, 12, 13, 14, 0, 1], dtype=torch.int32)
+    slot = torch.tensor([0, 0, 0, 0, 0, 1, 1], dtype=torch.int32)
+    ang = torch.arange(32, dtype=torch.float64)[:, None] * (100.0 ** (-torch.arange(rot // 2, dtype=torch.float64) * 2 / rot))
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    q_d = torch.empty(T, nq * hd, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    ops.rope_kv_write(parts.to(DEV), pos.to(DEV), slot.to(DEV), cos.to(DEV), sin.to(DEV), rot, q_d, dv, nq, nkv, hd, True,
+                      status, bias=bias.to(DEV), style="interleaved")
+    q_r = torch.empty(T, nq * hd, dtype=torch.float64)
+    ref.rope_kv_write(parts, pos, slot, cos, sin, rot, q_r, cv, nq, nkv, hd, True, None, bias=bias, style="interleaved")
+    close(q_d, q_r, 1e-5, 1e-5)
+    close(dv.k, cv.k, 1e-5, 1e-5)
+    close(dv.v, cv.v, 1e-5, 1e-5)
+    # by hand for one element pair: (x0, x1) of head 0 of token 0 rotate by the angle of position 10, pair 0
+    x = parts.double().sum(0)[0] + bias.double()
+    c, s_ = math.cos(10.0), math.sin(10.0)
+    assert abs(q_d[0, 0].item() - (x[0] * c - x[1] * s_).item()) < 1e-4
+    assert abs(q_d[0, 1].item() - (x[1] * c + x[0] * s_).item()) < 1e-4
+    assert int(status.item()) == 0
+
+
 def test_attention_far_key_stands_out(ops, ref):
     """One key far back among hundreds gets a large score: the output must be (almost) its value."""
     nq, nkv, hd, P = 2, 1, 32, 16

@@ -229,9 +229,8 @@ def test_toy_architecture_with_a_stateful_mixer_is_built_and_stepped():
         from flint_b200.engine.model import architecture_of
         spec = architecture_of({"architectures": ["ToyStateLM"]}).model_spec({})
         from flint_b200.engine.model import Layer, expected_tensors
-        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers])
-        for n, ws in NORMS.get("rmsnorm")(spec.final_norm.params, ctx_for("float32")).weights().items():
-            expected["norm." + n] = ws
+        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers],
+                                    NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx_for("float32")))
         src = RandomSource(expected, 3, dtype=torch.float32)
         model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=12, max_slots=3)
         assert sorted(model.cache.state) == [0, 2] and len(model.cache.groups) == 1
@@ -377,9 +376,8 @@ def test_toy_architecture_with_its_own_routing_and_position_encoding():
     try:
         from flint_b200.engine.model import Layer, architecture_of, expected_tensors
         spec = architecture_of({"architectures": ["ToyRoutedLM"]}).model_spec({})
-        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers])
-        for n, ws in NORMS.get("layernorm")(spec.final_norm.params, ctx_for("float32")).weights().items():
-            expected["norm." + n] = ws
+        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers],
+                                    NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx_for("float32")))
         src = RandomSource(expected, 5, dtype=torch.float32)
         model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=8, max_slots=2)
         w = {n: src.read(n).double() for n in expected}
@@ -402,3 +400,203 @@ def test_toy_architecture_with_its_own_routing_and_position_encoding():
         FEED_FORWARDS.unregister("test_switch_ffn")
         POSITION_ENCODINGS.unregister("test_interpolated_rotary")
         ARCHITECTURES.unregister("ToyRoutedLM")
+
+
+def test_a_stateful_mixer_is_recomputed_from_zero_after_preemption():
+    """The toy model with the running-sum mixer through ``Engine`` with so few pages that requests are preempted
+    and later recomputed from their prompt and generated tokens: the mixer's state slab must start from zero on
+    every re-admission, or the recomputed tokens differ from the plain whole-sequence result."""
+    from flint_b200.engine.engine import Engine
+    from flint_b200.sampling.params import SamplingParams
+    MIXERS.register("test_running_sum", RunningSumMixer, replace=True)
+    try:
+        from flint_b200.engine.model import Layer, expected_tensors
+        spec = toy_spec()
+        expected = expected_tensors(spec, [Layer(ls, ctx_for("float32")) for ls in spec.layers],
+                                    NORMS.get(spec.final_norm.kind)(spec.final_norm.params, ctx_for("float32")))
+        src = RandomSource(expected, 3, dtype=torch.float32)
+        w = {n: src.read(n).double() for n in expected}
+        prompts = [[(i * 7 + 3 * k) % 97 for i in range(n)] for k, n in enumerate((21, 30, 26))]
+        preempted = 0
+        for n_pages in (12, 5):
+            model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=n_pages, max_slots=3,
+                          max_step_tokens=32)
+            eng = Engine(model, SamplingParams.greedy(), prefill_chunk=16, stop=())
+            got = eng.generate(prompts, 14)
+            preempted += eng.scheduler.preemptions
+            for p, g in zip(prompts, got):
+                assert len(g) == 14
+                logits = toy_plain(spec, w, list(p) + g)
+                for j, tok in enumerate(g):
+                    row = logits[len(p) - 1 + j]
+                    best = int(torch.argmax(row))
+                    assert tok == best or float(row[best] - row[tok]) < 1e-5, (n_pages, j, tok, best)
+            assert model.cache.free_slots == 3
+        assert preempted > 0, "pages never ran out"
+    finally:
+        MIXERS.unregister("test_running_sum")
+
+
+# ------------------------------------------------------------------------------------------------
+# a third toy architecture: positions added to the embedding, a rotation of neighbouring dims, and a mixer whose
+# values are wider than its keys
+
+class LearnedPositions(PositionEncoding):
+    """h[t] += table[position of row t]: a position encoding that acts on the embedded rows."""
+
+    graph_safe = True
+
+    def weights(self):
+        return {"weight": mat(int(self.params["max_positions"]), int(self.params["width"]))}
+
+    def load(self, t):
+        self.table = t["weight"].float()
+
+    def after_embedding(self, h, step):
+        h += self.table[step.pos.long()]
+
+
+class NeighbourRotary(PositionEncoding):
+    """Plain rotary angles, but dims 2i and 2i + 1 of a head rotate together."""
+    style = "interleaved"
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.rotary_dim = int(params["rotary_dim"])
+
+    def tables(self):
+        half = self.rotary_dim // 2
+        inv = float(self.params["theta"]) ** (-2.0 * torch.arange(half, dtype=torch.float64) / self.rotary_dim)
+        ang = torch.arange(int(self.params["max_positions"]), dtype=torch.float64)[:, None] * inv
+        return torch.cos(ang).float().to(self.ctx.device), torch.sin(ang).float().to(self.ctx.device)
+
+
+class WideValueMixer(Mixer):
+    """Causal attention with keys of 16 numbers and values of 24, written with ordinary tensor operations over
+    the pages the cache manager gives it."""
+    KD, VD, HEADS = 16, 24, 2
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width = params["width"]
+
+    def weights(self):
+        n = self.HEADS
+        return {"q.weight": mat(n * self.KD, self.width), "k.weight": mat(n * self.KD, self.width),
+                "v.weight": mat(n * self.VD, self.width), "o.weight": mat(self.width, n * self.VD)}
+
+    def load(self, t):
+        self.w = {k: v.float() for k, v in t.items()}
+
+    def input_dtypes(self):
+        return (torch.float32,)
+
+    def cache_spec(self):
+        return KVSpec(self.HEADS, self.KD, 0, value_dim=self.VD)
+
+    def forward(self, x, residual, step, cache, state, writes_cache=True):
+        x32, n, P = x[torch.float32], self.HEADS, cache.page_size
+        assert tuple(cache.k.shape[1:]) == (n, P, self.KD) and tuple(cache.v.shape[1:]) == (n, P, self.VD)
+        q = (x32 @ self.w["q.weight"].T).view(-1, n, self.KD)
+        k = (x32 @ self.w["k.weight"].T).view(-1, n, self.KD)
+        v = (x32 @ self.w["v.weight"].T).view(-1, n, self.VD)
+        pos, slot = step.pos.long(), step.slot.long()
+        pages = cache.block_table[slot, pos // P].long()
+        cache.k[pages, :, pos % P] = k.to(cache.k.dtype)
+        cache.v[pages, :, pos % P] = v.to(cache.v.dtype)
+        out = torch.zeros((x32.shape[0], n * self.VD), device=x32.device)
+        for e, row0 in zip(step.entries, step.entry_start):
+            js = torch.arange(e.start_pos + len(e.tokens), device=x32.device)
+            pg = cache.block_table[e.slot, js // P].long()
+            ks, vs = cache.k[pg, :, js % P].float(), cache.v[pg, :, js % P].float()      # [keys, heads, dim]
+            for r in range(len(e.tokens)):
+                seen = e.start_pos + r + 1
+                s = torch.einsum("hd,khd->hk", q[row0 + r], ks[:seen]) / math.sqrt(self.KD)
+                out[row0 + r] = torch.einsum("hk,khd->hd", torch.softmax(s, -1), vs[:seen]).reshape(-1)
+        residual += out @ self.w["o.weight"].T
+
+
+def wide_spec(H=40, V=53):
+    rot = PartSpec("test_neighbour_rotary", {"rotary_dim": 8, "theta": 50.0, "max_positions": 96})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "window": 0,
+                                  "qkv_bias": False, "out_bias": False, "position": rot})
+    wide = PartSpec("test_wide_value", {"width": H})
+    ln = PartSpec("layernorm", {"width": H, "eps": 1e-5, "bias": True})
+    mlp = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": 32, "act": "silu"})
+    names = {"norm1": "n1.", "mixer": "mix.", "norm2": "n2.", "ffn": "ff."}
+    layers = (LayerSpec("prenorm", {"norm1": ln, "mixer": attn, "norm2": ln, "ffn": mlp}, "layers.0.", names),
+              LayerSpec("prenorm", {"norm1": ln, "mixer": wide, "norm2": ln, "ffn": mlp}, "layers.1.", names))
+    return ModelSpec(architecture="ToyWideLM", vocab_size=V, hidden_size=H, max_positions=96, layers=layers,
+                     order=(LayerCall(0), LayerCall(1)), final_norm=ln, head_bias=False, tie_word_embeddings=True,
+                     embed_position=PartSpec("test_learned_positions", {"max_positions": 96, "width": H}))
+
+
+def wide_plain(w, tokens):
+    T = len(tokens)
+    h = P.embed(tokens, w["embed_tokens.weight"]) + w["embed_positions.weight"][:T]
+    mlp = lambda x, p: P.expert_mlp(x, w[p + "gate_proj.weight"], w[p + "up_proj.weight"], w[p + "down_proj.weight"])
+    inv = 50.0 ** (-2.0 * torch.arange(4, dtype=torch.float64) / 8)
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * inv
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rotate(x):                      # dims 2i and 2i + 1 of the first 8 dims of a head
+        a, b = x[..., 0:8:2], x[..., 1:8:2]
+        both = torch.stack([a * cos - b * sin, b * cos + a * sin], -1).reshape(*x.shape[:-1], 8)
+        return torch.cat([both, x[..., 8:]], -1)
+    p = "layers.0."
+    x = P.layer_norm(h, w[p + "n1.weight"], w[p + "n1.bias"], 1e-5)
+    q = rotate((x @ w[p + "mix.q_proj.weight"].T).view(T, 4, 16))
+    k = rotate((x @ w[p + "mix.k_proj.weight"].T).view(T, 2, 16))
+    v = (x @ w[p + "mix.v_proj.weight"].T).view(T, 2, 16)
+    h = h + P.attention(q, k, v, 0).reshape(T, 64) @ w[p + "mix.o_proj.weight"].T
+    h = h + mlp(P.layer_norm(h, w[p + "n2.weight"], w[p + "n2.bias"], 1e-5), p + "ff.")
+    p = "layers.1."
+    x = P.layer_norm(h, w[p + "n1.weight"], w[p + "n1.bias"], 1e-5)
+    q = (x @ w[p + "mix.q.weight"].T).view(T, 2, 16)
+    k = (x @ w[p + "mix.k.weight"].T).view(T, 2, 16)
+    v = (x @ w[p + "mix.v.weight"].T).view(T, 2, 24)
+    a = torch.zeros(T, 2, 24, dtype=torch.float64)
+    for t in range(T):
+        s = torch.einsum("hd,khd->hk", q[t], k[:t + 1]) / 4.0
+        a[t] = torch.einsum("hk,khd->hd", torch.softmax(s, -1), v[:t + 1])
+    h = h + a.reshape(T, 48) @ w[p + "mix.o.weight"].T
+    h = h + mlp(P.layer_norm(h, w[p + "n2.weight"], w[p + "n2.bias"], 1e-5), p + "ff.")
+    return P.layer_norm(h, w["norm.weight"], w["norm.bias"], 1e-5) @ w["embed_tokens.weight"].T
+
+
+def test_toy_architecture_with_embedded_positions_neighbour_rotation_and_wide_values():
+    """Positions added to the embedding through the spec's hook, the package's attention with a position
+    encoding of the other rotation style, and a mixer whose cached values are wider than its keys (a cache group
+    of its own): registered and built from here, stepped in portions and token by token."""
+    POSITION_ENCODINGS.register("test_learned_positions", LearnedPositions, replace=True)
+    POSITION_ENCODINGS.register("test_neighbour_rotary", NeighbourRotary, replace=True)
+    MIXERS.register("test_wide_value", WideValueMixer, replace=True)
+    try:
+        from flint_b200.engine.model import Layer, expected_tensors
+        spec = wide_spec()
+        c = ctx_for("float32")
+        expected = expected_tensors(spec, [Layer(ls, c) for ls in spec.layers],
+                                    NORMS.get(spec.final_norm.kind)(spec.final_norm.params, c),
+                                    POSITION_ENCODINGS.get(spec.embed_position.kind)(spec.embed_position.params, c))
+        assert "embed_positions.weight" in expected
+        src = RandomSource(expected, 8, dtype=torch.float32)
+        model = Model(spec, src, dtype="float32", device=DEV, page_size=16, n_pages=8, max_slots=2)
+        assert len(model.cache.groups) == 2                     # keys of 16 with values of 16, and with values of 24
+        assert {g.spec.value_width for g in model.cache.groups} == {16, 24}
+        w = {n: src.read(n).double() for n in expected}
+        tokens = [(i * 5 + 2) % 53 for i in range(60)]
+        want = wide_plain(w, tokens)
+        slot = model.cache.admit()
+        got, done = [], 0
+        for n in [7, 2, 19, 1, 1, 25, 1, 1, 1, 1, 1]:
+            n = min(n, len(tokens) - done)
+            model.cache.ensure(slot, done, done + n)
+            got.append(model.step([StepEntry(slot, done, tokens[done:done + n], list(range(n)))]).cpu())
+            done += n
+            model.cache.advance(slot, done)
+        err = (torch.cat(got).double() - want[:done]).abs().max().item()
+        assert err < 1e-4, f"{err:.2e}"
+    finally:
+        POSITION_ENCODINGS.unregister("test_learned_positions")
+        POSITION_ENCODINGS.unregister("test_neighbour_rotary")
+        MIXERS.unregister("test_wide_value")
