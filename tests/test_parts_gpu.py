@@ -78,7 +78,7 @@ def test_attention_part_alone(dtype):
                       dtype=store, device=DEV)
     slot = cm.admit()
     x = torch.randn(T, H)
-    staging = StepStaging(64, DEV)
+    staging = StepStaging(64, DEV, needs=[part.step_needs()])
     res = torch.zeros(T, H, device=DEV)
     for a, b in ((0, 33), (33, 50)):
         cm.ensure(slot, a, b)
