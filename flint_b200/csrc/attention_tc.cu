@@ -395,6 +395,18 @@ struct DecodeParams {
   int fresh_keys;    // at most this many of a row's newest keys (its own included) are written by the kernel before
   float scale;
   long long wait_cycles;     // limit of every wait on an mbarrier
+  // Fused form (decoded tokens only): instead of q, the projection's output [qkv_slices][rows, (nq + 2 nkv) hd]
+  // float32 (partial sums qkv_stride floats apart, plus qkv_bias), of which this kernel makes q (rotated), and the
+  // row's new key (rotated) and value, which it writes into the cache and uses itself.
+  const float* qkv;
+  const float* qkv_bias;
+  const float* cos_t;
+  const float* sin_t;
+  __nv_bfloat16* k_cache;
+  __nv_bfloat16* v_cache;
+  int* page_error;
+  long long qkv_stride;
+  int qkv_slices, rot;
 };
 
 // Merge records [0, n_rec) of the ng query heads of one item, by a whole block of 128 threads:
@@ -446,7 +458,14 @@ __device__ __forceinline__ void merge_records(const DecodeParams& p, int ti, int
 
 // DKT: keys per stage of the ring, 16 or 32 (a stage of 32 keys is worked through as two halves of 16; it takes
 // half as many copies and waits per key, and pages must be multiples of 32 keys)
-template <int HD, int DKT>
+// FUSED: the kernel also does the work of the rotary kernel for its rows (each one decoded token): the four warps
+// of a block (four splits of one row and kv head) add up the projection's partial sums and the bias for the
+// group's query heads, rotate them and keep q in shared memory; the block whose keys include the row's own position
+// does the same for the new key and value, writes them into the cache page, and the warp that reaches that position
+// puts them into its tile in shared memory (what the copy brought there is the page's old content).  So nothing
+// in the cache that this kernel reads is written in this step, and every tile is asked for before the wait for the
+// projection.
+template <int HD, int DKT, bool FUSED>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                            const DecodeParams p) {
@@ -457,6 +476,8 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   constexpr int SB = 2 * 2 * DKT * 128;        // bytes of a stage: K and V, two chunks of 64 dims
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[4 * DSTAGES];
+  __shared__ __align__(16) float x_s[FUSED ? (MG + 2) * HD : 4];              // sums of 8 query heads, the key, the value
+  __shared__ __align__(16) __nv_bfloat16 q_s[FUSED ? (MG + 2) * HD : 8];      // the same rotated and narrowed
   pdl_launch();
   // Nothing below reads what the kernels before this one write, until pdl_wait(): positions, slots and block
   // tables come from the host, and of the cache only a row's newest p.fresh_keys keys and values are written
@@ -523,17 +544,130 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
   // the queries) may still run; a tile that holds a key written in this step waits for it
   int issued = 0;
   if (lane == 0)
-    for (; issued < DSTAGES - 1 && issued < n_steps && first + (issued + 1) * DKT <= pq + 1 - p.fresh_keys; ++issued)
+    for (; issued < DSTAGES - 1 && issued < n_steps &&
+           (FUSED || first + (issued + 1) * DKT <= pq + 1 - p.fresh_keys); ++issued)
       issue(issued, issued);
+  // the warp whose keys include the row's own position, and the step and row of its ring that hold it
+  const bool owner_warp = FUSED && lo <= pq && hi == pq + 1;
+  const int own_step = owner_warp ? (pq - first) / DKT : -1;
+  // FUSED: what this warp prepares: two of the group's query heads, and, in the block that holds the split with
+  // the row's own position, warp 0 the new key and warp 1 the new value.  A lane takes four neighbouring dims.
+  // What does not come from the projection (bias, the rotation's cos and sin) is read before the wait for it.
+  constexpr int JOBS = 3;
+  const int d4 = lane * 4;
+  int job_slot[JOBS], job_head[JOBS];
+  bool job_on[JOBS];
+  float4 job_bias[JOBS];
+  float rc[4], rs[4];
+  if (FUSED) {
+    const int own_split = (pq - lo_row) / sk;
+    const bool owner_block = (own_split >> 2) == (split >> 2);
+    const int half = p.rot >> 1;
+#pragma unroll
+    for (int job = 0; job < JOBS; ++job) {
+      if (job < 2) {
+        const int g = warp * 2 + job;
+        job_on[job] = g < ng && d4 < hd;
+        job_slot[job] = g;
+        job_head[job] = h0 + g;
+      } else {
+        job_on[job] = owner_block && warp < 2 && d4 < hd;
+        job_slot[job] = MG + warp;
+        job_head[job] = warp == 0 ? nq + kvh : nq + p.nkv + kvh;
+      }
+      job_bias[job] = (job_on[job] && p.qkv_bias)
+                          ? *reinterpret_cast<const float4*>(p.qkv_bias + (size_t)job_head[job] * hd + d4)
+                          : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int dd = d4 + e;
+      rc[e] = 1.f;
+      rs[e] = 0.f;
+      if (dd < p.rot) {                              // dims i and i + rot/2 rotate together
+        const int i = dd < half ? dd : dd - half;
+        rc[e] = p.cos_t[(size_t)pq * half + i];
+        rs[e] = p.sin_t[(size_t)pq * half + i];
+      }
+    }
+  }
   pdl_wait();
   if (lane == 0)
     for (; issued < DSTAGES - 1 && issued < n_steps; ++issued) issue(issued, issued);
+  if (FUSED) {
+    const int half = p.rot >> 1;
+    const size_t row_off = (size_t)t * (nq + 2 * p.nkv) * hd;
+    // the partial sums of all of the warp's heads, five slices at a time in flight, added in order
+    float4 acc[JOBS];
+#pragma unroll
+    for (int job = 0; job < JOBS; ++job) acc[job] = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int INFL = 5;
+    for (int z0 = 0; z0 < p.qkv_slices; z0 += INFL) {
+      float4 part[JOBS][INFL];
+#pragma unroll
+      for (int job = 0; job < JOBS; ++job)
+#pragma unroll
+        for (int u = 0; u < INFL; ++u)
+          part[job][u] = (job_on[job] && z0 + u < p.qkv_slices)
+                             ? *reinterpret_cast<const float4*>(p.qkv + (size_t)(z0 + u) * p.qkv_stride + row_off +
+                                                                (size_t)job_head[job] * hd + d4)
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int job = 0; job < JOBS; ++job)
+#pragma unroll
+        for (int u = 0; u < INFL; ++u) {
+          acc[job].x += part[job][u].x; acc[job].y += part[job][u].y;
+          acc[job].z += part[job][u].z; acc[job].w += part[job][u].w;
+        }
+    }
+#pragma unroll
+    for (int job = 0; job < JOBS; ++job)
+      if (job_on[job]) {
+        acc[job].x += job_bias[job].x; acc[job].y += job_bias[job].y;
+        acc[job].z += job_bias[job].z; acc[job].w += job_bias[job].w;
+        *reinterpret_cast<float4*>(&x_s[job_slot[job] * HD + d4]) = acc[job];
+      }
+    __syncwarp();                                    // a head's partner dims were summed by other lanes of this warp
+#pragma unroll
+    for (int job = 0; job < JOBS; ++job)
+      if (job_on[job]) {
+        const float* xr = &x_s[job_slot[job] * HD];
+        const bool rotate = job < 2 || warp == 0;    // queries and the key; the value stays as it is
+        const float own[4] = {acc[job].x, acc[job].y, acc[job].z, acc[job].w};
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int dd = d4 + e;
+          y[e] = own[e];
+          if (rotate && dd < p.rot)
+            y[e] = dd < half ? own[e] * rc[e] - xr[dd + half] * rs[e] : own[e] * rc[e] + xr[dd - half] * rs[e];
+        }
+        const __nv_bfloat162 lo2 = __floats2bfloat162_rn(y[0], y[1]), hi2 = __floats2bfloat162_rn(y[2], y[3]);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo2);
+        pk.y = *reinterpret_cast<const uint32_t*>(&hi2);
+        *reinterpret_cast<uint2*>(&q_s[job_slot[job] * HD + d4]) = pk;
+        if (job == 2 && gchunk == 0) {               // into the cache page, for the steps to come
+          const int lp = pq / p.page_size;
+          const int page = lp < p.max_pages ? bt[lp] : -1;
+          if (page < 0) {
+            if (lane == 0) atomicExch(p.page_error, 1);
+          } else {
+            __nv_bfloat16* dst = (warp == 0 ? p.k_cache : p.v_cache) +
+                                 ((size_t)(page * p.nkv + kvh) * p.page_size + pq % p.page_size) * hd + d4;
+            *reinterpret_cast<uint2*>(dst) = pk;
+          }
+        }
+      }
+    __syncthreads();
+  }
   uint32_t qa[KB][2];
 #pragma unroll
   for (int kb = 0; kb < KB; ++kb) {
     qa[kb][0] = qa[kb][1] = 0u;
     if (gid < ng && kb < kb_n) {
-      const __nv_bfloat16* qp = p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
+      const __nv_bfloat16* qp = FUSED ? &q_s[gid * HD + kb * 16 + tid4 * 2]
+                                      : p.q + ((size_t)t * nq + h0 + gid) * hd + kb * 16 + tid4 * 2;
       qa[kb][0] = *reinterpret_cast<const uint32_t*>(qp);
       qa[kb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
     }
@@ -554,6 +688,19 @@ attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __gr
       }
     }
     if (__any_sync(0xffffffffu, failed)) break;
+    if (FUSED && step == own_step) {
+      // the row's own key and value: over what the copy brought from the page (its old content)
+      const int r = pq - (first + step * DKT);
+      for (int u = lane; u < 2 * (hd >> 3); u += 32) {            // 16-byte units of the key, then of the value
+        const int is_v = u >= (hd >> 3), uu = is_v ? u - (hd >> 3) : u;
+        const uint32_t dst = ring + stage * SB + is_v * 2 * DKT * 128 + (uu >> 3) * DKT * 128 + r * 128 +
+                             (((uu & 7) ^ (r & 7)) << 4);
+        const uint4 val = *reinterpret_cast<const uint4*>(&q_s[(MG + is_v) * HD + uu * 8]);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(val.x), "r"(val.y), "r"(val.z), "r"(val.w)
+                     : "memory");
+      }
+      __syncwarp();
+    }
 #pragma unroll
     for (int sub = 0; sub < DKT / 16; ++sub) {
     const uint32_t ks = ring + stage * SB + sub * 16 * 128, vs = ks + 2 * DKT * 128;
@@ -1005,6 +1152,70 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
 // fresh_keys: how many of a row's newest keys (its own included) the kernel before this one in the stream may
 // have written (1 for decoded tokens; the length of the longest portion otherwise): tiles below them are
 // fetched before that kernel has finished.
+static int launch_decode_tc(bool fused, DecodeParams& p, const void* k_cache, const void* v_cache, int n_pages,
+                            int T, int nq, int nkv, int hd, int page_size, int split_keys, int n_splits, float* scratch,
+                            const int* row_list, void* out, int* arrivals, int n_arrivals, cudaStream_t stream) {
+  const char* who = fused ? "attention_decode_fused" : "attention_decode_tc";
+  if (hd <= 0 || hd % 16 || hd > 128) return fail("%s: head size %d (multiples of 16 up to 128)", who, hd);
+  if (nkv <= 0 || nq % nkv) return fail("%s: %d query heads do not divide into %d kv heads", who, nq, nkv);
+  // Keys per stage: 32 for a row or two (one block of four warps per SM is then enough, and a stage of 32 keys
+  // takes half as many copies and waits per key: -2.5 % of a decode step at batch 1), else 16, with which two
+  // blocks share an SM (at batch 8 stages of 32 keys cost 8 % of the step)
+  const int dk = (page_size % 32 == 0 && (long long)T * nkv * ((nq / nkv + 7) / 8) <= 8) ? 32 : DK;
+  if (page_size <= 0 || page_size % DK) return fail("%s: page size %d must be a multiple of %d", who, page_size, DK);
+  if (n_splits < 1 || split_keys < 1) return fail("%s: bad split (%d keys, %d splits)", who, split_keys, n_splits);
+  if (n_splits > 1 && !scratch) return fail("%s: splits need scratch memory", who);
+  if (!p.error_flag) return fail("%s: needs an error flag", who);
+  CUtensorMap mk, mv;
+  const long long kv_rows = (long long)n_pages * nkv * page_size;
+  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, dk);
+  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, dk);
+  if (rc) return fail("%s: cuTensorMapEncodeTiled failed (%d)", who, rc);
+  p.row_list = row_list;
+  p.out = (__nv_bfloat16*)out; p.scratch = scratch;
+  p.n_rows = T; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd;
+  p.split_keys = split_keys; p.n_splits = n_splits;
+  p.g_chunks = (nq / nkv + 7) / 8;
+  p.wait_cycles = wait_limit();
+  // with splits in fours and a counter for every (row, kv head, chunk of query heads) the pieces are merged by
+  // the block that finishes last; else by a kernel of its own
+  p.arrivals = (arrivals && n_splits % 4 == 0 && (long long)T * nkv * p.g_chunks <= n_arrivals) ? arrivals : nullptr;
+  if (fused && !p.arrivals)
+    return fail("%s: needs splits in fours (got %d) and an arrival counter for each of the %lld items", who, n_splits,
+                (long long)T * nkv * p.g_chunks);
+  const long long items = (long long)T * nkv * p.g_chunks * n_splits;
+  const long long blocks = (items + 3) / 4;
+  if (blocks > 0x7fffffffLL) return fail("%s: too many work items", who);
+  const size_t smem = (size_t)4 * DSTAGES * (2 * 2 * dk * 128) + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const int big = 4 * DSTAGES * (2 * 2 * 32 * 128) + 1024;
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    configured = true;
+  }
+#define GO(H, D, F) launch_pdl(attention_decode_tc_kernel<H, D, F>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p)
+  if (fused) {
+    if (dk == 32) { if (hd <= 64) GO(64, 32, true); else GO(128, 32, true); }
+    else { if (hd <= 64) GO(64, 16, true); else GO(128, 16, true); }
+  } else {
+    if (dk == 32) { if (hd <= 64) GO(64, 32, false); else GO(128, 32, false); }
+    else { if (hd <= 64) GO(64, 16, false); else GO(128, 16, false); }
+  }
+#undef GO
+  rc = check_launch(who);
+  if (rc || n_splits == 1 || p.arrivals) return rc;
+  launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
+             dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
+  return check_launch("attention_combine");
+}
+
 extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, const void* v_cache, int n_pages,
                                          const int* block_table, int max_pages, int page_size, const int* pos,
                                          const int* slot, void* out, int T, int nq, int nkv, int hd, int window,
@@ -1012,58 +1223,42 @@ extern "C" int flint_attention_decode_tc(const void* q, const void* k_cache, con
                                          const int* row_list, int* error_flag, int* arrivals, int n_arrivals,
                                          int fresh_keys, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (hd <= 0 || hd % 16 || hd > 128) return fail("attention_decode_tc: head size %d (multiples of 16 up to 128)", hd);
-  if (nkv <= 0 || nq % nkv) return fail("attention_decode_tc: %d query heads do not divide into %d kv heads", nq, nkv);
-  // Keys per stage: 32 for a row or two (one block of four warps per SM is then enough, and a stage of 32 keys
-  // takes half as many copies and waits per key: -2.5 % of a decode step at batch 1), else 16, with which two
-  // blocks share an SM (at batch 8 stages of 32 keys cost 8 % of the step)
-  const int dk = (page_size % 32 == 0 && (long long)T * nkv * ((nq / nkv + 7) / 8) <= 8) ? 32 : DK;
-  if (page_size <= 0 || page_size % DK) return fail("attention_decode_tc: page size %d must be a multiple of %d", page_size, DK);
-  if (n_splits < 1 || split_keys < 1) return fail("attention_decode_tc: bad split (%d keys, %d splits)", split_keys, n_splits);
-  if (n_splits > 1 && !scratch) return fail("attention_decode_tc: splits need scratch memory");
-  if (!error_flag) return fail("attention_decode_tc: needs an error flag");
-  CUtensorMap mk, mv;
-  const long long kv_rows = (long long)n_pages * nkv * page_size;
-  int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, dk);
-  if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, dk);
-  if (rc) return fail("attention_decode_tc: cuTensorMapEncodeTiled failed (%d)", rc);
-  DecodeParams p;
-  p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot; p.row_list = row_list;
-  p.out = (__nv_bfloat16*)out; p.scratch = scratch; p.error_flag = error_flag;
-  p.n_rows = T; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd;
-  p.window = window; p.split_keys = split_keys; p.n_splits = n_splits;
-  p.g_chunks = (nq / nkv + 7) / 8;
-  p.scale = scale;
-  p.wait_cycles = wait_limit();
-  // with splits in fours and a counter for every (row, kv head, chunk of query heads) the pieces are merged by
-  // the block that finishes last; else by a kernel of its own
-  p.arrivals = (arrivals && n_splits % 4 == 0 && (long long)T * nkv * p.g_chunks <= n_arrivals) ? arrivals : nullptr;
+  DecodeParams p = {};
+  p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot;
+  p.error_flag = error_flag; p.max_pages = max_pages; p.window = window; p.scale = scale;
   p.fresh_keys = fresh_keys < 1 ? 1 : fresh_keys;
-  const long long items = (long long)T * nkv * p.g_chunks * n_splits;
-  const long long blocks = (items + 3) / 4;
-  if (blocks > 0x7fffffffLL) return fail("attention_decode_tc: too many work items");
-  const size_t smem = (size_t)4 * DSTAGES * (2 * 2 * dk * 128) + 1024;
-  static bool configured = false;
-  if (!configured) {
-    const int big = 4 * DSTAGES * (2 * 2 * 32 * 128) + 1024;
-    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(attention_decode_tc_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    cudaFuncSetAttribute(attention_decode_tc_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
-    configured = true;
-  }
-  if (dk == 32) {
-    if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64, 32>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
-    else launch_pdl(attention_decode_tc_kernel<128, 32>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
-  } else {
-    if (hd <= 64) launch_pdl(attention_decode_tc_kernel<64, 16>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
-    else launch_pdl(attention_decode_tc_kernel<128, 16>, dim3((unsigned)blocks), dim3(128), smem, stream, mk, mv, p);
-  }
-  rc = check_launch("attention_decode_tc");
-  if (rc || n_splits == 1 || p.arrivals) return rc;
-  launch_pdl(flint_attn::attention_combine_kernel<__nv_bfloat16>, dim3((unsigned)((long long)T * nq)),
-             dim3(hd >= 128 ? 128 : 64), 0, stream, (const float*)scratch, (__nv_bfloat16*)out, hd, n_splits, nq, row_list);
-  return check_launch("attention_combine");
+  return launch_decode_tc(false, p, k_cache, v_cache, n_pages, T, nq, nkv, hd, page_size, split_keys, n_splits, scratch,
+                          row_list, out, arrivals, n_arrivals, stream);
+}
+
+// The decode kernel doing the rotary kernel's work as well, for rows that are one decoded token each (every row
+// of the batch, no row list).  qkv [qkv_slices][T, (nq + 2 nkv) hd] float32: the q/k/v projection as partial
+// sums qkv_stride floats apart, without its bias; bias [(nq + 2 nkv) hd] float32 or null; cos/sin
+// [positions, rot/2] float32; q and k rotate over their first rot dims, dims i and i + rot/2 together.  The row's
+// new key and value go into the cache (k_cache, v_cache: bfloat16 pages [page, nkv, page_size, hd]) and into the
+// attention of this very launch.  n_splits must be a multiple of four and arrivals must hold a counter per
+// (row, kv head, chunk of eight query heads).  page_error: set to 1 if a row's page is missing.
+extern "C" int flint_attention_decode_fused(const float* qkv, int qkv_slices, long long qkv_stride, const float* bias,
+                                            const float* cos_t, const float* sin_t, int rot, void* k_cache,
+                                            void* v_cache, int n_pages, const int* block_table, int max_pages,
+                                            int page_size, const int* pos, const int* slot, void* out, int T, int nq,
+                                            int nkv, int hd, int window, float scale, int split_keys, int n_splits,
+                                            float* scratch, int* error_flag, int* page_error, int* arrivals,
+                                            int n_arrivals, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (!qkv || qkv_slices < 1 || !cos_t || !sin_t || !page_error) return fail("attention_decode_fused: missing inputs");
+  if (rot < 0 || rot > hd || (rot & 1)) return fail("attention_decode_fused: rotary size %d does not fit head size %d", rot, hd);
+  if ((qkv_stride & 3) || ((uintptr_t)qkv & 15) || (bias && ((uintptr_t)bias & 15)))
+    return fail("attention_decode_fused: the projection's rows must be 16-byte aligned");
+  DecodeParams p = {};
+  p.block_table = block_table; p.pos = pos; p.slot = slot;
+  p.error_flag = error_flag; p.max_pages = max_pages; p.window = window; p.scale = scale;
+  p.fresh_keys = 1;
+  p.qkv = qkv; p.qkv_bias = bias; p.cos_t = cos_t; p.sin_t = sin_t; p.rot = rot;
+  p.qkv_slices = qkv_slices; p.qkv_stride = qkv_stride;
+  p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache; p.page_error = page_error;
+  return launch_decode_tc(true, p, k_cache, v_cache, n_pages, T, nq, nkv, hd, page_size, split_keys, n_splits, scratch,
+                          nullptr, out, arrivals, n_arrivals, stream);
 }
 
 // The same contract with the work cut into equal runs of keys on the device (see the stream kernel): any mix of
@@ -1087,7 +1282,7 @@ extern "C" int flint_attention_decode_stream(const void* q, const void* k_cache,
   int rc = make_map_bf16(&mk, k_cache, kv_rows, hd, hd, DK);
   if (!rc) rc = make_map_bf16(&mv, v_cache, kv_rows, hd, hd, DK);
   if (rc) return fail("attention_decode_stream: cuTensorMapEncodeTiled failed (%d)", rc);
-  DecodeParams p;
+  DecodeParams p = {};
   p.q = (const __nv_bfloat16*)q; p.block_table = block_table; p.pos = pos; p.slot = slot; p.row_list = row_list;
   p.out = (__nv_bfloat16*)out; p.scratch = scratch; p.error_flag = error_flag;
   p.n_rows = T; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.hd = hd;

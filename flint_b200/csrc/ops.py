@@ -555,6 +555,45 @@ class CudaOps:
             self.paged_attention(q, cache, step.pos, step.slot, out, nq, nkv, hd, window, scale, step.max_kv_len,
                                  rows=tiling.other_rows, fresh_keys=step.longest_entry)
 
+    def rope_attention_decode(self, qkv, bias, cos, sin, rot, style, cache, step, out, nq, nkv, hd, window, scale):
+        """The rotary write and the attention of a batch of decoded tokens in one launch: qkv [S, T, W] float32
+        (partial sums of the q/k/v projection, bias apart) becomes q, the rows' new keys and values go into the
+        cache pages, and every row attends over its request's keys.  Returns False, having launched nothing, when
+        the batch is not of the kind this kernel takes (then the caller runs the two kernels one after the
+        other): it takes bfloat16 caches and outputs, head sizes up to 128, the half-split rotation, and batches
+        whose requests are about equally long."""
+        T = qkv.shape[1]
+        if (style != "half" or step.attention_splits is not None or out.dtype != torch.bfloat16
+                or cache.k.dtype != torch.bfloat16 or hd > 128 or step.n_tokens != len(step.entries) or T != step.n_tokens):
+            return False
+        span = min(step.max_kv_len, window) if window else step.max_kv_len
+        kernel, keys, n = self.attention_plan(T, nq, nkv, span, hd, True, not step.even_lengths)
+        g_chunks = -(-(nq // nkv) // 8)
+        if kernel != "tma" or T * nkv * g_chunks > self.attention_arrivals.numel():
+            return False
+        if n % 4:
+            # splits in fours: the four warps of a block share the row's queries and its new key and value
+            n = max(4, n // 4 * 4)
+            keys = -(-(-(-max(span, 1) // n)) // 16) * 16
+        _check(qkv, "qkv", torch.float32, 3)
+        _check(out, "out", torch.bfloat16, 2)
+        if qkv.shape[2] != (nq + 2 * nkv) * hd or tuple(out.shape) != (T, nq * hd):
+            raise KernelError("rope_attention_decode: widths do not match the head counts")
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != qkv.shape[2]):
+            raise KernelError("rope_attention_decode: bias must be float32 of the qkv width")
+        if tuple(cache.k.shape[1:]) != (nkv, cache.page_size, hd) or tuple(cache.v.shape[1:]) != (nkv, cache.page_size, hd):
+            raise KernelError("rope_attention_decode: cache pages do not match the head counts")
+        if rot and cos.shape[1] * 2 != rot:
+            raise KernelError("rope_attention_decode: table width must be rot/2")
+        scratch = torch.empty(T * nq * n * (hd + 2), dtype=torch.float32, device=qkv.device)
+        self._run("attention_tc", "flint_attention_decode_fused", _ptr(qkv), c_int(qkv.shape[0]), c_longlong(qkv.stride(0)),
+                  _ptr(bias), _ptr(cos), _ptr(sin), c_int(rot), _ptr(cache.k), _ptr(cache.v), c_int(cache.k.shape[0]),
+                  _ptr(cache.block_table), c_int(cache.block_table.shape[1]), c_int(cache.page_size), _ptr(step.pos),
+                  _ptr(step.slot), _ptr(out), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(window), c_float(scale),
+                  c_int(keys), c_int(n), _ptr(scratch), _ptr(self.tc_error), _ptr(step.status),
+                  _ptr(self.attention_arrivals), c_int(self.attention_arrivals.numel()))
+        return True
+
     def attention_prefill_tc(self, q, cache, tiles, n_tiles, out, nq, nkv, hd, window, scale):
         _check(q, "q", torch.bfloat16, 2)
         _check(out, "out", torch.bfloat16, 2)

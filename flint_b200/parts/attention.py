@@ -117,9 +117,19 @@ class Attention(Mixer):
         T = xin.shape[0]
         act = self.ctx.act_dtype
         q = torch.empty((T, nq * hd), dtype=act, device=xin.device)
+        fused = None
         if writes_cache:
             # the projection is left as partial sums over pieces of K; the rotary kernel adds them and the bias
             qkv = ops.gemm_partials(xin, self.w_qkv)
+            if T == len(step.entries) and hasattr(ops, "rope_attention_decode"):
+                # decoded tokens: one kernel rotates, writes the cache pages and attends
+                attn = torch.empty_like(q)
+                if ops.rope_attention_decode(qkv, self.b_qkv, self.cos, self.sin, self.rot, self.rot_style, cache, step,
+                                             attn, nq, nkv, hd, self.window, self.scale):
+                    fused = attn
+        if fused is not None:
+            attn = fused
+        elif writes_cache:
             ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
                               True, step.status, bias=self.b_qkv, style=self.rot_style)
         else:   # reads another call's cache: only the queries are needed
@@ -128,7 +138,8 @@ class Attention(Mixer):
             ops.gemm(xin, self.w_qkv[:nqd], qkv[0, :, :nqd], bias=self.b_qkv[:nqd] if self.b_qkv is not None else None)
             ops.rope_kv_write(qkv, step.pos, step.slot, self.cos, self.sin, self.rot, q, cache, nq, nkv, hd,
                               False, step.status, style=self.rot_style)
-        attn = torch.empty_like(q)
-        ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale, tiling=step.tiling(self.NEEDS))
+        if fused is None:
+            attn = torch.empty_like(q)
+            ops.attention(q, cache, step, attn, nq, nkv, hd, self.window, self.scale, tiling=step.tiling(self.NEEDS))
         # the output projection is handed to the next norm as partial sums (and its bias)
         return Pending(partials=ops.gemm_partials(attn, self.w_o), bias=self.b_o)

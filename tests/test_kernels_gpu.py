@@ -655,3 +655,72 @@ def test_argmax(ops, R, V):
     ops.argmax(lg.to(DEV), out)
     assert out.cpu().tolist() == torch.argmax(lg, -1).tolist()
     assert out.cpu()[0].item() == 3
+
+
+@pytest.mark.parametrize("nq,nkv,hd,P,window,lens,rot,slices", [
+    (32, 8, 128, 64, 0, (2049, 2040, 2030, 2048, 2047, 2046, 2001, 2049), 128, 9),   # a batch of eight at the measured sizes
+    (32, 8, 128, 64, 0, (2049,), 128, 9),                                         # one row: stages of 32 keys
+    (8, 2, 64, 16, 0, (300, 290, 310), 32, 3),                                    # part of the head rotates
+    (6, 2, 48, 16, 40, (100, 90, 95), 16, 1),                                     # a window, three query heads per kv head
+    (48, 2, 96, 64, 0, (700, 690), 96, 2),                                        # 24 query heads per kv head: three chunks
+    (4, 4, 16, 16, 0, (5, 6, 7, 6), 16, 2),                                       # rows shorter than one split
+    (32, 8, 128, 64, 0, (1, 1), 128, 4),                                          # first tokens: nothing cached yet
+    (8, 2, 128, 32, 0, (65, 64, 63), 0, 2),                                       # no rotation at all, a page's edge
+])
+def test_rotary_write_and_decode_attention_in_one_kernel(ops, ref, nq, nkv, hd, P, window, lens, rot, slices):
+    """The decode kernel that also sums the projection's partial slices, adds the bias, rotates q and k, writes the
+    rows' new keys and values into their pages and uses them itself: the same output and the same cache content
+    as the rotary kernel followed by attention, computed in float64."""
+    g = torch.Generator().manual_seed(nq * 7 + hd + len(lens))
+    T = len(lens)
+    need = [-(-n // P) for n in lens]
+    n_pages = sum(need) + 2
+    k = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    bt = torch.full((T, max(need) + 1), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    o = 0
+    for s_, n in enumerate(need):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    W = (nq + 2 * nkv) * hd
+    parts = torch.randn(slices, T, W, generator=g) * 0.6
+    bias = torch.randn(W, generator=g) * 0.3
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slot = torch.arange(T, dtype=torch.int32)
+    half = max(rot // 2, 1)
+    ang = torch.arange(max(lens) + 1, dtype=torch.float64)[:, None] * (10000.0 ** (-torch.arange(half, dtype=torch.float64) / half))
+    cos, sin = (torch.cos(ang) * 1.1).float(), (torch.sin(ang) * 1.1).float()
+    spec = KVSpec(nkv, hd, window)
+    dv = CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec)
+    cv = CacheView(k.clone(), v.clone(), bt.clone(), P, spec)
+    scale = 1 / math.sqrt(hd)
+    # the reference: rotary write, then attention over the cache as the write left it
+    q_r = torch.empty(T, nq * hd, dtype=torch.float64)
+    ref.rope_kv_write(parts, pos, slot, cos, sin, rot, q_r, cv, nq, nkv, hd, True, None, bias=bias)
+    exp = torch.zeros(T, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q_r.to(torch.bfloat16), cv, pos, slot, exp, nq, nkv, hd, window, scale, max(lens))
+
+    class Step:
+        pass
+    step = Step()
+    step.pos, step.slot, step.n_tokens, step.entries = pos.to(DEV), slot.to(DEV), T, [None] * T
+    step.max_kv_len, step.even_lengths, step.attention_splits = max(lens), True, None
+    step.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for _ in range(2):                   # twice: the second launch finds the first one's keys in the pages already
+        done = ops.rope_attention_decode(parts.to(DEV), bias.to(DEV), cos.to(DEV), sin.to(DEV), rot, "half", dv, step, out,
+                                         nq, nkv, hd, window, scale)
+        assert done
+        assert int(ops.tc_error.item()) == 0 and int(step.status.item()) == 0
+        assert int(ops.attention_arrivals.abs().sum().item()) == 0
+        close(out, exp, 2e-2, 2e-2)
+        close(dv.k, cv.k, 1e-2, 1e-2)
+        close(dv.v, cv.v, 1e-2, 1e-2)
+    # a row whose page is missing raises the flag and writes nothing outside its pages
+    bt2 = bt.clone()
+    bt2[0, (lens[0] - 1) // P] = -1
+    dv2 = CacheView(dv.k, dv.v, bt2.to(DEV), P, spec)
+    ops.rope_attention_decode(parts.to(DEV), bias.to(DEV), cos.to(DEV), sin.to(DEV), rot, "half", dv2, step, out, nq, nkv,
+                              hd, window, scale)
+    assert int(step.status.item()) == 1
