@@ -353,6 +353,25 @@ def run_long(cfg, pk, rng, lengths, decode_tokens, chunk=2048):
             "config": config_of(cfg, len(lengths), max(lengths), ctx, pk)}
 
 
+def run_sweep(cfg, pk, rng, steps, warmup):
+    """``--sweep``: decode at further batch sizes and context lengths, each with its roofline fraction: batch 1 and
+    8 at contexts of 16,384 and 65,536 tokens, batch 1 at 131,008, and batch 128 and 256 at 2,048.  One model, the
+    cache sized for the largest point (about 70 GB)."""
+    import torch
+    points = [(1, 16384), (8, 16384), (1, 65536), (8, 65536), (1, 131072 - 64), (128, 2048), (256, 2048)]
+    n_pages = max(b * -(-(c + 64) // 64) for b, c in points) + 8
+    model = build_model(cfg, max(b for b, _ in points), 131072, n_pages=n_pages)
+    out = {}
+    for b, c in points:
+        r = run_decode(model, cfg, b, c, steps, warmup, rng)
+        frac = decode_bytes(cfg, model, r["kv_lens"], r["distinct"]) / (r["ms"] * 1e-3) / 1e9 / pk["hbm_gbs"]
+        out[f"decode_b{b}_ctx{c}"] = {"tok_s": round(r["tok_s"], 1), "ms_per_step": round(r["ms"], 3),
+                                      "roofline_frac": round(frac, 4)}
+        torch.cuda.empty_cache()
+    return {"metric": "decode tok/s at further batch sizes and context lengths", "points": out,
+            "config": config_of(cfg, 0, 0, 131072, pk)}
+
+
 def run_tiny(which, reps=5):
     """The tiny workloads of the two test configurations, in 32-bit: through ``Engine`` on the GPU (wall clock,
     host tokens in and out) and on the timed CPU baseline, the plain C++ implementation of the test-suite
@@ -637,6 +656,9 @@ def main():
                          "use with --expert-intermediate 6400 for the Phi-3.5-MoE sizes")
     ap.add_argument("--long-prompts", type=int, nargs="+", default=None, help="other prompt lengths for --long")
     ap.add_argument("--no-kernels", action="store_true", help="skip the per-kernel table")
+    ap.add_argument("--sweep", action="store_true",
+                    help="instead of the default run: decode at batch 1 and 8 with contexts of 16,384 and 65,536 tokens, "
+                         "batch 1 with 131,008, and batch 128 and 256 with 2,048, each with its roofline fraction")
     ap.add_argument("--profile", action="store_true",
                     help="print per-kernel device times of one prefill and one decode step to stderr and exit")
     args = ap.parse_args()
@@ -665,6 +687,9 @@ def main():
     rng = random.Random(0)
     if args.tiny:
         print(json.dumps(run_tiny(args.tiny)))
+        return 0
+    if args.sweep:
+        print(json.dumps(run_sweep(cfg, pk, rng, max(8, args.steps // 4), warmup)))
         return 0
     if args.long:
         print(json.dumps(run_long(cfg, pk, rng, args.long_prompts or [32768] * 4 + [131072 - 128], 128)))
