@@ -1161,7 +1161,16 @@ static int launch_decode_tc(bool fused, DecodeParams& p, const void* k_cache, co
   // Keys per stage: 32 for a row or two (one block of four warps per SM is then enough, and a stage of 32 keys
   // takes half as many copies and waits per key: -2.5 % of a decode step at batch 1), else 16, with which two
   // blocks share an SM (at batch 8 stages of 32 keys cost 8 % of the step)
-  const int dk = (page_size % 32 == 0 && (long long)T * nkv * ((nq / nkv + 7) / 8) <= 8) ? 32 : DK;
+  // (while its blocks fit one to an SM: a long context cut into more splits than that runs with stages of 16)
+  const long long groups = (long long)T * nkv * ((nq / nkv + 7) / 8);
+  static int sm_count = 0;
+  if (!sm_count) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int dk = (page_size % 32 == 0 && groups <= 8 && groups * n_splits <= 4LL * sm_count) ? 32 : DK;
   if (page_size <= 0 || page_size % DK) return fail("%s: page size %d must be a multiple of %d", who, page_size, DK);
   if (n_splits < 1 || split_keys < 1) return fail("%s: bad split (%d keys, %d splits)", who, split_keys, n_splits);
   if (n_splits > 1 && !scratch) return fail("%s: splits need scratch memory", who);
