@@ -306,3 +306,25 @@ def test_chat_program_prints_the_plain_arg_max_tokens(tmp_path, source):
         want.append(t)
         toks.append(t)
     assert got == want and len(got) >= 1
+
+
+def test_more_rows_than_a_captured_step_takes(setup):
+    """260 live requests: their short prompts in one step, then one token each per step.  Batches above 256 rows
+    run eagerly (no captured graph) and their attention goes row by row; a sample of the requests is compared
+    with the plain implementation at every decoded position."""
+    which, dtype, folder, reqs, plain = setup
+    V = tiny.CONFIGS[which]["vocab_size"]
+    many = traces.make_requests(V, [6 + (i * 7) % 11 for i in range(262)], seed=23)
+    tail = 4
+    steps = [{"step": 0, "end": [], "entries": [{"id": rid, "tokens": t[:-tail], "want": [len(t) - tail - 1] if i % 13 == 0 else []}
+                                                for i, (rid, t) in enumerate(many.items()) if len(t) > tail]}]
+    live = [rid for rid, t in many.items() if len(t) > tail]
+    assert len(live) > 256
+    sampled = {rid: many[rid] for i, rid in enumerate(many) if i % 13 == 0 and rid in live}
+    for j in range(tail):
+        steps.append({"step": len(steps), "end": live if j == tail - 1 else [],
+                      "entries": [{"id": rid, "tokens": [many[rid][len(many[rid]) - tail + j]],
+                                   "want": [0] if rid in sampled else []} for rid in live]})
+    out, rp = replay(folder, dtype, steps, 16, max_requests=len(live))
+    assert not any(k[0] > 256 for k in rp.model._graphs), "a batch above the graph limit was captured"
+    compare(out, steps, plain_all(folder, sampled), dtype, rp.routing, sampled, folder, router_logits=rp.router_logits)
