@@ -103,3 +103,28 @@ def test_real_sizes_eight_requests_decoded_together(big, dtype):
     out, rp = replay(folder, dtype, steps, 64, max_requests=8)
     assert any(k[0] == 8 for k in rp.model._graphs), "the batch of eight did not go through the captured graph"
     compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits, DIFFERING[dtype])
+
+
+@pytest.fixture(scope="module")
+def windowed(tmp_path_factory):
+    """The same layer sizes with a sliding window of 1,000 positions (not a multiple of the page or of a key tile)."""
+    cfg = dict(MINI_2_OF_32, sliding_window=1000)
+    folder = write_random_model(tmp_path_factory.mktemp("mini2w"), cfg, seed=22, dtype=torch.bfloat16)
+    reqs = traces.make_requests(cfg["vocab_size"], (2100, 1300), seed=19)
+    keep = {rid: kept_positions(len(t)) | set(range(990, 1012)) for rid, t in reqs.items()}
+    loaded = plain_phimoe.load_model_dir(folder)
+    return folder, reqs, keep, plain_all(folder, reqs, keep, loaded), loaded
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cut", ["tail", "mixed"])
+def test_real_sizes_with_a_window(windowed, cut, dtype):
+    """Prompts twice the window: the tensor-core attention's tiles at the window's edge, decoded tokens whose first
+    visible key lies inside a page, and pages behind the window given back and used again."""
+    folder, reqs, keep, plain, loaded = windowed
+    steps = {"tail": lambda r: traces.tail_decoded(r, keep=keep),
+             "mixed": lambda r: traces.mixed(r, seed=6, decode_tail=24, sizes=(2, 16, 33, 257, 700), keep=keep)}[cut](reqs)
+    out, rp = replay(folder, dtype, steps, 64)
+    compare(out, steps, plain, dtype, rp.routing, reqs, folder, keep, loaded, rp.router_logits, DIFFERING[dtype])
+    if cut == "mixed":
+        assert max(rp.model.cache.groups[0].pages.pool.served) >= 2, "no page behind the window was used again"
