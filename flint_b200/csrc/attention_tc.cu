@@ -468,7 +468,7 @@ __device__ __forceinline__ void merge_records(const DecodeParams& p, int ti, int
 template <int HD, int DKT, bool FUSED>
 __global__ void __launch_bounds__(128)
 attention_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                           const DecodeParams p) {
+                           const __grid_constant__ DecodeParams p) {
   using flint_attn::ldsm4;
   using flint_attn::ldsm4t;
   using flint_attn::mma16816;
@@ -874,7 +874,7 @@ constexpr int MIN_STREAM_STEPS = 3;      // a warp takes at least 48 keys
 template <int HD>
 __global__ void __launch_bounds__(128)
 attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                           const DecodeParams p) {
+                           const __grid_constant__ DecodeParams p) {
   using flint_attn::ldsm4;
   using flint_attn::ldsm4t;
   using flint_attn::mma16816;

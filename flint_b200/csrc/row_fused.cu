@@ -106,7 +106,7 @@ __device__ __forceinline__ void select_two_serial(const float* s, int E, float j
 // One block per row; a thread holds VPT vectors of four values of its row.
 template <int VPT, typename TW>
 __global__ void __launch_bounds__(1024)
-row_norm_kernel(const RowArgs a) {
+row_norm_kernel(const __grid_constant__ RowArgs a) {
   extern __shared__ float smem[];          // router only: H floats of the normalised row, then partial logits
   __shared__ float red[32];
   pdl_launch();
@@ -328,7 +328,7 @@ __device__ __forceinline__ float cluster_sum(float block_value, float* slots, ui
 
 template <int VPT, typename TW>
 __global__ void __launch_bounds__(256)
-row_norm_cluster_kernel(const RowArgs a, const int vec_per_block) {
+row_norm_cluster_kernel(const __grid_constant__ RowArgs a, const int vec_per_block) {
   extern __shared__ float smem[];          // router only: this block's columns of the normalised row, partial logits
   __shared__ float red[32];
   __shared__ float sum_slots[MAX_CL], sq_slots[MAX_CL];
