@@ -91,6 +91,21 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
       :: "r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 32 consecutive 32-bit columns of this thread's lane (here: 64 bfloat16 of a row of P, two to a column)
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      :: "r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31]) : "memory");
+}
+// D += A B with A [128, 16] bfloat16 in tensor memory (lane = row, two elements of K to a column) and B in shared memory
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
 
 // 2^x on the special-function unit (float32 in and out, about 2 ulp)
 __device__ __forceinline__ float ex2(float x) {
@@ -112,9 +127,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ int abort_flag;
 
   if (*(volatile int*)p.error_flag) return;
-  const int* tile = p.tiles + 4 * (gridDim.x - 1 - blockIdx.x);   // later tiles see more keys: start them first
+  // Blocks start in the order of their index, heads fastest: all heads of the last tile first.  Later tiles see
+  // more keys, so the long blocks start first and the short ones fill in behind them; the heads of a kv group
+  // run side by side and share their keys in L2.
+  const int* tile = p.tiles + 4 * (gridDim.y - 1 - blockIdx.y);
   const int row0 = tile[0], n_rows = tile[1], slot = tile[2], pos0 = tile[3];
-  const int head = blockIdx.y;
+  const int head = blockIdx.x;
   const int hd = p.hd;
   const int kvh = head / (p.nq / p.nkv);
   const int chunks = (hd + 63) / 64;
@@ -234,7 +252,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int k = 0; k < BKV / 16; ++k) {      // O_tile = P V over the 64 keys
         // V [keys, hd] is MN-major for B: 16 keys down = 2048 bytes; 64-wide chunks of hd are BKV*128 apart
         const uint64_t vd = smem_desc_mn(v_src + k * 16 * 128, BKV * 128, 1024);
-        umma_bf16(tmem_o, smem_desc(p_smem + k * 32), vd, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        umma_bf16_a_tmem(tmem_o, tmem_s + (i & 1) * BKV + k * 8, vd, idesc_o, (i > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(bar_o);
       umma_commit(bar_vempty0 + 8 * s);
@@ -259,31 +277,35 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const bool need_mask = (kv0 + BKV - 1 > pos0) || (p.window > 0 && kv0 < pos0 + n_rows - p.window);
       float sc[BKV];
       tmem_ld64(tmem_s + (i & 1) * BKV + lane_addr, sc);
-      // the maximum of the raw scores (the scale is positive), in four strands so that the chain is short
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // keys a row does not see get a score of minus infinity (their probability is then exactly zero); one pass
+      // on the few tiles that need it keeps the loops below in one form
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BKV; ++c) {
           const int kj = kv0 + c;
-          if (kj <= q_pos && kj >= first) m4[c & 3] = fmaxf(m4[c & 3], sc[c]);
+          if (!(kj <= q_pos && kj >= first)) sc[c] = -INFINITY;
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < BKV; ++c) m4[c & 3] = fmaxf(m4[c & 3], sc[c]);
       }
+      // the maximum of the raw scores (the scale is positive), in four strands so that the chain is short
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < BKV; ++c) m4[c & 3] = fmaxf(m4[c & 3], sc[c]);
       const float mraw = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       const float mx = fmaxf(ref, mraw * p.scale_log2);
-      // P V of the previous tile must be done before O is touched or P's buffer is written again
-      if (i > 0) {
-        ok = mbar_wait(bar_o, (i - 1) & 1, ab, p.wait_cycles);
-        if (!ok) break;
-        tc_fence_after();
-      }
+      // Every thread waits for every P V in turn, each before it arrives for the next one (a wait by parity cannot
+      // tell a barrier that is two phases ahead from one that is in step).  P V of the previous tile only has to
+      // be done before O is touched; otherwise the wait comes after this tile's probabilities are written, when
+      // it has long been done.
+      bool o_seen = i == 0;
       if (__any_sync(0xffffffffu, mx - ref > kRescaleStep)) {      // uniform in the warp: tcgen05.ld/st are
         const float alpha = ex2(ref - mx);                          // warp-wide; every row of the warp moves
         ref = mx;
         l *= alpha;
         if (i > 0) {
+          ok = mbar_wait(bar_o, (i - 1) & 1, ab, p.wait_cycles);
+          if (!ok) break;
+          o_seen = true;
+          tc_fence_after();
           for (int d0 = 0; d0 < hd; d0 += 16) {
             float v[16];
             tmem_ld16(tmem_o + lane_addr + d0, v);
@@ -294,37 +316,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           tmem_st_wait();
         }
       }
-      // probabilities, as bf16 into shared memory (row r, 16-byte unit u at (u ^ (r & 7)))
-      // the row's sum is kept in float32 from the unrounded probabilities (four strands)
+      // probabilities, as bf16 back into tensor memory over the first half of the scores they came from (two
+      // to a column: the A operand of P V); the row's sum is kept in float32 from the unrounded probabilities
+      // (four strands)
       float s4[4] = {0.f, 0.f, 0.f, 0.f};
       const float neg_ref = -ref;
+      uint32_t packed[BKV / 2];
 #pragma unroll
-      for (int c0 = 0; c0 < BKV; c0 += 8) {
-        uint32_t packed[4];
+      for (int c = 0; c < BKV; c += 2) {
+        float pr[2];
 #pragma unroll
-        for (int c = 0; c < 8; c += 2) {
-          float pr[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            pr[e] = ex2(fmaf(sc[c0 + c + e], p.scale_log2, neg_ref));
-            if (need_mask) {
-              const int kj = kv0 + c0 + c + e;
-              if (!(kj <= q_pos && kj >= first)) pr[e] = 0.f;
-            }
-          }
-          const __nv_bfloat162 b = __floats2bfloat162_rn(pr[0], pr[1]);
-          s4[c & 2] += pr[0];
-          s4[(c & 2) + 1] += pr[1];
-          packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
+        for (int e = 0; e < 2; ++e) {
+          pr[e] = ex2(fmaf(sc[c + e], p.scale_log2, neg_ref));
         }
-        const uint32_t addr = p_smem + r * 128 + (((c0 >> 3) ^ (r & 7)) << 4);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(packed[0]), "r"(packed[1]),
-                     "r"(packed[2]), "r"(packed[3]) : "memory");
+        const __nv_bfloat162 b = __floats2bfloat162_rn(pr[0], pr[1]);
+        s4[c & 2] += pr[0];
+        s4[(c & 2) + 1] += pr[1];
+        packed[c >> 1] = *reinterpret_cast<const uint32_t*>(&b);
+      }
+      tmem_st32(tmem_s + (i & 1) * BKV + lane_addr, packed);
+      tmem_st_wait();
+      if (!o_seen) {
+        ok = mbar_wait(bar_o, (i - 1) & 1, ab, p.wait_cycles);
+        if (!ok) break;
       }
       l += (s4[0] + s4[1]) + (s4[2] + s4[3]);
-      // hand P (and the rescaled O) to the tensor core: make this row's shared-memory writes visible to
-      // the async proxy, then arrive (the barrier counts all 128 rows; no thread waits on another here)
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // hand P (and the rescaled O) to the tensor core (the barrier counts all 128 rows; no thread waits on
+      // another here)
       tc_fence_before();
       mbar_arrive(bar_p);
     }
@@ -1117,7 +1135,7 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   if (nkv <= 0 || nq % nkv) return fail("attention_tc: %d query heads do not divide into %d kv heads", nq, nkv);
   if (!(page_size > 0 && (BKV % page_size == 0 || page_size % BKV == 0)) || page_size % 8)
     return fail("attention_tc: page size %d must divide 64 or be a multiple of 64", page_size);
-  if (n_tiles > 0x7fffffff / 4 || nq > 65535) return fail("attention_tc: too many tiles or heads");
+  if (n_tiles > 65535 || nq > 0x7fffffff / 4) return fail("attention_tc: too many tiles or heads");
   if (!error_flag) return fail("attention_tc: needs an error flag");
   if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
     return fail("attention_tc: operands must be 16-byte aligned");
@@ -1135,7 +1153,7 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   p.wait_cycles = wait_limit();
   const int chunks = (hd + 63) / 64;
   const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128;
-  dim3 grid(n_tiles, nq);
+  dim3 grid(nq, n_tiles);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);

@@ -786,6 +786,13 @@ int flint_rt_pack_step(int n_entries, const int* slots, const int* start_pos, co
     }
     max_kv = std::max(max_kv, p0 + n);
   }
+  // tiles in the order of their last position: a kernel whose work grows with the keys a tile sees starts
+  // from the far end and fills in with the short ones
+  {
+    struct Tile { int v[4]; };
+    Tile* t = reinterpret_cast<Tile*>(tiles);
+    std::stable_sort(t, t + n_tiles, [](const Tile& a, const Tile& b) { return a.v[3] + a.v[1] < b.v[3] + b.v[1]; });
+  }
   meta[0] = T;
   meta[1] = R;
   meta[2] = n_tiles;

@@ -36,8 +36,9 @@ class StepNeeds:
 
 @dataclass
 class Tiling:
-    """Rows of long portions as tiles ([n, 4] int32: first row, rows, slot, position of the first row) and the
-    rows that are in no tile (decoded tokens, short portions)."""
+    """Rows of long portions as tiles ([n, 4] int32: first row, rows, slot, position of the first row), in the
+    order of their last position (a kernel whose work grows with the keys a tile sees starts from the far end),
+    and the rows that are in no tile (decoded tokens, short portions)."""
     tiles: torch.Tensor
     n_tiles: int
     other_rows: torch.Tensor
@@ -172,6 +173,8 @@ class StepStaging:
                 tiles += (row0 + r, min(needs.tile_rows, n - r), e.slot, e.start_pos + r)
         if len(tiles) // 4 > self.max_tiles:
             raise ModelError("a step has more tiles than its staging buffer holds")
+        quads = sorted((tiles[i:i + 4] for i in range(0, len(tiles), 4)), key=lambda t: t[3] + t[1])
+        tiles = [v for t in quads for v in t]
         o = per * k
         host[o:o + len(others)] = torch.tensor(others, dtype=torch.int32)
         host[o + M:o + M + len(tiles)] = torch.tensor(tiles, dtype=torch.int32)

@@ -234,6 +234,30 @@ def test_packing_a_step_with_tokens_fed_on_the_device():
         st.pack([StepEntry(0, 0, [1], [0], feed=32)], 50, 64)
 
 
+def test_tiles_of_a_step_come_in_the_order_of_their_last_position():
+    """Long portions are cut into tiles, short ones and decoded tokens are listed row by row; the tiles are ordered
+    by the position of their last row, whichever request they belong to, and a second mixer's tiling (cut by the
+    Python packer) agrees with the first's (cut by the native one)."""
+    from flint_b200.engine.step import StepEntry, StepNeeds, StepStaging
+    needs = [StepNeeds(tile_rows=8, tile_min_rows=4), StepNeeds(tile_rows=8, tile_min_rows=4), StepNeeds(tile_rows=16, tile_min_rows=2)]
+    st = StepStaging(96, "cpu", needs=needs)
+    entries = [StepEntry(0, 40, list(range(20)), []), StepEntry(1, 7, [1], [0]), StepEntry(2, 0, list(range(9)), [8]),
+               StepEntry(3, 25, list(range(3)), []), StepEntry(4, 30, list(range(12)), [])]
+    ctx = st.pack(entries, vocab_size=50, max_positions=128)
+    first, second, third = (ctx.tiling(n) for n in needs)
+    tiles = first.tiles[:first.n_tiles].tolist()
+    # rows: request 0 at 0..19, 1 at 20, 2 at 21..29, 3 at 30..32, 4 at 33..44
+    assert sorted(tiles) == sorted([[0, 8, 0, 40], [8, 8, 0, 48], [16, 4, 0, 56], [21, 8, 2, 0], [29, 1, 2, 8],
+                                    [33, 8, 4, 30], [41, 4, 4, 38]])
+    ends = [t[3] + t[1] for t in tiles]
+    assert ends == sorted(ends) == [8, 9, 38, 42, 48, 56, 60]
+    assert first.other_rows[:first.n_other_rows].tolist() == [20, 30, 31, 32]
+    assert second.tiles[:second.n_tiles].tolist() == tiles
+    assert second.other_rows[:second.n_other_rows].tolist() == [20, 30, 31, 32]
+    ends3 = [t[3] + t[1] for t in third.tiles[:third.n_tiles].tolist()]
+    assert ends3 == sorted(ends3) and third.other_rows[:third.n_other_rows].tolist() == [20]
+
+
 def test_decode_attention_is_cut_into_splits_that_cover_the_keys():
     """The plan of the decode attention: the splits cover every key, and with more than four of them they come
     in fours (the four warps of a block then hold one row's splits and merge them themselves)."""
