@@ -7,9 +7,12 @@
 //                    tensor memory (128 lanes = query rows, 64 columns = keys)
 //   softmax          one thread per query row reads its row of S with tcgen05.ld, applies scale,
 //                    the causal and window mask, keeps the running reference and sum in float32,
-//                    and writes P = exp2(s - reference) as bfloat16 into shared memory (K-major, swizzled)
-//   O += P V         tcgen05.mma with V [64 keys, hd] as an MN-major B operand; O stays in tensor
-//                    memory over all key tiles of the block
+//                    and writes P = exp2(s - reference) as bfloat16 back into tensor memory, over the first
+//                    half of the scores it came from (tcgen05.st, two probabilities to a column)
+//   O += P V         tcgen05.mma with P as the A operand from tensor memory and V [64 keys, hd] as an
+//                    MN-major B operand from shared memory; O stays in tensor memory over all key tiles
+//                    of the block.  (P in shared memory cost a 16 KB store and a proxy fence per tile and
+//                    made every tile's probabilities wait for the P V of the tile before.)
 // The reference of a row is its running maximum, but it only moves when the maximum has grown by more
 // than 8 (a factor of 256 in P; any reference gives the same softmax as long as the sum and O use the
 // same one).  Only then does the row's warp rescale its rows of O in tensor memory (load, multiply,
@@ -126,6 +129,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
+  pdl_launch();
   if (*(volatile int*)p.error_flag) return;
   // Blocks start in the order of their index, heads fastest: all heads of the last tile first.  Later tiles see
   // more keys, so the long blocks start first and the short ones fill in behind them; the heads of a kv group
@@ -154,7 +158,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t q_smem = base;                                       // chunks x [128 rows][128 B]
   const uint32_t kv_smem = q_smem + chunks * BQ * 128;                // per stage: K chunks, then V chunks
   const uint32_t kv_stage_bytes = 2u * chunks * BKV * 128;
-  const uint32_t p_smem = kv_smem + STAGES * kv_stage_bytes;          // [128 rows][128 B]
   // Keys and values have rings of their own: a key tile is free as soon as its scores are computed, well
   // before the values of the same tile are, so the next keys are on their way while the softmax still runs
   const uint32_t bar_q = smem_u32(&bars[0]), bar_kfull0 = smem_u32(&bars[1]), bar_kempty0 = smem_u32(&bars[3]);
@@ -188,6 +191,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
   if (warp == 0 && lane == 0) {
     // ---------------------------------------------------------------- loads
+    // The barriers and the tensor memory above need nothing from earlier kernels; the queries and the newest
+    // keys and values come from the kernel before this one.
+    pdl_wait();
     mbar_expect_tx(bar_q, chunks * BQ * 128);
     for (int c = 0; c < chunks; ++c) tma_load_2d(q_smem + c * BQ * 128, &map_q, head * hd + c * 64, row0, bar_q);
     const int* bt = p.block_table + (size_t)slot * p.max_pages;
@@ -349,6 +355,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) ok = mbar_wait(bar_o, (n_kv_tiles - 1) & 1, ab, p.wait_cycles);
     if (ok) {
       tc_fence_after();
+      pdl_wait();             // every thread that writes waits for the earlier kernels itself (long over by now)
       const float inv = l > 0.f ? 1.0f / l : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.nq + head) * hd;
       for (int d0 = 0; d0 < hd; d0 += 16) {           // the loads are warp-wide: rows beyond the tile join in
@@ -1152,14 +1159,14 @@ extern "C" int flint_attention_prefill_tc(const void* q, const void* k_cache, co
   p.scale_log2 = scale * 1.4426950408889634f;
   p.wait_cycles = wait_limit();
   const int chunks = (hd + 63) / 64;
-  const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128 + BQ * 128;
+  const size_t smem = (size_t)chunks * BQ * 128 + (size_t)STAGES * 2 * chunks * BKV * 128;
   dim3 grid(nq, n_tiles);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
     configured = true;
   }
-  attention_prefill_tc_kernel<<<grid, THREADS, smem, stream>>>(mq, mk, mv, p);
+  launch_pdl(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, stream, mq, mk, mv, p);
   return check_launch("attention_prefill_tc");
 }
 
