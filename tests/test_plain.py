@@ -75,7 +75,7 @@ def test_sparsemixer_by_hand():
     assert (i1, i2) == (0, 1)
     assert abs(g1.item() - 1 / (1 + math.exp(-0.1))) < 1e-12      # only 1.9 survives the mask beside the winner
     assert abs(g2.item() - 1.0) < 1e-12                            # 0.5 and -1 are masked against 1.9
-    # runner-up inside the band of the second round: (1.9-1.6)/1.9 = 0.158 < 0.2
+    # runner-up inside the band of the second selection: (1.9-1.6)/1.9 = 0.158 < 0.2
     s = torch.tensor([2.0, 1.9, 1.6, -4.0], dtype=D)
     _, g1, _, g2 = P.sparsemixer_top2(s, 0.1)
     assert abs(g1.item() - 1 / (1 + math.exp(-0.1) + math.exp(-0.4))) < 1e-12
