@@ -525,6 +525,12 @@ class CudaOps:
                 # (the kernel divides a row's keys evenly over the splits; the last one may stay empty)
                 n = n // 4 * 4
                 keys = -(-(-(-span // n)) // 16) * 16
+            if n == 4 and keys >= 384:
+                # 19 to 31 rows of many keys: there is room for four to seven splits a row, and four leave up to
+                # half of the warps without work while the others walk 24 steps and more; equal runs fill the
+                # device (2,048 keys: -10 % of a decode step at 20 rows, -8 % at 24, -4 % at 28, -2 % at 31;
+                # with 512 keys four splits of 8 steps are the faster)
+                return "stream", span, self._stream_slices(base8)
             return "tma", keys, n
         if T <= 256:
             n = max(1, min(-(-span // 128), -(-8 * self.sm_count // base)))
