@@ -524,13 +524,15 @@ class CudaOps:
             # tensor-core decode kernel fed by TMA: 8 query heads per warp, at most one wave of 8 warps
             # per SM (a second, nearly empty wave would cost as much as a full one), at least 64 keys per warp
             base8 = T * nkv * -(-(nq // nkv) // 8)
-            if span > 64 and (ragged or base8 >= 256 or (base8 >= 64 and span >= 8192)):
+            if span > 64 and (ragged or base8 >= 256 or (base8 >= 24 and base8 * span >= 24 * 16384)):
                 # rows of different lengths, or many rows: the kernel cuts the keys of all rows into equal runs
                 # itself; the count is the most pieces one (row, kv head) may be cut into: enough for one wave
                 # of 8 warps per SM.  (Few rows of about the same length are a little faster with the key
-                # range of each row cut into the same number of pieces, below; but from eight rows of 8,192
-                # keys on, splits in fours leave a seventh of the device idle, and equal runs win: +6 % of a
-                # decode step at batch 8 with 8,192 keys, +19 % with 65,536.)
+                # range of each row cut into the same number of pieces, below; but from three rows on and about
+                # 48 k keys in all, splits in fours leave part of the device idle, and equal runs win: measured
+                # at 8 kv heads, of a decode step: 8 rows of 6,144 keys -4 %, of 8,192 -6 %, of 65,536 -19 %;
+                # 16 rows of 3,072 -4 %, of 4,096 -5 %; 4 rows of 16,384 -3 %, of 65,536 -10 %; 3 rows of 32,768
+                # -4 %; below that line the plan below is the faster by 1 to 3 %, and for two rows at any length.)
                 return "stream", span, self._stream_slices(base8)
             n = max(1, min(span // 64, 8 * self.sm_count // base8))
             keys = -(-(-(-span // n)) // 16) * 16
