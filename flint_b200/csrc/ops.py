@@ -416,9 +416,10 @@ class CudaOps:
         kb = -(-K // 64)
         if tiles >= self.sm_count or kb < 8:
             return 1
-        # as many pieces as still fit one wave of resident blocks (three per SM with the narrow token tiles,
-        # else two; a second, partial wave would cost as much as a full one)
-        return max(1, min(((3 if bn < 64 else 2) * self.sm_count) // tiles, kb // 4, 16))
+        # as many pieces as still fit one wave of resident blocks (three per SM with the 16-row token tile, whose
+        # four stages take 72 KB, else two; a second, partial wave would cost as much as a full one: with the
+        # 32-row tile counted at three, 17 to 32 rows ran 432 items on 296 places and a decode step took 1.5 % longer)
+        return max(1, min(((3 if bn < 32 else 2) * self.sm_count) // tiles, kb // 4, 16))
 
     def _gemm(self, x, w, gated, out, bias, accumulate, act, plan):
         _check(x, "x", dims=2, contiguous=False)
