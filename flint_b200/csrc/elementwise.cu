@@ -135,17 +135,22 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
   const int n_items = heads * pairs;
   const int per_block = (n_items + gridDim.y - 1) / gridDim.y;
   const int item_end = min(n_items, (int)(blockIdx.y + 1) * per_block);
-  // fast path (one partial, head size and rotary size multiples of 8, 16-byte aligned pointers): a thread
+  // fast path (head size and rotary size multiples of 8, 16-byte aligned pointers and slices): a thread
   // takes 4 neighbouring pairs with 16-byte loads
   const bool aligned16 = ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(cos_t) |
                            reinterpret_cast<uintptr_t>(sin_t) | reinterpret_cast<uintptr_t>(bias) |
                            reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
                            reinterpret_cast<uintptr_t>(v_cache)) & 15) == 0;
-  if (n_partials == 1 && (half & 3) == 0 && (hd & 7) == 0 && gridDim.y == 1 && aligned16 && !interleaved) {
+  // (several blocks to a token only while each still has a block's worth of them: with 24 tokens and 13 blocks
+  // each, the item-by-item path below is the faster)
+  const int quads = pairs >> 2;
+  const int q_per_block = (heads * quads + gridDim.y - 1) / gridDim.y;
+  if ((half & 3) == 0 && (hd & 7) == 0 && aligned16 && !interleaved && (partial_stride & 3) == 0 &&
+      (gridDim.y == 1 || q_per_block >= 128)) {
     pdl_wait();
-    if (missing && threadIdx.x == 0) atomicExch(status, 1);
-    const int quads = pairs >> 2;
-    for (int item = threadIdx.x; item < heads * quads; item += blockDim.x) {
+    if (missing && threadIdx.x == 0 && blockIdx.y == 0) atomicExch(status, 1);
+    const int q_end = min(heads * quads, (int)(blockIdx.y + 1) * q_per_block);
+    for (int item = blockIdx.y * q_per_block + threadIdx.x; item < q_end; item += blockDim.x) {
       const int head = item / quads, i = (item % quads) * 4;      // first pair of the four
       const bool is_q = head < nq, is_v = head >= nq + nkv;
       int d0, d1;
@@ -156,6 +161,22 @@ rope_kv_kernel(const float* __restrict__ qkv, const int* __restrict__ pos,
       const size_t base = row_off + (size_t)head * hd;
       float4 x0 = *reinterpret_cast<const float4*>(qkv + base + d0);
       float4 x1 = *reinterpret_cast<const float4*>(qkv + base + d1);
+      // further partial sums of the projection, four slices in flight at a time, added in order
+      for (int z0 = 1; z0 < n_partials; z0 += 4) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const bool in = z0 + u < n_partials;
+          const float* sl = qkv + (size_t)(in ? z0 + u : 0) * partial_stride + base;
+          a[u] = in ? *reinterpret_cast<const float4*>(sl + d0) : make_float4(0.f, 0.f, 0.f, 0.f);
+          b[u] = in ? *reinterpret_cast<const float4*>(sl + d1) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          x0.x += a[u].x; x0.y += a[u].y; x0.z += a[u].z; x0.w += a[u].w;
+          x1.x += b[u].x; x1.y += b[u].y; x1.z += b[u].z; x1.w += b[u].w;
+        }
+      }
       if (bias) {
         const float4 b0 = *reinterpret_cast<const float4*>(bias + head * hd + d0);
         const float4 b1 = *reinterpret_cast<const float4*>(bias + head * hd + d1);
