@@ -67,6 +67,7 @@ struct Params {
   int defer;                   // write raw partial tiles even for a single split; the consumer sums them
   int stream_k;                // cut the K blocks of all tiles, laid end to end, into equal runs, one per block
   int w_expert_rows;           // rows between two experts in the stacked weight tensor
+  int plan_ready;              // grouped: the tile map was complete before this kernel could start (see flint_gemm_tc)
   long long wait_cycles;       // limit of every wait on an mbarrier
 };
 // Measured: with 232 bytes of parameters the compiler addressed them through a pointer and reloaded them after
@@ -95,9 +96,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
-  pdl_launch();
-  if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
+  // A product over experts that reads its tile map straight from the kernel that made it lets its own dependents
+  // start only after it has waited for that kernel (below): whatever starts after it may then read the map at once.
   const bool grouped = p.tile_expert != nullptr;
+  const bool map_pending = grouped && !p.plan_ready;
+  if (!map_pending) pdl_launch();
+  if (*(volatile int*)p.error_flag) return;   // an earlier block gave up: do not queue up behind it
   constexpr int FM = GATED ? GATED_FEATURES : BM;      // output features per tile
   const int tiles_m = (p.N + FM - 1) / FM;
   const int total_kb = (p.K + BK - 1) / BK;
@@ -132,8 +136,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   volatile int* ab = &abort_flag;
 
   // The barriers and the tensor memory above need nothing from earlier kernels.  With experts, the tile map
-  // comes from the routing plan of an earlier kernel: from here on the block has to wait for it.
-  if (grouped) pdl_wait();
+  // comes from the routing plan of an earlier kernel: from here on the block has to wait for it, unless the
+  // caller vouches that the map was complete before this kernel could start (an earlier product over the same
+  // plan waited for it before it let anything after it start); then the weights of the first ring are on their
+  // way while the kernel before this one still writes the rows.
+  if (map_pending) {
+    pdl_wait();
+    pdl_launch();
+  }
   const int tiles_n = grouped ? *p.n_tiles : (p.rows + BN - 1) / BN;
   const int n_items = tiles_m * tiles_n * p.splits;
   // Stream-K (few rows, partial sums deferred to the consumer): the K blocks of all tiles are laid end to end
@@ -465,12 +475,15 @@ extern "C" long long flint_gemm_tc_partial_floats(int rows, int N, int splits) {
 // cut into equal runs, one per resident block; a tile gets at most `splits` pieces and every one of the
 // `splits` slices of `partial` is written (pieces that do not exist as zeros).  The number of splits used is ceil(kb / ceil(kb / splits))
 // with kb = ceil(K / 64).
+// plan_ready (with a tile map): the map was written by a kernel that is certain to have finished when this one
+// starts, because a product over the same map ran between the two (it lets its dependents start only after its
+// own wait for the map's kernel); the first weight tiles are then fetched before the wait for the kernel before.
 // error_flag: device int, set to 1 if a bounded wait ran out.
 extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, const float* bias, void* out,
                              int out_dtype, int ldo, int accumulate, int act, const int* tile_expert,
                              const int* tile_row0, const int* n_tiles, const int* offsets, int max_tiles,
                              int n_experts, int rows, int N, int K, int bn, int splits, float* partial,
-                             int defer, int stream_k, int* error_flag, cudaStream_t stream) {
+                             int defer, int stream_k, int plan_ready, int* error_flag, cudaStream_t stream) {
   if (rows <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7)) return fail("gemm_tc: K=%d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   if (ldx < K || (ldx & 7)) return fail("gemm_tc: row stride %d must be a multiple of 8 and at least K", ldx);
@@ -501,6 +514,7 @@ extern "C" int flint_gemm_tc(const void* x, int ldx, const void* w, int gated, c
   p.rows = rows; p.N = N; p.K = K;
   p.kb_per_split = kbps; p.splits = splits; p.defer = defer; p.stream_k = stream_k;
   p.w_expert_rows = w_expert_rows;
+  p.plan_ready = (tile_expert && plan_ready) ? 1 : 0;
   p.wait_cycles = wait_limit();
   p.stages = flint_gemm_tc_stages(bn, w_up ? 1 : 0);
   // few rows: the product streams its weights and is bound by how many bytes an SM keeps in flight and by how

@@ -367,11 +367,13 @@ class CudaOps:
         plan (rows grouped by expert) [E, paired_rows(N), K]."""
         self._gemm(x, w13, True, out, None, False, act, plan)
 
-    def grouped_gemm(self, x, w, out, plan: MoePlan):
-        """out[r] = x[r] @ w[expert of row r].T; w [E, N, K]."""
-        self._gemm(x, w, False, out, None, False, "silu", plan)
+    def grouped_gemm(self, x, w, out, plan: MoePlan, plan_ready=False):
+        """out[r] = x[r] @ w[expert of row r].T; w [E, N, K].  ``plan_ready``: another product over the same plan
+        has run since the plan was made (the kernel may then read the plan before it waits for the kernel before
+        it, and fetch its first weights meanwhile)."""
+        self._gemm(x, w, False, out, None, False, "silu", plan, plan_ready=plan_ready)
 
-    def gemm_partials(self, x, w, splits=None, plan: MoePlan | None = None):
+    def gemm_partials(self, x, w, splits=None, plan: MoePlan | None = None, plan_ready=False):
         """x @ w.T left as S partial sums over pieces of the K range: float32 [S, M, N], no bias.
         The next kernel (rotary write, row norm, gated activation) adds them up; S is 1 when nothing
         was split.  With a plan, rows are grouped by expert and w is [E, N, K]."""
@@ -407,7 +409,7 @@ class CudaOps:
                   _ptr(plan.tile_row0 if plan else None), _ptr(plan.n_tiles if plan else None),
                   _ptr(plan.offsets if plan else None), c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M),
                   c_int(N), c_int(K), c_int(bn), c_int(splits), _ptr(out), c_int(1), c_int(stream_k),
-                  _ptr(self.tc_error))
+                  c_int(1 if plan_ready and plan is not None else 0), _ptr(self.tc_error))
         return out
 
     def _k_splits(self, M, N, K, bn):
@@ -421,7 +423,7 @@ class CudaOps:
         # 32-row tile counted at three, 17 to 32 rows ran 432 items on 296 places and a decode step took 1.5 % longer)
         return max(1, min(((3 if bn < 32 else 2) * self.sm_count) // tiles, kb // 4, 16))
 
-    def _gemm(self, x, w, gated, out, bias, accumulate, act, plan):
+    def _gemm(self, x, w, gated, out, bias, accumulate, act, plan, plan_ready=False):
         _check(x, "x", dims=2, contiguous=False)
         _check(out, "out", dims=2, contiguous=False)
         if x.stride(1) != 1 or out.stride(1) != 1:
@@ -454,7 +456,7 @@ class CudaOps:
                           c_longlong(parts.stride(0)), _ptr(out), c_int(_code(out.dtype)), c_int(M), c_int(N),
                           c_int(act_code))
                 return
-            self._gemm_tc(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K)
+            self._gemm_tc(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K, plan_ready)
         else:
             self._gemm_simt(x, w, gated, out, bias, accumulate, act_code, plan, M, N, K)
 
@@ -478,7 +480,7 @@ class CudaOps:
             return 64
         return self.token_tile(-(-2 * n_tokens // n_experts))
 
-    def _gemm_tc(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K):
+    def _gemm_tc(self, x, w, gated, out, bias, accumulate, act_code, plan, M, N, K, plan_ready=False):
         if plan is not None:
             bn, splits, E = plan.tile_rows, 1, plan.n_experts
         else:
@@ -494,7 +496,8 @@ class CudaOps:
                   c_int(act_code), _ptr(plan.tile_expert if plan else None), _ptr(plan.tile_row0 if plan else None),
                   _ptr(plan.n_tiles if plan else None), _ptr(plan.offsets if plan else None),
                   c_int(plan.max_tiles if plan else 0), c_int(E), c_int(M), c_int(N), c_int(K), c_int(bn),
-                  c_int(splits), _ptr(partial), c_int(0), c_int(0), _ptr(self.tc_error))
+                  c_int(splits), _ptr(partial), c_int(0), c_int(0), c_int(1 if plan_ready and plan is not None else 0),
+                  _ptr(self.tc_error))
 
     @staticmethod
     def _product_label(N, K, plan, gated):

@@ -109,7 +109,7 @@ class SparseMixerMoE(FeedForward):
         a = torch.empty((2 * T, self.inter), dtype=self.w13.dtype, device=dev)
         ops.gated_gemm(xs, self.w13, a, self.act, plan)
         y = torch.empty((2 * T, self.hidden), dtype=torch.float32, device=dev)
-        ops.grouped_gemm(a, self.w2, y, plan)
+        ops.grouped_gemm(a, self.w2, y, plan, plan_ready=True)     # the gate/up product ran over the same plan
         if step.record is not None:
             step.record.setdefault("experts", []).append(ids)
             step.record.setdefault("gates", []).append(gates)

@@ -161,7 +161,7 @@ class RefOps:
             u = xs[lo:hi] @ w13[e, n:].to(self.cd).T
             out[lo:hi] = (_act(g, act) * u).to(out.dtype)
 
-    def grouped_gemm(self, x, w, out, plan):
+    def grouped_gemm(self, x, w, out, plan, plan_ready=False):
         xs = x.to(self.cd)
         for e, lo, hi in self._rows_by_expert(plan):
             out[lo:hi] = (xs[lo:hi] @ w[e].to(self.cd).T).to(out.dtype)
