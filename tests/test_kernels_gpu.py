@@ -559,6 +559,42 @@ def test_attention_decode_stream_cuts_keys_into_equal_runs(ops, ref, nq, nkv, hd
         close(out2[0::2], exp[0::2], 2e-2, 2e-2)
 
 
+@pytest.mark.parametrize("rows,n_keys,expect", [
+    (8, 2049, "tma"), (18, 2049, "tma"), (20, 2049, "stream"), (24, 1600, "stream"), (31, 2049, "stream"),
+    (24, 513, "tma"), (3, 16400, "stream"), (2, 16400, "tma"), (16, 3100, "stream"), (12, 3072, "tma"),
+])
+def test_attention_decode_of_even_batches_by_the_planned_kernel(ops, ref, rows, n_keys, expect):
+    """Batches of decoded tokens of about equal length, the kernel and the cut chosen by the plan (not given):
+    on either side of the lines where the plan changes kernels, the result is the reference's."""
+    nq, nkv, hd, P = 32, 8, 128, 64
+    if ops.sm_count == 148:          # the lines are where they were measured, on a device of 148 SMs
+        assert ops.attention_plan(rows, nq, nkv, n_keys, hd, True, False)[0] == expect
+    g = torch.Generator().manual_seed(rows * 7 + n_keys)
+    lens = [n_keys - (i * 5) % 23 for i in range(rows)]            # about equal: within a few keys of each other
+    need = [-(-n // P) for n in lens]
+    n_pages = sum(need) + 2
+    k = (torch.randn(n_pages, nkv, P, hd, generator=g) * 0.5).to(torch.bfloat16)
+    v = torch.randn(n_pages, nkv, P, hd, generator=g).to(torch.bfloat16)
+    bt = torch.full((rows, max(need) + 1), -1, dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).to(torch.int32)
+    o = 0
+    for s_, n in enumerate(need):
+        bt[s_, :n] = perm[o:o + n]
+        o += n
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slot = torch.arange(rows, dtype=torch.int32)
+    q = (torch.randn(rows, nq * hd, generator=g) * 0.5).to(torch.bfloat16)
+    spec = KVSpec(nkv, hd, 0)
+    scale = 1 / math.sqrt(hd)
+    exp = torch.zeros(rows, nq * hd, dtype=torch.float64)
+    ref.paged_attention(q, CacheView(k, v, bt, P, spec), pos, slot, exp, nq, nkv, hd, 0, scale, max(lens))
+    out = torch.full((rows, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.paged_attention(q.to(DEV), CacheView(k.to(DEV), v.to(DEV), bt.to(DEV), P, spec), pos.to(DEV), slot.to(DEV), out,
+                        nq, nkv, hd, 0, scale, max(lens), ragged=False, fresh_keys=1)
+    assert int(ops.tc_error.item()) == 0
+    close(out, exp, 2e-2, 2e-2)
+
+
 @pytest.mark.parametrize("nq,nkv,hd,P,window,lens,splits", [
     (32, 8, 128, 64, 0, (2048, 2040, 1990, 2047), (128, 16)),     # four warps of a block merge, then the blocks of an item
     (32, 8, 128, 64, 0, (500, 512), (128, 4)),                    # four splits: the block writes the result itself
